@@ -1,0 +1,165 @@
+"""The cache of a model: a slot per sequence, keys and values per run of the schedule, each
+sequence with its own length, and a fixed-size state per sequence beside it.
+
+Storage is sized in tokens.  Keys and values live in pages of 64 positions; a sequence holds as
+many pages as its length needs, listed in its row of the block table, so `max_tokens` bounds the sum
+over live sequences of their lengths rounded up to 64, whatever their number.  Runs of the schedule
+whose mixers need the same thing (all keys of n heads of size d; a window; a state of some shape)
+form a group with storage, page allocator and block table of its own.  Pages and slots are given
+back when a sequence ends and are used again without being cleared: a kernel never reads a
+position at or beyond a sequence's length.  State blocks are zeroed when a slot is acquired.
+
+The reference preallocates [max_batch, kv heads, max_seq_len, head_dim] per layer with one length
+for the whole batch (crates/burn-lm-llama/src/nn/attention/kv_cache.rs:14-34, nn/transformer.rs:
+118-146); slots, pages and per-sequence lengths are this package's own.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..kernels import PAGE
+from .allocators import CacheError, CacheFull, ContextLengthExceeded, IdAllocator
+
+
+@dataclass
+class CacheView:
+    """What one run of the schedule sees of the cache."""
+    kind: str                               # "kv", "state" or "none"
+    writes: bool                            # False: the line belongs to an earlier run; read only
+    pool: Optional[torch.Tensor] = None     # kv: [pages, 2, n_kv_heads, PAGE, head_dim]
+    block_table: Optional[torch.Tensor] = None   # kv: int32 [max_seqs, max_pages_per_seq]
+    state: Optional[torch.Tensor] = None    # state: [max_seqs, *state_shape]
+    window: Optional[int] = None
+
+
+class _KVGroup:
+    def __init__(self, need, runs, n_pages, max_seqs, max_pages_per_seq, dtype, device):
+        self.need, self.runs = need, list(runs)
+        self.pool = torch.empty((len(runs), n_pages, 2, need.n_kv_heads, PAGE, need.head_dim), dtype=dtype, device=device)
+        self.pages = IdAllocator(n_pages, "cache page")
+        self.block_table = torch.zeros((max_seqs, max_pages_per_seq), dtype=torch.int32, device=device)
+        self.pages_of: list[list[int]] = [[] for _ in range(max_seqs)]
+
+    def bytes(self):
+        return self.pool.numel() * self.pool.element_size()
+
+
+class _StateGroup:
+    def __init__(self, need, runs, max_seqs, compute_dtype, device):
+        self.need, self.runs = need, list(runs)
+        dt = compute_dtype if need.state_dtype == "compute" else getattr(torch, need.state_dtype)
+        self.state = torch.zeros((len(runs), max_seqs, *need.state_shape), dtype=dt, device=device)
+
+
+class Cache:
+    def __init__(self, needs: list, schedule, max_tokens: int, max_seqs: int, max_seq_len: int, dtype, device):
+        """needs[run]: CacheNeed of every run of the schedule (None where the run reads another's)."""
+        if max_tokens < 1 or max_seqs < 1 or max_seq_len < 1:
+            raise CacheError("the cache needs room for at least one token of one sequence")
+        self.max_tokens, self.max_seqs, self.max_seq_len = max_tokens, max_seqs, max_seq_len
+        self.n_pages = (max_tokens + PAGE - 1) // PAGE
+        self.max_pages_per_seq = min((max_seq_len + PAGE - 1) // PAGE, self.n_pages)
+        self.dtype, self.device = dtype, device
+        self.slots = IdAllocator(max_seqs, "sequence slot")
+        self.seq_len = [0] * max_seqs
+        self._kv_groups: list[_KVGroup] = []
+        self._state_groups: list[_StateGroup] = []
+        self._where: dict[int, tuple] = {}      # run -> ("kv" | "state" | "none", group, index in group)
+        by_need: dict = {}
+        for run, need in enumerate(needs):
+            if need is not None:
+                by_need.setdefault(need, []).append(run)
+        for need, runs in by_need.items():
+            if need.kind == "kv":
+                # (a windowed group has storage of its own; the window is applied in the kernels and
+                # the group still keeps every page of a sequence)
+                g = _KVGroup(need, runs, self.n_pages, max_seqs, self.max_pages_per_seq, dtype, device)
+                self._kv_groups.append(g)
+                for i, r in enumerate(runs):
+                    self._where[r] = ("kv", g, i)
+            elif need.kind == "state":
+                g = _StateGroup(need, runs, max_seqs, dtype, device)
+                self._state_groups.append(g)
+                for i, r in enumerate(runs):
+                    self._where[r] = ("state", g, i)
+            elif need.kind == "none":
+                for r in runs:
+                    self._where[r] = ("none", None, 0)
+            else:
+                raise CacheError(f"unknown cache need {need.kind!r}")
+        self._views = []
+        for run, entry in enumerate(schedule):
+            src = run if entry.cache_of is None else entry.cache_of
+            kind, g, i = self._where[src]
+            writes = entry.cache_of is None
+            if kind == "kv":
+                self._views.append(CacheView("kv", writes, pool=g.pool[i], block_table=g.block_table, window=g.need.window))
+            elif kind == "state":
+                self._views.append(CacheView("state", writes, state=g.state[i]))
+            else:
+                self._views.append(CacheView("none", writes))
+
+    # -- what the model sees -------------------------------------------------------------------------
+    def view(self, run: int) -> CacheView:
+        return self._views[run]
+
+    def bytes(self) -> int:
+        return sum(g.bytes() for g in self._kv_groups)
+
+    @property
+    def free_pages(self) -> int:
+        return min((g.pages.free_count for g in self._kv_groups), default=self.n_pages)
+
+    # -- sequences -----------------------------------------------------------------------------------
+    def acquire(self) -> int:
+        """A free slot for a new sequence of length 0; its state blocks are zeroed."""
+        slot = self.slots.acquire()
+        self.seq_len[slot] = 0
+        for g in self._state_groups:
+            g.state[:, slot].zero_()
+        return slot
+
+    def release(self, slot: int) -> None:
+        """Give the slot and all its pages back."""
+        if not self.slots.held(slot):
+            raise CacheError(f"sequence slot {slot} is released but not held")
+        for g in self._kv_groups:
+            for p in g.pages_of[slot]:
+                g.pages.release(p)
+            g.pages_of[slot] = []
+        self.seq_len[slot] = 0
+        self.slots.release(slot)
+
+    def release_all(self) -> None:
+        for slot in range(self.max_seqs):
+            if self.slots.held(slot):
+                self.release(slot)
+
+    def reserve(self, growth: list) -> None:
+        """Make room for every (slot, new_length) pair, or change nothing and raise."""
+        plan = []
+        for slot, new_len in growth:
+            if not self.slots.held(slot):
+                raise CacheError(f"sequence slot {slot} is not held")
+            if new_len > self.max_seq_len:
+                raise ContextLengthExceeded(new_len, self.max_seq_len)
+            plan.append((slot, (new_len + PAGE - 1) // PAGE))
+        for g in self._kv_groups:
+            extra = sum(max(0, pages - len(g.pages_of[slot])) for slot, pages in plan)
+            if extra > g.pages.free_count:
+                held = self.n_pages - g.pages.free_count
+                raise CacheFull(f"the step needs {extra} more cache pages of {PAGE} tokens; {g.pages.free_count} of "
+                                f"{self.n_pages} are free ({held * PAGE} of {self.n_pages * PAGE} token places held)")
+        for g in self._kv_groups:
+            for slot, pages in plan:
+                have = len(g.pages_of[slot])
+                if pages > have:
+                    new = g.pages.acquire_many(pages - have)
+                    g.pages_of[slot].extend(new)
+                    g.block_table[slot, have:pages] = torch.tensor(new, dtype=torch.int32)
+
+    def set_length(self, slot: int, length: int) -> None:
+        self.seq_len[slot] = length

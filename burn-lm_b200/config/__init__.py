@@ -1,0 +1,5 @@
+"""Typed configurations, read from each architecture's own config.json keys."""
+from .reader import ConfigError, KeyReader, read_config_json
+from .llama import LlamaConfig, Llama3RopeScaling
+
+__all__ = ["ConfigError", "KeyReader", "read_config_json", "LlamaConfig", "Llama3RopeScaling"]

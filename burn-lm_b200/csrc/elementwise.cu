@@ -1,0 +1,240 @@
+// Row-wise kernels of a decoder step: embedding gather, residual add + RMS norm, rotary position
+// encoding fused with the cache append, gated activation, dtype conversion.
+// All statistics, angles and sums are fp32 (angles fp64); values are rounded once when stored.
+#include "common.cuh"
+
+BLM_API const char* blm_elementwise_last_error() { return g_blm_error; }
+
+// ---------------------------------------------------------------------------------------------
+// embedding: out[n, :] = table[tokens[n], :]  (fp32 residual stream from a bf16 or fp32 table)
+// ---------------------------------------------------------------------------------------------
+template <typename TT>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TT* __restrict__ table,
+                             float* __restrict__ out, int width, int vocab) {
+    const int n = blockIdx.x;
+    int tok = tokens[n];
+    if ((unsigned)tok >= (unsigned)vocab) tok = 0;  // ids are validated on the host; never read wild
+    const TT* row = table + (size_t)tok * width;
+    float* o = out + (size_t)n * width;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) o[d] = to_f32(row[d]);
+}
+
+BLM_API int blm_embed(const int* tokens, const void* table, int table_dtype, float* out,
+                      int n_tokens, int width, int vocab, cudaStream_t stream) {
+    if (n_tokens == 0) return BLM_OK;
+    BLM_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0, "embed: bad sizes");
+    const int threads = width >= 1024 ? 256 : 128;
+    if (table_dtype == BLM_F32)
+        embed_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, width, vocab);
+    else if (table_dtype == BLM_BF16)
+        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, out, width, vocab);
+    else
+        return blm_fail(BLM_BAD_ARGUMENT, "embed: table dtype %d", table_dtype);
+    return blm_check_launch("embed");
+}
+
+// ---------------------------------------------------------------------------------------------
+// residual add + RMS norm.
+//   rows == nullptr: for every row n: resid[n] += delta[n] (fp32, stored), out[n] = norm(resid[n])
+//   rows != nullptr: out[i] = norm(resid[rows[i]] + delta[rows[i]]), resid is left as it is
+// delta may be null (nothing to add).  gamma is fp32 or bf16 whatever the activations are.
+// ---------------------------------------------------------------------------------------------
+template <typename TA, typename TG>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
+                                   const TG* __restrict__ gamma, TA* __restrict__ out,
+                                   const int* __restrict__ rows, int width, float eps) {
+    extern __shared__ float row_buf[];  // [width] + 33 for the reduction
+    float* red = row_buf + width;
+    const int src = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* r = resid + (size_t)src * width;
+    const TA* dl = delta ? delta + (size_t)src * width : nullptr;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        float h = r[d];
+        if (dl) h += to_f32(dl[d]);
+        row_buf[d] = h;
+        ss += h * h;
+        if (!rows && dl) r[d] = h;
+    }
+    const float total = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(total / (float)width + eps);
+    TA* o = out + (size_t)blockIdx.x * width;
+    for (int d = threadIdx.x; d < width; d += blockDim.x)
+        o[d] = from_f32<TA>(row_buf[d] * inv * to_f32(gamma[d]));
+}
+
+template <typename TA, typename TG>
+static int launch_add_rmsnorm(float* resid, const void* delta, const void* gamma, void* out,
+                              const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
+    const size_t smem = (size_t)(width + 33) * sizeof(float);
+    BLM_REQUIRE(smem <= 200 * 1024, "rms norm: width %d is beyond the 51,000 this kernel holds in shared memory", width);
+    auto k = add_rmsnorm_kernel<TA, TG>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "rms norm: %s", cudaGetErrorString(e));
+    }
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    k<<<n_rows, threads, smem, stream>>>(resid, (const TA*)delta, (const TG*)gamma, (TA*)out, rows, width, eps);
+    return blm_check_launch("add_rmsnorm");
+}
+
+BLM_API int blm_add_rmsnorm(float* resid, const void* delta, const void* gamma, int gamma_dtype,
+                            void* out, int act_dtype, const int* rows, int n_rows, int width,
+                            float eps, cudaStream_t stream) {
+    if (n_rows == 0) return BLM_OK;
+    BLM_REQUIRE(n_rows > 0 && width > 0, "rms norm: bad sizes");
+    if (act_dtype == BLM_F32 && gamma_dtype == BLM_F32)
+        return launch_add_rmsnorm<float, float>(resid, delta, gamma, out, rows, n_rows, width, eps, stream);
+    if (act_dtype == BLM_F32 && gamma_dtype == BLM_BF16)
+        return launch_add_rmsnorm<float, __nv_bfloat16>(resid, delta, gamma, out, rows, n_rows, width, eps, stream);
+    if (act_dtype == BLM_BF16 && gamma_dtype == BLM_F32)
+        return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, gamma, out, rows, n_rows, width, eps, stream);
+    if (act_dtype == BLM_BF16 && gamma_dtype == BLM_BF16)
+        return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, gamma, out, rows, n_rows, width, eps, stream);
+    return blm_fail(BLM_BAD_ARGUMENT, "rms norm: dtypes %d/%d", act_dtype, gamma_dtype);
+}
+
+// ---------------------------------------------------------------------------------------------
+// rotary position encoding of q and k, fused with the append of k and v to the paged cache.
+//   qkv [N, (H + 2 KV) * hd]: q heads, then k heads, then v heads of every token.
+//   q is rotated in place; rotated k and plain v go to the page that holds the token's position.
+//   cache pool of one layer: [pages][2 (k, v)][KV][page_size][hd].
+//   The angle pos * inv_freq[i] and its sine and cosine are computed in fp64 and applied in fp32,
+//   so no position is too far for the table and long contexts lose nothing to the angle.
+//   pairing 0: lanes (i, i + rot/2); pairing 1: lanes (2i, 2i + 1).  rot == 0: no rotation.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ token_seq,
+                                   const int* __restrict__ token_pos, const int* __restrict__ slot_of_seq,
+                                   const int* __restrict__ block_table, int table_stride,
+                                   const double* __restrict__ inv_freq, int rot, int pairing,
+                                   T* __restrict__ pool, int n_heads, int n_kv, int hd, int page_size,
+                                   int write_cache) {
+    extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
+    const int n = blockIdx.x;
+    const int pos = token_pos[n];
+    const int half = rot >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        double s, c;
+        sincos((double)pos * inv_freq[i], &s, &c);
+        cs[i] = (float)c;
+        cs[half + i] = (float)s;
+    }
+    __syncthreads();
+    T* row = qkv + (size_t)n * (size_t)(n_heads + 2 * n_kv) * hd;
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (write_cache) {
+        const int slot = slot_of_seq[token_seq[n]];
+        const int page = block_table[(size_t)slot * table_stride + pos / page_size];
+        const size_t page_elems = (size_t)n_kv * page_size * hd;
+        kdst = pool + (size_t)page * 2 * page_elems + (size_t)(pos % page_size) * hd;
+        vdst = kdst + page_elems;
+    }
+    const size_t head_stride_cache = (size_t)page_size * hd;
+    // rotated pairs of q and k
+    const int rot_heads = n_heads + n_kv;
+    for (int item = threadIdx.x; item < rot_heads * half; item += blockDim.x) {
+        const int h = item / half, i = item % half;
+        const int la = pairing ? 2 * i : i, lb = pairing ? 2 * i + 1 : i + half;
+        T* hp = row + (size_t)h * hd;
+        const float a = to_f32(hp[la]), b = to_f32(hp[lb]);
+        const float c = cs[i], s = cs[half + i];
+        const T ra = from_f32<T>(a * c - b * s), rb = from_f32<T>(a * s + b * c);
+        if (h < n_heads) {
+            hp[la] = ra;
+            hp[lb] = rb;
+        } else if (kdst) {
+            T* kp = kdst + (size_t)(h - n_heads) * head_stride_cache;
+            kp[la] = ra;
+            kp[lb] = rb;
+        } else {  // a layer that reads another layer's cache still rotates its own k in place
+            hp[la] = ra;
+            hp[lb] = rb;
+        }
+    }
+    if (!write_cache) return;
+    // lanes of k beyond the rotated ones, and v
+    const int tail = hd - rot;
+    for (int item = threadIdx.x; item < n_kv * tail; item += blockDim.x) {
+        const int h = item / tail, l = rot + item % tail;
+        kdst[(size_t)h * head_stride_cache + l] = row[(size_t)(n_heads + h) * hd + l];
+    }
+    const T* vsrc = row + (size_t)(n_heads + n_kv) * hd;
+    for (int item = threadIdx.x; item < n_kv * hd; item += blockDim.x) {
+        const int h = item / hd, l = item % hd;
+        vdst[(size_t)h * head_stride_cache + l] = vsrc[item];
+    }
+}
+
+BLM_API int blm_rope_append(void* qkv, int dtype, const int* token_seq, const int* token_pos,
+                            const int* slot_of_seq, const int* block_table, int table_stride,
+                            const double* inv_freq, int rot, int pairing, void* pool, int n_tokens,
+                            int n_heads, int n_kv, int hd, int page_size, int write_cache,
+                            cudaStream_t stream) {
+    if (n_tokens == 0) return BLM_OK;
+    BLM_REQUIRE(rot >= 0 && rot <= hd && rot % 2 == 0, "rotary: %d rotated lanes of a head of %d", rot, hd);
+    BLM_REQUIRE(rot == 0 || inv_freq != nullptr, "rotary: no frequencies");
+    BLM_REQUIRE(pairing == 0 || pairing == 1, "rotary: pairing %d", pairing);
+    const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
+    const int threads = 128;
+    if (dtype == BLM_F32)
+        rope_append_kernel<float><<<n_tokens, threads, smem, stream>>>((float*)qkv, token_seq, token_pos, slot_of_seq, block_table, table_stride, inv_freq, rot, pairing, (float*)pool, n_heads, n_kv, hd, page_size, write_cache);
+    else if (dtype == BLM_BF16)
+        rope_append_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>((__nv_bfloat16*)qkv, token_seq, token_pos, slot_of_seq, block_table, table_stride, inv_freq, rot, pairing, (__nv_bfloat16*)pool, n_heads, n_kv, hd, page_size, write_cache);
+    else
+        return blm_fail(BLM_BAD_ARGUMENT, "rotary: dtype %d", dtype);
+    return blm_check_launch("rope_append");
+}
+
+// ---------------------------------------------------------------------------------------------
+// gated activation: out[n, i] = silu(gu[n, i]) * gu[n, I + i], computed in fp32
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inner, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = idx / inner;
+        const int i = (int)(idx % inner);
+        const float g = to_f32(gu[n * 2 * inner + i]);
+        const float u = to_f32(gu[n * 2 * inner + inner + i]);
+        out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+BLM_API int blm_swiglu(const void* gu, void* out, int dtype, int n_rows, int inner, cudaStream_t stream) {
+    if (n_rows == 0) return BLM_OK;
+    const size_t total = (size_t)n_rows * inner;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == BLM_F32)
+        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, inner, total);
+    else if (dtype == BLM_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inner, total);
+    else
+        return blm_fail(BLM_BAD_ARGUMENT, "swiglu: dtype %d", dtype);
+    return blm_check_launch("swiglu");
+}
+
+// ---------------------------------------------------------------------------------------------
+// dtype conversion (for a layer whose weights are stored in fp32 inside a bf16 model)
+// ---------------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x)
+        out[idx] = from_f32<TO>(to_f32(in[idx]));
+}
+
+BLM_API int blm_convert(const void* in, int in_dtype, void* out, int out_dtype, size_t total, cudaStream_t stream) {
+    if (total == 0) return BLM_OK;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (in_dtype == BLM_F32 && out_dtype == BLM_BF16)
+        convert_kernel<float, __nv_bfloat16><<<blocks, threads, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, total);
+    else if (in_dtype == BLM_BF16 && out_dtype == BLM_F32)
+        convert_kernel<__nv_bfloat16, float><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)in, (float*)out, total);
+    else
+        return blm_fail(BLM_BAD_ARGUMENT, "convert: %d -> %d", in_dtype, out_dtype);
+    return blm_check_launch("convert");
+}

@@ -1,0 +1,282 @@
+// Sampling from fp32 logits on the device: greedy, and temperature with an optional nucleus
+// (top-p).  One block per sequence.  Every decision of the nucleus and of the draw is made on
+// probabilities quantised to 2^-40, in integer arithmetic, so the result does not depend on the
+// order in which threads add things up.
+#include "common.cuh"
+
+BLM_API const char* blm_sampling_last_error() { return g_blm_error; }
+
+constexpr int kSampleThreads = 1024;
+
+// ---------------------------------------------------------------------------------------------
+// greedy: the largest logit; the lowest index wins a tie
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kSampleThreads) argmax_kernel(const float* __restrict__ logits, long long row_stride,
+                                                                int vocab, int* __restrict__ out) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const float* row = logits + (size_t)blockIdx.x * row_stride;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nwarp = blockDim.x >> 5;
+        best = lane < nwarp ? bv[lane] : -INFINITY;
+        idx = lane < nwarp ? bi[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+        }
+        if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+    }
+}
+
+BLM_API int blm_argmax(const float* logits, long long row_stride, int n_rows, int vocab, int* out, cudaStream_t stream) {
+    if (n_rows == 0) return BLM_OK;
+    BLM_REQUIRE(vocab > 0, "argmax: empty vocabulary");
+    argmax_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, row_stride, vocab, out);
+    return blm_check_launch("argmax");
+}
+
+// ---------------------------------------------------------------------------------------------
+// temperature + nucleus
+// ---------------------------------------------------------------------------------------------
+// The uniform number of sequence stream `stream_id` at its `counter`-th draw: a splitmix64 hash.
+__host__ __device__ inline unsigned long long blm_mix64(unsigned long long z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__host__ __device__ inline unsigned int blm_uniform32(unsigned long long seed, unsigned long long stream_id,
+                                                     unsigned long long counter) {
+    unsigned long long k = blm_mix64(seed + 0x9E3779B97F4A7C15ull);
+    k = blm_mix64(k ^ (stream_id * 0xD1342543DE82EF95ull + 0x2545F4914F6CDD1Dull));
+    k = blm_mix64(k + counter * 0x9E3779B97F4A7C15ull);
+    return (unsigned int)(k >> 32);
+}
+BLM_API unsigned int blm_sampling_uniform32(unsigned long long seed, unsigned long long stream_id, unsigned long long counter) {
+    return blm_uniform32(seed, stream_id, counter);
+}
+
+__device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v, unsigned long long* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long t = lane < nwarp ? red[lane] : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    const unsigned long long r = red[32];
+    __syncthreads();
+    return r;
+}
+
+// exclusive prefix over the threads of a block; `total` gets the sum
+__device__ __forceinline__ unsigned long long block_exclusive_scan_u64(unsigned long long v, unsigned long long* red,
+                                                                       unsigned long long* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    unsigned long long inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) red[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long w = lane < nwarp ? red[lane] : 0ull;
+        unsigned long long winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long t = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += t;
+        }
+        red[lane] = winc - w;  // exclusive prefix of the warps
+        if (lane == 31) red[32] = winc;
+    }
+    __syncthreads();
+    const unsigned long long r = red[warp] + inc - v;
+    *total = red[32];
+    __syncthreads();
+    return r;
+}
+
+constexpr double kQuant = 1099511627776.0;  // 2^40
+
+// The probability of token i.  Every pass below recomputes it through this one function, with the
+// roundings spelled out, so that all passes see the same bits.
+__device__ __forceinline__ float prob_of(const float* __restrict__ row, int i, float inv_t, float mx, float inv_z) {
+    return __fmul_rn(expf(__fsub_rn(__fmul_rn(row[i], inv_t), mx)), inv_z);
+}
+__device__ __forceinline__ unsigned long long quantise(float p) { return (unsigned long long)((double)p * kQuant); }
+
+__global__ void __launch_bounds__(kSampleThreads) sample_kernel(
+    const float* __restrict__ logits, long long row_stride, int vocab, const float* __restrict__ temperature,
+    const float* __restrict__ top_p, const unsigned long long* __restrict__ seeds,
+    const unsigned long long* __restrict__ stream_ids, const unsigned long long* __restrict__ counters,
+    int* __restrict__ out) {
+    __shared__ float redf[33];
+    __shared__ unsigned long long red[33];
+    __shared__ unsigned long long hist[256];
+    __shared__ unsigned int s_prefix;
+    __shared__ unsigned long long s_above;
+    __shared__ int s_result;
+
+    const int b = blockIdx.x;
+    const float* row = logits + (size_t)b * row_stride;
+    const float inv_t = 1.0f / temperature[b];
+    const int tid = threadIdx.x;
+
+    // max and normaliser of softmax(logits / temperature)
+    float mx = -INFINITY;
+    for (int i = tid; i < vocab; i += blockDim.x) mx = fmaxf(mx, __fmul_rn(row[i], inv_t));
+    mx = warp_max(mx);
+    if ((tid & 31) == 0) redf[tid >> 5] = mx;
+    __syncthreads();
+    if (tid < 32) {
+        float t = tid < (blockDim.x >> 5) ? redf[tid] : -INFINITY;
+        t = warp_max(t);
+        if (tid == 0) redf[32] = t;
+    }
+    __syncthreads();
+    mx = redf[32];
+    __syncthreads();
+    float z = 0.f;
+    for (int i = tid; i < vocab; i += blockDim.x) z += expf(__fsub_rn(__fmul_rn(row[i], inv_t), mx));
+    z = block_sum(z, redf);
+    const float inv_z = 1.0f / z;
+
+    // contiguous chunk of the vocabulary per thread (index order matters below)
+    const int per = (vocab + blockDim.x - 1) / blockDim.x;
+    const int lo = min(vocab, tid * per), hi = min(vocab, lo + per);
+
+    unsigned long long total = 0;
+    for (int i = lo; i < hi; ++i) total += quantise(prob_of(row, i, inv_t, mx, inv_z));
+    total = block_sum_u64(total, red);
+
+    // nucleus: the key tau (float bits of a probability) with mass(> tau) < target <= mass(>= tau)
+    const float pp = top_p[b];
+    unsigned int tau = 0;                 // 0: keep everything
+    unsigned long long above = 0;         // mass strictly above tau
+    unsigned long long tie_w = 0;         // quantised mass of one token at tau
+    unsigned long long ties_kept = ~0ull; // how many tokens at tau are kept, in index order
+    if (pp < 1.0f) {
+        unsigned long long target = (unsigned long long)((double)pp * (double)total);
+        if (target < 1) target = 1;
+        if (tid == 0) { s_prefix = 0; s_above = 0; }
+        __syncthreads();
+        for (int round = 0; round < 4; ++round) {
+            const int shift = 24 - 8 * round;
+            for (int i = tid; i < 256; i += blockDim.x) hist[i] = 0ull;
+            __syncthreads();
+            const unsigned int prefix = s_prefix;
+            const unsigned int mask = round == 0 ? 0u : (0xffffffffu << (shift + 8));
+            for (int i = lo; i < hi; ++i) {
+                const float p = prob_of(row, i, inv_t, mx, inv_z);
+                const unsigned int bits = __float_as_uint(p);
+                if ((bits & mask) == prefix)
+                    atomicAdd(&hist[(bits >> shift) & 255u], quantise(p));
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned long long run = s_above;
+                int bin = 255;
+                for (; bin > 0; --bin) {
+                    if (run + hist[bin] >= target) break;
+                    run += hist[bin];
+                }
+                s_above = run;
+                s_prefix = prefix | ((unsigned int)bin << shift);
+            }
+            __syncthreads();
+        }
+        tau = s_prefix;
+        above = s_above;
+        tie_w = quantise(__uint_as_float(tau));
+        // ties are kept while the mass before them is below the target
+        if (tie_w == 0) ties_kept = ~0ull;
+        else ties_kept = (target - above + tie_w - 1) / tie_w;  // smallest j with above + j * w >= target
+    }
+
+    // rank of this thread's first tie, in index order
+    unsigned long long my_ties = 0;
+    if (pp < 1.0f)
+        for (int i = lo; i < hi; ++i) {
+            const float p = prob_of(row, i, inv_t, mx, inv_z);
+            if (__float_as_uint(p) == tau) ++my_ties;
+        }
+    unsigned long long all_ties;
+    const unsigned long long ties_before = block_exclusive_scan_u64(my_ties, red, &all_ties);
+
+    // kept mass of the chunk, then its prefix
+    unsigned long long mass = 0, t_rank = ties_before;
+    for (int i = lo; i < hi; ++i) {
+        const float p = prob_of(row, i, inv_t, mx, inv_z);
+        const unsigned int bits = __float_as_uint(p);
+        const unsigned long long w = quantise(p);
+        if (pp >= 1.0f || bits > tau) mass += w;
+        else if (bits == tau) { if (t_rank < ties_kept) mass += w; ++t_rank; }
+    }
+    unsigned long long kept_total;
+    const unsigned long long before = block_exclusive_scan_u64(mass, red, &kept_total);
+
+    // draw: the first kept token, in vocabulary order, whose running kept mass exceeds u * kept_total
+    const unsigned int u = blm_uniform32(seeds[b], stream_ids[b], counters[b]);
+    const unsigned long long pick = __umul64hi(kept_total, (unsigned long long)u << 32);
+    if (tid == 0) s_result = -1;
+    __syncthreads();
+    if (kept_total > 0 && pick >= before && pick < before + mass) {
+        unsigned long long run = before;
+        t_rank = ties_before;
+        for (int i = lo; i < hi; ++i) {
+            const float p = prob_of(row, i, inv_t, mx, inv_z);
+            const unsigned int bits = __float_as_uint(p);
+            const unsigned long long w = quantise(p);
+            bool kept = false;
+            if (pp >= 1.0f || bits > tau) kept = true;
+            else if (bits == tau) { kept = t_rank < ties_kept; ++t_rank; }
+            if (kept) {
+                run += w;
+                if (run > pick) { s_result = i; break; }
+            }
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int r = s_result;
+        if (r < 0) {  // every probability underflowed the quantum: fall back to the largest logit
+            float best = -INFINITY; r = 0;
+            for (int i = 0; i < vocab; ++i) if (row[i] > best) { best = row[i]; r = i; }
+        }
+        out[b] = r;
+    }
+}
+
+BLM_API int blm_sample(const float* logits, long long row_stride, int n_rows, int vocab, const float* temperature,
+                       const float* top_p, const unsigned long long* seeds, const unsigned long long* stream_ids,
+                       const unsigned long long* counters, int* out, cudaStream_t stream) {
+    if (n_rows == 0) return BLM_OK;
+    BLM_REQUIRE(vocab > 0, "sample: empty vocabulary");
+    sample_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, row_stride, vocab, temperature, top_p, seeds,
+                                                         stream_ids, counters, out);
+    return blm_check_launch("sample");
+}

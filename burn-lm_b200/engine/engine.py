@@ -1,0 +1,156 @@
+"""The step function: a batch of sequences that start together with unequal lengths, their prompts
+in one step, then one token each; only the tokens a step brings are run, as one packed batch, from
+the cache, and logits come back for the wanted places only.
+
+The reference's step is `Transformer::forward(input [B, T], cache, pos, mask) -> [B, T, V]` after
+`cache.prepare(T)` (crates/burn-lm-llama/src/nn/transformer.rs:88-103, generation/generate.rs:
+75-85): rectangular batches of one shared length, logits for every position.  Here tokens of all
+sequences are packed without padding, every sequence has its own cached length, and the final norm
+and output projection run on the wanted rows only.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from ..cache import Cache, CacheError
+from ..model import Model, load_model
+from ..parts.base import StepContext
+
+
+@dataclass
+class StepEntry:
+    """One sequence's share of a step: its slot, its next tokens, and the places among these tokens
+    whose logits are wanted (may be empty)."""
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class Workspace:
+    """Scratch memory kernels ask for by name; grown when a larger request comes, never shrunk."""
+
+    def __init__(self, device):
+        self.device = device
+        self._buffers: dict[str, torch.Tensor] = {}
+
+    def scratch(self, name: str, n_floats: int) -> torch.Tensor:
+        buf = self._buffers.get(name)
+        if buf is None or buf.numel() < n_floats:
+            buf = torch.empty(max(n_floats, 1), dtype=torch.float32, device=self.device)
+            self._buffers[name] = buf
+        return buf
+
+
+class Engine:
+    """A model with its cache.  `acquire()` starts a sequence, `step()` feeds tokens, `release()` ends it."""
+
+    def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None,
+                 max_seq_len: Optional[int] = None):
+        self.model = model
+        rt = model.runtime
+        if rt.device.type != "cuda":
+            raise RuntimeError("burn-lm_b200 runs on a CUDA device only; there is no CPU path")
+        page = 64
+        pages = (max_tokens + page - 1) // page
+        if max_seqs is None:
+            max_seqs = max(1, min(pages, 1024))
+        if max_seq_len is None:
+            max_seq_len = model.plan.max_positions
+        max_seq_len = min(max_seq_len, pages * page)
+        self.cache = Cache(model.cache_needs(), model.plan.schedule, max_tokens, max_seqs, max_seq_len,
+                           rt.dtype, rt.device)
+        self.workspace = Workspace(rt.device)
+        self.vocab_size = model.plan.vocab_size
+        self._staging = None    # pinned int32 staging for the step's metadata
+
+    @classmethod
+    def from_folder(cls, folder, dtype="bfloat16", max_tokens=4096, max_seqs=None, max_seq_len=None, device="cuda"):
+        return cls(load_model(folder, dtype, device), max_tokens, max_seqs, max_seq_len)
+
+    # -- sequences -----------------------------------------------------------------------------------
+    def acquire(self) -> int:
+        return self.cache.acquire()
+
+    def release(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.seq_len[slot]
+
+    # -- the step ------------------------------------------------------------------------------------
+    def _pack(self, entries):
+        """Validate the entries and lay their metadata out in one int32 array (host)."""
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        seen = set()
+        tokens, token_seq, token_pos, cu, slots, starts, want_rows = [], [], [], [0], [], [], []
+        growth = []
+        max_q = max_kv = 0
+        for s, e in enumerate(entries):
+            if e.slot in seen:
+                raise ValueError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if not self.cache.slots.held(e.slot):
+                raise CacheError(f"slot {e.slot} is not held")
+            toks = list(e.tokens)
+            if not toks:
+                raise ValueError(f"the entry of slot {e.slot} brings no token")
+            for t in toks:
+                if not 0 <= t < self.vocab_size:
+                    raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
+            start = self.cache.seq_len[e.slot]
+            for w in e.want:
+                if not 0 <= w < len(toks):
+                    raise ValueError(f"wanted place {w} is outside the {len(toks)} tokens of slot {e.slot}")
+                want_rows.append(cu[-1] + w)
+            tokens.extend(toks)
+            token_seq.extend([s] * len(toks))
+            token_pos.extend(range(start, start + len(toks)))
+            cu.append(cu[-1] + len(toks))
+            slots.append(e.slot)
+            starts.append(start)
+            growth.append((e.slot, start + len(toks)))
+            max_q = max(max_q, len(toks))
+            max_kv = max(max_kv, start + len(toks))
+        return tokens, token_seq, token_pos, cu, slots, starts, want_rows, growth, max_q, max_kv
+
+    def _upload(self, arrays):
+        """One pinned staging buffer, one host-to-device copy; returns the device views."""
+        total = sum(len(a) for a in arrays)
+        if self._staging is None or self._staging.numel() < total:
+            self._staging = torch.empty(max(total, 1024), dtype=torch.int32, pin_memory=True)
+        host = self._staging[:total]
+        off = 0
+        for a in arrays:
+            if a:
+                host[off: off + len(a)] = torch.tensor(a, dtype=torch.int32)
+            off += len(a)
+        dev = host.to(self.model.runtime.device, non_blocking=True)
+        views, off = [], 0
+        for a in arrays:
+            views.append(dev[off: off + len(a)])
+            off += len(a)
+        return views
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the entries' tokens as one batch from the cache.
+
+        Returns fp32 logits [wanted, vocab] in the order of the entries and of their `want`, or None
+        when nothing is wanted.  Every sequence's cached length grows by its tokens."""
+        (tokens, token_seq, token_pos, cu, slots, starts, want_rows, growth, max_q, max_kv) = self._pack(entries)
+        self.cache.reserve(growth)          # raises before anything is launched, changing nothing
+        d_tokens, d_seq, d_pos, d_cu, d_slots, d_starts, d_want = self._upload(
+            [tokens, token_seq, token_pos, cu, slots, starts, want_rows])
+        ctx = StepContext(
+            n_tokens=len(tokens), n_seqs=len(entries), max_q_len=max_q, max_kv_len=max_kv,
+            tokens=d_tokens, token_seq=d_seq, token_pos=d_pos, cu_seqlens=d_cu, slot_of_seq=d_slots,
+            start_pos=d_starts, want_rows=d_want if want_rows else None, n_want=len(want_rows),
+            workspace=self.workspace,
+            host={"cu_seqlens": cu, "slots": slots, "start_pos": starts})
+        logits = self.model.forward(ctx, self.cache)
+        for slot, new_len in growth:
+            self.cache.set_length(slot, new_len)
+        return logits

@@ -1,0 +1,248 @@
+"""Python faces of the CUDA kernels in `csrc/`.
+
+Each function checks what it is given, hands raw device pointers to the C entry point of the same
+name, and raises `KernelError` with the kernel's own message when that refuses.  Kernels run on
+torch's current CUDA stream, so they can be captured in a CUDA graph with the matrix products
+around them.  There is no fallback: without a CUDA device or without the compiled library these
+functions raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_size_t, c_uint, c_ulonglong, c_void_p
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+PAGE = 64  # positions per cache page; the attention kernels are written for this size
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, not {dtype}")
+
+
+def _ptr(t):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("burn-lm_b200 kernels run on a CUDA device only; got a CPU tensor")
+        if t is not None and not t.is_contiguous():
+            raise KernelError("kernel arguments must be contiguous")
+
+
+_protos = {
+    "elementwise": {
+        "blm_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "blm_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                            c_float, c_void_p],
+        "blm_rope_append": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                            c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "blm_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "blm_convert": [c_void_p, c_int, c_void_p, c_int, c_size_t, c_void_p],
+    },
+    "attention": {
+        "blm_attention": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                          c_int, c_int, c_float, c_void_p],
+    },
+    "gemm": {
+        "blm_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
+                         c_longlong, c_void_p],
+    },
+    "sampling": {
+        "blm_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
+        "blm_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_void_p],
+    },
+}
+_bound: dict[str, ctypes.CDLL] = {}
+
+
+def _lib(module: str) -> ctypes.CDLL:
+    lib = _bound.get(module)
+    if lib is None:
+        lib = _build.load(module)
+        for name, argtypes in _protos.get(module, {}).items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        err = getattr(lib, f"blm_{module}_last_error")
+        err.restype = ctypes.c_char_p
+        err.argtypes = []
+        _bound[module] = lib
+    return lib
+
+
+def _call(module: str, name: str, *args):
+    lib = _lib(module)
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        msg = getattr(lib, f"blm_{module}_last_error")().decode(errors="replace")
+        raise KernelError(f"{name}: {msg}")
+
+
+def loaded_modules():
+    return sorted(_bound)
+
+
+# ------------------------------------------------------------------------------------------------
+def embed(tokens, table, out):
+    """out[n, :] = table[tokens[n], :] as fp32.  tokens int32 [N]; table [V, D]; out fp32 [N, D]."""
+    _need_cuda(tokens, table, out)
+    n, (v, d) = tokens.numel(), table.shape
+    if tokens.dtype != torch.int32 or out.dtype != torch.float32 or tuple(out.shape) != (n, d):
+        raise KernelError("embed: tokens int32 [N], out float32 [N, D]")
+    _call("elementwise", "blm_embed", _ptr(tokens), _ptr(table), _code(table.dtype), _ptr(out), n, d, v, _stream())
+
+
+def add_rmsnorm(resid, delta, gamma, eps, out, rows=None):
+    """Residual add fused with the RMS norm, in fp32.
+
+    rows is None: resid[n] += delta[n] (stored), out[n] = norm(resid[n]) * gamma for every row.
+    rows given (int32 [R]): out[i] = norm(resid[rows[i]] + delta[rows[i]]) * gamma; resid unchanged.
+    delta may be None.  resid is fp32 [N, D]; delta and out have the activation dtype."""
+    _need_cuda(resid, delta, gamma, out, rows)
+    d = resid.shape[-1]
+    n_out = rows.numel() if rows is not None else resid.shape[0]
+    if resid.dtype != torch.float32 or gamma.numel() != d or tuple(out.shape) != (n_out, d):
+        raise KernelError("add_rmsnorm: resid float32 [N, D], gamma [D], out [rows, D]")
+    if delta is not None and (delta.dtype != out.dtype or delta.shape != resid.shape):
+        raise KernelError("add_rmsnorm: delta must match resid's shape and out's dtype")
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("add_rmsnorm: rows must be int32")
+    _call("elementwise", "blm_add_rmsnorm", _ptr(resid), _ptr(delta), _ptr(gamma), _code(gamma.dtype), _ptr(out),
+          _code(out.dtype), _ptr(rows), n_out, d, c_float(eps), _stream())
+
+
+def rope_append(qkv, token_seq, token_pos, slot_of_seq, block_table, inv_freq, rotary_dim, interleaved,
+                pool, n_heads, n_kv, head_dim, write_cache=True):
+    """Rotate q (in place) and k of every token by its position, and append k, v to the paged cache.
+
+    qkv [N, (n_heads + 2 n_kv) * head_dim]; pool [pages, 2, n_kv, PAGE, head_dim] of one cache line;
+    inv_freq float64 [rotary_dim / 2] or None when rotary_dim == 0."""
+    _need_cuda(qkv, token_seq, token_pos, slot_of_seq, block_table, inv_freq, pool)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv) * head_dim:
+        raise KernelError("rope_append: qkv width does not match the head counts")
+    if write_cache:
+        if pool.dtype != qkv.dtype or tuple(pool.shape[1:]) != (2, n_kv, PAGE, head_dim):
+            raise KernelError(f"rope_append: pool must be [pages, 2, {n_kv}, {PAGE}, {head_dim}] of {qkv.dtype}")
+    if rotary_dim:
+        if inv_freq.dtype != torch.float64 or inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("rope_append: inv_freq must be float64 [rotary_dim / 2]")
+    _call("elementwise", "blm_rope_append", _ptr(qkv), _code(qkv.dtype), _ptr(token_seq), _ptr(token_pos),
+          _ptr(slot_of_seq), _ptr(block_table), block_table.shape[1], _ptr(inv_freq), rotary_dim,
+          1 if interleaved else 0, _ptr(pool), n, n_heads, n_kv, head_dim, PAGE, 1 if write_cache else 0, _stream())
+
+
+def swiglu(gate_up, out):
+    """out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]."""
+    _need_cuda(gate_up, out)
+    n, two_i = gate_up.shape
+    if tuple(out.shape) != (n, two_i // 2) or out.dtype != gate_up.dtype or two_i % 2:
+        raise KernelError("swiglu: out must be [N, I] for gate_up [N, 2 I], same dtype")
+    _call("elementwise", "blm_swiglu", _ptr(gate_up), _ptr(out), _code(out.dtype), n, two_i // 2, _stream())
+
+
+def convert(src, dst):
+    """dst = src in the other of float32 / bfloat16."""
+    _need_cuda(src, dst)
+    if src.numel() != dst.numel():
+        raise KernelError("convert: sizes differ")
+    _call("elementwise", "blm_convert", _ptr(src), _code(src.dtype), _ptr(dst), _code(dst.dtype),
+          c_size_t(src.numel()), _stream())
+
+
+def attention_scratch_floats(n_tokens, n_heads, head_dim, n_splits):
+    return 0 if n_splits <= 1 else n_tokens * n_heads * n_splits * (head_dim + 2)
+
+
+def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos, out, n_tokens, n_seqs,
+              max_q_len, n_heads, n_kv, head_dim, scale, window=0, n_splits=1, scratch=None):
+    """Causal grouped-query attention of the step's tokens over the paged cache (after the append).
+
+    q: tensor whose token n, head h starts at element n * q_stride + h * head_dim (the qkv buffer).
+    Token t of sequence s sits at position start_pos[s] + t and sees keys 0..that position (the last
+    `window` of them when window > 0).  n_splits > 1 cuts every sequence's keys over that many
+    blocks and combines the partial results; it needs `scratch` (float32,
+    attention_scratch_floats(...) elements)."""
+    _need_cuda(q, pool, block_table, cu_seqlens, slot_of_seq, start_pos, out, scratch)
+    if tuple(out.shape) != (n_tokens, n_heads * head_dim) or out.dtype != q.dtype or pool.dtype != q.dtype:
+        raise KernelError("attention: out must be [N, heads * head_dim] in q's dtype, as the pool")
+    if tuple(pool.shape[1:]) != (2, n_kv, PAGE, head_dim):
+        raise KernelError(f"attention: pool must be [pages, 2, {n_kv}, {PAGE}, {head_dim}]")
+    if n_splits > 1:
+        need = attention_scratch_floats(n_tokens, n_heads, head_dim, n_splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"attention: {n_splits} splits need {need} float32 of scratch")
+    _call("attention", "blm_attention", _ptr(q), q_stride, _ptr(pool), _code(q.dtype), _ptr(block_table),
+          block_table.shape[1], _ptr(cu_seqlens), _ptr(slot_of_seq), _ptr(start_pos), _ptr(out), _ptr(scratch),
+          n_tokens, n_seqs, max_q_len, n_heads, n_kv, head_dim, PAGE, int(window or 0), n_splits,
+          c_float(scale), _stream())
+
+
+def gemm_f32(x, w, out=None):
+    """x [N, K] times w [M, K] transposed, in true fp32 (no tensor-core mode)."""
+    _need_cuda(x, w, out)
+    if x.dtype != torch.float32 or w.dtype != torch.float32 or x.shape[1] != w.shape[1]:
+        raise KernelError("gemm_f32: float32 x [N, K] and w [M, K]")
+    n, k = x.shape
+    m = w.shape[0]
+    if out is None:
+        out = torch.empty((n, m), dtype=torch.float32, device=x.device)
+    elif tuple(out.shape) != (n, m) or out.dtype != torch.float32:
+        raise KernelError("gemm_f32: out must be float32 [N, M]")
+    _call("gemm", "blm_gemm_f32", _ptr(x), _ptr(w), _ptr(out), n, m, k, k, k, m, _stream())
+    return out
+
+
+def argmax(logits, out):
+    """out[b] = index of the largest logit of row b (the lowest index on a tie)."""
+    _need_cuda(logits, out)
+    if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() < logits.shape[0]:
+        raise KernelError("argmax: float32 logits [B, V], int32 out [B]")
+    _call("sampling", "blm_argmax", _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(out),
+          _stream())
+
+
+def sample(logits, temperature, top_p, seeds, stream_ids, counters, out):
+    """Draw out[b] from softmax(logits[b] / temperature[b]) restricted to its top-p nucleus.
+
+    temperature, top_p float32 [B]; seeds, stream_ids, counters int64 [B] (read as unsigned): the
+    uniform number of a draw is a hash of the three, so it does not depend on the batch."""
+    _need_cuda(logits, temperature, top_p, seeds, stream_ids, counters, out)
+    b = logits.shape[0]
+    if logits.dtype != torch.float32 or out.dtype != torch.int32:
+        raise KernelError("sample: float32 logits, int32 out")
+    for t, dt in ((temperature, torch.float32), (top_p, torch.float32), (seeds, torch.int64),
+                  (stream_ids, torch.int64), (counters, torch.int64)):
+        if t.dtype != dt or t.numel() < b:
+            raise KernelError("sample: per-row arguments must be float32/int64 of length B")
+    _call("sampling", "blm_sample", _ptr(logits), logits.stride(0), b, logits.shape[1], _ptr(temperature),
+          _ptr(top_p), _ptr(seeds), _ptr(stream_ids), _ptr(counters), _ptr(out), _stream())
+
+
+def uniform32(seed, stream_id, counter) -> int:
+    """The 32-bit uniform number the sampling kernel uses for (seed, stream, counter); host side."""
+    lib = _lib("sampling")
+    fn = lib.blm_sampling_uniform32
+    fn.argtypes = [c_ulonglong, c_ulonglong, c_ulonglong]
+    fn.restype = c_uint
+    return int(fn(seed & (2**64 - 1), stream_id & (2**64 - 1), counter & (2**64 - 1)))

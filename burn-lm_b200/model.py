@@ -1,0 +1,122 @@
+"""The generic model: parts built from a `ModelPlan`, weights bound by name, and one forward over
+the packed tokens of a step.  It knows no architecture; the plan's schedule says which layer runs
+when and whose cache line it reads.
+"""
+from __future__ import annotations
+
+import torch
+
+from .config.reader import read_config_json
+from .parts.base import Runtime
+from .plan import ModelPlan
+from .registry import architecture_of, part_class
+from .weights.loader import load_tensors
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           "f32": torch.float32}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"compute dtype must be bfloat16 or float32, got {dtype}")
+        return dtype
+    try:
+        return _DTYPES[str(dtype).lower()]
+    except KeyError:
+        raise ValueError(f"compute dtype must be 'bfloat16' or 'float32', got {dtype!r}") from None
+
+
+def plan_of(config: dict):
+    """(architecture, typed configuration, plan) of a config.json dict."""
+    arch = architecture_of(config)
+    typed = arch.config_class.from_dict(config)
+    return arch, typed, arch.plan(typed)
+
+
+def _build(plan_part, family, runtime):
+    return part_class(family, plan_part.kind)(plan_part.spec, plan_part.tensors, runtime)
+
+
+class Layer:
+    def __init__(self, lp, runtime):
+        self.mixer = _build(lp.mixer, "mixer", runtime)
+        self.feed_forward = _build(lp.feed_forward, "feed_forward", runtime)
+        self.block = part_class("block", lp.block)(
+            _build(lp.mixer_norm, "norm", runtime), self.mixer,
+            _build(lp.feed_forward_norm, "norm", runtime), self.feed_forward)
+
+    def parts(self):
+        return self.block.parts()
+
+
+class Model:
+    def __init__(self, plan: ModelPlan, runtime: Runtime, config=None):
+        self.plan, self.runtime, self.config = plan, runtime, config
+        self.embedding = _build(plan.embedding, "embedding", runtime)
+        self.layers = [Layer(lp, runtime) for lp in plan.layers]
+        self.final_norm = _build(plan.final_norm, "norm", runtime)
+        self.head = _build(plan.head, "head", runtime)
+        self.bound = False
+
+    # -- weights ---------------------------------------------------------------------------------
+    def parts(self):
+        out = [self.embedding]
+        for layer in self.layers:
+            out.extend(layer.parts())
+        out.extend([self.final_norm, self.head])
+        return out
+
+    def tensor_specs(self):
+        seen, out = {}, []
+        for p in self.parts():
+            for s in p.tensor_specs():
+                if s.name in seen:
+                    if tuple(seen[s.name].shape) != tuple(s.shape):
+                        raise ValueError(f"tensor {s.name!r} is wanted with shapes {seen[s.name].shape} and {s.shape}")
+                    continue
+                seen[s.name] = s
+                out.append(s)
+        return out
+
+    def bind(self, loaded: dict):
+        for p in self.parts():
+            p.bind(loaded)
+        self.bound = True
+
+    def cache_needs(self):
+        """The cache need of every run of the schedule (None for a run that reads another's line)."""
+        return [None if e.cache_of is not None else self.layers[e.layer].mixer.cache_need()
+                for e in self.plan.schedule]
+
+    # -- forward ---------------------------------------------------------------------------------
+    def forward(self, step, cache):
+        """Logits (fp32 [n_want, vocab]) at the wanted rows of the step, or None when none is wanted."""
+        if not self.bound:
+            raise RuntimeError("the model has no weights yet")
+        resid = torch.empty((step.n_tokens, self.plan.hidden_size), dtype=torch.float32, device=self.runtime.device)
+        self.embedding.forward(step.tokens, resid)
+        delta = None
+        for run, entry in enumerate(self.plan.schedule):
+            delta = self.layers[entry.layer].block.forward(resid, delta, step, cache.view(run))
+        if step.n_want == 0:
+            return None
+        x = self.final_norm.add_norm(resid, delta, rows=step.want_rows)
+        return self.head.forward(x)
+
+
+def tensor_specs_of(config: dict):
+    """The stored tensors the architecture of `config` needs (no device work)."""
+    _, _, plan = plan_of(config)
+    return Model(plan, Runtime(torch.bfloat16, torch.device("cpu"))).tensor_specs()
+
+
+def load_model(folder: str, dtype="bfloat16", device="cuda") -> Model:
+    """Build the model a folder's config.json names and bind its safetensors weights."""
+    config = read_config_json(folder)
+    _, typed, plan = plan_of(config)
+    runtime = Runtime(parse_dtype(dtype), torch.device(device))
+    model = Model(plan, runtime, typed)
+    loaded = load_tensors(folder, model.tensor_specs(), runtime.dtype, runtime.device, plan.ignorable_tensors)
+    model.bind(loaded)
+    return model

@@ -1,0 +1,104 @@
+"""The attention mixer: grouped-query causal attention over the paged cache.
+
+q = x Wq, k = x Wk, v = x Wv without bias, feature c of q belonging to head c // head_dim
+(crates/burn-lm-llama/src/nn/attention/mha.rs:121-140); q and k are rotated, k and v appended to
+the cache (:91-95); query head h reads kv head h // (heads / kv heads) (:174-185); scores are
+q.k / sqrt(head_dim), keys after the query's position are hidden, softmax, times v (:157-166);
+heads are merged and projected by Wo (:168-170, :118).  The three projections run as one product
+with a fused [q; k; v] weight built when the weights are bound.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .. import kernels as K
+from ..registry import part_class, register_part
+from ..plan import PartPlan
+from ..weights.loader import TensorSpec
+from .base import CacheNeed, Part
+from .linear import Linear
+
+_TARGET_BLOCKS = 2 * 148  # blocks a decode step should offer the 148 SMs
+
+
+@dataclass(frozen=True)
+class AttentionSpec:
+    hidden_size: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    position: PartPlan                   # family "position"
+    window: Optional[int] = None         # None: every earlier key; n: the latest n keys
+    softmax_scale: Optional[float] = None  # None: 1 / sqrt(head_dim)
+
+
+@register_part("mixer", "attention")
+class Attention(Part):
+    family = "mixer"
+    roles = ("q", "k", "v", "o")
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        if spec.n_heads % spec.n_kv_heads:
+            raise ValueError(f"{spec.n_heads} heads do not divide into {spec.n_kv_heads} kv heads")
+        if spec.head_dim % 16 or not 16 <= spec.head_dim <= 256:
+            raise ValueError(f"head_dim {spec.head_dim}: the attention kernels take multiples of 16 from 16 to 256")
+        self.position = part_class("position", spec.position.kind)(spec.position.spec, spec.position.tensors, runtime)
+        self.scale = spec.softmax_scale if spec.softmax_scale is not None else 1.0 / math.sqrt(spec.head_dim)
+
+    def tensor_specs(self):
+        s, t = self.spec, self.tensor_names
+        return [TensorSpec(t["q"], (s.n_heads * s.head_dim, s.hidden_size)),
+                TensorSpec(t["k"], (s.n_kv_heads * s.head_dim, s.hidden_size)),
+                TensorSpec(t["v"], (s.n_kv_heads * s.head_dim, s.hidden_size)),
+                TensorSpec(t["o"], (s.hidden_size, s.n_heads * s.head_dim))] + self.position.tensor_specs()
+
+    def bind(self, loaded):
+        t = self.tensor_names
+        q, k, v = loaded[t["q"]], loaded[t["k"]], loaded[t["v"]]
+        if not (q.dtype == k.dtype == v.dtype):
+            raise ValueError(f"{t['q']}, {t['k']}, {t['v']} are stored in different dtypes")
+        fused = torch.cat([q, k, v], dim=0).contiguous()
+        self.qkv = Linear(fused)
+        self.q_only = Linear(fused[: self.spec.n_heads * self.spec.head_dim])
+        self.o = Linear(loaded[t["o"]])
+        self.position.bind(loaded)
+
+    def cache_need(self) -> CacheNeed:
+        s = self.spec
+        return CacheNeed("kv", n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window)
+
+    def _splits(self, step) -> int:
+        if step.max_q_len != 1:
+            return 1
+        s = self.spec
+        group = s.n_heads // s.n_kv_heads
+        blocks = step.n_seqs * s.n_kv_heads * ((group + 31) // 32)
+        pages = (step.max_kv_len + K.PAGE - 1) // K.PAGE
+        return max(1, min(pages, (_TARGET_BLOCKS + blocks - 1) // blocks, 64))
+
+    def forward(self, x, step, cache):
+        s, rt = self.spec, self.runtime
+        inv_freq, rot, interleaved = self.position.rotation()
+        n = step.n_tokens
+        if cache.writes:
+            qkv = self.qkv(x, out_dtype=rt.dtype)
+            n_kv_in_row = s.n_kv_heads
+        else:  # this run reads the cache line another run has written: only q is needed
+            qkv = self.q_only(x, out_dtype=rt.dtype)
+            n_kv_in_row = 0
+        K.rope_append(qkv, step.token_seq, step.token_pos, step.slot_of_seq, cache.block_table, inv_freq, rot,
+                      interleaved, cache.pool, s.n_heads, n_kv_in_row, s.head_dim, write_cache=cache.writes)
+        out = torch.empty((n, s.n_heads * s.head_dim), dtype=rt.dtype, device=x.device)
+        n_splits = self._splits(step)
+        scratch = None
+        if n_splits > 1:
+            scratch = step.workspace.scratch("attention", K.attention_scratch_floats(n, s.n_heads, s.head_dim, n_splits))
+        K.attention(qkv, qkv.shape[1], cache.pool, cache.block_table, step.cu_seqlens, step.slot_of_seq,
+                    step.start_pos, out, n, step.n_seqs, step.max_q_len, s.n_heads, s.n_kv_heads, s.head_dim,
+                    self.scale, window=s.window or 0, n_splits=n_splits, scratch=scratch)
+        return self.o(out, out_dtype=rt.dtype)

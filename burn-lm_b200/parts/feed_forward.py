@@ -1,0 +1,48 @@
+"""The dense gated feed-forward: (silu(x Wgate) * (x Wup)) Wdown, no biases
+(crates/burn-lm-llama/src/nn/fftn.rs:26-36,44-46).  Gate and up run as one product with a fused
+[gate; up] weight; the activation and the product of the two halves are fp32.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .. import kernels as K
+from ..registry import register_part
+from ..weights.loader import TensorSpec
+from .base import Part
+from .linear import Linear
+
+
+@dataclass(frozen=True)
+class SwiGLUSpec:
+    hidden_size: int
+    intermediate_size: int
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGLU(Part):
+    family = "feed_forward"
+    roles = ("gate", "up", "down")
+
+    def tensor_specs(self):
+        s, t = self.spec, self.tensor_names
+        return [TensorSpec(t["gate"], (s.intermediate_size, s.hidden_size)),
+                TensorSpec(t["up"], (s.intermediate_size, s.hidden_size)),
+                TensorSpec(t["down"], (s.hidden_size, s.intermediate_size))]
+
+    def bind(self, loaded):
+        t = self.tensor_names
+        g, u = loaded[t["gate"]], loaded[t["up"]]
+        if g.dtype != u.dtype:
+            raise ValueError(f"{t['gate']} and {t['up']} are stored in different dtypes")
+        self.gate_up = Linear(torch.cat([g, u], dim=0).contiguous())
+        self.down = Linear(loaded[t["down"]])
+
+    def forward(self, x, step):
+        rt = self.runtime
+        gu = self.gate_up(x, out_dtype=rt.dtype)
+        act = torch.empty((x.shape[0], self.spec.intermediate_size), dtype=rt.dtype, device=x.device)
+        K.swiglu(gu, act)
+        return self.down(act, out_dtype=rt.dtype)

@@ -1,0 +1,40 @@
+"""RMS norm fused with the residual add.
+
+y = x / sqrt(mean(x^2) + eps) * gamma; it stands before the mixer, before the feed-forward and once
+after the last block (crates/burn-lm-llama/src/nn/transformer.rs:248-255,101; eps at :60-62 and
+:211-216).  The sum of squares, the root and the product with gamma are fp32 in both paths.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .. import kernels as K
+from ..registry import register_part
+from ..weights.loader import TensorSpec
+from .base import Part
+
+
+@dataclass(frozen=True)
+class RMSNormSpec:
+    size: int
+    eps: float
+
+
+@register_part("norm", "rmsnorm")
+class RMSNorm(Part):
+    family = "norm"
+    roles = ("weight",)
+
+    def tensor_specs(self):
+        return [TensorSpec(self.tensor_names["weight"], (self.spec.size,), init="one_plus_normal:0.1")]
+
+    def bind(self, loaded):
+        self.gamma = loaded[self.tensor_names["weight"]]
+
+    def add_norm(self, resid, delta, rows=None):
+        n = rows.numel() if rows is not None else resid.shape[0]
+        out = torch.empty((n, self.spec.size), dtype=self.runtime.dtype, device=resid.device)
+        K.add_rmsnorm(resid, delta, self.gamma, self.spec.eps, out, rows)
+        return out

@@ -1,0 +1,300 @@
+"""Each kernel alone against a plain PyTorch fp32/fp64 restatement of the same operation, at sizes
+other than the engine's test models."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def K():
+    from burn_lm_b200 import kernels
+    return kernels
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("table_dtype", DTYPES)
+def test_embed(table_dtype):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    table = torch.randn(301, 72, device="cuda", generator=g).to(table_dtype)
+    tokens = torch.randint(0, 301, (17,), device="cuda", generator=g, dtype=torch.int32)
+    out = torch.empty(17, 72, device="cuda")
+    K().embed(tokens, table, out)
+    torch.testing.assert_close(out, table[tokens.long()].float(), rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("act", DTYPES)
+@pytest.mark.parametrize("gdt", DTYPES)
+@pytest.mark.parametrize("width", [72, 1000, 4100])
+def test_add_rmsnorm(act, gdt, width):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    n = 13
+    resid = torch.randn(n, width, device="cuda", generator=g)
+    delta = torch.randn(n, width, device="cuda", generator=g).to(act)
+    gamma = (1 + 0.1 * torch.randn(width, device="cuda", generator=g)).to(gdt)
+    eps = 3e-6
+    h = resid.double() + delta.double()
+    want = h / torch.sqrt((h * h).mean(-1, keepdim=True) + eps) * gamma.double()
+    r = resid.clone()
+    out = torch.empty(n, width, device="cuda", dtype=act)
+    K().add_rmsnorm(r, delta, gamma, eps, out)
+    torch.testing.assert_close(r.double(), h, rtol=1e-6, atol=1e-6)       # the sum is stored in fp32
+    torch.testing.assert_close(out.double(), want, **tol(act))
+    # rows mode leaves the stream alone; a missing delta adds nothing
+    rows = torch.tensor([5, 0, 12], device="cuda", dtype=torch.int32)
+    r2 = resid.clone()
+    out2 = torch.empty(3, width, device="cuda", dtype=act)
+    K().add_rmsnorm(r2, delta, gamma, eps, out2, rows)
+    torch.testing.assert_close(r2, resid, rtol=0, atol=0)
+    torch.testing.assert_close(out2.double(), want[rows.long()], **tol(act))
+    out3 = torch.empty(n, width, device="cuda", dtype=act)
+    K().add_rmsnorm(r2, None, gamma, eps, out3)
+    h0 = resid.double()
+    torch.testing.assert_close(out3.double(), h0 / torch.sqrt((h0 * h0).mean(-1, keepdim=True) + eps) * gamma.double(), **tol(act))
+
+
+def rope_reference(x, pos, inv_freq, rot, interleaved):
+    """x [N, heads, hd] float64."""
+    ang = pos.double()[:, None] * inv_freq[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    out = x.clone()
+    if interleaved:
+        a, b = x[..., 0:rot:2], x[..., 1:rot:2]
+        out[..., 0:rot:2] = a * c - b * s
+        out[..., 1:rot:2] = a * s + b * c
+    else:
+        a, b = x[..., : rot // 2], x[..., rot // 2: rot]
+        out[..., : rot // 2] = a * c - b * s
+        out[..., rot // 2: rot] = a * s + b * c
+    return out
+
+
+def paged_setup(lens_before, lens_new, n_kv, hd, dtype, seed, n_pages=None, shuffle=True):
+    """Block tables with shuffled pages and a pool full of NaN, as a reused cache would be."""
+    k = K()
+    g = torch.Generator().manual_seed(seed)
+    n_seqs = len(lens_new)
+    total = [a + b for a, b in zip(lens_before, lens_new)]
+    need = [(t + k.PAGE - 1) // k.PAGE for t in total]
+    n_pages = n_pages or sum(need) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist() if shuffle else list(range(n_pages))
+    max_pages = max(need) + 1
+    slots = torch.randperm(n_seqs + 2, generator=g)[:n_seqs].tolist()
+    table = torch.zeros(n_seqs + 2, max_pages, dtype=torch.int32)
+    it = iter(perm)
+    for s in range(n_seqs):
+        for p in range(need[s]):
+            table[slots[s], p] = next(it)
+    pool = torch.full((n_pages, 2, n_kv, k.PAGE, hd), float("nan"), dtype=dtype, device="cuda")
+    cu = [0]
+    for n in lens_new:
+        cu.append(cu[-1] + n)
+    token_seq = [s for s, n in enumerate(lens_new) for _ in range(n)]
+    token_pos = [lens_before[s] + t for s, n in enumerate(lens_new) for t in range(n)]
+    dev = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")
+    return dict(table=table.cuda(), pool=pool, cu=dev(cu), token_seq=dev(token_seq), token_pos=dev(token_pos),
+                slots=dev(slots), starts=dev(lens_before), host_table=table, host_slots=slots, total=total)
+
+
+def write_history(setup, k_hist, v_hist):
+    """Put per-sequence history [len, n_kv, hd] into the pool through the block table."""
+    P = K().PAGE
+    for s, (kh, vh) in enumerate(zip(k_hist, v_hist)):
+        for pos in range(kh.shape[0]):
+            page = int(setup["host_table"][setup["host_slots"][s], pos // P])
+            setup["pool"][page, 0, :, pos % P] = kh[pos].to(setup["pool"].dtype)
+            setup["pool"][page, 1, :, pos % P] = vh[pos].to(setup["pool"].dtype)
+
+
+def read_history(setup, s, length):
+    P = K().PAGE
+    ks, vs = [], []
+    for pos in range(length):
+        page = int(setup["host_table"][setup["host_slots"][s], pos // P])
+        ks.append(setup["pool"][page, 0, :, pos % P])
+        vs.append(setup["pool"][page, 1, :, pos % P])
+    return torch.stack(ks), torch.stack(vs)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("hd,rot", [(48, 48), (32, 16), (64, 0)])
+def test_rope_append(dtype, interleaved, hd, rot):
+    k = K()
+    H, KV = 5, 3
+    lens_before, lens_new = [0, 70, 63, 129], [9, 1, 3, 66]
+    st = paged_setup(lens_before, lens_new, KV, hd, dtype, seed=2)
+    n = sum(lens_new)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    qkv = torch.randn(n, (H + 2 * KV) * hd, device="cuda", generator=g).to(dtype)
+    inv_freq = None
+    if rot:
+        inv_freq = torch.tensor([1e4 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float64, device="cuda")
+    before = qkv.clone()
+    k.rope_append(qkv, st["token_seq"], st["token_pos"], st["slots"], st["table"], inv_freq, rot, interleaved,
+                  st["pool"], H, KV, hd)
+    x = before.double().view(n, H + 2 * KV, hd)
+    want_q = x[:, :H]
+    want_k = x[:, H:H + KV]
+    if rot:
+        want_q = rope_reference(want_q, st["token_pos"], inv_freq, rot, interleaved)
+        want_k = rope_reference(want_k, st["token_pos"], inv_freq, rot, interleaved)
+    t = tol(dtype)
+    torch.testing.assert_close(qkv.double().view(n, H + 2 * KV, hd)[:, :H], want_q, **t)
+    # k and v sit at their positions in the pages
+    row = 0
+    for s, new in enumerate(lens_new):
+        kh, vh = read_history(st, s, st["total"][s])
+        torch.testing.assert_close(kh[lens_before[s]:].double(), want_k[row:row + new], **t)
+        torch.testing.assert_close(vh[lens_before[s]:].double(), x[row:row + new, H + KV:], rtol=0, atol=0)
+        assert torch.isnan(kh[: lens_before[s]].float()).all()      # nothing else was touched
+        row += new
+
+
+def attention_reference(q, k_all, v_all, start, scale, window):
+    """q [T, H, hd], k_all/v_all [S, KV, hd] float64; token t at position start + t."""
+    T, H, hd = q.shape
+    S, KV, _ = k_all.shape
+    G = H // KV
+    out = torch.empty_like(q)
+    for h in range(H):
+        s = (q[:, h] @ k_all[:, h // G].T) * scale
+        i = torch.arange(T, device=q.device)[:, None] + start
+        j = torch.arange(S, device=q.device)[None, :]
+        hidden = j > i
+        if window:
+            hidden = hidden | (j <= i - window)
+        s = s.masked_fill(hidden, float("-inf"))
+        out[:, h] = torch.softmax(s, dim=-1) @ v_all[:, h // G]
+    return out
+
+
+def run_attention_case(dtype, H, KV, hd, lens_before, lens_new, window, n_splits, seed):
+    k = K()
+    st = paged_setup(lens_before, lens_new, KV, hd, dtype, seed=seed)
+    g = torch.Generator(device="cuda").manual_seed(seed + 100)
+    n = sum(lens_new)
+    q_stride = (H + 2 * KV) * hd
+    qkv = torch.randn(n, q_stride, device="cuda", generator=g).to(dtype)
+    k_hist = [torch.randn(t, KV, hd, device="cuda", generator=g).to(dtype) for t in st["total"]]
+    v_hist = [torch.randn(t, KV, hd, device="cuda", generator=g).to(dtype) for t in st["total"]]
+    write_history(st, k_hist, v_hist)
+    out = torch.empty(n, H * hd, device="cuda", dtype=dtype)
+    scale = 1.0 / math.sqrt(hd)
+    scratch = None
+    if n_splits > 1:
+        scratch = torch.empty(k.attention_scratch_floats(n, H, hd, n_splits), device="cuda")
+    k.attention(qkv, q_stride, st["pool"], st["table"], st["cu"], st["slots"], st["starts"], out, n, len(lens_new),
+                max(lens_new), H, KV, hd, scale, window=window, n_splits=n_splits, scratch=scratch)
+    row = 0
+    for s, new in enumerate(lens_new):
+        q = qkv[row:row + new].double().view(new, -1, hd)[:, :H]
+        want = attention_reference(q, k_hist[s].double(), v_hist[s].double(), lens_before[s], scale, window)
+        got = out[row:row + new].double().view(new, H, hd)
+        assert not torch.isnan(got).any()
+        torch.testing.assert_close(got, want, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)))
+        row += new
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KV,hd", [(4, 2, 16), (6, 1, 32), (5, 5, 48), (8, 2, 128), (3, 1, 256), (40, 1, 64)])
+def test_attention_prompts(dtype, H, KV, hd):
+    run_attention_case(dtype, H, KV, hd, [0, 0, 0, 0], [1, 7, 64, 131], 0, 1, seed=5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KV,hd", [(4, 2, 16), (6, 1, 32), (32, 8, 64), (7, 7, 80)])
+@pytest.mark.parametrize("n_splits", [1, 3, 8])
+def test_attention_single_tokens(dtype, H, KV, hd, n_splits):
+    run_attention_case(dtype, H, KV, hd, [0, 63, 64, 300, 129], [1, 1, 1, 1, 1], 0, n_splits, seed=6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_continued_prompts_and_window(dtype):
+    run_attention_case(dtype, 6, 2, 32, [10, 100, 64], [5, 40, 70], 0, 1, seed=7)
+    run_attention_case(dtype, 6, 2, 32, [10, 100, 64], [5, 40, 70], 37, 1, seed=8)
+    run_attention_case(dtype, 6, 2, 32, [200, 70, 5], [1, 1, 1], 65, 4, seed=9)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_a_far_key(dtype):
+    """One key among hundreds is made to match the query: the output must be that key's value."""
+    k = K()
+    H, KV, hd, S = 4, 2, 64, 700
+    for target in (0, 63, 64, 377, 699):
+        for n_splits in (1, 5):
+            st = paged_setup([S - 1], [1], KV, hd, dtype, seed=target)
+            g = torch.Generator(device="cuda").manual_seed(11)
+            kh = (0.01 * torch.randn(S, KV, hd, device="cuda", generator=g)).to(dtype)
+            vh = torch.randn(S, KV, hd, device="cuda", generator=g).to(dtype)
+            q = torch.zeros(1, (H + 2 * KV) * hd, device="cuda", dtype=dtype)
+            q[0, : H * hd] = 1.0
+            kh[target] = 4.0
+            write_history(st, [kh], [vh])
+            out = torch.empty(1, H * hd, device="cuda", dtype=dtype)
+            scratch = torch.empty(max(1, k.attention_scratch_floats(1, H, hd, n_splits)), device="cuda")
+            k.attention(q, q.shape[1], st["pool"], st["table"], st["cu"], st["slots"], st["starts"], out, 1, 1, 1,
+                        H, KV, hd, 1.0, n_splits=n_splits, scratch=scratch)
+            want = vh[target].float().repeat_interleave(H // KV, dim=0).reshape(-1)
+            torch.testing.assert_close(out[0].float(), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    g = torch.Generator(device="cuda").manual_seed(12)
+    gu = torch.randn(11, 2 * 200, device="cuda", generator=g).to(dtype)
+    out = torch.empty(11, 200, device="cuda", dtype=dtype)
+    K().swiglu(gu, out)
+    a, b = gu.double()[:, :200], gu.double()[:, 200:]
+    torch.testing.assert_close(out.double(), a / (1 + torch.exp(-a)) * b, **tol(dtype))
+
+
+@pytest.mark.parametrize("n,m,k_", [(1, 7, 5), (65, 130, 33), (200, 300, 1000)])
+def test_gemm_f32(n, m, k_):
+    g = torch.Generator(device="cuda").manual_seed(13)
+    x = torch.randn(n, k_, device="cuda", generator=g)
+    w = torch.randn(m, k_, device="cuda", generator=g)
+    y = K().gemm_f32(x, w)
+    torch.testing.assert_close(y.double(), x.double() @ w.double().T, rtol=1e-5, atol=1e-4)
+    # a row's result does not depend on the other rows of the batch
+    y1 = K().gemm_f32(x[:1].contiguous(), w)
+    assert torch.equal(y1[0], y[0])
+
+
+def test_convert():
+    x = torch.randn(1000, device="cuda")
+    b = torch.empty(1000, device="cuda", dtype=torch.bfloat16)
+    K().convert(x, b)
+    assert torch.equal(b, x.to(torch.bfloat16))
+    f = torch.empty(1000, device="cuda")
+    K().convert(b, f)
+    assert torch.equal(f, b.float())
+
+
+def test_argmax_lowest_index_wins():
+    g = torch.Generator(device="cuda").manual_seed(14)
+    logits = torch.randn(5, 5003, device="cuda", generator=g)
+    logits[1, 4000] = logits[1, 17] = 50.0
+    logits[2, 5002] = 60.0
+    out = torch.empty(5, device="cuda", dtype=torch.int32)
+    K().argmax(logits, out)
+    want = logits.argmax(-1)
+    want[1] = 17
+    assert out.tolist() == want.tolist()
+
+
+def test_refusals():
+    k = K()
+    with pytest.raises(k.KernelError):
+        k.embed(torch.zeros(3, dtype=torch.int32), torch.zeros(4, 4), torch.zeros(3, 4))   # CPU tensors
+    q = torch.zeros(1, 3 * 24, device="cuda")
+    pool = torch.zeros(2, 2, 1, k.PAGE, 24, device="cuda")
+    z = torch.zeros(2, dtype=torch.int32, device="cuda")
+    with pytest.raises(k.KernelError, match="multiple of 16"):
+        k.attention(q, 72, pool, z.view(1, 2), z, z, z, torch.zeros(1, 24, device="cuda"), 1, 1, 1, 1, 1, 24, 1.0)

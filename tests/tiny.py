@@ -1,0 +1,57 @@
+"""Tiny configurations of the architecture, differing in every size and option, and helpers that
+write them as model folders with random weights."""
+import os
+
+import numpy as np
+
+TINY_A = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 16, "intermediate_size": 160, "vocab_size": 256, "rope_theta": 10000.0,
+    "rope_scaling": None, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+    "max_position_embeddings": 128, "hidden_act": "silu",
+}
+
+TINY_B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 3, "hidden_size": 192, "num_attention_heads": 6, "num_key_value_heads": 1,
+    "head_dim": 32, "intermediate_size": 512, "vocab_size": 384, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 64},
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 256,
+    "hidden_act": "silu", "eos_token_id": [7, 11],
+}
+
+# head_dim 48 (not a power of two), 5 query heads on 5 kv heads, a width that is no multiple of 64,
+# room for long decoding
+TINY_C = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 112, "num_attention_heads": 5, "num_key_value_heads": 5,
+    "head_dim": 48, "intermediate_size": 200, "vocab_size": 1000, "rope_theta": 50000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 2.0,
+                     "original_max_position_embeddings": 128},
+    "rms_norm_eps": 3e-6, "tie_word_embeddings": True, "max_position_embeddings": 2048,
+    "hidden_act": "silu",
+}
+
+CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
+
+
+def make_folder(tmp_path, name, seed=0, dtype="float32"):
+    from burn_lm_b200 import write_random_model
+
+    folder = os.path.join(str(tmp_path), f"{name}-{dtype}-{seed}")
+    if not os.path.exists(os.path.join(folder, "model.safetensors")):
+        write_random_model(folder, CONFIGS[name], seed=seed, dtype=dtype)
+    return folder
+
+
+def random_tokens(seed, n, vocab):
+    return [int(t) for t in np.random.default_rng(seed).integers(0, vocab, size=n)]
+
+
+def row_error(got, want):
+    """max |got - want| of every row, relative to the row's largest |want|."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    return np.abs(got - want).max(axis=-1) / np.abs(want).max(axis=-1)
