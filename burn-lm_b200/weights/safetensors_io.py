@@ -11,6 +11,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 
 import torch
 
@@ -82,7 +83,9 @@ class SafetensorsFile:
         if hi == lo:
             return torch.empty(shape, dtype=_DTYPES[dt][0])
         buf = memoryview(self._mm)[self._base + lo: self._base + hi]
-        return torch.frombuffer(buf, dtype=_DTYPES[dt][0]).reshape(shape)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)   # the read-only mapping is only ever read
+            return torch.frombuffer(buf, dtype=_DTYPES[dt][0]).reshape(shape)
 
     def close(self):
         try:
