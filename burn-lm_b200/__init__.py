@@ -12,6 +12,8 @@ from .registry import (Architecture, architecture, architecture_of, architecture
 from .weights import TensorSpec, WeightsError, write_random_model
 from .model import Model, load_model, plan_of
 from .cache import Cache, CacheError, CacheFull, ContextLengthExceeded
-from .engine import Engine, StepEntry
+from .engine import Engine, GenerateOptions, GenerationLoop, StepEntry
+from .sampling import Sampler, SamplingParams
+from .api import LanguageModel, load
 
 __version__ = "0.1.0"

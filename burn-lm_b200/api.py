@@ -1,0 +1,82 @@
+"""The Python entry point: load a model folder, generate from token ids, step by hand.
+
+It follows the reference's server interface (trait InferenceServer: load, is_loaded, unload,
+run_job, clear_state; crates/burn-lm-inference/src/server.rs:21-52) and its per-request options
+(Llama3ServerConfig: top_p 0.9, temperature 0.0, max_seq_len 8192, sample_len 4096, seed 0;
+crates/burn-lm-llama/src/server/llama3.rs:14-31).  Text is out of scope: prompts and answers are
+token ids.
+"""
+from __future__ import annotations
+
+import time
+from typing import Callable, Optional, Sequence
+
+from .engine.engine import Engine
+from .engine.generate import GenerateOptions, GenerationLoop, GenerationOutput
+from .model import load_model
+from .sampling.sampler import Sampler
+
+
+class LanguageModel:
+    """A loaded model with its cache, generation loop and sampler."""
+
+    def __init__(self, folder: str, dtype: str = "bfloat16", max_seq_len: int = 8192, max_batch: int = 8,
+                 max_tokens: Optional[int] = None, device: str = "cuda:0"):
+        self.folder, self.dtype, self.device = folder, dtype, device
+        self.max_seq_len, self.max_batch, self.max_tokens = max_seq_len, max_batch, max_tokens
+        self.engine: Optional[Engine] = None
+        self.loop: Optional[GenerationLoop] = None
+        self.load_seconds = 0.0
+
+    # -- the reference's server interface --------------------------------------------------------
+    def load(self) -> "LanguageModel":
+        if self.engine is None:
+            t0 = time.perf_counter()
+            model = load_model(self.folder, self.dtype, self.device)
+            seq = min(self.max_seq_len, model.plan.max_positions)
+            tokens = self.max_tokens or -(-seq // 64) * 64 * self.max_batch
+            self.engine = Engine(model, max_tokens=tokens, max_seqs=max(self.max_batch, 1), max_seq_len=seq)
+            self.loop = GenerationLoop(self.engine, Sampler(model.runtime.device), model.plan.stop_ids)
+            self.load_seconds = time.perf_counter() - t0
+        return self
+
+    def is_loaded(self) -> bool:
+        return self.engine is not None
+
+    def unload(self) -> None:
+        self.engine = self.loop = None
+        import torch
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+
+    def clear_state(self) -> None:
+        """Give every slot and page back (every request re-reads its whole prompt anyway)."""
+        if self.engine is not None:
+            self.engine.cache.release_all()
+
+    def run_job(self, prompts, **options) -> GenerationOutput:
+        return self.generate(prompts, **options)
+
+    # -- generation ------------------------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], temperature: float = 0.0, top_p: float = 0.9,
+                 sample_len: int = 4096, seed: int = 0, stop_ids: Sequence[int] = (), ignore_stop: bool = False,
+                 batch_size: Optional[int] = None, on_token: Optional[Callable] = None) -> GenerationOutput:
+        """Generate up to sample_len tokens for every prompt (lists of token ids).
+
+        temperature 0 is greedy; otherwise tokens are drawn from the top_p nucleus of
+        softmax(logits / temperature).  seed 0 takes a new random seed.  Prompts run in batches of
+        unequal lengths, batch after batch; a sequence ends at a stop id (the model's eos ids and
+        `stop_ids`), at sample_len or at the context limit."""
+        self.load()
+        single = bool(prompts) and isinstance(prompts[0], int)
+        if single:
+            prompts = [prompts]
+        opts = GenerateOptions(temperature=temperature, top_p=top_p, sample_len=sample_len, seed=seed,
+                               stop_ids=tuple(stop_ids), ignore_stop=ignore_stop, batch_size=batch_size)
+        return self.loop.generate(prompts, opts, on_token)
+
+
+def load(folder: str, dtype: str = "bfloat16", max_seq_len: int = 8192, max_batch: int = 8,
+         max_tokens: Optional[int] = None, device: str = "cuda:0") -> LanguageModel:
+    """Load the model a folder's config.json names; see LanguageModel."""
+    return LanguageModel(folder, dtype, max_seq_len, max_batch, max_tokens, device).load()

@@ -1,0 +1,143 @@
+"""The generation loop's decisions, with stand-ins for the engine and the sampler (no GPU): batches
+in order, stop ids, lengths, the context limit, early leavers, release of every slot."""
+import pytest
+import torch
+
+from burn_lm_b200.cache import Cache, ContextLengthExceeded
+from burn_lm_b200.engine.generate import GenerateOptions, GenerationLoop, plan_batches
+from burn_lm_b200.parts.base import CacheNeed
+from burn_lm_b200.plan import ScheduleEntry
+
+VOCAB = 50
+
+
+class ScriptedEngine:
+    """Keeps a real cache (CPU) and returns logits whose argmax is a function of the sequence so far:
+    next = (sum of the sequence's tokens + its length) % VOCAB."""
+
+    def __init__(self, max_tokens=64 * 8, max_seqs=4, max_seq_len=256):
+        need = CacheNeed("kv", n_kv_heads=1, head_dim=16)
+        self.cache = Cache([need], [ScheduleEntry(0)], max_tokens, max_seqs, max_seq_len, torch.float32, torch.device("cpu"))
+        self.history = {}
+        self.steps = []
+
+    def acquire(self):
+        s = self.cache.acquire()
+        self.history[s] = []
+        return s
+
+    def release(self, slot):
+        self.cache.release(slot)
+        del self.history[slot]
+
+    def step(self, entries):
+        self.cache.reserve([(e.slot, self.cache.seq_len[e.slot] + len(e.tokens)) for e in entries])
+        self.steps.append([(e.slot, len(e.tokens)) for e in entries])
+        rows = []
+        for e in entries:
+            self.history[e.slot].extend(e.tokens)
+            self.cache.set_length(e.slot, len(self.history[e.slot]))
+            for w in e.want:
+                assert w == len(e.tokens) - 1
+                h = self.history[e.slot]
+                row = torch.zeros(VOCAB)
+                row[(sum(h) + len(h)) % VOCAB] = 1.0
+                rows.append(row)
+        return torch.stack(rows)
+
+
+class ArgmaxSampler:
+    def __init__(self):
+        self.calls = []
+
+    def sample(self, logits, params, stream_ids, counters):
+        self.calls.append((params, list(stream_ids), list(counters)))
+        return logits.argmax(-1).tolist()
+
+
+def expected(prompt, n, stop=()):
+    h, out = list(prompt), []
+    for _ in range(n):
+        t = (sum(h) + len(h)) % VOCAB
+        if t in stop:
+            return out, "stop"
+        out.append(t)
+        h.append(t)
+    return out, "length"
+
+
+def test_unequal_prompts_lengths_and_stops():
+    eng, smp = ScriptedEngine(), ArgmaxSampler()
+    loop = GenerationLoop(eng, smp, default_stop_ids=(13,))
+    prompts = [[1, 2, 3], [4], [5, 6, 7, 8, 9, 10, 11], [2, 2]]
+    out = loop.generate(prompts, GenerateOptions(sample_len=12, stop_ids=(29,)))
+    for p, r in zip(prompts, out.results):
+        toks, why = expected(p, 12, stop=(13, 29))
+        assert r.tokens == toks and r.finish_reason == why
+    assert {r.finish_reason for r in out.results} == {"stop", "length"}    # the script makes both happen
+    # one prefill step with all four, then single tokens for those still alive
+    assert [n for _, n in eng.steps[0]] == [3, 1, 7, 2]
+    assert all(n == 1 for st in eng.steps[1:] for _, n in st)
+    sizes = [len(st) for st in eng.steps]
+    assert sizes == sorted(sizes, reverse=True) and sizes[-1] < sizes[0]   # shorter requests left earlier
+    assert eng.cache.slots.held_count == 0 and eng.cache.free_pages == eng.cache.n_pages
+    assert out.stats.generated_tokens == sum(len(r.tokens) + (r.finish_reason == "stop") for r in out.results)
+    assert out.stats.prompt_tokens == 13 and out.stats.batches == 1
+    # draw numbers: a request's own stream, counting its own tokens
+    assert smp.calls[0][1] == [0, 1, 2, 3] and smp.calls[0][2] == [0, 0, 0, 0]
+    assert all(c == k for k, (_, _, cs) in enumerate(smp.calls) for c in cs)
+
+
+def test_batches_follow_one_another_and_reuse_slots():
+    eng, smp = ScriptedEngine(max_seqs=2), ArgmaxSampler()
+    loop = GenerationLoop(eng, smp)
+    prompts = [[i + 1, i + 2] for i in range(5)]
+    out = loop.generate(prompts, GenerateOptions(sample_len=3))
+    assert out.stats.batches == 3
+    for p, r in zip(prompts, out.results):
+        assert r.tokens == expected(p, 3)[0]
+    prefills = [st for st in eng.steps if any(n > 1 for _, n in st)]
+    assert [len(st) for st in prefills] == [2, 2, 1]
+    assert {s for st in eng.steps for s, _ in st} == {0, 1}                # the same two slots again and again
+
+
+def test_ignore_stop_and_seed():
+    eng, smp = ScriptedEngine(), ArgmaxSampler()
+    loop = GenerationLoop(eng, smp, default_stop_ids=(13,))
+    out = loop.generate([[4]], GenerateOptions(sample_len=20, ignore_stop=True, seed=77, temperature=0.5, top_p=0.8))
+    assert out.results[0].tokens == expected([4], 20)[0] and out.results[0].finish_reason == "length"
+    p = smp.calls[0][0]
+    assert (p.seed, p.temperature, p.top_p) == (77, 0.5, 0.8) and out.stats.seed == 77
+    out2 = loop.generate([[4]], GenerateOptions(sample_len=1))
+    assert out2.stats.seed != 0                                            # seed 0: a fresh one is drawn
+
+
+def test_context_limit_and_rejections():
+    eng, smp = ScriptedEngine(max_tokens=64 * 8, max_seqs=4, max_seq_len=70), ArgmaxSampler()
+    loop = GenerationLoop(eng, smp)
+    prompts = [list(range(1, 68)), list(range(80)), [], [3]]
+    out = loop.generate(prompts, GenerateOptions(sample_len=10))
+    r0, r1, r2, r3 = out.results
+    assert r0.finish_reason == "context" and len(r0.tokens) == 4           # 67 + 3 fed = 70 places, one more sampled
+    assert r1.finish_reason == "error" and isinstance(r1.error, ContextLengthExceeded) and r1.error.actual == 80
+    assert r2.finish_reason == "error" and r3.finish_reason == "length" and len(r3.tokens) == 10
+    assert eng.cache.slots.held_count == 0
+
+
+def test_on_token_streams_in_order():
+    eng, smp = ScriptedEngine(), ArgmaxSampler()
+    seen = []
+    out = GenerationLoop(eng, smp).generate([[1], [2, 3]], GenerateOptions(sample_len=4), on_token=lambda i, t: seen.append((i, t)))
+    for i, r in enumerate(out.results):
+        assert [t for j, t in seen if j == i] == r.tokens
+
+
+def test_plan_batches_respects_pages_slots_and_batch_size():
+    b, rej = plan_batches([10, 10, 10, 10, 10], sample_len=100, free_pages=4, free_slots=8, max_seq_len=1000)
+    assert b == [[0, 1], [2, 3], [4]] and not rej                          # 2 pages each at the longest
+    b, _ = plan_batches([10] * 5, sample_len=10, free_pages=100, free_slots=2, max_seq_len=1000)
+    assert b == [[0, 1], [2, 3], [4]]
+    b, _ = plan_batches([10] * 5, sample_len=10, free_pages=100, free_slots=8, max_seq_len=1000, batch_size=4)
+    assert b == [[0, 1, 2, 3], [4]]
+    b, rej = plan_batches([10, 500, 0], sample_len=10, free_pages=4, free_slots=8, max_seq_len=1000)
+    assert b == [[0]] and set(rej) == {1, 2}

@@ -1,0 +1,171 @@
+"""Generation through the Python entry point, sampling kernels against the plain sampler, long
+decoding, and the first tokens of a sequence."""
+import numpy as np
+import pytest
+import torch
+
+import traces
+from plain import llama_plain as P
+from tiny import CONFIGS, make_folder, random_tokens, row_error
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_greedy_generation_float32_matches_plain(tmp_path, name):
+    import burn_lm_b200 as blm
+    folder = make_folder(tmp_path, name, seed=8, dtype="bfloat16")
+    cfg, tensors = P.read_model_folder(folder)
+    lm = blm.load(folder, dtype="float32", max_seq_len=128, max_batch=3)
+    prompts = [random_tokens(20 + n, length, cfg["vocab_size"]) for n, length in enumerate([5, 11, 17, 1, 30])]
+    out = lm.generate(prompts, sample_len=8, batch_size=3, ignore_stop=True)
+    assert out.stats.batches == 2
+    for p, r in zip(prompts, out.results):
+        assert r.tokens == P.greedy_generate(cfg, tensors, p, 8) and r.finish_reason == "length"
+    assert lm.engine.cache.slots.held_count == 0 and lm.engine.cache.free_pages == lm.engine.cache.n_pages
+    # stop ids end a sequence and are not part of the answer
+    stop = out.results[1].tokens[3]
+    out2 = lm.generate(prompts[:3], sample_len=8, stop_ids=[stop], ignore_stop=False)
+    want = P.greedy_generate(cfg, tensors, prompts[1], 8, stop_ids=set(cfg.get("eos_token_id", [])) | {stop})
+    assert out2.results[1].tokens == want and out2.results[1].finish_reason == "stop"
+
+
+def test_greedy_generation_bfloat16_follows_plain_up_to_near_ties(tmp_path):
+    import burn_lm_b200 as blm
+    folder = make_folder(tmp_path, "tiny_b", seed=9, dtype="bfloat16")
+    cfg, tensors = P.read_model_folder(folder)
+    lm = blm.load(folder, dtype="bfloat16", max_seq_len=256, max_batch=4)
+    prompts = [random_tokens(40 + n, length, cfg["vocab_size"]) for n, length in enumerate([1, 7, 30, 64])]
+    out = lm.generate(prompts, sample_len=16, ignore_stop=True)
+    agree = 0
+    for p, r in zip(prompts, out.results):
+        seq = list(p)
+        for tok in r.tokens:
+            logits = P.forward(cfg, tensors, seq)[-1]
+            best = int(np.argmax(logits))
+            if tok != best:      # allowed only where the plain logits nearly tie
+                assert logits[best] - logits[tok] < 3e-2 * np.abs(logits).max(), (len(seq), tok, best)
+                break
+            agree += 1
+            seq.append(tok)
+    assert agree >= 48       # of 64: ties are rare
+
+
+def test_sampling_matches_plain_on_the_same_logits():
+    from burn_lm_b200 import kernels as K
+    from burn_lm_b200.sampling import Sampler, SamplingParams
+    g = torch.Generator(device="cuda").manual_seed(0)
+    B, V = 64, 1531
+    logits = 3.0 * torch.randn(B, V, device="cuda", generator=g)
+    smp = Sampler("cuda")
+    for temperature, top_p in [(0.8, 0.9), (1.3, 0.5), (0.6, 1.0), (1.0, 0.05)]:
+        params = SamplingParams(temperature, top_p, seed=1234)
+        streams, counters = list(range(100, 100 + B)), [b % 7 for b in range(B)]
+        got = smp.sample(logits, params, streams, counters)
+        same = 0
+        for b in range(B):
+            probs = P.temperature_softmax(logits[b].cpu().numpy(), temperature)
+            u = K.uniform32(1234, streams[b], counters[b]) / 2.0 ** 32
+            keep = P.top_p_keep(probs, top_p)
+            # the boundary of the nucleus may differ by a token or two between fp32 and fp64
+            assert keep[got[b]] or probs[got[b]] >= probs[keep].min() * 0.999
+            same += int(got[b] == P.top_p_draw(probs, top_p, u))
+        assert same >= B - 2, (temperature, top_p, same)
+        # a draw is a function of (seed, stream, counter), not of the row or the batch
+        perm = torch.randperm(B).tolist()
+        again = smp.sample(logits[perm].contiguous(), params, [streams[i] for i in perm], [counters[i] for i in perm])
+        assert again == [got[i] for i in perm]
+        alone = smp.sample(logits[5:6].contiguous(), params, streams[5:6], counters[5:6])
+        assert alone == got[5:6]
+    assert smp.sample(logits, SamplingParams(0.0), [0] * B, [0] * B) == logits.argmax(-1).tolist()
+
+
+def test_sampling_frequencies_follow_the_nucleus():
+    from burn_lm_b200.sampling import Sampler, SamplingParams
+    logits = torch.tensor([[2.0, 1.0, 0.5, 0.0, -1.0, -2.0, 1.5, -8.0]], device="cuda")
+    n = 4000
+    rows = logits.repeat(n, 1).contiguous()
+    got = Sampler("cuda").sample(rows, SamplingParams(0.7, 0.8, seed=5), [3] * n, list(range(n)))
+    probs = P.temperature_softmax(logits[0].cpu().numpy(), 0.7)
+    keep = P.top_p_keep(probs, 0.8)
+    want = np.where(keep, probs, 0.0)
+    want /= want.sum()
+    freq = np.bincount(got, minlength=8) / n
+    assert (freq[~keep] == 0).all()
+    assert np.abs(freq - want).max() < 4 * np.sqrt(0.25 / n)
+
+
+def test_temperature_generation_is_seeded_and_batch_independent(tmp_path):
+    import burn_lm_b200 as blm
+    folder = make_folder(tmp_path, "tiny_b", seed=10, dtype="bfloat16")
+    lm = blm.load(folder, dtype="float32", max_seq_len=256, max_batch=4)
+    cfg = CONFIGS["tiny_b"]
+    prompts = [random_tokens(60 + n, length, cfg["vocab_size"]) for n, length in enumerate([1, 7, 30, 64])]
+    a = lm.generate(prompts, sample_len=16, temperature=0.8, seed=42, ignore_stop=True).tokens
+    b = lm.generate(prompts, sample_len=16, temperature=0.8, seed=42, ignore_stop=True).tokens
+    c = lm.generate(prompts, sample_len=16, temperature=0.8, seed=43, ignore_stop=True).tokens
+    assert a == b and a != c
+    one_by_one = lm.generate(prompts, sample_len=16, temperature=0.8, seed=42, ignore_stop=True, batch_size=1).tokens
+    assert one_by_one[0] == a[0]            # request 0 draws the same alone as in the batch
+
+
+def test_long_decoding(tmp_path):
+    """600 tokens one by one after a short prompt: positions cross many pages and the scaled rotary
+    frequencies turn many times."""
+    from burn_lm_b200 import Engine
+    folder = make_folder(tmp_path, "tiny_c", seed=11, dtype="bfloat16")
+    cfg, tensors = P.read_model_folder(folder)
+    reqs = {"long": random_tokens(70, 610, cfg["vocab_size"])}
+    want = P.forward(cfg, tensors, reqs["long"])
+    for dtype, tolerance in (("float32", 1e-4), ("bfloat16", 3e-2)):
+        steps = traces.tail(reqs, 600)
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=traces.max_live_tokens(steps))
+        got = traces.run_in_process(eng, steps, str(tmp_path / dtype), cfg["vocab_size"])
+        err = row_error(got["long"], want)
+        assert err.max() < tolerance, (dtype, float(err.max()), int(err.argmax()))
+
+
+@pytest.mark.parametrize("dtype,tolerance", [("float32", 1e-4), ("bfloat16", 3e-2)])
+def test_first_tokens_of_a_sequence(tmp_path, dtype, tolerance):
+    """Prompts of one, two and three tokens, then single tokens from the very first position."""
+    from burn_lm_b200 import Engine
+    folder = make_folder(tmp_path, "tiny_a", seed=12, dtype="bfloat16")
+    cfg, tensors = P.read_model_folder(folder)
+    reqs = {f"f{n}": random_tokens(80 + n, n + 1 + 6, cfg["vocab_size"]) for n in range(3)}
+    steps = traces.batched(reqs, 3, [6, 6, 6])      # prompts of 1, 2, 3 tokens, then 6 single tokens each
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=traces.max_live_tokens(steps))
+    got = traces.run_in_process(eng, steps, str(tmp_path / "o"), cfg["vocab_size"])
+    for rid, toks in reqs.items():
+        err = row_error(got[rid], P.forward(cfg, tensors, toks))
+        assert err.max() < tolerance, (rid, float(err.max()))
+
+
+def test_a_far_key_decides_the_logits(tmp_path):
+    """Random weights make attention nearly uniform, which would hide a lost key.  Here the last
+    layer's query and key projections are scaled up so that scores are sharp, on a sequence long
+    enough that the keys that matter lie pages away; batched and token-by-token replays must still
+    agree with the plain implementation."""
+    from burn_lm_b200 import Engine
+    from burn_lm_b200.weights import SafetensorsFile, write_safetensors
+    import os
+    folder = make_folder(tmp_path, "tiny_c", seed=13, dtype="float32")
+    f = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    tensors = {n: f.get(n).clone() for n in f.names()}
+    f.close()
+    for n in range(2):
+        tensors[f"model.layers.{n}.self_attn.q_proj.weight"] *= 12.0
+        tensors[f"model.layers.{n}.self_attn.k_proj.weight"] *= 12.0
+        tensors[f"model.layers.{n}.self_attn.v_proj.weight"] *= 6.0
+        tensors[f"model.layers.{n}.self_attn.o_proj.weight"] *= 6.0
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+    cfg, t = P.read_model_folder(folder)
+    reqs = {"a": random_tokens(90, 500, cfg["vocab_size"]), "b": random_tokens(91, 200, cfg["vocab_size"]),
+            "c": random_tokens(92, 333, cfg["vocab_size"])}
+    want = {rid: P.forward(cfg, t, toks) for rid, toks in reqs.items()}
+    # the sharpened attention really is far from uniform: logits differ a lot from the unscaled model's
+    for what, steps in (("batched", traces.batched(reqs, 3, [32, 7, 19])), ("tail", traces.tail(reqs, 32))):
+        eng = Engine.from_folder(folder, dtype="float32", max_tokens=traces.max_live_tokens(steps))
+        got = traces.run_in_process(eng, steps, str(tmp_path / what), cfg["vocab_size"])
+        for rid in reqs:
+            err = row_error(got[rid], want[rid])
+            assert err.max() < 1e-4, (what, rid, float(err.max()), int(err.argmax()))

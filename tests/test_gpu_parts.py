@@ -1,0 +1,301 @@
+"""Each part of a layer alone against its plain twin, built directly from its spec with random
+tensors, and a toy architecture with a toy mixer (state of its own), a layer that runs twice and a
+run that reads another run's cache: all registered from here, without touching the package."""
+import dataclasses
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+
+
+def runtime(dtype):
+    from burn_lm_b200.parts import Runtime
+    return Runtime(dtype, torch.device("cuda"))
+
+
+def step_for(lengths, starts=None, slots=None):
+    """A StepContext for sequences of the given new lengths."""
+    from burn_lm_b200.engine import Workspace
+    from burn_lm_b200.parts import StepContext
+    starts = starts or [0] * len(lengths)
+    slots = slots or list(range(len(lengths)))
+    cu = [0]
+    for n in lengths:
+        cu.append(cu[-1] + n)
+    dev = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")
+    return StepContext(
+        n_tokens=cu[-1], n_seqs=len(lengths), max_q_len=max(lengths), max_kv_len=max(s + n for s, n in zip(starts, lengths)),
+        tokens=dev([0] * cu[-1]), token_seq=dev([s for s, n in enumerate(lengths) for _ in range(n)]),
+        token_pos=dev([starts[s] + t for s, n in enumerate(lengths) for t in range(n)]), cu_seqlens=dev(cu),
+        slot_of_seq=dev(slots), start_pos=dev(starts), want_rows=None, n_want=0, workspace=Workspace(torch.device("cuda")),
+        host={"cu_seqlens": cu, "slots": slots, "start_pos": starts})
+
+
+# largest error of an output row relative to the row's largest value (outputs may cross zero, so an
+# element-wise relative tolerance would mean nothing)
+TOL = {torch.float32: 1e-5, torch.bfloat16: 3e-2}   # bfloat16: the bound used for logits everywhere
+
+
+def assert_rows_close(got, want, dtype):
+    from tiny import row_error
+    err = row_error(got.double().cpu().numpy(), want)
+    assert err.max() < TOL[dtype], (float(err.max()), int(err.argmax()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rms_norm_part(dtype):
+    from burn_lm_b200.parts import RMSNorm, RMSNormSpec
+    part = RMSNorm(RMSNormSpec(size=88, eps=2e-6), {"weight": "g"}, runtime(dtype))
+    assert [(s.name, s.shape) for s in part.tensor_specs()] == [("g", (88,))]
+    g = (1 + 0.1 * torch.randn(88)).to(dtype).cuda()
+    part.bind({"g": g})
+    resid = torch.randn(9, 88, device="cuda")
+    delta = torch.randn(9, 88, device="cuda").to(dtype)
+    want = P.rms_norm((resid.double() + delta.double()).cpu().numpy(), g.double().cpu().numpy(), 2e-6)
+    got = part.add_norm(resid, delta)
+    assert_rows_close(got, want, dtype)
+
+
+def test_rotary_part_frequencies():
+    from burn_lm_b200.parts import Llama3Scaling, Rotary, RotarySpec
+    spec = RotarySpec(head_dim=48, theta=77777.0, scaling=Llama3Scaling(5.0, 1.0, 3.0, 100))
+    part = Rotary(spec, {}, runtime(torch.float32))
+    want = P.llama3_frequency_scaling(P.rope_inverse_frequencies(48, 77777.0), 5.0, 1.0, 3.0, 100)
+    inv, rot, inter = part.rotation()
+    assert rot == 48 and not inter
+    np.testing.assert_allclose(inv.cpu().numpy(), want, rtol=1e-14)
+    part2 = Rotary(RotarySpec(head_dim=48, theta=10.0, rotary_dim=16, interleaved=True), {}, runtime(torch.float32))
+    assert part2.rotation()[1:] == (16, True) and part2.rotation()[0].numel() == 8
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_attention_part(dtype, interleaved):
+    """The mixer alone with a cache of its own: two prompts, then both continue by single tokens."""
+    from burn_lm_b200.cache import Cache
+    from burn_lm_b200.parts import Attention, AttentionSpec, RotarySpec
+    from burn_lm_b200.plan import PartPlan, ScheduleEntry
+    D, H, KV, hd = 72, 6, 3, 16
+    spec = AttentionSpec(D, H, KV, hd, PartPlan("rotary", RotarySpec(head_dim=hd, theta=500.0, interleaved=interleaved)))
+    part = Attention(spec, {"q": "q", "k": "k", "v": "v", "o": "o"}, runtime(dtype))
+    g = torch.Generator().manual_seed(1)
+    w = {n: (0.3 * torch.randn(*s, generator=g)).to(dtype).cuda()
+         for n, s in (("q", (H * hd, D)), ("k", (KV * hd, D)), ("v", (KV * hd, D)), ("o", (D, H * hd)))}
+    part.bind(w)
+    cache = Cache([part.cache_need()], [ScheduleEntry(0)], 64 * 4, 2, 128, dtype, torch.device("cuda"))
+    lens = [70, 9]
+    xs = [(torch.randn(n + 5, D, generator=g)).to(dtype).cuda() for n in lens]
+    slots = [cache.acquire(), cache.acquire()]
+    wn = {n: t.double().cpu().numpy() for n, t in w.items()}
+    inv = P.rope_inverse_frequencies(hd, 500.0)
+    want = [P.attention(x.double().cpu().numpy(), wn["q"], wn["k"], wn["v"], wn["o"], H, KV, hd, inv,
+                        "interleaved" if interleaved else "half") for x in xs]
+    cache.reserve([(s, n) for s, n in zip(slots, lens)])
+    out = part.forward(torch.cat([x[:n] for x, n in zip(xs, lens)]), step_for(lens, slots=slots), cache.view(0))
+    got = [out[:70], out[70:]]
+    for s, n in zip(slots, lens):
+        cache.set_length(s, n)
+    for t in range(5):
+        starts = [n + t for n in lens]
+        cache.reserve([(s, st + 1) for s, st in zip(slots, starts)])
+        o = part.forward(torch.stack([x[st] for x, st in zip(xs, starts)]), step_for([1, 1], starts, slots), cache.view(0))
+        got = [torch.cat([gg, o[i:i + 1]]) for i, gg in enumerate(got)]
+    for gg, ww in zip(got, want):
+        assert_rows_close(gg, ww, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_part(dtype):
+    from burn_lm_b200.parts import SwiGLU, SwiGLUSpec
+    part = SwiGLU(SwiGLUSpec(hidden_size=40, intermediate_size=104), {"gate": "g", "up": "u", "down": "d"}, runtime(dtype))
+    gen = torch.Generator().manual_seed(2)
+    w = {"g": torch.randn(104, 40, generator=gen) * 0.3, "u": torch.randn(104, 40, generator=gen) * 0.3,
+         "d": torch.randn(40, 104, generator=gen) * 0.3}
+    w = {k: v.to(dtype).cuda() for k, v in w.items()}
+    part.bind(w)
+    x = torch.randn(7, 40, generator=gen).to(dtype).cuda()
+    want = P.feed_forward(x.double().cpu().numpy(), *(w[k].double().cpu().numpy() for k in ("g", "u", "d")))
+    assert_rows_close(part.forward(x, None), want, dtype)
+
+
+def test_a_layer_stored_in_32_bit_inside_a_bfloat16_model():
+    """A tensor stored in 32-bit stays so: its products run through the fp32 kernel."""
+    from burn_lm_b200.parts import SwiGLU, SwiGLUSpec
+    part = SwiGLU(SwiGLUSpec(hidden_size=40, intermediate_size=104), {"gate": "g", "up": "u", "down": "d"},
+                  runtime(torch.bfloat16))
+    gen = torch.Generator().manual_seed(3)
+    w = {"g": torch.randn(104, 40, generator=gen).cuda(), "u": torch.randn(104, 40, generator=gen).cuda(),
+         "d": torch.randn(40, 104, generator=gen).cuda()}
+    part.bind(w)
+    assert part.gate_up.weight.dtype == torch.float32
+    x = torch.randn(7, 40, generator=gen).to(torch.bfloat16).cuda()
+    want = P.feed_forward(x.double().cpu().numpy(), *(w[k].double().cpu().numpy() for k in ("g", "u", "d")))
+    got = part.forward(x, None)
+    assert got.dtype == torch.bfloat16
+    assert_rows_close(got, want, torch.bfloat16)
+
+
+# --------------------------------------------------------------------------------------------------
+# a toy architecture, registered from the test
+# --------------------------------------------------------------------------------------------------
+@dataclasses.dataclass(frozen=True)
+class DecaySpec:
+    hidden_size: int
+    decay: float
+
+
+def register_toy():
+    """A mixer with fixed-size state of its own: s_t = decay * s_{t-1} + x_t W_in; out_t = s_t W_out.
+    Written with torch operations here in the test; it uses the cache's state block of its slot."""
+    from burn_lm_b200 import register_architecture, register_part, Architecture, TensorSpec
+    from burn_lm_b200.config import KeyReader
+    from burn_lm_b200.parts import CacheNeed, Part, RMSNormSpec, SwiGLUSpec, AttentionSpec, NoPositionSpec, EmbeddingSpec, HeadSpec
+    from burn_lm_b200.plan import LayerPlan, ModelPlan, PartPlan, ScheduleEntry
+    from burn_lm_b200 import registry
+
+    if "ToyDecayLM" in [a.name for a in registry.architectures()]:
+        return
+
+    @register_part("mixer", "toy_decay")
+    class DecayMixer(Part):
+        family = "mixer"
+
+        def tensor_specs(self):
+            d = self.spec.hidden_size
+            return [TensorSpec(self.tensor_names["w_in"], (d, d), init="normal:0.1"),
+                    TensorSpec(self.tensor_names["w_out"], (d, d), init="normal:0.1")]
+
+        def bind(self, loaded):
+            self.w_in = loaded[self.tensor_names["w_in"]].float()
+            self.w_out = loaded[self.tensor_names["w_out"]].float()
+
+        def cache_need(self):
+            return CacheNeed("state", state_shape=(self.spec.hidden_size,), state_dtype="float32")
+
+        def forward(self, x, step, cache):
+            u = x.float() @ self.w_in.T
+            out = torch.empty_like(u)
+            cu, slots = step.host["cu_seqlens"], step.host["slots"]
+            for s, slot in enumerate(slots):
+                state = cache.state[slot]
+                for t in range(cu[s], cu[s + 1]):
+                    state.mul_(self.spec.decay).add_(u[t])
+                    out[t] = state
+            return (out @ self.w_out.T).to(x.dtype)
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyConfig:
+        width: int
+        depth: int
+        words: int
+        decay: float
+        eps: float
+        heads: int
+        inner: int
+
+        @classmethod
+        def from_dict(cls, d):
+            r = KeyReader(d)
+            return cls(r.integer("toy_width"), r.integer("toy_depth"), r.integer("toy_words"), r.number("toy_decay"),
+                       r.number("toy_eps"), r.integer("toy_heads"), r.integer("toy_inner"))
+
+    def plan(cfg):
+        norm = RMSNormSpec(cfg.width, cfg.eps)
+        layers = []
+        for n in range(cfg.depth):
+            p = f"toy.{n}."
+            if n % 2 == 0:
+                mixer = PartPlan("toy_decay", DecaySpec(cfg.width, cfg.decay), {"w_in": p + "in", "w_out": p + "out"})
+            else:   # attention without position encoding, between the state layers
+                mixer = PartPlan("attention", AttentionSpec(cfg.width, cfg.heads, 1, cfg.width // cfg.heads,
+                                                            PartPlan("none", NoPositionSpec())),
+                                 {"q": p + "q", "k": p + "k", "v": p + "v", "o": p + "o"})
+            layers.append(LayerPlan("prenorm", PartPlan("rmsnorm", norm, {"weight": p + "n1"}), mixer,
+                                    PartPlan("rmsnorm", norm, {"weight": p + "n2"}),
+                                    PartPlan("swiglu", SwiGLUSpec(cfg.width, cfg.inner),
+                                             {"gate": p + "g", "up": p + "u", "down": p + "d"})))
+        # layer 0 runs twice (two state blocks), and the last run reads the cache line of run 1
+        schedule = [ScheduleEntry(n) for n in range(cfg.depth)] + [ScheduleEntry(0), ScheduleEntry(1, cache_of=1)]
+        return ModelPlan("ToyDecayLM", cfg.words, cfg.width,
+                         PartPlan("table", EmbeddingSpec(cfg.words, cfg.width), {"table": "toy.embed"}),
+                         tuple(layers), tuple(schedule), PartPlan("rmsnorm", norm, {"weight": "toy.norm"}),
+                         PartPlan("linear", HeadSpec(cfg.words, cfg.width), {"weight": "toy.embed"}), max_positions=512)
+
+    register_architecture(Architecture("ToyDecayLM", ToyConfig, plan, description="test-only"))
+
+
+TOY = {"architectures": ["ToyDecayLM"], "toy_width": 48, "toy_depth": 2, "toy_words": 90, "toy_decay": 0.8,
+       "toy_eps": 1e-5, "toy_heads": 3, "toy_inner": 80}
+
+
+def toy_plain(tensors, tokens):
+    """The toy model on one whole sequence, float64, written out plainly."""
+    t = {k: v for k, v in tensors.items()}
+    h = P.embedding(t["toy.embed"], tokens)
+    T = len(tokens)
+
+    def decay_mixer(x, p):
+        u = x @ t[p + "in"].T
+        s = np.zeros(48)
+        out = np.zeros_like(u)
+        for i in range(T):
+            s = 0.8 * s + u[i]
+            out[i] = s
+        return out @ t[p + "out"].T
+
+    def attn(x, p, kv_from=None):
+        kx = x if kv_from is None else kv_from
+        q = (x @ t[p + "q"].T).reshape(T, 3, 16)
+        k = (kx @ t[p + "k"].T).reshape(T, 1, 16)
+        v = (kx @ t[p + "v"].T).reshape(T, 1, 16)
+        o = np.zeros((T, 3, 16))
+        for hh in range(3):
+            s = q[:, hh] @ k[:, 0].T / 4.0
+            s = np.where(np.triu(np.ones((T, T), bool), 1), -np.inf, s)
+            o[:, hh] = P.softmax(s) @ v[:, 0]
+        return o.reshape(T, 48) @ t[p + "o"].T
+
+    def ffn(x, p):
+        return P.feed_forward(x, t[p + "g"], t[p + "u"], t[p + "d"])
+
+    runs = [(0, None), (1, None), (0, None), (1, "shared")]
+    kv_input = None
+    for layer, shared in runs:
+        p = f"toy.{layer}."
+        xn = P.rms_norm(h, t[p + "n1"], 1e-5)
+        if layer == 0:
+            a = decay_mixer(xn, p)
+        elif shared is None:
+            kv_input = xn
+            a = attn(xn, p)
+        else:
+            a = attn(xn, p, kv_from=kv_input)        # keys and values of the earlier run
+        h = h + a
+        h = h + ffn(P.rms_norm(h, t[p + "n2"], 1e-5), p)
+    return P.rms_norm(h, t["toy.norm"], 1e-5) @ t["toy.embed"].T
+
+
+def test_toy_architecture_registers_builds_and_steps(tmp_path):
+    import traces
+    from burn_lm_b200 import Engine, write_random_model
+    from tiny import random_tokens, row_error
+    register_toy()
+    folder = write_random_model(str(tmp_path / "toy"), TOY, seed=1, dtype="float32")
+    cfg, tensors = P.read_model_folder(folder)
+    reqs = {"a": random_tokens(1, 75, 90), "b": random_tokens(2, 20, 90), "c": random_tokens(3, 130, 90), "d": random_tokens(4, 9, 90)}
+    want = {rid: toy_plain(tensors, toks) for rid, toks in reqs.items()}
+    for what, steps in (("whole", traces.whole(reqs)), ("tail", traces.tail(reqs, 32)), ("batched", traces.batched(reqs, 2, [5, 32]))):
+        eng = Engine.from_folder(folder, dtype="float32", max_tokens=traces.max_live_tokens(steps), max_seqs=2)
+        kinds = [eng.cache.view(r).kind for r in range(4)]
+        assert kinds == ["state", "kv", "state", "kv"] and not eng.cache.view(3).writes
+        assert eng.cache.view(0).state.data_ptr() != eng.cache.view(2).state.data_ptr()
+        got = traces.run_in_process(eng, steps, str(tmp_path / what), 90)
+        for rid in reqs:
+            err = row_error(got[rid], want[rid])
+            assert err.max() < 1e-4, (what, rid, float(err.max()), int(err.argmax()))
