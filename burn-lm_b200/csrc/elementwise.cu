@@ -238,3 +238,32 @@ BLM_API int blm_convert(const void* in, int in_dtype, void* out, int out_dtype, 
         return blm_fail(BLM_BAD_ARGUMENT, "convert: %d -> %d", in_dtype, out_dtype);
     return blm_check_launch("convert");
 }
+
+// ---------------------------------------------------------------------------------------------
+// between two decode steps that run without the host: the sampled token becomes the next input,
+// every position moves on by one, and the token is appended to the history of the run
+// ---------------------------------------------------------------------------------------------
+__global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict__ pos, const int* __restrict__ sampled,
+                                      int* __restrict__ history, int* __restrict__ step_no, long long* __restrict__ counters,
+                                      int batch, int history_steps) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    const int s = *step_no;
+    if (b < batch) {
+        const int t = sampled[b];
+        tokens[b] = t;
+        pos[b] += 1;
+        if (counters) counters[b] += 1;
+        if (history && s < history_steps) history[(size_t)s * batch + b] = t;
+    }
+}
+// a launch of its own, so that every block of the kernel above has read the old value
+__global__ void bump_kernel(int* step_no) { *step_no += 1; }
+
+BLM_API int blm_decode_advance(int* tokens, int* pos, const int* sampled, int* history, int* step_no,
+                               long long* counters, int batch, int history_steps, cudaStream_t stream) {
+    if (batch == 0) return BLM_OK;
+    BLM_REQUIRE(step_no != nullptr, "decode_advance: no step counter");
+    decode_advance_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(tokens, pos, sampled, history, step_no, counters, batch, history_steps);
+    bump_kernel<<<1, 1, 0, stream>>>(step_no);
+    return blm_check_launch("decode_advance");
+}

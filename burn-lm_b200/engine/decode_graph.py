@@ -1,0 +1,104 @@
+"""Decode steps as CUDA graphs: one token for each of B sequences, with every launch of the step
+captured once and replayed.
+
+What changes from step to step (tokens, positions, slots, block tables, lengths) lives in device
+buffers with fixed addresses, so one graph per batch size serves every step and every set of
+sequences.  `DecodeGraph.step` takes a step's tokens from pinned host memory and leaves the logits
+in a fixed buffer; `DecodeGraph.run` goes on for many steps without the host in between: the greedy
+token of a step is written back as the next step's input by a kernel inside the graph.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels as K
+from ..parts.base import StepContext
+from .engine import Workspace
+
+
+class DecodeGraph:
+    def __init__(self, engine, batch: int):
+        self.engine, self.batch = engine, batch
+        dev = engine.model.runtime.device
+        b = batch
+        # tokens | positions | slots: what a step brings, in one buffer, one copy
+        self.meta = torch.zeros(3 * b, dtype=torch.int32, device=dev)
+        self.host_meta = torch.zeros(3 * b, dtype=torch.int32, pin_memory=True)
+        self.tokens, self.pos, self.slots = self.meta[:b], self.meta[b:2 * b], self.meta[2 * b:]
+        ar = torch.arange(b + 1, dtype=torch.int32, device=dev)
+        self.ctx = StepContext(
+            n_tokens=b, n_seqs=b, max_q_len=1, max_kv_len=engine.cache.max_seq_len,
+            tokens=self.tokens, token_seq=ar[:b], token_pos=self.pos, cu_seqlens=ar, slot_of_seq=self.slots,
+            start_pos=self.pos, want_rows=ar[:b], n_want=b,
+            workspace=Workspace(dev),     # its own: a captured graph keeps the addresses it saw
+           
+            host={"cu_seqlens": list(range(b + 1)), "slots": None, "start_pos": None})
+        self.sampled = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.step_no = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.history = None
+        self.logits = None
+        self._graph = None          # forward only
+        self._loop_graph = None     # forward + argmax + advance
+        self._loop_history_steps = 0
+        self._copied = None
+        self.launches_per_step = 0
+
+    def bytes_in_per_step(self) -> int:
+        return self.host_meta.numel() * 4
+
+    def load(self, tokens, positions, slots) -> None:
+        """Bring a step's inputs from (pinned) host memory to the graph's buffers."""
+        b = self.batch
+        if self._copied is not None:
+            self._copied.synchronize()       # the last copy has left the pinned buffer
+        self.host_meta[:b] = torch.tensor(tokens, dtype=torch.int32)
+        self.host_meta[b:2 * b] = torch.tensor(positions, dtype=torch.int32)
+        self.host_meta[2 * b:] = torch.tensor(slots, dtype=torch.int32)
+        self.meta.copy_(self.host_meta, non_blocking=True)
+        self._copied = torch.cuda.Event()
+        self._copied.record()
+        self.ctx.host["slots"], self.ctx.host["start_pos"] = list(slots), list(positions)
+
+    def _forward(self):
+        return self.engine.model.forward(self.ctx, self.engine.cache)
+
+    def step(self) -> torch.Tensor:
+        """One decode step on the loaded inputs; fp32 logits [B, vocab] in a buffer that the next
+        step overwrites."""
+        if self._graph is None:
+            self.logits = self._forward()            # the first step runs plainly and warms everything up
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._captured_logits = self._forward()
+            self._graph = g
+            return self.logits
+        self._graph.replay()
+        return self._captured_logits
+
+    def run(self, n_steps: int, keep_history: bool = True) -> torch.Tensor:
+        """n_steps greedy decode steps without the host in between, starting from the loaded inputs.
+        Pages for positions up to (loaded position + n_steps) must be reserved.  Returns the sampled
+        tokens int32 [n_steps, B] (on the device)."""
+        if self._loop_graph is None or (keep_history and self._loop_history_steps < n_steps):
+            self._loop_history_steps = max(n_steps, 256)
+            self.history = torch.zeros((self._loop_history_steps, self.batch), dtype=torch.int32, device=self.meta.device)
+            saved = self.meta.clone()
+            self._one_loop_step()                    # warm-up, undone below
+            torch.cuda.synchronize()
+            self.meta.copy_(saved)
+            g = torch.cuda.CUDAGraph()
+            before = K.launch_count()
+            with torch.cuda.graph(g):
+                self._one_loop_step()
+            self.launches_per_step = K.launch_count() - before   # this package's kernels in one replay
+            self._loop_graph = g
+        self.step_no.zero_()
+        for _ in range(n_steps):
+            self._loop_graph.replay()
+        return self.history[:n_steps]
+
+    def _one_loop_step(self):
+        logits = self._forward()
+        K.argmax(logits, self.sampled)
+        K.decode_advance(self.tokens, self.pos, self.sampled, self.history, self.step_no)

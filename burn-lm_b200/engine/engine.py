@@ -65,6 +65,10 @@ class Engine:
         self.workspace = Workspace(rt.device)
         self.vocab_size = model.plan.vocab_size
         self._staging = None    # pinned int32 staging for the step's metadata
+        # decode steps (one token each, its logits wanted) replay a CUDA graph when every part allows it
+        self.use_graphs = all(getattr(p, "graph_safe", False) for p in model.parts())
+        self._staging_free = None
+        self._decode_graphs: dict = {}
 
     @classmethod
     def from_folder(cls, folder, dtype="bfloat16", max_tokens=4096, max_seqs=None, max_seq_len=None, device="cuda"):
@@ -79,6 +83,26 @@ class Engine:
 
     def length(self, slot: int) -> int:
         return self.cache.seq_len[slot]
+
+    def decode_graph(self, batch: int):
+        """The captured decode step for `batch` sequences (made at first use)."""
+        from .decode_graph import DecodeGraph
+        g = self._decode_graphs.get(batch)
+        if g is None:
+            g = self._decode_graphs[batch] = DecodeGraph(self, batch)
+        return g
+
+    def decode_run(self, slots, tokens, n_steps: int) -> torch.Tensor:
+        """n_steps greedy decode steps for the sequences in `slots`, fed `tokens` first, without the
+        host in between.  Returns the sampled tokens, int32 [n_steps, len(slots)], on the device."""
+        starts = [self.cache.seq_len[s] for s in slots]
+        self.cache.reserve([(s, st + n_steps) for s, st in zip(slots, starts)])
+        g = self.decode_graph(len(slots))
+        g.load(tokens, starts, slots)
+        history = g.run(n_steps)
+        for s, st in zip(slots, starts):
+            self.cache.set_length(s, st + n_steps)
+        return history
 
     # -- the step ------------------------------------------------------------------------------------
     def _pack(self, entries):
@@ -122,6 +146,8 @@ class Engine:
         total = sum(len(a) for a in arrays)
         if self._staging is None or self._staging.numel() < total:
             self._staging = torch.empty(max(total, 1024), dtype=torch.int32, pin_memory=True)
+        if self._staging_free is not None:
+            self._staging_free.synchronize()    # the last step's copy has left the staging buffer
         host = self._staging[:total]
         off = 0
         for a in arrays:
@@ -129,6 +155,8 @@ class Engine:
                 host[off: off + len(a)] = torch.tensor(a, dtype=torch.int32)
             off += len(a)
         dev = host.to(self.model.runtime.device, non_blocking=True)
+        self._staging_free = torch.cuda.Event()
+        self._staging_free.record()
         views, off = [], 0
         for a in arrays:
             views.append(dev[off: off + len(a)])
@@ -139,9 +167,18 @@ class Engine:
         """Run the entries' tokens as one batch from the cache.
 
         Returns fp32 logits [wanted, vocab] in the order of the entries and of their `want`, or None
-        when nothing is wanted.  Every sequence's cached length grows by its tokens."""
+        when nothing is wanted.  Every sequence's cached length grows by its tokens.  The logits of a
+        decode step (one token each) live in a buffer that the next such step overwrites: use or
+        copy them before stepping again."""
         (tokens, token_seq, token_pos, cu, slots, starts, want_rows, growth, max_q, max_kv) = self._pack(entries)
         self.cache.reserve(growth)          # raises before anything is launched, changing nothing
+        if self.use_graphs and max_q == 1 and want_rows == list(range(len(entries))):
+            g = self.decode_graph(len(entries))
+            g.load(tokens, starts, slots)
+            logits = g.step()
+            for slot, new_len in growth:
+                self.cache.set_length(slot, new_len)
+            return logits
         d_tokens, d_seq, d_pos, d_cu, d_slots, d_starts, d_want = self._upload(
             [tokens, token_seq, token_pos, cu, slots, starts, want_rows])
         ctx = StepContext(

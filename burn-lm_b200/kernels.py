@@ -56,6 +56,7 @@ _protos = {
                             c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "blm_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "blm_convert": [c_void_p, c_int, c_void_p, c_int, c_size_t, c_void_p],
+        "blm_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     },
     "attention": {
         "blm_attention": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
@@ -90,9 +91,19 @@ def _lib(module: str) -> ctypes.CDLL:
     return lib
 
 
-def _call(module: str, name: str, *args):
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels of this package have been launched (or captured) by this process."""
+    return _launches
+
+
+def _call(module: str, name: str, *args, kernels: int = 1):
+    global _launches
     lib = _lib(module)
     rc = getattr(lib, name)(*args)
+    _launches += kernels
     if rc != 0:
         msg = getattr(lib, f"blm_{module}_last_error")().decode(errors="replace")
         raise KernelError(f"{name}: {msg}")
@@ -170,6 +181,16 @@ def convert(src, dst):
           c_size_t(src.numel()), _stream())
 
 
+def decode_advance(tokens, pos, sampled, history, step_no, counters=None):
+    """Between two decode steps that run without the host: tokens = sampled, pos += 1 (and counters += 1),
+    history[step_no] = sampled, step_no += 1.  All int32 on the device (counters int64)."""
+    _need_cuda(tokens, pos, sampled, history, step_no, counters)
+    b = tokens.numel()
+    steps = history.shape[0] if history is not None else 0
+    _call("elementwise", "blm_decode_advance", _ptr(tokens), _ptr(pos), _ptr(sampled), _ptr(history), _ptr(step_no),
+          _ptr(counters), b, steps, _stream(), kernels=2)
+
+
 def attention_scratch_floats(n_tokens, n_heads, head_dim, n_splits):
     return 0 if n_splits <= 1 else n_tokens * n_heads * n_splits * (head_dim + 2)
 
@@ -195,7 +216,7 @@ def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos
     _call("attention", "blm_attention", _ptr(q), q_stride, _ptr(pool), _code(q.dtype), _ptr(block_table),
           block_table.shape[1], _ptr(cu_seqlens), _ptr(slot_of_seq), _ptr(start_pos), _ptr(out), _ptr(scratch),
           n_tokens, n_seqs, max_q_len, n_heads, n_kv, head_dim, PAGE, int(window or 0), n_splits,
-          c_float(scale), _stream())
+          c_float(scale), _stream(), kernels=2 if n_splits > 1 else 1)
 
 
 def gemm_f32(x, w, out=None):

@@ -39,6 +39,7 @@ class AttentionSpec:
 @register_part("mixer", "attention")
 class Attention(Part):
     family = "mixer"
+    graph_safe = True
     roles = ("q", "k", "v", "o")
 
     def __init__(self, spec, tensors, runtime):

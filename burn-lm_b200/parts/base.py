@@ -78,6 +78,10 @@ class StepContext:
 
 class Part:
     family = ""
+    # True when forward() only launches work on the current stream that depends on the step through
+    # the device buffers of the StepContext (never through step.host or Python branches on its
+    # values): such a part can be captured in a CUDA graph and replayed for other sequences.
+    graph_safe = False
 
     def __init__(self, spec, tensors: dict, runtime: Runtime):
         self.spec = spec

@@ -24,6 +24,7 @@ class EmbeddingSpec:
 @register_part("embedding", "table")
 class Embedding(Part):
     family = "embedding"
+    graph_safe = True
     roles = ("table",)
 
     def tensor_specs(self):
@@ -46,6 +47,7 @@ class HeadSpec:
 class Head(Part):
     """logits = x W^T in fp32; `weight` may name the embedding table (tied)."""
     family = "head"
+    graph_safe = True
     roles = ("weight",)
 
     def tensor_specs(self):

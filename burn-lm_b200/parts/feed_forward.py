@@ -24,6 +24,7 @@ class SwiGLUSpec:
 @register_part("feed_forward", "swiglu")
 class SwiGLU(Part):
     family = "feed_forward"
+    graph_safe = True
     roles = ("gate", "up", "down")
 
     def tensor_specs(self):

@@ -25,6 +25,7 @@ class RMSNormSpec:
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
     family = "norm"
+    graph_safe = True
     roles = ("weight",)
 
     def tensor_specs(self):

@@ -63,6 +63,7 @@ def rotary_inverse_frequencies(spec: RotarySpec) -> list:
 @register_part("position", "rotary")
 class Rotary(Part):
     family = "position"
+    graph_safe = True
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
@@ -88,6 +89,7 @@ class NoPositionSpec:
 class NoPosition(Part):
     """No position encoding: the mixer's kernels append k and v unrotated."""
     family = "position"
+    graph_safe = True
 
     def rotation(self):
         return None, 0, False
