@@ -233,6 +233,13 @@ def run_ours(args):
                            max_tokens=64 * CONTEXT).load()
     engine = lm.engine
 
+    if args.only == "decode":      # a short run of one workload, for profilers
+        r = device_decode(engine, batch, steps, warmup, cfg)
+        print(json.dumps({"only": "decode", "batch": batch, "ms_per_step": round(r["ms_per_step"], 4)}))
+        return 0
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(time_prefill(engine, cfg, reps=1), 3)}))
+        return 0
     main = device_decode(engine, batch, steps, warmup, cfg, sample_clocks=True)
     points = {}
     for b in (1, 64):
@@ -292,6 +299,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--only", default=None, choices=["decode", "prefill"], help="run one workload briefly (for profilers)")
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration's 16 (named in config)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -9,6 +9,7 @@
 // hold anything.
 #include <math.h>
 
+#include "attention_decode.cuh"
 #include "common.cuh"
 
 BLM_API const char* blm_attention_last_error() { return g_blm_error; }
@@ -330,7 +331,7 @@ BLM_API int blm_attention(const void* q, long long q_stride, const void* pool, i
                           const int* block_table, int table_stride, const int* cu_seqlens,
                           const int* slot_of_seq, const int* start_pos, void* out, float* scratch,
                           int n_tokens, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd,
-                          int page_size, int window, int n_splits, float scale, cudaStream_t stream) {
+                          int page_size, int window, int n_splits, float scale, int general_only, cudaStream_t stream) {
     if (n_tokens == 0 || n_seqs == 0) return BLM_OK;
     BLM_REQUIRE(page_size == kPage, "attention: the cache page holds %d positions, the kernel wants %d", page_size, kPage);
     BLM_REQUIRE(hd >= 16 && hd <= 8 * kColGroups * kChunksMax && hd % 16 == 0,
@@ -339,6 +340,24 @@ BLM_API int blm_attention(const void* q, long long q_stride, const void* pool, i
     BLM_REQUIRE(n_splits >= 1 && (n_splits == 1 || scratch != nullptr), "attention: split without scratch");
     BLM_REQUIRE(max_q_len >= 1, "attention: empty step");
     const int group = n_heads / n_kv;
+    if (dtype == BLM_BF16 && max_q_len == 1 && n_tokens == n_seqs && !general_only) {
+        // one new token per sequence: the specialised kernel, where it has the shape
+        AttnDecodeArgs d;
+        d.q = (const __nv_bfloat16*)q; d.q_stride = q_stride; d.pool = (const __nv_bfloat16*)pool;
+        d.block_table = block_table; d.table_stride = table_stride; d.cu_seqlens = cu_seqlens;
+        d.slot_of_seq = slot_of_seq; d.start_pos = start_pos; d.out = (__nv_bfloat16*)out;
+        d.part_acc = scratch;
+        d.part_ml = scratch ? scratch + (size_t)n_tokens * n_heads * n_splits * hd : nullptr;
+        d.n_heads = n_heads; d.n_kv = n_kv; d.window = window; d.n_splits = n_splits;
+        d.scale_log2e = scale * 1.4426950408889634f;
+        if (launch_attn_decode(d, hd, group, n_seqs, stream)) {
+            int rc = blm_check_launch("attention decode");
+            if (rc != BLM_OK || n_splits == 1) return rc;
+            attn_combine_kernel<__nv_bfloat16><<<n_tokens * n_heads, hd >= 128 ? 128 : 64, 0, stream>>>(
+                d.part_acc, d.part_ml, (__nv_bfloat16*)out, n_splits, hd);
+            return blm_check_launch("attention combine");
+        }
+    }
     AttnArgs a;
     a.q = q; a.q_stride = q_stride; a.pool = pool; a.block_table = block_table; a.table_stride = table_stride;
     a.cu_seqlens = cu_seqlens; a.slot_of_seq = slot_of_seq; a.start_pos = start_pos; a.out = out;

@@ -29,9 +29,10 @@ MODULES = {
     "elementwise": ["elementwise.cu"],
     "attention": ["attention.cu"],
     "gemm": ["gemm_f32.cu"],
+    "gemv": ["gemv.cu"],
     "sampling": ["sampling.cu"],
 }
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "attention_decode.cuh"]
 
 _lock = threading.Lock()
 _loaded: dict[str, ctypes.CDLL] = {}
@@ -106,6 +107,12 @@ def build(module: str, verbose: bool = True) -> str:
             os.remove(tmp)
         raise BuildError(f"nvcc failed for module {module!r}:\n{log}")
     os.replace(tmp, out)
+    for old in os.listdir(os.path.dirname(out)):    # libraries of older sources of this module
+        if old.startswith(f"libblm_{module}_") and old.endswith(".so") and old != os.path.basename(out):
+            try:
+                os.remove(os.path.join(os.path.dirname(out), old))
+            except OSError:
+                pass
     if verbose:
         print(f"[burn-lm_b200] compiled '{module}' in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
     return out

@@ -109,16 +109,22 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ 
                                    const int* __restrict__ block_table, int table_stride,
                                    const double* __restrict__ inv_freq, int rot, int pairing,
                                    T* __restrict__ pool, int n_heads, int n_kv, int hd, int page_size,
-                                   int write_cache) {
+                                   int write_cache, const float2* __restrict__ table, int table_len) {
     extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
     const int n = blockIdx.x;
     const int pos = token_pos[n];
     const int half = rot >> 1;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        double s, c;
-        sincos((double)pos * inv_freq[i], &s, &c);
-        cs[i] = (float)c;
-        cs[half + i] = (float)s;
+        if (pos < table_len) {       // the same numbers, computed once by rope_table_kernel
+            const float2 v = table[(size_t)pos * half + i];
+            cs[i] = v.x;
+            cs[half + i] = v.y;
+        } else {
+            double s, c;
+            sincos((double)pos * inv_freq[i], &s, &c);
+            cs[i] = (float)c;
+            cs[half + i] = (float)s;
+        }
     }
     __syncthreads();
     T* row = qkv + (size_t)n * (size_t)(n_heads + 2 * n_kv) * hd;
@@ -171,7 +177,7 @@ BLM_API int blm_rope_append(void* qkv, int dtype, const int* token_seq, const in
                             const int* slot_of_seq, const int* block_table, int table_stride,
                             const double* inv_freq, int rot, int pairing, void* pool, int n_tokens,
                             int n_heads, int n_kv, int hd, int page_size, int write_cache,
-                            cudaStream_t stream) {
+                            const float2* table, int table_len, cudaStream_t stream) {
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(rot >= 0 && rot <= hd && rot % 2 == 0, "rotary: %d rotated lanes of a head of %d", rot, hd);
     BLM_REQUIRE(rot == 0 || inv_freq != nullptr, "rotary: no frequencies");
@@ -179,12 +185,30 @@ BLM_API int blm_rope_append(void* qkv, int dtype, const int* token_seq, const in
     const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
     const int threads = 128;
     if (dtype == BLM_F32)
-        rope_append_kernel<float><<<n_tokens, threads, smem, stream>>>((float*)qkv, token_seq, token_pos, slot_of_seq, block_table, table_stride, inv_freq, rot, pairing, (float*)pool, n_heads, n_kv, hd, page_size, write_cache);
+        rope_append_kernel<float><<<n_tokens, threads, smem, stream>>>((float*)qkv, token_seq, token_pos, slot_of_seq, block_table, table_stride, inv_freq, rot, pairing, (float*)pool, n_heads, n_kv, hd, page_size, write_cache, table, table_len);
     else if (dtype == BLM_BF16)
-        rope_append_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>((__nv_bfloat16*)qkv, token_seq, token_pos, slot_of_seq, block_table, table_stride, inv_freq, rot, pairing, (__nv_bfloat16*)pool, n_heads, n_kv, hd, page_size, write_cache);
+        rope_append_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>((__nv_bfloat16*)qkv, token_seq, token_pos, slot_of_seq, block_table, table_stride, inv_freq, rot, pairing, (__nv_bfloat16*)pool, n_heads, n_kv, hd, page_size, write_cache, table, table_len);
     else
         return blm_fail(BLM_BAD_ARGUMENT, "rotary: dtype %d", dtype);
     return blm_check_launch("rope_append");
+}
+
+// (cos, sin) of pos * inv_freq[i] for pos < n_pos, in fp64, rounded to fp32: what rope_append_kernel
+// computes on the fly, once for all steps
+__global__ void rope_table_kernel(const double* __restrict__ inv_freq, float2* __restrict__ table, int n_pos, int half) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_pos * half) return;
+    const int pos = (int)(idx / half), i = (int)(idx % half);
+    double s, c;
+    sincos((double)pos * inv_freq[i], &s, &c);
+    table[idx] = make_float2((float)c, (float)s);
+}
+
+BLM_API int blm_rope_table(const double* inv_freq, float* table, int n_pos, int half, cudaStream_t stream) {
+    if (n_pos == 0 || half == 0) return BLM_OK;
+    const size_t total = (size_t)n_pos * half;
+    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(inv_freq, (float2*)table, n_pos, half);
+    return blm_check_launch("rope_table");
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -45,10 +45,74 @@ __global__ void __launch_bounds__(kSampleThreads) argmax_kernel(const float* __r
     }
 }
 
-BLM_API int blm_argmax(const float* logits, long long row_stride, int n_rows, int vocab, int* out, cudaStream_t stream) {
+// Large vocabularies: many blocks per row find the best of their chunk, one block per row merges.
+constexpr int kArgmaxChunk = 4096;
+
+__global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
+                                                           float* __restrict__ part_val, int* __restrict__ part_idx) {
+    __shared__ float bv[8];
+    __shared__ int bi[8];
+    const float* row = logits + (size_t)blockIdx.y * row_stride;
+    const int lo = blockIdx.x * kArgmaxChunk, hi = min(vocab, lo + kArgmaxChunk);
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
+        part_val[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = best;
+        part_idx[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = idx;
+    }
+}
+
+__global__ void argmax_merge_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int chunks,
+                                    int* __restrict__ out) {
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < chunks; i += 32) {
+        const float v = part_val[(size_t)blockIdx.x * chunks + i];
+        const int vi = part_idx[(size_t)blockIdx.x * chunks + i];
+        if (v > best || (v == best && vi < idx)) { best = v; idx = vi; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+}
+
+// How many floats of scratch blm_argmax wants for a vocabulary (0: none).
+BLM_API int blm_argmax_scratch_floats(int n_rows, int vocab) {
+    if (vocab <= 2 * kArgmaxChunk) return 0;
+    return 2 * n_rows * ((vocab + kArgmaxChunk - 1) / kArgmaxChunk);
+}
+
+BLM_API int blm_argmax(const float* logits, long long row_stride, int n_rows, int vocab, int* out, float* scratch,
+                       cudaStream_t stream) {
     if (n_rows == 0) return BLM_OK;
     BLM_REQUIRE(vocab > 0, "argmax: empty vocabulary");
-    argmax_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, row_stride, vocab, out);
+    if (vocab <= 2 * kArgmaxChunk || scratch == nullptr) {
+        argmax_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, row_stride, vocab, out);
+        return blm_check_launch("argmax");
+    }
+    const int chunks = (vocab + kArgmaxChunk - 1) / kArgmaxChunk;
+    float* part_val = scratch;
+    int* part_idx = reinterpret_cast<int*>(scratch + (size_t)n_rows * chunks);
+    argmax_chunk_kernel<<<dim3(chunks, n_rows), 256, 0, stream>>>(logits, row_stride, vocab, part_val, part_idx);
+    argmax_merge_kernel<<<n_rows, 32, 0, stream>>>(part_val, part_idx, chunks, out);
     return blm_check_launch("argmax");
 }
 

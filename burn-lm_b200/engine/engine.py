@@ -63,6 +63,7 @@ class Engine:
         self.cache = Cache(model.cache_needs(), model.plan.schedule, max_tokens, max_seqs, max_seq_len,
                            rt.dtype, rt.device)
         self.workspace = Workspace(rt.device)
+        model.prepare(self.cache.max_seq_len)
         self.vocab_size = model.plan.vocab_size
         self._staging = None    # pinned int32 staging for the step's metadata
         # decode steps (one token each, its logits wanted) replay a CUDA graph when every part allows it

@@ -53,7 +53,8 @@ _protos = {
         "blm_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                             c_float, c_void_p],
         "blm_rope_append": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                            c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                            c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+        "blm_rope_table": [c_void_p, c_void_p, c_int, c_int, c_void_p],
         "blm_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "blm_convert": [c_void_p, c_int, c_void_p, c_int, c_size_t, c_void_p],
         "blm_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -61,14 +62,20 @@ _protos = {
     "attention": {
         "blm_attention": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                          c_int, c_int, c_float, c_void_p],
+                          c_int, c_int, c_float, c_int, c_void_p],
     },
     "gemm": {
         "blm_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
                          c_longlong, c_void_p],
     },
+    "gemv": {
+        "blm_gemv": [c_void_p, c_longlong, c_int, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
+                     c_float, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p],
+        "blm_gemv_supported": [c_int, c_int, c_int],
+    },
     "sampling": {
-        "blm_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
+        "blm_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "blm_argmax_scratch_floats": [c_int, c_int],
         "blm_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_void_p, c_void_p],
     },
@@ -142,13 +149,26 @@ def add_rmsnorm(resid, delta, gamma, eps, out, rows=None):
           _code(out.dtype), _ptr(rows), n_out, d, c_float(eps), _stream())
 
 
+def rope_table(inv_freq, n_positions):
+    """(cos, sin) of position * inv_freq for positions below n_positions: float32 [n_positions, half, 2],
+    computed in float64 on the device; rope_append reads it instead of computing angles per token."""
+    _need_cuda(inv_freq)
+    half = inv_freq.numel()
+    table = torch.empty((n_positions, half, 2), dtype=torch.float32, device=inv_freq.device)
+    _call("elementwise", "blm_rope_table", _ptr(inv_freq), _ptr(table), n_positions, half, _stream())
+    return table
+
+
 def rope_append(qkv, token_seq, token_pos, slot_of_seq, block_table, inv_freq, rotary_dim, interleaved,
-                pool, n_heads, n_kv, head_dim, write_cache=True):
+                pool, n_heads, n_kv, head_dim, write_cache=True, table=None):
     """Rotate q (in place) and k of every token by its position, and append k, v to the paged cache.
 
     qkv [N, (n_heads + 2 n_kv) * head_dim]; pool [pages, 2, n_kv, PAGE, head_dim] of one cache line;
-    inv_freq float64 [rotary_dim / 2] or None when rotary_dim == 0."""
-    _need_cuda(qkv, token_seq, token_pos, slot_of_seq, block_table, inv_freq, pool)
+    inv_freq float64 [rotary_dim / 2] or None when rotary_dim == 0; `table` (from rope_table) spares
+    the per-token angles for positions it covers."""
+    _need_cuda(qkv, token_seq, token_pos, slot_of_seq, block_table, inv_freq, pool, table)
+    if table is not None and (table.dtype != torch.float32 or tuple(table.shape[1:]) != (rotary_dim // 2, 2)):
+        raise KernelError("rope_append: table must be float32 [positions, rotary_dim / 2, 2]")
     n = qkv.shape[0]
     if qkv.shape[1] != (n_heads + 2 * n_kv) * head_dim:
         raise KernelError("rope_append: qkv width does not match the head counts")
@@ -160,7 +180,8 @@ def rope_append(qkv, token_seq, token_pos, slot_of_seq, block_table, inv_freq, r
             raise KernelError("rope_append: inv_freq must be float64 [rotary_dim / 2]")
     _call("elementwise", "blm_rope_append", _ptr(qkv), _code(qkv.dtype), _ptr(token_seq), _ptr(token_pos),
           _ptr(slot_of_seq), _ptr(block_table), block_table.shape[1], _ptr(inv_freq), rotary_dim,
-          1 if interleaved else 0, _ptr(pool), n, n_heads, n_kv, head_dim, PAGE, 1 if write_cache else 0, _stream())
+          1 if interleaved else 0, _ptr(pool), n, n_heads, n_kv, head_dim, PAGE, 1 if write_cache else 0,
+          _ptr(table), table.shape[0] if table is not None else 0, _stream())
 
 
 def swiglu(gate_up, out):
@@ -196,14 +217,16 @@ def attention_scratch_floats(n_tokens, n_heads, head_dim, n_splits):
 
 
 def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos, out, n_tokens, n_seqs,
-              max_q_len, n_heads, n_kv, head_dim, scale, window=0, n_splits=1, scratch=None):
+              max_q_len, n_heads, n_kv, head_dim, scale, window=0, n_splits=1, scratch=None, general_only=False):
     """Causal grouped-query attention of the step's tokens over the paged cache (after the append).
 
     q: tensor whose token n, head h starts at element n * q_stride + h * head_dim (the qkv buffer).
     Token t of sequence s sits at position start_pos[s] + t and sees keys 0..that position (the last
     `window` of them when window > 0).  n_splits > 1 cuts every sequence's keys over that many
     blocks and combines the partial results; it needs `scratch` (float32,
-    attention_scratch_floats(...) elements)."""
+    attention_scratch_floats(...) elements).  bfloat16 steps of one token per sequence with a head
+    size of 64 or 128 and 1, 2, 4 or 8 query heads per kv head run a specialised kernel unless
+    `general_only`."""
     _need_cuda(q, pool, block_table, cu_seqlens, slot_of_seq, start_pos, out, scratch)
     if tuple(out.shape) != (n_tokens, n_heads * head_dim) or out.dtype != q.dtype or pool.dtype != q.dtype:
         raise KernelError("attention: out must be [N, heads * head_dim] in q's dtype, as the pool")
@@ -216,7 +239,7 @@ def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos
     _call("attention", "blm_attention", _ptr(q), q_stride, _ptr(pool), _code(q.dtype), _ptr(block_table),
           block_table.shape[1], _ptr(cu_seqlens), _ptr(slot_of_seq), _ptr(start_pos), _ptr(out), _ptr(scratch),
           n_tokens, n_seqs, max_q_len, n_heads, n_kv, head_dim, PAGE, int(window or 0), n_splits,
-          c_float(scale), _stream(), kernels=2 if n_splits > 1 else 1)
+          c_float(scale), 1 if general_only else 0, _stream(), kernels=2 if n_splits > 1 else 1)
 
 
 def gemm_f32(x, w, out=None):
@@ -234,13 +257,52 @@ def gemm_f32(x, w, out=None):
     return out
 
 
+EPI_STORE, EPI_SWIGLU, EPI_RESID_ADD = 0, 1, 2
+
+
+def gemv_supported(n_tokens, m, k) -> bool:
+    return bool(_lib("gemv").blm_gemv_supported(n_tokens, m, k))
+
+
+def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, out=None, add_into=None, swiglu=False):
+    """Skinny product of n_tokens <= 64 tokens with a bfloat16 weight [M, K], with fused ends.
+
+    Input: `x` bfloat16 [N, K], or the fp32 residual stream `stream_rows` [*, K] to be RMS-normalised
+    with `gamma`, `eps` (optionally gathering `rows`).  Output: `out` [N, M] bfloat16 or float32;
+    with `swiglu` the weight is [2 I, K] = [gate; up] and out [N, I] = silu(gate) * up; with
+    `add_into` (fp32 [N, M]) the product is added into it and nothing else is written."""
+    _need_cuda(w, x, stream_rows, gamma, rows, out, add_into)
+    m_rows, k = w.shape
+    if w.dtype != torch.bfloat16:
+        raise KernelError("gemv: the weight must be bfloat16")
+    m = m_rows // 2 if swiglu else m_rows
+    epi = EPI_SWIGLU if swiglu else (EPI_RESID_ADD if add_into is not None else EPI_STORE)
+    if x is not None and (x.dtype != torch.bfloat16 or tuple(x.shape) != (n_tokens, k)):
+        raise KernelError("gemv: x must be bfloat16 [N, K]")
+    if stream_rows is not None and (stream_rows.dtype != torch.float32 or stream_rows.shape[1] != k or gamma is None):
+        raise KernelError("gemv: the stream must be float32 [*, K] with a gamma")
+    if epi == EPI_RESID_ADD:
+        if add_into.dtype != torch.float32 or tuple(add_into.shape) != (n_tokens, m):
+            raise KernelError("gemv: add_into must be float32 [N, M]")
+    elif out is None or tuple(out.shape) != (n_tokens, m) or out.dtype not in (torch.bfloat16, torch.float32) \
+            or (swiglu and out.dtype != torch.bfloat16):
+        raise KernelError("gemv: out must be [N, M] bfloat16 (or float32 for a plain store)")
+    _call("gemv", "blm_gemv", _ptr(w), w.stride(0), m, k, m if swiglu else 0, _ptr(x), x.stride(0) if x is not None else 0,
+          _ptr(stream_rows), _ptr(gamma), 1 if (gamma is not None and gamma.dtype == torch.float32) else 0, c_float(eps),
+          _ptr(rows), n_tokens, _ptr(out), out.stride(0) if out is not None else 0,
+          1 if (out is not None and out.dtype == torch.float32) else 0, _ptr(add_into), epi, _stream())
+
+
 def argmax(logits, out):
     """out[b] = index of the largest logit of row b (the lowest index on a tie)."""
     _need_cuda(logits, out)
     if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() < logits.shape[0]:
         raise KernelError("argmax: float32 logits [B, V], int32 out [B]")
-    _call("sampling", "blm_argmax", _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(out),
-          _stream())
+    b, v = logits.shape
+    need = _lib("sampling").blm_argmax_scratch_floats(b, v)
+    scratch = torch.empty(need, dtype=torch.float32, device=logits.device) if need else None
+    _call("sampling", "blm_argmax", _ptr(logits), logits.stride(0), b, v, _ptr(out), _ptr(scratch), _stream(),
+          kernels=2 if need else 1)
 
 
 def sample(logits, temperature, top_p, seeds, stream_ids, counters, out):

@@ -101,8 +101,14 @@ class Model:
             delta = self.layers[entry.layer].block.forward(resid, delta, step, cache.view(run))
         if step.n_want == 0:
             return None
-        x = self.final_norm.add_norm(resid, delta, rows=step.want_rows)
+        x = self.final_norm.add_norm(resid, delta, rows=step.want_rows, lazy=getattr(self.head, "takes_pending_norm", False))
         return self.head.forward(x)
+
+    def prepare(self, max_positions: int) -> None:
+        """Let parts precompute what depends on the longest sequence the cache can hold."""
+        for p in self.parts():
+            if hasattr(p, "prepare"):
+                p.prepare(max_positions)
 
 
 def tensor_specs_of(config: dict):

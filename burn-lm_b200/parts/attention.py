@@ -69,6 +69,10 @@ class Attention(Part):
         self.o = Linear(loaded[t["o"]])
         self.position.bind(loaded)
 
+    def prepare(self, max_positions: int) -> None:
+        if hasattr(self.position, "prepare"):
+            self.position.prepare(max_positions)
+
     def cache_need(self) -> CacheNeed:
         s = self.spec
         return CacheNeed("kv", n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window)
@@ -82,9 +86,13 @@ class Attention(Part):
         pages = (step.max_kv_len + K.PAGE - 1) // K.PAGE
         return max(1, min(pages, (_TARGET_BLOCKS + blocks - 1) // blocks, 64))
 
-    def forward(self, x, step, cache):
+    takes_pending_norm = True
+    adds_to_stream = True
+
+    def forward(self, x, step, cache, stream=None):
         s, rt = self.spec, self.runtime
         inv_freq, rot, interleaved = self.position.rotation()
+        table = self.position.table() if hasattr(self.position, "table") else None
         n = step.n_tokens
         if cache.writes:
             qkv = self.qkv(x, out_dtype=rt.dtype)
@@ -93,8 +101,8 @@ class Attention(Part):
             qkv = self.q_only(x, out_dtype=rt.dtype)
             n_kv_in_row = 0
         K.rope_append(qkv, step.token_seq, step.token_pos, step.slot_of_seq, cache.block_table, inv_freq, rot,
-                      interleaved, cache.pool, s.n_heads, n_kv_in_row, s.head_dim, write_cache=cache.writes)
-        out = torch.empty((n, s.n_heads * s.head_dim), dtype=rt.dtype, device=x.device)
+                      interleaved, cache.pool, s.n_heads, n_kv_in_row, s.head_dim, write_cache=cache.writes, table=table)
+        out = torch.empty((n, s.n_heads * s.head_dim), dtype=rt.dtype, device=qkv.device)
         n_splits = self._splits(step)
         scratch = None
         if n_splits > 1:
@@ -102,4 +110,4 @@ class Attention(Part):
         K.attention(qkv, qkv.shape[1], cache.pool, cache.block_table, step.cu_seqlens, step.slot_of_seq,
                     step.start_pos, out, n, step.n_seqs, step.max_q_len, s.n_heads, s.n_kv_heads, s.head_dim,
                     self.scale, window=s.window or 0, n_splits=n_splits, scratch=scratch)
-        return self.o(out, out_dtype=rt.dtype)
+        return self.o.into_stream(out, stream, rt.dtype)

@@ -22,7 +22,16 @@ class PreNormBlock:
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
 
     def forward(self, resid, delta, step, cache_view):
-        x = self.mixer_norm.add_norm(resid, delta)
-        a = self.mixer.forward(x, step, cache_view)
-        x = self.feed_forward_norm.add_norm(resid, a)
-        return self.feed_forward.forward(x, step)
+        # Two optional abilities of a mixer or feed-forward shorten the path: `takes_pending_norm`
+        # (its first product normalises on the fly) and `adds_to_stream` (its last product adds its
+        # result into the residual stream itself and returns None).
+        mixer, ff = self.mixer, self.feed_forward
+        x = self.mixer_norm.add_norm(resid, delta, lazy=getattr(mixer, "takes_pending_norm", False))
+        if getattr(mixer, "adds_to_stream", False):
+            a = mixer.forward(x, step, cache_view, stream=resid)
+        else:
+            a = mixer.forward(x, step, cache_view)
+        x = self.feed_forward_norm.add_norm(resid, a, lazy=getattr(ff, "takes_pending_norm", False))
+        if getattr(ff, "adds_to_stream", False):
+            return ff.forward(x, step, stream=resid)
+        return ff.forward(x, step)

@@ -56,5 +56,7 @@ class Head(Part):
     def bind(self, loaded):
         self.linear = Linear(loaded[self.tensor_names["weight"]])
 
+    takes_pending_norm = True
+
     def forward(self, x):
         return self.linear(x, out_dtype=torch.float32)

@@ -41,9 +41,10 @@ class SwiGLU(Part):
         self.gate_up = Linear(torch.cat([g, u], dim=0).contiguous())
         self.down = Linear(loaded[t["down"]])
 
-    def forward(self, x, step):
+    takes_pending_norm = True
+    adds_to_stream = True
+
+    def forward(self, x, step, stream=None):
         rt = self.runtime
-        gu = self.gate_up(x, out_dtype=rt.dtype)
-        act = torch.empty((x.shape[0], self.spec.intermediate_size), dtype=rt.dtype, device=x.device)
-        K.swiglu(gu, act)
-        return self.down(act, out_dtype=rt.dtype)
+        act = self.gate_up.gated(x, rt.dtype)
+        return self.down.into_stream(act, stream, rt.dtype)

@@ -14,6 +14,7 @@ from .. import kernels as K
 from ..registry import register_part
 from ..weights.loader import TensorSpec
 from .base import Part
+from .linear import NormedStream
 
 
 @dataclass(frozen=True)
@@ -34,7 +35,11 @@ class RMSNorm(Part):
     def bind(self, loaded):
         self.gamma = loaded[self.tensor_names["weight"]]
 
-    def add_norm(self, resid, delta, rows=None):
+    def add_norm(self, resid, delta, rows=None, lazy=False):
+        """`lazy`: the caller can take a norm that is not computed yet (parts.linear.NormedStream);
+        it gets one when nothing has to be added into the stream first."""
+        if lazy and delta is None:
+            return NormedStream(resid, self.gamma, self.spec.eps, rows, self.runtime.dtype)
         n = rows.numel() if rows is not None else resid.shape[0]
         out = torch.empty((n, self.spec.size), dtype=self.runtime.dtype, device=resid.device)
         K.add_rmsnorm(resid, delta, self.gamma, self.spec.eps, out, rows)

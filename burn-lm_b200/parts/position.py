@@ -72,9 +72,20 @@ class Rotary(Part):
             raise ValueError(f"rotary_dim {dim} must be even and at most head_dim {spec.head_dim}")
         self.rotary_dim = dim
         self.inv_freq = torch.tensor(rotary_inverse_frequencies(spec), dtype=torch.float64, device=runtime.device)
+        self._table = None
 
     def rotation(self):
         return self.inv_freq, self.rotary_dim, self.spec.interleaved
+
+    def prepare(self, max_positions: int) -> None:
+        """Compute (cos, sin) for positions below max_positions once (on the device, in float64);
+        positions beyond the table are still computed per token by the kernel."""
+        from .. import kernels as K
+        if self.inv_freq.is_cuda and self.rotary_dim and (self._table is None or self._table.shape[0] < max_positions):
+            self._table = K.rope_table(self.inv_freq, max_positions)
+
+    def table(self):
+        return self._table
 
     def on_embedding(self, resid, step):
         return None

@@ -192,6 +192,12 @@ def run_attention_case(dtype, H, KV, hd, lens_before, lens_new, window, n_splits
         scratch = torch.empty(k.attention_scratch_floats(n, H, hd, n_splits), device="cuda")
     k.attention(qkv, q_stride, st["pool"], st["table"], st["cu"], st["slots"], st["starts"], out, n, len(lens_new),
                 max(lens_new), H, KV, hd, scale, window=window, n_splits=n_splits, scratch=scratch)
+    if dtype == torch.bfloat16 and max(lens_new) == 1:
+        # whichever kernel took the step, the general one must say the same (up to bf16 rounding of the output)
+        out_general = torch.empty_like(out)
+        k.attention(qkv, q_stride, st["pool"], st["table"], st["cu"], st["slots"], st["starts"], out_general, n, len(lens_new),
+                    max(lens_new), H, KV, hd, scale, window=window, n_splits=n_splits, scratch=scratch, general_only=True)
+        torch.testing.assert_close(out.float(), out_general.float(), rtol=2e-2, atol=1e-2)
     row = 0
     for s, new in enumerate(lens_new):
         q = qkv[row:row + new].double().view(new, -1, hd)[:, :H]
@@ -298,3 +304,108 @@ def test_refusals():
     z = torch.zeros(2, dtype=torch.int32, device="cuda")
     with pytest.raises(k.KernelError, match="multiple of 16"):
         k.attention(q, 72, pool, z.view(1, 2), z, z, z, torch.zeros(1, 24, device="cuda"), 1, 1, 1, 1, 1, 24, 1.0)
+
+
+def gemv_reference(w, x):
+    return x.double() @ w.double().T
+
+
+@pytest.mark.parametrize("n", [1, 3, 8, 9, 24, 64])
+@pytest.mark.parametrize("m,k", [(40, 64), (200, 160), (3072, 2048), (1000, 8192), (77, 4104)])
+def test_gemv_store(n, m, k):
+    g = torch.Generator(device="cuda").manual_seed(n * 1000 + m)
+    w = (torch.randn(m, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    x = torch.randn(n, k, device="cuda", generator=g).to(torch.bfloat16)
+    assert K().gemv_supported(n, m, k)
+    want = gemv_reference(w, x)
+    scale = want.abs().max().item()
+    out32 = torch.empty(n, m, device="cuda")
+    K().gemv(w, n, x=x, out=out32)
+    assert (out32.double() - want).abs().max().item() < 2e-5 * scale + 1e-6     # fp32 accumulation of exact products
+    out16 = torch.empty(n, m, device="cuda", dtype=torch.bfloat16)
+    K().gemv(w, n, x=x, out=out16)
+    assert (out16.double() - want).abs().max().item() < 5e-3 * scale
+    # a token's result does not depend on the other tokens of the batch, beyond the rounding of an
+    # fp32 sum taken in another order (larger batches stage K in smaller chunks)
+    one = torch.empty(1, m, device="cuda")
+    K().gemv(w, 1, x=x[:1].contiguous(), out=one)
+    if n <= 8:
+        assert torch.equal(one[0], out32[0])
+    assert (one[0] - out32[0]).abs().max().item() < 2e-6 * scale
+
+
+@pytest.mark.parametrize("n", [1, 8, 16])
+@pytest.mark.parametrize("gdt", DTYPES)
+def test_gemv_norm_prologue_swiglu_and_stream_add(n, gdt):
+    g = torch.Generator(device="cuda").manual_seed(n)
+    k, inner, m = 192, 520, 192
+    resid = torch.randn(n + 3, k, device="cuda", generator=g)
+    gamma = (1 + 0.1 * torch.randn(k, device="cuda", generator=g)).to(gdt)
+    rows = torch.randperm(n + 3, device="cuda", generator=g)[:n].to(torch.int32)
+    eps = 1e-5
+    h = resid.double()[rows.long()]
+    xn = (h / torch.sqrt((h * h).mean(-1, keepdim=True) + eps) * gamma.double()).to(torch.bfloat16)   # rounded as the kernel rounds
+    wgu = (torch.randn(2 * inner, k, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    act = torch.empty(n, inner, device="cuda", dtype=torch.bfloat16)
+    K().gemv(wgu, n, stream_rows=resid, gamma=gamma, eps=eps, rows=rows, out=act, swiglu=True)
+    gu = gemv_reference(wgu, xn)
+    want = gu[:, :inner] / (1 + torch.exp(-gu[:, :inner])) * gu[:, inner:]
+    assert (act.double() - want).abs().max().item() < 1e-2 * want.abs().max().item()
+    # without rows, and adding into the stream
+    wd = (torch.randn(m, inner, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    stream = torch.randn(n, m, device="cuda", generator=g)
+    before = stream.clone()
+    K().gemv(wd, n, x=act, add_into=stream)
+    want2 = before.double() + gemv_reference(wd, act)
+    assert (stream.double() - want2).abs().max().item() < 2e-5 * want2.abs().max().item()
+    out = torch.empty(n, m, device="cuda")
+    K().gemv(wd[:, :k].contiguous(), n, stream_rows=resid[:n].contiguous(), gamma=gamma, eps=eps, out=out)
+    h2 = resid.double()[:n]
+    xn2 = (h2 / torch.sqrt((h2 * h2).mean(-1, keepdim=True) + eps) * gamma.double()).to(torch.bfloat16)
+    want3 = gemv_reference(wd[:, :k], xn2)
+    assert (out.double() - want3).abs().max().item() < 1e-3 * want3.abs().max().item()
+
+
+def test_gemv_refuses_what_it_cannot_do():
+    k = K()
+    assert not k.gemv_supported(65, 10, 64) and not k.gemv_supported(4, 10, 36)
+    w = torch.zeros(16, 36, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(k.KernelError, match="multiple of 8"):
+        k.gemv(w, 1, x=torch.zeros(1, 36, device="cuda", dtype=torch.bfloat16), out=torch.zeros(1, 16, device="cuda"))
+
+
+@pytest.mark.parametrize("H,KV,hd", [(32, 8, 64), (8, 8, 64), (16, 2, 128), (4, 2, 128)])
+@pytest.mark.parametrize("n_splits", [1, 4, 11])
+def test_decode_attention_specialised_equals_general(H, KV, hd, n_splits):
+    """The specialised decode kernel and the general kernel on the same cache, and both against the
+    plain restatement (through run_attention_case)."""
+    run_attention_case(torch.bfloat16, H, KV, hd, [0, 63, 64, 700, 129, 15], [1] * 6, 0, n_splits, seed=21)
+    run_attention_case(torch.bfloat16, H, KV, hd, [300, 64, 5], [1] * 3, 100, n_splits, seed=22)
+
+
+def test_rope_table_equals_on_the_fly():
+    k = K()
+    H, KV, hd = 4, 2, 64
+    st = paged_setup([0, 100], [90, 30], KV, hd, torch.bfloat16, seed=30)
+    inv_freq = torch.tensor([5e5 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(31)
+    qkv = torch.randn(120, (H + 2 * KV) * hd, device="cuda", generator=g).to(torch.bfloat16)
+    a, b = qkv.clone(), qkv.clone()
+    pool_b = st["pool"].clone()
+    k.rope_append(a, st["token_seq"], st["token_pos"], st["slots"], st["table"], inv_freq, hd, False, st["pool"], H, KV, hd)
+    table = k.rope_table(inv_freq, 110)          # covers some positions, not all
+    k.rope_append(b, st["token_seq"], st["token_pos"], st["slots"], st["table"], inv_freq, hd, False, pool_b, H, KV, hd, table=table)
+    assert torch.equal(a, b)
+    assert torch.equal(torch.nan_to_num(st["pool"].float()), torch.nan_to_num(pool_b.float()))
+
+
+def test_argmax_large_vocabulary():
+    g = torch.Generator(device="cuda").manual_seed(40)
+    logits = torch.randn(9, 128256, device="cuda", generator=g)
+    logits[3, 100000] = logits[3, 5000] = 30.0       # a tie across chunks: the lower index
+    logits[4, 128255] = 31.0
+    out = torch.empty(9, device="cuda", dtype=torch.int32)
+    K().argmax(logits, out)
+    want = logits.argmax(-1)
+    want[3] = 5000
+    assert out.tolist() == want.tolist()
