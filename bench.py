@@ -187,9 +187,10 @@ def device_decode(engine, batch, steps, warmup, cfg, sample_clocks=False):
         if sampler:
             sampler.__exit__()
         ms = start.elapsed_time(stop)
-        g = engine.decode_graph(batch)
+        g = engine.decode_graph(batch, PROMPT + steps)
         launches = g.launches_per_step * steps + (kernels.launch_count() - before)
         assert history.shape == (steps, batch)
+        engine.verify()        # no kernel gave up a bounded wait
         return {"ms_per_step": ms / steps, "tokens_per_s": batch * steps / (ms / 1e3), "launches": launches,
                 "clocks": sampler.summary() if sampler else None}
     finally:
@@ -252,7 +253,7 @@ def run_ours(args):
     out = lm.generate(prompts, sample_len=steps + 1, ignore_stop=True)             # steps decode steps after the prefill
     st = out.stats
     e2e_value = batch * st.decode_steps / st.decode_seconds
-    g = engine.decode_graph(batch)
+    g = engine.decode_graph(batch, PROMPT + steps)
 
     prefill_ms = time_prefill(engine, cfg)
     flops = prefill_flops(cfg, PREFILL_TOKENS)

@@ -350,13 +350,8 @@ BLM_API int blm_attention(const void* q, long long q_stride, const void* pool, i
         d.part_ml = scratch ? scratch + (size_t)n_tokens * n_heads * n_splits * hd : nullptr;
         d.n_heads = n_heads; d.n_kv = n_kv; d.window = window; d.n_splits = n_splits;
         d.scale_log2e = scale * 1.4426950408889634f;
-        if (launch_attn_decode(d, hd, group, n_seqs, stream)) {
-            int rc = blm_check_launch("attention decode");
-            if (rc != BLM_OK || n_splits == 1) return rc;
-            attn_combine_kernel<__nv_bfloat16><<<n_tokens * n_heads, hd >= 128 ? 128 : 64, 0, stream>>>(
-                d.part_acc, d.part_ml, (__nv_bfloat16*)out, n_splits, hd);
-            return blm_check_launch("attention combine");
-        }
+        BLM_REQUIRE(n_splits <= 64, "attention: at most 64 splits, got %d", n_splits);
+        if (launch_attn_decode(d, hd, group, n_seqs, stream)) return blm_check_launch("attention decode");
     }
     AttnArgs a;
     a.q = q; a.q_stride = q_stride; a.pool = pool; a.block_table = block_table; a.table_stride = table_stride;

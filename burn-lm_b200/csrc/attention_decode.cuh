@@ -23,6 +23,12 @@ struct AttnDecodeArgs {
     float scale_log2e;           // softmax scale times log2(e): scores live in base-2 units
 };
 
+// How many of the n_splits blocks of a (sequence, kv head) work: one for every 64 keys.
+__host__ __device__ inline int attn_decode_active_splits(int span, int n_splits) {
+    const int want = (span + 63) / 64;
+    return want < 1 ? 1 : (want > n_splits ? n_splits : want);
+}
+
 template <int HD, int G>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a) {
     constexpr int LPK = HD / 8;        // lanes per key
@@ -62,23 +68,36 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
         for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
     }
 
-    // the keys of this split, in units of 16
+    // the keys of this split, in units of 16.  Only as many splits as the sequence has pages are
+    // active (the grid is sized for the longest sequence the cache can hold); the others leave at once
+    // and the combine kernel, which computes the same number, does not look at them.
     const int key_lo = a.window > 0 ? max(0, kv_len - a.window) : 0;
     const int span = kv_len - key_lo;
-    const int per = (((span + 15) / 16 + a.n_splits - 1) / a.n_splits) * 16;
+    const int active = attn_decode_active_splits(span, a.n_splits);
+    if (split >= active) return;
+    const int per = (((span + 15) / 16 + active - 1) / active) * 16;
     const int k_begin = key_lo + split * per;
     const int k_end = min(kv_len, k_begin + per);
 
-    for (int base = k_begin + warp * KPW; base < k_end; base += WARPS * KPW) {
+    auto fetch = [&](int base, uint4& k4, uint4& v4) {
         const int key = base + sub;
-        const bool live = key < k_end;
-        uint4 kv4 = make_uint4(0u, 0u, 0u, 0u), vv4 = kv4;
-        if (live) {
+        k4 = make_uint4(0u, 0u, 0u, 0u);
+        v4 = k4;
+        if (key < k_end) {
             const int page = pages[key >> 6];
             const __nv_bfloat16* kp = a.pool + (size_t)page * 2 * page_elems + ((size_t)kvh * 64 + (key & 63)) * HD + li * 8;
-            kv4 = *reinterpret_cast<const uint4*>(kp);
-            vv4 = *reinterpret_cast<const uint4*>(kp + page_elems);
+            k4 = *reinterpret_cast<const uint4*>(kp);
+            v4 = *reinterpret_cast<const uint4*>(kp + page_elems);
         }
+    };
+    int base = k_begin + warp * KPW;
+    uint4 kv4, vv4;
+    fetch(base, kv4, vv4);
+    while (base < k_end) {
+        const int nbase = base + WARPS * KPW;
+        uint4 kn4, vn4;
+        fetch(nbase, kn4, vn4);        // the next trip's loads fly while this trip computes
+        const bool live = base + sub < k_end;
         float kf[8], vf[8];
         {
             const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&kv4);
@@ -114,6 +133,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
                 for (int e = 0; e < 8; ++e) acc[g][e] += p * vf[e];
             }
         }
+        kv4 = kn4;
+        vv4 = vn4;
+        base = nbase;
     }
 
     // merge the key slots of a warp (lanes that differ above the LPK bits)
@@ -158,7 +180,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
             o += sm_acc[w][g][d] * sc;
         }
         const int head = kvh * G + g;
-        if (a.n_splits == 1) {
+        if (active == 1) {
             a.out[(size_t)tok * a.n_heads * HD + (size_t)head * HD + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
         } else {
             const size_t pi = ((size_t)tok * a.n_heads + head) * a.n_splits + split;
@@ -169,6 +191,43 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
             }
         }
     }
+}
+
+// Merges the partial results of the active splits: one warp per (token, head).
+template <int HD>
+__global__ void __launch_bounds__(128) attn_decode_combine_kernel(const AttnDecodeArgs a, int n_rows) {
+    constexpr int DPL = HD / 32;       // dims per lane
+    __shared__ float wts[4][64];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x * 4 + warp;          // tok * n_heads + head
+    if (row >= n_rows) return;
+    const int tok = row / a.n_heads;                // one token per sequence: tok is the sequence
+    const int kv_len = a.start_pos[tok] + 1;
+    const int span = a.window > 0 ? min(kv_len, a.window) : kv_len;
+    const int active = attn_decode_active_splits(span, a.n_splits);
+    if (active == 1) return;                        // the split kernel wrote the output itself
+    const float* ml = a.part_ml + (size_t)row * a.n_splits * 2;
+    float m0 = lane < active ? ml[lane * 2] : -INFINITY, m1 = lane + 32 < active ? ml[(lane + 32) * 2] : -INFINITY;
+    float l0 = lane < active ? ml[lane * 2 + 1] : 0.f, l1 = lane + 32 < active ? ml[(lane + 32) * 2 + 1] : 0.f;
+    const float M = warp_max(fmaxf(m0, m1));
+    const float w0 = m0 == -INFINITY ? 0.f : expf(m0 - M), w1 = m1 == -INFINITY ? 0.f : expf(m1 - M);
+    const float L = warp_sum(l0 * w0 + l1 * w1);
+    wts[warp][lane] = w0;
+    wts[warp][lane + 32] = w1;
+    __syncwarp();
+    const float* acc = a.part_acc + (size_t)row * a.n_splits * HD;
+    float o[DPL];
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) o[e] = 0.f;
+#pragma unroll 4
+    for (int z = 0; z < active; ++z) {
+        const float w = wts[warp][z];
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) o[e] += acc[(size_t)z * HD + e * 32 + lane] * w;
+    }
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) a.out[(size_t)row * HD + e * 32 + lane] = __float2bfloat16_rn(o[e] * inv);
 }
 
 template <int HD>
@@ -182,10 +241,19 @@ static bool launch_attn_decode_g(const AttnDecodeArgs& a, int group, dim3 grid, 
     }
 }
 
-// true when the specialised kernel was launched; false: the shape is left to the general kernel
+// true when the specialised kernels were launched; false: the shape is left to the general kernel
 static bool launch_attn_decode(const AttnDecodeArgs& a, int hd, int group, int n_seqs, cudaStream_t stream) {
     const dim3 grid(a.n_splits, a.n_kv, n_seqs);
-    if (hd == 64) return launch_attn_decode_g<64>(a, group, grid, stream);
-    if (hd == 128) return launch_attn_decode_g<128>(a, group, grid, stream);
+    const int n_rows = n_seqs * a.n_heads;
+    if (hd == 64) {
+        if (!launch_attn_decode_g<64>(a, group, grid, stream)) return false;
+        if (a.n_splits > 1) attn_decode_combine_kernel<64><<<(n_rows + 3) / 4, 128, 0, stream>>>(a, n_rows);
+        return true;
+    }
+    if (hd == 128) {
+        if (!launch_attn_decode_g<128>(a, group, grid, stream)) return false;
+        if (a.n_splits > 1) attn_decode_combine_kernel<128><<<(n_rows + 3) / 4, 128, 0, stream>>>(a, n_rows);
+        return true;
+    }
     return false;
 }

@@ -110,23 +110,15 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ 
                                    const double* __restrict__ inv_freq, int rot, int pairing,
                                    T* __restrict__ pool, int n_heads, int n_kv, int hd, int page_size,
                                    int write_cache, const float2* __restrict__ table, int table_len) {
-    extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
-    const int n = blockIdx.x;
-    const int pos = token_pos[n];
+    // one item per thread: a rotated pair of q or k, a lane of k beyond the rotated ones, or two lanes of v
+    const int n = blockIdx.y;
+    const int item = blockIdx.x * blockDim.x + threadIdx.x;
     const int half = rot >> 1;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        if (pos < table_len) {       // the same numbers, computed once by rope_table_kernel
-            const float2 v = table[(size_t)pos * half + i];
-            cs[i] = v.x;
-            cs[half + i] = v.y;
-        } else {
-            double s, c;
-            sincos((double)pos * inv_freq[i], &s, &c);
-            cs[i] = (float)c;
-            cs[half + i] = (float)s;
-        }
-    }
-    __syncthreads();
+    const int n_pairs = (n_heads + n_kv) * half;
+    const int n_tail = write_cache ? n_kv * (hd - rot) : 0;
+    const int n_v = write_cache ? n_kv * (hd >> 1) : 0;
+    if (item >= n_pairs + n_tail + n_v) return;
+    const int pos = token_pos[n];
     T* row = qkv + (size_t)n * (size_t)(n_heads + 2 * n_kv) * hd;
     T* kdst = nullptr;
     T* vdst = nullptr;
@@ -138,38 +130,37 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ 
         vdst = kdst + page_elems;
     }
     const size_t head_stride_cache = (size_t)page_size * hd;
-    // rotated pairs of q and k
-    const int rot_heads = n_heads + n_kv;
-    for (int item = threadIdx.x; item < rot_heads * half; item += blockDim.x) {
+    if (item < n_pairs) {
         const int h = item / half, i = item % half;
+        float c, s;
+        if (pos < table_len) {       // the same numbers, computed once by rope_table_kernel
+            const float2 v = table[(size_t)pos * half + i];
+            c = v.x;
+            s = v.y;
+        } else {
+            double sd, cd;
+            sincos((double)pos * inv_freq[i], &sd, &cd);
+            c = (float)cd;
+            s = (float)sd;
+        }
         const int la = pairing ? 2 * i : i, lb = pairing ? 2 * i + 1 : i + half;
         T* hp = row + (size_t)h * hd;
         const float a = to_f32(hp[la]), b = to_f32(hp[lb]);
-        const float c = cs[i], s = cs[half + i];
         const T ra = from_f32<T>(a * c - b * s), rb = from_f32<T>(a * s + b * c);
-        if (h < n_heads) {
-            hp[la] = ra;
-            hp[lb] = rb;
-        } else if (kdst) {
-            T* kp = kdst + (size_t)(h - n_heads) * head_stride_cache;
-            kp[la] = ra;
-            kp[lb] = rb;
-        } else {  // a layer that reads another layer's cache still rotates its own k in place
-            hp[la] = ra;
-            hp[lb] = rb;
-        }
-    }
-    if (!write_cache) return;
-    // lanes of k beyond the rotated ones, and v
-    const int tail = hd - rot;
-    for (int item = threadIdx.x; item < n_kv * tail; item += blockDim.x) {
-        const int h = item / tail, l = rot + item % tail;
+        T* dst = (h < n_heads || !kdst) ? hp : kdst + (size_t)(h - n_heads) * head_stride_cache;
+        dst[la] = ra;
+        dst[lb] = rb;
+    } else if (item < n_pairs + n_tail) {
+        const int tail = hd - rot, j = item - n_pairs;
+        const int h = j / tail, l = rot + j % tail;
         kdst[(size_t)h * head_stride_cache + l] = row[(size_t)(n_heads + h) * hd + l];
-    }
-    const T* vsrc = row + (size_t)(n_heads + n_kv) * hd;
-    for (int item = threadIdx.x; item < n_kv * hd; item += blockDim.x) {
-        const int h = item / hd, l = item % hd;
-        vdst[(size_t)h * head_stride_cache + l] = vsrc[item];
+    } else {
+        const int j = item - n_pairs - n_tail;
+        const int h = j / (hd >> 1), l = 2 * (j % (hd >> 1));
+        const T* vsrc = row + (size_t)(n_heads + n_kv + h) * hd + l;
+        T* vd = vdst + (size_t)h * head_stride_cache + l;
+        vd[0] = vsrc[0];
+        vd[1] = vsrc[1];
     }
 }
 
@@ -182,12 +173,17 @@ BLM_API int blm_rope_append(void* qkv, int dtype, const int* token_seq, const in
     BLM_REQUIRE(rot >= 0 && rot <= hd && rot % 2 == 0, "rotary: %d rotated lanes of a head of %d", rot, hd);
     BLM_REQUIRE(rot == 0 || inv_freq != nullptr, "rotary: no frequencies");
     BLM_REQUIRE(pairing == 0 || pairing == 1, "rotary: pairing %d", pairing);
-    const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
+    BLM_REQUIRE(hd % 2 == 0, "rotary: odd head size %d", hd);
     const int threads = 128;
+    const int items = (n_heads + n_kv) * (rot / 2) + (write_cache ? n_kv * (hd - rot) + n_kv * (hd / 2) : 0);
+    if (items == 0) return BLM_OK;
+    const dim3 grid((items + threads - 1) / threads, n_tokens);
+    BLM_REQUIRE(grid.y <= 65535, "rotary: %d tokens in one step (at most 65535)", n_tokens);
+    const size_t smem = 0;
     if (dtype == BLM_F32)
-        rope_append_kernel<float><<<n_tokens, threads, smem, stream>>>((float*)qkv, token_seq, token_pos, slot_of_seq, block_table, table_stride, inv_freq, rot, pairing, (float*)pool, n_heads, n_kv, hd, page_size, write_cache, table, table_len);
+        rope_append_kernel<float><<<grid, threads, smem, stream>>>((float*)qkv, token_seq, token_pos, slot_of_seq, block_table, table_stride, inv_freq, rot, pairing, (float*)pool, n_heads, n_kv, hd, page_size, write_cache, table, table_len);
     else if (dtype == BLM_BF16)
-        rope_append_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>((__nv_bfloat16*)qkv, token_seq, token_pos, slot_of_seq, block_table, table_stride, inv_freq, rot, pairing, (__nv_bfloat16*)pool, n_heads, n_kv, hd, page_size, write_cache, table, table_len);
+        rope_append_kernel<__nv_bfloat16><<<grid, threads, smem, stream>>>((__nv_bfloat16*)qkv, token_seq, token_pos, slot_of_seq, block_table, table_stride, inv_freq, rot, pairing, (__nv_bfloat16*)pool, n_heads, n_kv, hd, page_size, write_cache, table, table_len);
     else
         return blm_fail(BLM_BAD_ARGUMENT, "rotary: dtype %d", dtype);
     return blm_check_launch("rope_append");
@@ -212,29 +208,33 @@ BLM_API int blm_rope_table(const double* inv_freq, float* table, int n_pos, int 
 }
 
 // ---------------------------------------------------------------------------------------------
-// gated activation: out[n, i] = silu(gu[n, i]) * gu[n, I + i], computed in fp32
+// gated activation: out[n, i] = silu(gate_i) * up_i, computed in fp32.  The fused product gu[n, 2 I]
+// holds gate then up (tile == 0), or tiles of `tile` gates followed by the `tile` ups of the same outputs.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inner, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inner, size_t total, int tile) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t n = idx / inner;
         const int i = (int)(idx % inner);
-        const float g = to_f32(gu[n * 2 * inner + i]);
-        const float u = to_f32(gu[n * 2 * inner + inner + i]);
+        const size_t gi = tile ? (size_t)(i / tile) * 2 * tile + i % tile : (size_t)i;
+        const size_t ui = tile ? gi + tile : (size_t)inner + i;
+        const float g = to_f32(gu[n * 2 * inner + gi]);
+        const float u = to_f32(gu[n * 2 * inner + ui]);
         out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
     }
 }
 
-BLM_API int blm_swiglu(const void* gu, void* out, int dtype, int n_rows, int inner, cudaStream_t stream) {
+BLM_API int blm_swiglu(const void* gu, void* out, int dtype, int n_rows, int inner, int tile, cudaStream_t stream) {
     if (n_rows == 0) return BLM_OK;
+    BLM_REQUIRE(tile >= 0 && (tile == 0 || inner % tile == 0), "swiglu: tiles of %d do not divide %d", tile, inner);
     const size_t total = (size_t)n_rows * inner;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
     if (dtype == BLM_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, inner, total);
+        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, inner, total, tile);
     else if (dtype == BLM_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inner, total);
+        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inner, total, tile);
     else
         return blm_fail(BLM_BAD_ARGUMENT, "swiglu: dtype %d", dtype);
     return blm_check_launch("swiglu");

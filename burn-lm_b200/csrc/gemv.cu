@@ -1,35 +1,51 @@
-// Skinny matrix products for decode steps: y[N, M] = x[N, K] . W[M, K]^T with N <= 64 tokens, bf16
-// weights streamed once from HBM at full width, fp32 accumulation on the tensor cores.
+// Skinny matrix products for decode steps: y[N, M] = x[N, K] . W[M, K]^T with N <= 16 tokens, bf16
+// weights streamed once from HBM, fp32 accumulation on the tensor cores.
 //
-// The weight matrix is the "A" operand of mma.sync.m16n8k16 (16 weight rows per warp), the tokens
-// are the "B" operand (8 tokens per instruction), so one pass over W serves every token.  A thread
-// loads 16 contiguous bytes of a weight row straight from global memory; the k index inside an
-// instruction is permuted the same way for both operands, which a dot product does not notice, so
-// no shuffle or shared-memory transpose of the weights is needed.  The tokens sit in shared memory.
+// One persistent block per SM.  A producer thread feeds a ring of shared-memory stages with TMA
+// tile copies (cp.async.bulk.tensor, one 8 KB box of 16 weight rows by 256 k per stage, 128-byte
+// swizzle, completion counted on mbarriers), so ~100 KB of weights are in flight per SM whatever
+// the consumers do.  Each of the eight consumer warps owns a tile of 16 weight rows at a time and
+// walks its whole K, stage after stage, through a part of the ring that is its own (so that it sees
+// every phase of its barriers, which a parity wait needs); the producer deals the stages of the
+// warps' tiles in turn,
+// multiplying with mma.sync.m16n8k16: the weight rows are the "A" operand, the tokens (staged once
+// per block in shared memory) the "B" operand.  A thread reads 16 contiguous bytes of a weight row;
+// the k index inside an instruction is permuted the same way for both operands, which a dot
+// product does not notice, so the rows need no transpose.  A warp sums its tile alone, in one fixed
+// order, and writes it from registers: no reduction between warps, no barrier after the start.
+// The weight is seen by the TMA as [K / 64][rows][64]: a box is 4 chunks of 64 k for 16 rows, which
+// lands in shared memory as [chunk][row][128 bytes].
 //
 // Fused around the product, to save launches and activation traffic:
 //   prologue  x = rmsnorm(resid[rows]) * gamma computed by every block from the fp32 residual stream
-//   epilogue  store (bf16 or fp32) | silu(gate) * up (rows i and I + i of a fused [gate; up] weight)
+//   epilogue  store (bf16 or fp32) | silu(gate) * up (a fused weight whose 16-row tiles hold 8 gate
+//             rows, then the 8 up rows of the same outputs)
 //             | resid += y (the residual add of the stream, exactly one writer per element)
-// A block is WR row tiles x WK slices of K (8 warps); the K slices are summed through shared memory
-// in a fixed order, so results are deterministic and do not depend on the other tokens of the batch.
-#include <mma.h>
+// Every wait on an mbarrier is bounded: after kSpinLimit polls the thread records the failure in
+// the status word the caller gave and leaves the kernel.
+#include <cuda.h>
+
+#include <map>
+#include <tuple>
 
 #include "common.cuh"
 
 BLM_API const char* blm_gemv_last_error() { return g_blm_error; }
 
-constexpr int kGemvThreads = 256;
-constexpr int kUnroll = 4;  // 32-wide k units per loop trip: 8 x 16-byte loads in flight per thread
+constexpr int kConsumerWarps = 8;
+constexpr int kGemvThreads = (kConsumerWarps + 1) * 32;   // + the producer warp
+constexpr int kStageK = 256;                              // k elements per stage: 8 units of 32
+constexpr int kStageBytes = 16 * kStageK * 2;             // [4 chunks][16 rows][128 bytes], swizzled
+constexpr unsigned kSpinLimit = 1u << 20;   // polls of a wait before it gives up (seconds; a real wait is microseconds)
 
 enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESID_ADD = 2 };
+enum { GEMV_OK = 0, GEMV_TIMEOUT_FULL = 1, GEMV_TIMEOUT_EMPTY = 2 };
 
 struct GemvArgs {
     const __nv_bfloat16* w;
     long long ldw;
-    int M;              // outputs (for EPI_SWIGLU: the inner size I; W has 2 I rows, up at row I + i)
+    int M;              // outputs (for EPI_SWIGLU: the inner size I; W has 2 I rows in tiles of 8 gate + 8 up)
     int K;
-    long long up_off;   // row offset of the "up" half for EPI_SWIGLU
     const __nv_bfloat16* x;  // plain input [N, K] (ldx), or null when the norm prologue is used
     long long ldx;
     const float* resid;      // norm prologue: fp32 stream [*, K]
@@ -43,8 +59,8 @@ struct GemvArgs {
     int y_f32;
     float* acc;              // EPI_RESID_ADD: fp32 [N, M] (ld = M)
     int epi;
-    int wr, wk;              // warps: row tiles x k slices (wr * wk == 8)
-    int kc;                  // k chunk staged in shared memory at a time (multiple of 32)
+    int n_stages;            // ring depth
+    int* status;             // device word: 0, or the first failure (a bounded wait ran out)
 };
 
 __device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -55,245 +71,344 @@ __device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 ld_stream(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// false when the phase did not complete within the poll limit
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    const unsigned addr = smem_u32(bar);
+    for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+        unsigned done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+// one box of the weight: chunks [chunk0, chunk0 + 4) of rows [row0, row0 + 16); what lies outside the
+// matrix arrives as zeros
+__device__ __forceinline__ void tma_load_box(void* dst, const CUtensorMap* map, int row0, int chunk0, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(0), "r"(row0), "r"(chunk0), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerWarps * 32) : "memory"); }
+
+// Stages all tokens in shared memory as bf16 (zero beyond K and N); run by the consumer warps.
+template <int NBT>
+__device__ __forceinline__ void gemv_stage_tokens(const GemvArgs& a, __nv_bfloat16* xs, int xstride, int kpad,
+                                                  int tid, int lane, int warp) {
+    constexpr int nrows = NBT * 8;
+    constexpr int n_threads = kConsumerWarps * 32;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    if (a.resid == nullptr) {
+        // plain tokens: asynchronous 16-byte copies straight into shared memory
+        const int vec = kpad / 8;
+        for (int idx = tid; idx < nrows * vec; idx += n_threads) {
+            const int r = idx / vec, k = (idx % vec) * 8;
+            __nv_bfloat16* dst = xs + (size_t)r * xstride + k;
+            if (r < a.N && k < a.K) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(a.x + (size_t)r * a.ldx + k));
+            } else {
+                *reinterpret_cast<uint4*>(dst) = zero4;
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+        asm volatile("cp.async.wait_group 0;\n" ::);
+        return;
+    }
+    // norm prologue: a warp takes a stream row through registers in passes of 2048 lanes (sixteen
+    // independent 16-byte loads per lane), first for the sum of squares, then to scale and store
+    for (int r = warp; r < nrows; r += kConsumerWarps) {
+        const bool live = r < a.N;
+        const float* src = a.resid + (size_t)(live ? (a.rows ? a.rows[r] : r) : 0) * a.K;
+        float4 v[16];
+        auto load_pass = [&](int k0) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int k = k0 + (i * 32 + lane) * 4;
+                v[i] = (live && k < a.K) ? *reinterpret_cast<const float4*>(src + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        };
+        float ss = 0.f;
+        for (int k0 = 0; k0 < a.K; k0 += 2048) {
+            load_pass(k0);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+        ss = warp_sum(ss);
+        const float sc = 1.0f / sqrtf(ss / (float)a.K + a.eps);
+        for (int k0 = 0; k0 < kpad; k0 += 2048) {
+            if (a.K > 2048) load_pass(k0);      // a single pass is still in registers
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int k = k0 + (i * 32 + lane) * 4;
+                if (k < kpad) {
+                    float g0 = 0.f, g1 = 0.f, g2 = 0.f, g3 = 0.f;
+                    if (k < a.K) {
+                        if (a.gamma_f32) {
+                            const float4 gv = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.gamma) + k);
+                            g0 = gv.x; g1 = gv.y; g2 = gv.z; g3 = gv.w;
+                        } else {
+                            const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(a.gamma) + k);
+                            const float2 ga = __bfloat1622float2(gp[0]), gb = __bfloat1622float2(gp[1]);
+                            g0 = ga.x; g1 = ga.y; g2 = gb.x; g3 = gb.y;
+                        }
+                    }
+                    __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(xs + (size_t)r * xstride + k);
+                    dst[0] = __floats2bfloat162_rn(v[i].x * sc * g0, v[i].y * sc * g1);
+                    dst[1] = __floats2bfloat162_rn(v[i].z * sc * g2, v[i].w * sc * g3);
+                }
+            }
+        }
+    }
 }
 
 template <int NBT>
-__global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
-    extern __shared__ __align__(16) unsigned char smem[];
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap wmap) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    constexpr int nrows = NBT * 8;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int wr = warp / a.wk, wk = warp % a.wk;
-    const int nrows = NBT * 8;
-    const int xstride = a.kc + 8;                                  // bf16 elements; 16 bytes of padding
-    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);    // [nrows][xstride]
-    float* red = reinterpret_cast<float*>(smem + (size_t)nrows * xstride * 2);   // [wk][wr*16][nrows]
-    float* inv_rms = red + (size_t)a.wk * a.wr * 16 * nrows;       // [nrows]
+    const int kpad = (a.K + kStageK - 1) / kStageK * kStageK;
+    const int xstride = kpad + 8;                                   // bf16 elements; 16 bytes of padding
+    // layout: ring | tokens | barriers
+    unsigned char* ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);   // the swizzle wants 1024-byte alignment
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ring + (size_t)a.n_stages * kStageBytes);
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(xs) + (size_t)nrows * xstride * 2);
+    unsigned long long* empty = full + a.n_stages;
 
-    // the two weight rows of this thread
-    long long row_lo, row_hi;
-    bool ok_lo, ok_hi;
-    if (a.epi == EPI_SWIGLU) {
-        const int i = (blockIdx.x * a.wr + wr) * 8 + g;
-        ok_lo = ok_hi = i < a.M;
-        row_lo = i;
-        row_hi = a.up_off + i;
-    } else {
-        const int r = (blockIdx.x * a.wr + wr) * 16 + g;
-        ok_lo = r < a.M;
-        ok_hi = r + 8 < a.M;
-        row_lo = r;
-        row_hi = r + 8;
-    }
-    const __nv_bfloat16* wlo = a.w + row_lo * a.ldw + 8 * t;
-    const __nv_bfloat16* whi = a.w + row_hi * a.ldw + 8 * t;
+    const int out_per_tile = a.epi == EPI_SWIGLU ? 8 : 16;
+    const int n_tiles = (a.M + out_per_tile - 1) / out_per_tile;
+    const int stages_per_tile = kpad / kStageK;
+    // this block's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...; the i-th of them goes to warp i % 8,
+    // in rounds of eight tiles
+    const int my_tiles = n_tiles > (int)blockIdx.x ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int n_rounds = (my_tiles + kConsumerWarps - 1) / kConsumerWarps;
+    // the ring is dealt out to the warps that work (fewer tiles than warps: fewer, deeper parts)
+    const int depth = a.n_stages / max(1, min(kConsumerWarps, my_tiles));
 
-    float c[NBT][4];
-#pragma unroll
-    for (int j = 0; j < NBT; ++j)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) c[j][e] = 0.f;
-
-    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-    auto load_w = [&](int unit, int unit_end, uint4& lo, uint4& hi) {
-        const int k = unit * 32 + 8 * t;
-        const bool in = unit < unit_end && k < a.K;
-        lo = (in && ok_lo) ? ld_stream(wlo + (size_t)unit * 32) : zero4;
-        hi = (in && ok_hi) ? ld_stream(whi + (size_t)unit * 32) : zero4;
-    };
-
-    for (int kc0 = 0; kc0 < a.K; kc0 += a.kc) {
-        const int kc_len = min(a.kc, a.K - kc0);
-        // this warp's units of the chunk
-        const int units = (kc_len + 31) / 32;
-        const int per = (units + a.wk - 1) / a.wk;
-        const int u_begin = kc0 / 32 + wk * per;
-        const int u_end = kc0 / 32 + min(units, (wk + 1) * per);
-        // weights do not depend on the tokens: start streaming them before the tokens are staged
-        uint4 lo[kUnroll], hi[kUnroll];
-#pragma unroll
-        for (int i = 0; i < kUnroll; ++i) load_w(u_begin + i, u_end, lo[i], hi[i]);
-
-        if (kc0 == 0 && a.resid != nullptr) {
-            // row statistics of the norm prologue: one pass over the stream rows (they sit in L2)
-            for (int r = warp; r < nrows; r += kGemvThreads / 32) {
-                float ss = 0.f;
-                if (r < a.N) {
-                    const float* src = a.resid + (size_t)(a.rows ? a.rows[r] : r) * a.K;
-                    for (int k = lane * 4; k < a.K; k += 128) {
-                        const float4 v = *reinterpret_cast<const float4*>(src + k);
-                        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                    }
-                }
-                ss = warp_sum(ss);
-                if (lane == 0) inv_rms[r] = 1.0f / sqrtf(ss / (float)a.K + a.eps);
-            }
+    if (tid == 0) {
+        for (int s = 0; s < a.n_stages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
         }
-
-        __syncthreads();   // the chunk before this one is consumed; inv_rms is visible
-        const int staged = units * 32;   // whole units: what lies beyond K is zero, never left as it was
-        for (int idx = tid; idx < nrows * (staged / 4); idx += kGemvThreads) {
-            const int r = idx / (staged / 4), k = (idx % (staged / 4)) * 4;
-            __nv_bfloat162 p0, p1;
-            if (r < a.N && k < kc_len) {
-                if (a.resid != nullptr) {
-                    const float* src = a.resid + (size_t)(a.rows ? a.rows[r] : r) * a.K + kc0 + k;
-                    const float4 v = *reinterpret_cast<const float4*>(src);
-                    const float s = inv_rms[r];
-                    float g0, g1, g2, g3;
-                    if (a.gamma_f32) {
-                        const float4 gv = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.gamma) + kc0 + k);
-                        g0 = gv.x; g1 = gv.y; g2 = gv.z; g3 = gv.w;
-                    } else {
-                        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(a.gamma) + kc0 + k);
-                        const float2 ga = __bfloat1622float2(gp[0]), gb = __bfloat1622float2(gp[1]);
-                        g0 = ga.x; g1 = ga.y; g2 = gb.x; g3 = gb.y;
-                    }
-                    p0 = __floats2bfloat162_rn(v.x * s * g0, v.y * s * g1);
-                    p1 = __floats2bfloat162_rn(v.z * s * g2, v.w * s * g3);
-                } else {
-                    const __nv_bfloat162* src = reinterpret_cast<const __nv_bfloat162*>(a.x + (size_t)r * a.ldx + kc0 + k);
-                    p0 = src[0];
-                    p1 = src[1];
-                }
-            } else {
-                p0 = p1 = __floats2bfloat162_rn(0.f, 0.f);
-            }
-            __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(xs + (size_t)r * xstride + k);
-            dst[0] = p0;
-            dst[1] = p1;
-        }
-        __syncthreads();
-
-        for (int u = u_begin; u < u_end; u += kUnroll) {
-            uint4 nlo[kUnroll], nhi[kUnroll];
-#pragma unroll
-            for (int i = 0; i < kUnroll; ++i) load_w(u + kUnroll + i, u_end, nlo[i], nhi[i]);
-#pragma unroll
-            for (int i = 0; i < kUnroll; ++i) {
-                if (u + i < u_end) {
-                    const int k = (u + i) * 32 - kc0 + 8 * t;
-#pragma unroll
-                    for (int j = 0; j < NBT; ++j) {
-                        const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)(j * 8 + g) * xstride + k);
-                        mma16816(c[j], lo[i].x, hi[i].x, lo[i].y, hi[i].y, xv.x, xv.y);
-                        mma16816(c[j], lo[i].z, hi[i].z, lo[i].w, hi[i].w, xv.z, xv.w);
-                    }
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < kUnroll; ++i) { lo[i] = nlo[i]; hi[i] = nhi[i]; }
-        }
-    }
-
-    // sum the k slices in a fixed order, then the epilogue
-    const int tile_rows = a.wr * 16;
-#pragma unroll
-    for (int j = 0; j < NBT; ++j) {
-        float* dst = red + ((size_t)wk * tile_rows + wr * 16) * nrows;
-        dst[(size_t)g * nrows + j * 8 + 2 * t] = c[j][0];
-        dst[(size_t)g * nrows + j * 8 + 2 * t + 1] = c[j][1];
-        dst[(size_t)(g + 8) * nrows + j * 8 + 2 * t] = c[j][2];
-        dst[(size_t)(g + 8) * nrows + j * 8 + 2 * t + 1] = c[j][3];
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
-    auto total = [&](int r, int b) {
-        float s = 0.f;
-        for (int z = 0; z < a.wk; ++z) s += red[((size_t)z * tile_rows + r) * nrows + b];
-        return s;
-    };
-    if (a.epi == EPI_SWIGLU) {
-        const int outs = a.wr * 8;
-        for (int idx = tid; idx < outs * a.N; idx += kGemvThreads) {
-            const int b = idx / outs, o = idx % outs;
-            const int i = blockIdx.x * outs + o;
-            if (i < a.M) {
-                const int r = (o / 8) * 16 + (o % 8);
-                const float gate = total(r, b), up = total(r + 8, b);
-                const float v = gate / (1.0f + expf(-gate)) * up;
-                reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)b * a.ldy + i] = __float2bfloat16_rn(v);
+
+    if (warp == kConsumerWarps) {
+        // ---------------- producer: one thread deals stages to the warps' tiles ----------------
+        if (lane != 0) return;
+        for (int round = 0; round < n_rounds; ++round) {
+            const int live = min(kConsumerWarps, my_tiles - round * kConsumerWarps);
+            for (int st = 0; st < stages_per_tile; ++st) {
+                const unsigned q = (unsigned)(round * stages_per_tile + st);      // the warp's q-th stage
+                for (int w = 0; w < live; ++w) {
+                    const int slot = w * depth + (int)(q % depth);
+                    if (q >= (unsigned)depth && !mbar_wait(empty + slot, ((q / depth) - 1) & 1)) {
+                        atomicCAS(a.status, GEMV_OK, GEMV_TIMEOUT_EMPTY);
+                        return;
+                    }
+                    const int tile = blockIdx.x + (round * kConsumerWarps + w) * gridDim.x;
+                    mbar_expect_tx(full + slot, kStageBytes);
+                    tma_load_box(ring + (size_t)slot * kStageBytes, &wmap, tile * 16, st * (kStageK / 64), full + slot);
+                }
             }
         }
-    } else {
-        for (int idx = tid; idx < tile_rows * a.N; idx += kGemvThreads) {
-            const int b = idx / tile_rows, r = idx % tile_rows;
-            const int m = blockIdx.x * tile_rows + r;
-            if (m < a.M) {
-                const float v = total(r, b);
-                if (a.epi == EPI_RESID_ADD) a.acc[(size_t)b * a.M + m] += v;
-                else if (a.y_f32) reinterpret_cast<float*>(a.y)[(size_t)b * a.ldy + m] = v;
-                else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)b * a.ldy + m] = __float2bfloat16_rn(v);
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    gemv_stage_tokens<NBT>(a, xs, xstride, kpad, tid, lane, warp);
+    consumer_barrier();
+
+    const int g = lane >> 2, t = lane & 3;
+    for (int round = 0; round < n_rounds; ++round) {
+        const int live = min(kConsumerWarps, my_tiles - round * kConsumerWarps);
+        if (warp < live) {
+            const int tile = blockIdx.x + (round * kConsumerWarps + warp) * gridDim.x;
+            float c[2][NBT][4];     // two sets, used in turn: two chains of dependent instructions instead of one
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < NBT; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) c[h][j][e] = 0.f;
+            for (int st = 0; st < stages_per_tile; ++st) {
+                const unsigned q = (unsigned)(round * stages_per_tile + st);      // this warp's q-th stage
+                const int slot = warp * depth + (int)(q % depth);
+                if (!mbar_wait(full + slot, (q / depth) & 1)) {
+                    if (lane == 0) atomicCAS(a.status, GEMV_OK, GEMV_TIMEOUT_FULL);
+                    return;
+                }
+                const unsigned char* stage = ring + (size_t)slot * kStageBytes;
+#pragma unroll
+                for (int u = 0; u < kStageK / 32; ++u) {
+                    const int k = st * kStageK + u * 32;
+                    if (k < a.K) {
+                        // unit u of the stage: chunk u / 2, 64-byte half u % 2; the 16-byte slot of a line is
+                        // XORed with the line's number mod 8 (the 128-byte swizzle), here the row's
+                        const unsigned char* chunk = stage + (u >> 1) * (16 * 128);
+                        const int s16 = (u & 1) * 4 + t;
+                        const uint4 lo = *reinterpret_cast<const uint4*>(chunk + g * 128 + ((s16 ^ g) << 4));
+                        const uint4 hi = *reinterpret_cast<const uint4*>(chunk + (g + 8) * 128 + ((s16 ^ g) << 4));
+#pragma unroll
+                        for (int j = 0; j < NBT; ++j) {
+                            const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)(j * 8 + g) * xstride + k + 8 * t);
+                            mma16816(c[0][j], lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
+                            mma16816(c[1][j], lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty + slot);          // the stage is read: the producer may refill it
+            }
+            // the tile is done: rows g and g + 8, tokens 2t and 2t + 1 of every token tile
+#pragma unroll
+            for (int j = 0; j < NBT; ++j) {
+                const float v00 = c[0][j][0] + c[1][j][0], v01 = c[0][j][1] + c[1][j][1];   // row g
+                const float v10 = c[0][j][2] + c[1][j][2], v11 = c[0][j][3] + c[1][j][3];   // row g + 8
+                const int b0 = j * 8 + 2 * t, b1 = b0 + 1;
+                if (a.epi == EPI_SWIGLU) {
+                    const int i = tile * 8 + g;      // rows 0..7 of the tile are gates, rows 8..15 their ups
+                    if (i < a.M) {
+                        __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(a.y);
+                        if (b0 < a.N) y[(size_t)b0 * a.ldy + i] = __float2bfloat16_rn(v00 / (1.0f + expf(-v00)) * v10);
+                        if (b1 < a.N) y[(size_t)b1 * a.ldy + i] = __float2bfloat16_rn(v01 / (1.0f + expf(-v01)) * v11);
+                    }
+                } else {
+                    const float v[2][2] = {{v00, v01}, {v10, v11}};
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        const int m = tile * 16 + g + 8 * rr;
+                        if (m >= a.M) continue;
+#pragma unroll
+                        for (int bb = 0; bb < 2; ++bb) {
+                            const int b = b0 + bb;
+                            if (b >= a.N) continue;
+                            if (a.epi == EPI_RESID_ADD) a.acc[(size_t)b * a.M + m] += v[rr][bb];
+                            else if (a.y_f32) reinterpret_cast<float*>(a.y)[(size_t)b * a.ldy + m] = v[rr][bb];
+                            else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)b * a.ldy + m] = __float2bfloat16_rn(v[rr][bb]);
+                        }
+                    }
+                }
             }
         }
     }
 }
 
-// Shared memory the kernel needs for a shape, and the k chunk it picks; 0 when the shape does not fit.
-static size_t gemv_plan(int N, int K, int wr, int wk, int* kc_out, int* nbt_out) {
+// Shared memory for a shape and the ring depth it leaves room for; 0 when the tokens do not fit.
+static size_t gemv_plan(int N, int K, int* n_stages_out, int* nbt_out) {
     int nbt = 1;
     while (nbt * 8 < N) nbt *= 2;
-    if (nbt > 8) return 0;
+    if (nbt > 2) return 0;
     const int nrows = nbt * 8;
-    const size_t fixed = (size_t)wk * wr * 16 * nrows * 4 + (size_t)nrows * 4;
-    const size_t budget = 100 * 1024;     // two blocks per SM
-    int kc = (K + 31) / 32 * 32;
-    while ((size_t)nrows * (kc + 8) * 2 + fixed > budget && kc > 256) kc = ((kc / 2) + 31) / 32 * 32;
-    if ((size_t)nrows * (kc + 8) * 2 + fixed > 200 * 1024) return 0;
-    *kc_out = kc;
+    const int kpad = (K + kStageK - 1) / kStageK * kStageK;
+    const size_t tokens = (size_t)nrows * (kpad + 8) * 2;
+    const size_t red = 0;
+    const size_t limit = 220 * 1024;
+    int stages = 16;
+    while (stages > 8 && (size_t)stages * kStageBytes + tokens + red + (size_t)stages * 16 + 1024 > limit) --stages;
+    const size_t total = (size_t)stages * kStageBytes + tokens + red + (size_t)stages * 16 + 1024;
+    if (total > limit) return 0;
+    *n_stages_out = stages;
     *nbt_out = nbt;
-    return (size_t)nrows * (kc + 8) * 2 + fixed;
+    return total;
 }
 
 // 1 when blm_gemv takes the shape, else 0 (the caller then uses the library product).
 BLM_API int blm_gemv_supported(int N, int M, int K) {
-    int kc, nbt;
-    return N >= 1 && N <= 64 && K % 8 == 0 && K >= 32 && M >= 1 && gemv_plan(N, K, 1, 8, &kc, &nbt) > 0;
+    int st, nbt;
+    return N >= 1 && N <= 16 && K % 64 == 0 && M >= 1 && gemv_plan(N, K, &st, &nbt) > 0;
 }
 
-BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, long long up_off, const void* x, long long ldx,
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The TMA's view of a weight [rows, K] (row stride ldw): dims (64 k, rows, K / 64); box (64, 16, 4).
+static int weight_map(const void* w, long long ldw, int rows, int K, CUtensorMap* out) {
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+            return blm_fail(BLM_CUDA_ERROR, "gemv: the driver has no cuTensorMapEncodeTiled");
+        encode = (EncodeTiledFn)fn;
+    }
+    static std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> cache;
+    const auto key = std::make_tuple(w, ldw, rows, K);
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+        CUtensorMap m;
+        const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(K / 64)};
+        const cuuint64_t strides[2] = {(cuuint64_t)ldw * 2, 128};     // bytes: between rows, between chunks
+        const cuuint32_t box[3] = {64, 16, kStageK / 64};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return blm_fail(BLM_CUDA_ERROR, "gemv: cuTensorMapEncodeTiled failed (%d)", (int)r);
+        if (cache.size() > 4096) cache.clear();
+        it = cache.emplace(key, m).first;
+    }
+    *out = it->second;
+    return BLM_OK;
+}
+
+BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, long long ldx,
                      const float* resid, const void* gamma, int gamma_f32, float eps, const int* rows, int N,
-                     void* y, long long ldy, int y_f32, float* acc, int epi, cudaStream_t stream) {
+                     void* y, long long ldy, int y_f32, float* acc, int epi, int* status, cudaStream_t stream) {
     if (N == 0 || M == 0) return BLM_OK;
-    BLM_REQUIRE(N >= 1 && N <= 64, "gemv: %d tokens (1..64)", N);
-    BLM_REQUIRE(K % 8 == 0 && K >= 32, "gemv: K = %d must be a multiple of 8, at least 32", K);
+    BLM_REQUIRE(N >= 1 && N <= 16, "gemv: %d tokens (1..16)", N);
+    BLM_REQUIRE(K % 64 == 0 && K >= 64, "gemv: K = %d must be a multiple of 64", K);
     BLM_REQUIRE((x != nullptr) != (resid != nullptr), "gemv: give either x or the stream to normalise");
-    BLM_REQUIRE(x == nullptr || ldx % 8 == 0, "gemv: x rows must be 16-byte aligned");
-    BLM_REQUIRE(ldw % 8 == 0, "gemv: weight rows must be 16-byte aligned");
+    BLM_REQUIRE(x == nullptr || (ldx % 8 == 0 && ((size_t)x & 15) == 0), "gemv: x rows must be 16-byte aligned");
+    BLM_REQUIRE(ldw % 8 == 0 && ((size_t)w & 15) == 0, "gemv: weight rows must be 16-byte aligned");
     BLM_REQUIRE(epi == EPI_STORE || epi == EPI_SWIGLU || epi == EPI_RESID_ADD, "gemv: epilogue %d", epi);
+    BLM_REQUIRE(epi != EPI_SWIGLU || M % 8 == 0, "gemv: the gated epilogue needs an inner size that is a multiple of 8, got %d", M);
     BLM_REQUIRE(epi != EPI_RESID_ADD || acc != nullptr, "gemv: no stream to add into");
     BLM_REQUIRE(epi == EPI_RESID_ADD || y != nullptr, "gemv: no output");
-    BLM_REQUIRE(resid == nullptr || K % 4 == 0, "gemv: norm prologue needs K %% 4 == 0");
+    BLM_REQUIRE(resid == nullptr || ((size_t)resid & 15) == 0, "gemv: the stream must be 16-byte aligned");
+    BLM_REQUIRE(status != nullptr, "gemv: no status word");
     GemvArgs a;
-    a.w = (const __nv_bfloat16*)w; a.ldw = ldw; a.M = M; a.K = K; a.up_off = up_off;
+    a.w = (const __nv_bfloat16*)w; a.ldw = ldw; a.M = M; a.K = K;
     a.x = (const __nv_bfloat16*)x; a.ldx = ldx; a.resid = resid; a.gamma = gamma; a.gamma_f32 = gamma_f32; a.eps = eps;
-    a.rows = rows; a.N = N; a.y = y; a.ldy = ldy; a.y_f32 = y_f32; a.acc = acc; a.epi = epi;
-    // blocks: enough of them to fill 148 SMs a few times over; small M takes more k slices per block
+    a.rows = rows; a.N = N; a.y = y; a.ldy = ldy; a.y_f32 = y_f32; a.acc = acc; a.epi = epi; a.status = status;
+    int nbt;
+    const size_t smem = gemv_plan(N, K, &a.n_stages, &nbt);
+    BLM_REQUIRE(smem > 0, "gemv: the shape N=%d K=%d does not fit shared memory", N, K);
+    CUtensorMap wmap;
+    int rc = weight_map(w, ldw, epi == EPI_SWIGLU ? 2 * M : M, K, &wmap);
+    if (rc != BLM_OK) return rc;
     const int out_per_tile = epi == EPI_SWIGLU ? 8 : 16;
     const int tiles = (M + out_per_tile - 1) / out_per_tile;
-    int wr = 1;
-    while (wr < 8 && tiles / (wr * 2) >= 2 * 148) wr *= 2;
-    a.wr = wr; a.wk = 8 / wr;
-    int nbt;
-    const size_t smem = gemv_plan(N, K, a.wr, a.wk, &a.kc, &nbt);
-    BLM_REQUIRE(smem > 0, "gemv: the shape N=%d K=%d does not fit shared memory", N, K);
-    const int grid = (tiles + wr - 1) / wr;
+    const int grid = tiles < 148 ? tiles : 148;
+    static bool opted_in[3] = {false, false, false};     // per token-tile variant of the kernel
     auto launch = [&](auto kernel) -> int {
-        if (smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (!opted_in[nbt]) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
             if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "gemv: %s", cudaGetErrorString(e));
+            opted_in[nbt] = true;
         }
-        kernel<<<grid, kGemvThreads, smem, stream>>>(a);
+        kernel<<<grid, kGemvThreads, smem, stream>>>(a, wmap);
         return blm_check_launch("gemv");
     };
-    switch (nbt) {
-        case 1: return launch(gemv_kernel<1>);
-        case 2: return launch(gemv_kernel<2>);
-        case 4: return launch(gemv_kernel<4>);
-        default: return launch(gemv_kernel<8>);
-    }
+    return nbt == 1 ? launch(gemv_kernel<1>) : launch(gemv_kernel<2>);
 }

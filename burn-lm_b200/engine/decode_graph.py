@@ -9,6 +9,10 @@ token of a step is written back as the next step's input by a kernel inside the 
 """
 from __future__ import annotations
 
+import contextlib
+import gc
+import weakref
+
 import torch
 
 from .. import kernels as K
@@ -16,9 +20,25 @@ from ..parts.base import StepContext
 from .engine import Workspace
 
 
+@contextlib.contextmanager
+def _capturing(graph):
+    """Capture with the garbage collector held back: a collection in the middle of a capture may
+    destroy an older CUDA graph, which CUDA does not permit while a stream is capturing."""
+    gc.collect()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph):
+            yield
+    finally:
+        if was_enabled:
+            gc.enable()
+
+
 class DecodeGraph:
-    def __init__(self, engine, batch: int):
-        self.engine, self.batch = engine, batch
+    def __init__(self, engine, batch: int, max_kv_len: int):
+        self._engine = weakref.ref(engine)      # the engine owns its graphs, not the other way round
+        self.batch, self.max_kv_len = batch, max_kv_len
         dev = engine.model.runtime.device
         b = batch
         # tokens | positions | slots: what a step brings, in one buffer, one copy
@@ -27,7 +47,7 @@ class DecodeGraph:
         self.tokens, self.pos, self.slots = self.meta[:b], self.meta[b:2 * b], self.meta[2 * b:]
         ar = torch.arange(b + 1, dtype=torch.int32, device=dev)
         self.ctx = StepContext(
-            n_tokens=b, n_seqs=b, max_q_len=1, max_kv_len=engine.cache.max_seq_len,
+            n_tokens=b, n_seqs=b, max_q_len=1, max_kv_len=max_kv_len,
             tokens=self.tokens, token_seq=ar[:b], token_pos=self.pos, cu_seqlens=ar, slot_of_seq=self.slots,
             start_pos=self.pos, want_rows=ar[:b], n_want=b,
             workspace=Workspace(dev),     # its own: a captured graph keeps the addresses it saw
@@ -42,6 +62,10 @@ class DecodeGraph:
         self._loop_history_steps = 0
         self._copied = None
         self.launches_per_step = 0
+
+    @property
+    def engine(self):
+        return self._engine()
 
     def bytes_in_per_step(self) -> int:
         return self.host_meta.numel() * 4
@@ -69,7 +93,7 @@ class DecodeGraph:
             self.logits = self._forward()            # the first step runs plainly and warms everything up
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with _capturing(g):
                 self._captured_logits = self._forward()
             self._graph = g
             return self.logits
@@ -89,7 +113,7 @@ class DecodeGraph:
             self.meta.copy_(saved)
             g = torch.cuda.CUDAGraph()
             before = K.launch_count()
-            with torch.cuda.graph(g):
+            with _capturing(g):
                 self._one_loop_step()
             self.launches_per_step = K.launch_count() - before   # this package's kernels in one replay
             self._loop_graph = g

@@ -85,12 +85,23 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.seq_len[slot]
 
-    def decode_graph(self, batch: int):
-        """The captured decode step for `batch` sequences (made at first use)."""
+    def verify(self) -> None:
+        """Raise if a kernel gave up a bounded wait since the last call (synchronises with the device)."""
+        from .. import kernels
+        kernels.check_status(self.model.runtime.device)
+
+    def decode_graph(self, batch: int, max_kv_len: int):
+        """The captured decode step for `batch` sequences of at most `max_kv_len` tokens (made at first
+        use).  Lengths come in buckets (64 tokens times a power of two), because the number of blocks
+        that split a sequence's keys is fixed in a captured graph."""
         from .decode_graph import DecodeGraph
-        g = self._decode_graphs.get(batch)
+        pages = 1
+        while pages * 64 < max_kv_len:
+            pages *= 2
+        bucket = min(pages * 64, -(-self.cache.max_seq_len // 64) * 64)
+        g = self._decode_graphs.get((batch, bucket))
         if g is None:
-            g = self._decode_graphs[batch] = DecodeGraph(self, batch)
+            g = self._decode_graphs[(batch, bucket)] = DecodeGraph(self, batch, bucket)
         return g
 
     def decode_run(self, slots, tokens, n_steps: int) -> torch.Tensor:
@@ -98,7 +109,7 @@ class Engine:
         host in between.  Returns the sampled tokens, int32 [n_steps, len(slots)], on the device."""
         starts = [self.cache.seq_len[s] for s in slots]
         self.cache.reserve([(s, st + n_steps) for s, st in zip(slots, starts)])
-        g = self.decode_graph(len(slots))
+        g = self.decode_graph(len(slots), max(starts) + n_steps)
         g.load(tokens, starts, slots)
         history = g.run(n_steps)
         for s, st in zip(slots, starts):
@@ -174,7 +185,7 @@ class Engine:
         (tokens, token_seq, token_pos, cu, slots, starts, want_rows, growth, max_q, max_kv) = self._pack(entries)
         self.cache.reserve(growth)          # raises before anything is launched, changing nothing
         if self.use_graphs and max_q == 1 and want_rows == list(range(len(entries))):
-            g = self.decode_graph(len(entries))
+            g = self.decode_graph(len(entries), max_kv)
             g.load(tokens, starts, slots)
             logits = g.step()
             for slot, new_len in growth:

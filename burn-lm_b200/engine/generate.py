@@ -175,6 +175,9 @@ class GenerationLoop:
                 tokens = self.sampler.sample(logits, params, live, [len(results[i].tokens) for i in live])
                 stats.decode_steps += 1
             stats.decode_seconds += time.perf_counter() - t0
+            verify = getattr(engine, "verify", None)
+            if verify is not None:
+                verify()                      # no kernel gave up a bounded wait during this batch
         finally:
             for slot in slots.values():
                 engine.release(slot)

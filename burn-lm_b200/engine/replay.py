@@ -38,6 +38,7 @@ class Replayer:
                     fresh.append(rid)
                 entries.append(StepEntry(self.slot_of[rid], e["tokens"], e.get("want", ())))
             logits = self.engine.step(entries) if entries else None
+            self.engine.verify()
         except Exception:
             for rid in fresh:   # a refused step leaves nothing behind
                 self.engine.release(self.slot_of.pop(rid))

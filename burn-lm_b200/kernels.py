@@ -55,7 +55,7 @@ _protos = {
         "blm_rope_append": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                             c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
         "blm_rope_table": [c_void_p, c_void_p, c_int, c_int, c_void_p],
-        "blm_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "blm_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "blm_convert": [c_void_p, c_int, c_void_p, c_int, c_size_t, c_void_p],
         "blm_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     },
@@ -69,8 +69,8 @@ _protos = {
                          c_longlong, c_void_p],
     },
     "gemv": {
-        "blm_gemv": [c_void_p, c_longlong, c_int, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
-                     c_float, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p],
+        "blm_gemv": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
+                     c_float, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p],
         "blm_gemv_supported": [c_int, c_int, c_int],
     },
     "sampling": {
@@ -184,13 +184,17 @@ def rope_append(qkv, token_seq, token_pos, slot_of_seq, block_table, inv_freq, r
           _ptr(table), table.shape[0] if table is not None else 0, _stream())
 
 
-def swiglu(gate_up, out):
-    """out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]."""
+GATE_TILE = 8   # a fused [gate; up] weight for the skinny kernel: tiles of 8 gate rows, then their 8 up rows
+
+
+def swiglu(gate_up, out, tile=0):
+    """out[n, i] = silu(gate_i) * up_i.  gate_up [N, 2 I] holds all gates then all ups (tile 0), or
+    tiles of `tile` gates followed by the ups of the same outputs."""
     _need_cuda(gate_up, out)
     n, two_i = gate_up.shape
     if tuple(out.shape) != (n, two_i // 2) or out.dtype != gate_up.dtype or two_i % 2:
         raise KernelError("swiglu: out must be [N, I] for gate_up [N, 2 I], same dtype")
-    _call("elementwise", "blm_swiglu", _ptr(gate_up), _ptr(out), _code(out.dtype), n, two_i // 2, _stream())
+    _call("elementwise", "blm_swiglu", _ptr(gate_up), _ptr(out), _code(out.dtype), n, two_i // 2, tile, _stream())
 
 
 def convert(src, dst):
@@ -210,6 +214,12 @@ def decode_advance(tokens, pos, sampled, history, step_no, counters=None):
     steps = history.shape[0] if history is not None else 0
     _call("elementwise", "blm_decode_advance", _ptr(tokens), _ptr(pos), _ptr(sampled), _ptr(history), _ptr(step_no),
           _ptr(counters), b, steps, _stream(), kernels=2)
+
+
+def attention_decode_is_specialised(dtype, head_dim, group) -> bool:
+    """Whether a step of one token per sequence runs the specialised decode kernel (whose blocks
+    split the keys by pages and skip splits a sequence does not need)."""
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and group in (1, 2, 4, 8)
 
 
 def attention_scratch_floats(n_tokens, n_heads, head_dim, n_splits):
@@ -264,12 +274,36 @@ def gemv_supported(n_tokens, m, k) -> bool:
     return bool(_lib("gemv").blm_gemv_supported(n_tokens, m, k))
 
 
+_status: dict = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """The device word in which kernels with bounded waits record that a wait ran out (0: all well)."""
+    dev = torch.device(device)
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+    w = _status.get(key)
+    if w is None:
+        w = _status[key] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return w
+
+
+def check_status(device) -> None:
+    """Raise if a kernel gave up a bounded wait since the last check (reads one word from the device)."""
+    w = status_word(device)
+    code = int(w.item())
+    if code:
+        w.zero_()
+        what = {1: "a consumer waited in vain for a weight stage", 2: "the producer waited in vain for a free stage"}
+        raise KernelError(f"gemv: {what.get(code, 'status ' + str(code))}; the step's results are not valid")
+
+
 def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, out=None, add_into=None, swiglu=False):
-    """Skinny product of n_tokens <= 64 tokens with a bfloat16 weight [M, K], with fused ends.
+    """Skinny product of n_tokens <= 16 tokens with a bfloat16 weight [M, K], with fused ends.
 
     Input: `x` bfloat16 [N, K], or the fp32 residual stream `stream_rows` [*, K] to be RMS-normalised
     with `gamma`, `eps` (optionally gathering `rows`).  Output: `out` [N, M] bfloat16 or float32;
-    with `swiglu` the weight is [2 I, K] = [gate; up] and out [N, I] = silu(gate) * up; with
+    with `swiglu` the weight is [2 I, K] in tiles of GATE_TILE gate rows followed by the up rows of the
+    same outputs, and out [N, I] = silu(gate) * up; with
     `add_into` (fp32 [N, M]) the product is added into it and nothing else is written."""
     _need_cuda(w, x, stream_rows, gamma, rows, out, add_into)
     m_rows, k = w.shape
@@ -287,10 +321,11 @@ def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, 
     elif out is None or tuple(out.shape) != (n_tokens, m) or out.dtype not in (torch.bfloat16, torch.float32) \
             or (swiglu and out.dtype != torch.bfloat16):
         raise KernelError("gemv: out must be [N, M] bfloat16 (or float32 for a plain store)")
-    _call("gemv", "blm_gemv", _ptr(w), w.stride(0), m, k, m if swiglu else 0, _ptr(x), x.stride(0) if x is not None else 0,
+    _call("gemv", "blm_gemv", _ptr(w), w.stride(0), m, k, _ptr(x), x.stride(0) if x is not None else 0,
           _ptr(stream_rows), _ptr(gamma), 1 if (gamma is not None and gamma.dtype == torch.float32) else 0, c_float(eps),
           _ptr(rows), n_tokens, _ptr(out), out.stride(0) if out is not None else 0,
-          1 if (out is not None and out.dtype == torch.float32) else 0, _ptr(add_into), epi, _stream())
+          1 if (out is not None and out.dtype == torch.float32) else 0, _ptr(add_into), epi,
+          _ptr(status_word(w.device)), _stream())
 
 
 def argmax(logits, out):

@@ -82,8 +82,10 @@ class Attention(Part):
             return 1
         s = self.spec
         group = s.n_heads // s.n_kv_heads
-        blocks = step.n_seqs * s.n_kv_heads * ((group + 31) // 32)
         pages = (step.max_kv_len + K.PAGE - 1) // K.PAGE
+        if K.attention_decode_is_specialised(self.runtime.dtype, s.head_dim, group):
+            return max(1, min(pages, 64))      # a block per page; blocks beyond a sequence's pages leave at once
+        blocks = step.n_seqs * s.n_kv_heads * ((group + 31) // 32)
         return max(1, min(pages, (_TARGET_BLOCKS + blocks - 1) // blocks, 64))
 
     takes_pending_norm = True

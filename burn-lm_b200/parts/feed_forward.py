@@ -38,7 +38,15 @@ class SwiGLU(Part):
         g, u = loaded[t["gate"]], loaded[t["up"]]
         if g.dtype != u.dtype:
             raise ValueError(f"{t['gate']} and {t['up']} are stored in different dtypes")
-        self.gate_up = Linear(torch.cat([g, u], dim=0).contiguous())
+        inner = self.spec.intermediate_size
+        if g.dtype == torch.bfloat16 and inner % K.GATE_TILE == 0:
+            # tiles of 8 gate rows followed by the 8 up rows of the same outputs: the skinny kernel's
+            # gated epilogue finds both halves of an output in one 16-row tile
+            tile = K.GATE_TILE
+            fused = torch.stack([g.view(inner // tile, tile, -1), u.view(inner // tile, tile, -1)], dim=1).reshape(2 * inner, -1)
+            self.gate_up = Linear(fused.contiguous(), gate_tile=tile)
+        else:
+            self.gate_up = Linear(torch.cat([g, u], dim=0).contiguous())
         self.down = Linear(loaded[t["down"]])
 
     takes_pending_norm = True

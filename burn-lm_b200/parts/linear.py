@@ -1,7 +1,7 @@
 """The matrix product y = x W^T of a weight stored [out, in], picked by the weight's dtype and the
 number of tokens.
 
-bfloat16 weights: steps of up to 64 tokens run this package's skinny kernel (weights streamed once,
+bfloat16 weights: steps of up to 16 tokens run this package's skinny kernel (weights streamed once,
 tensor-core accumulation in fp32), which can also take the RMS norm in front of it and the gated
 activation or the residual add behind it; larger steps go through the library product (cuBLAS via
 torch.mm), as the reference's engine uses its library's `Linear`
@@ -18,8 +18,8 @@ import torch
 
 from .. import kernels as K
 
-SKINNY_TOKENS = 64        # the skinny kernel takes up to this many tokens
-FUSED_NORM_TOKENS = 16    # ... and normalises in its prologue up to this many (every block redoes it)
+SKINNY_TOKENS = 16        # the skinny kernel takes up to this many tokens
+FUSED_NORM_TOKENS = 16    # ... and normalises them in its prologue (every block redoes it)
 
 
 @dataclass
@@ -43,10 +43,13 @@ class NormedStream:
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor):
+    def __init__(self, weight: torch.Tensor, gate_tile: int = 0):
+        """gate_tile: for a fused gate/up weight, how its rows are laid out: 0 = all gate rows then all up
+        rows; n = tiles of n gate rows followed by the n up rows of the same outputs."""
         if weight.dim() != 2:
             raise ValueError("a linear weight is [out, in]")
         self.weight = weight
+        self.gate_tile = gate_tile
         self.out_features, self.in_features = weight.shape
 
     def _skinny(self, n_tokens: int, m: int) -> bool:
@@ -96,10 +99,10 @@ class Linear:
         n = self._tokens(x)
         inner = self.out_features // 2
         act = torch.empty((n, inner), dtype=out_dtype, device=self.weight.device)
-        if out_dtype == torch.bfloat16 and self._skinny(n, inner):
+        if out_dtype == torch.bfloat16 and self.gate_tile == K.GATE_TILE and self._skinny(n, inner):
             K.gemv(self.weight, n, out=act, swiglu=True, **self._source(x))
             return act
-        K.swiglu(self(x, out_dtype), act)
+        K.swiglu(self(x, out_dtype), act, tile=self.gate_tile)
         return act
 
     def _library(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:

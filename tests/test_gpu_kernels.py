@@ -310,13 +310,16 @@ def gemv_reference(w, x):
     return x.double() @ w.double().T
 
 
-@pytest.mark.parametrize("n", [1, 3, 8, 9, 24, 64])
-@pytest.mark.parametrize("m,k", [(40, 64), (200, 160), (3072, 2048), (1000, 8192), (77, 4104)])
+@pytest.mark.parametrize("n", [1, 3, 8, 9, 16])
+# (18944, 2048): eight tiles for every block, all warps busy; (40016, 512): several rounds, the last one partial
+@pytest.mark.parametrize("m,k", [(40, 64), (200, 192), (3072, 2048), (1000, 8192), (77, 4160), (2500, 512), (18944, 2048), (40016, 512)])
 def test_gemv_store(n, m, k):
     g = torch.Generator(device="cuda").manual_seed(n * 1000 + m)
     w = (torch.randn(m, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
     x = torch.randn(n, k, device="cuda", generator=g).to(torch.bfloat16)
-    assert K().gemv_supported(n, m, k)
+    if not K().gemv_supported(n, m, k):
+        assert n > 8 and k >= 8192          # only: too many tokens of too wide rows for shared memory
+        pytest.skip("the tokens do not fit shared memory; the library product takes this shape")
     want = gemv_reference(w, x)
     scale = want.abs().max().item()
     out32 = torch.empty(n, m, device="cuda")
@@ -325,31 +328,34 @@ def test_gemv_store(n, m, k):
     out16 = torch.empty(n, m, device="cuda", dtype=torch.bfloat16)
     K().gemv(w, n, x=x, out=out16)
     assert (out16.double() - want).abs().max().item() < 5e-3 * scale
-    # a token's result does not depend on the other tokens of the batch, beyond the rounding of an
-    # fp32 sum taken in another order (larger batches stage K in smaller chunks)
+    # a token's result does not depend on the other tokens of the batch
     one = torch.empty(1, m, device="cuda")
     K().gemv(w, 1, x=x[:1].contiguous(), out=one)
-    if n <= 8:
-        assert torch.equal(one[0], out32[0])
-    assert (one[0] - out32[0]).abs().max().item() < 2e-6 * scale
+    assert torch.equal(one[0], out32[0])
+    K().check_status("cuda")
 
 
 @pytest.mark.parametrize("n", [1, 8, 16])
 @pytest.mark.parametrize("gdt", DTYPES)
 def test_gemv_norm_prologue_swiglu_and_stream_add(n, gdt):
     g = torch.Generator(device="cuda").manual_seed(n)
-    k, inner, m = 192, 520, 192
+    k, inner, m = 192, 576, 192
     resid = torch.randn(n + 3, k, device="cuda", generator=g)
     gamma = (1 + 0.1 * torch.randn(k, device="cuda", generator=g)).to(gdt)
     rows = torch.randperm(n + 3, device="cuda", generator=g)[:n].to(torch.int32)
     eps = 1e-5
     h = resid.double()[rows.long()]
     xn = (h / torch.sqrt((h * h).mean(-1, keepdim=True) + eps) * gamma.double()).to(torch.bfloat16)   # rounded as the kernel rounds
-    wgu = (torch.randn(2 * inner, k, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    wgu = (torch.randn(2 * inner, k, device="cuda", generator=g) * 0.1).to(torch.bfloat16)        # [gate; up]
+    tiled = torch.stack([wgu[:inner].view(inner // 8, 8, k), wgu[inner:].view(inner // 8, 8, k)], dim=1).reshape(2 * inner, k).contiguous()
     act = torch.empty(n, inner, device="cuda", dtype=torch.bfloat16)
-    K().gemv(wgu, n, stream_rows=resid, gamma=gamma, eps=eps, rows=rows, out=act, swiglu=True)
+    K().gemv(tiled, n, stream_rows=resid, gamma=gamma, eps=eps, rows=rows, out=act, swiglu=True)
     gu = gemv_reference(wgu, xn)
     want = gu[:, :inner] / (1 + torch.exp(-gu[:, :inner])) * gu[:, inner:]
+    # the element-wise kernel reads the same tiled layout
+    act2 = torch.empty(n, inner, device="cuda", dtype=torch.bfloat16)
+    K().swiglu(gemv_reference(tiled, xn).to(torch.bfloat16), act2, tile=8)
+    assert (act2.double() - want).abs().max().item() < 2e-2 * want.abs().max().item()
     assert (act.double() - want).abs().max().item() < 1e-2 * want.abs().max().item()
     # without rows, and adding into the stream
     wd = (torch.randn(m, inner, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
@@ -368,10 +374,10 @@ def test_gemv_norm_prologue_swiglu_and_stream_add(n, gdt):
 
 def test_gemv_refuses_what_it_cannot_do():
     k = K()
-    assert not k.gemv_supported(65, 10, 64) and not k.gemv_supported(4, 10, 36)
-    w = torch.zeros(16, 36, device="cuda", dtype=torch.bfloat16)
-    with pytest.raises(k.KernelError, match="multiple of 8"):
-        k.gemv(w, 1, x=torch.zeros(1, 36, device="cuda", dtype=torch.bfloat16), out=torch.zeros(1, 16, device="cuda"))
+    assert not k.gemv_supported(17, 10, 64) and not k.gemv_supported(4, 10, 96)
+    w = torch.zeros(16, 96, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(k.KernelError, match="multiple of 64"):
+        k.gemv(w, 1, x=torch.zeros(1, 96, device="cuda", dtype=torch.bfloat16), out=torch.zeros(1, 16, device="cuda"))
 
 
 @pytest.mark.parametrize("H,KV,hd", [(32, 8, 64), (8, 8, 64), (16, 2, 128), (4, 2, 128)])
