@@ -60,6 +60,7 @@ struct GemvArgs {
     float* acc;              // EPI_RESID_ADD: fp32 [N, M] (ld = M)
     int epi;
     int n_stages;            // ring depth
+    int ksplit;              // warps that share a tile, each walking 1/ksplit of K (1, 2, 4 or 8)
     int* status;             // device word: 0, or the first failure (a bounded wait ran out)
 };
 
@@ -132,8 +133,10 @@ __device__ __forceinline__ void gemv_stage_tokens(const GemvArgs& a, __nv_bfloat
         asm volatile("cp.async.wait_group 0;\n" ::);
         return;
     }
-    // norm prologue: a warp takes a stream row through registers in passes of 2048 lanes (sixteen
-    // independent 16-byte loads per lane), first for the sum of squares, then to scale and store
+    // norm prologue: a warp takes a stream row through registers in passes of 2048 lanes: sixteen
+    // independent 16-byte loads of the row per lane and the matching gamma, all through the read-only
+    // path and all issued before anything is stored, so that they overlap instead of queueing behind
+    // the stores; first for the sum of squares, then to scale and store
     for (int r = warp; r < nrows; r += kConsumerWarps) {
         const bool live = r < a.N;
         const float* src = a.resid + (size_t)(live ? (a.rows ? a.rows[r] : r) : 0) * a.K;
@@ -142,8 +145,16 @@ __device__ __forceinline__ void gemv_stage_tokens(const GemvArgs& a, __nv_bfloat
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const int k = k0 + (i * 32 + lane) * 4;
-                v[i] = (live && k < a.K) ? *reinterpret_cast<const float4*>(src + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[i] = (live && k < a.K) ? __ldg(reinterpret_cast<const float4*>(src + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
+        };
+        auto gamma_at = [&](int k) -> float4 {
+            if (k >= a.K) return make_float4(0.f, 0.f, 0.f, 0.f);
+            if (a.gamma_f32) return __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.gamma) + k));
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.gamma) + k));
+            const float2 ga = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+            const float2 gb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+            return make_float4(ga.x, ga.y, gb.x, gb.y);
         };
         float ss = 0.f;
         for (int k0 = 0; k0 < a.K; k0 += 2048) {
@@ -151,28 +162,26 @@ __device__ __forceinline__ void gemv_stage_tokens(const GemvArgs& a, __nv_bfloat
 #pragma unroll
             for (int i = 0; i < 16; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
         }
+        float4 gm[16];
+        if (a.K <= 2048) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) gm[i] = gamma_at((i * 32 + lane) * 4);     // in flight during the reduction
+        }
         ss = warp_sum(ss);
         const float sc = 1.0f / sqrtf(ss / (float)a.K + a.eps);
         for (int k0 = 0; k0 < kpad; k0 += 2048) {
-            if (a.K > 2048) load_pass(k0);      // a single pass is still in registers
+            if (a.K > 2048) {      // a single pass is still in registers
+                load_pass(k0);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) gm[i] = gamma_at(k0 + (i * 32 + lane) * 4);
+            }
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const int k = k0 + (i * 32 + lane) * 4;
                 if (k < kpad) {
-                    float g0 = 0.f, g1 = 0.f, g2 = 0.f, g3 = 0.f;
-                    if (k < a.K) {
-                        if (a.gamma_f32) {
-                            const float4 gv = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.gamma) + k);
-                            g0 = gv.x; g1 = gv.y; g2 = gv.z; g3 = gv.w;
-                        } else {
-                            const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(a.gamma) + k);
-                            const float2 ga = __bfloat1622float2(gp[0]), gb = __bfloat1622float2(gp[1]);
-                            g0 = ga.x; g1 = ga.y; g2 = gb.x; g3 = gb.y;
-                        }
-                    }
                     __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(xs + (size_t)r * xstride + k);
-                    dst[0] = __floats2bfloat162_rn(v[i].x * sc * g0, v[i].y * sc * g1);
-                    dst[1] = __floats2bfloat162_rn(v[i].z * sc * g2, v[i].w * sc * g3);
+                    dst[0] = __floats2bfloat162_rn(v[i].x * sc * gm[i].x, v[i].y * sc * gm[i].y);
+                    dst[1] = __floats2bfloat162_rn(v[i].z * sc * gm[i].z, v[i].w * sc * gm[i].w);
                 }
             }
         }
@@ -186,48 +195,91 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int kpad = (a.K + kStageK - 1) / kStageK * kStageK;
     const int xstride = kpad + 8;                                   // bf16 elements; 16 bytes of padding
-    // layout: ring | tokens | barriers
+    // layout: ring | tokens | partial sums of warps that share a tile | barriers
     unsigned char* ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);   // the swizzle wants 1024-byte alignment
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ring + (size_t)a.n_stages * kStageBytes);
-    unsigned long long* full = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(xs) + (size_t)nrows * xstride * 2);
+    float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs) + (size_t)nrows * xstride * 2);   // [warp][16][nrows]
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(red + kConsumerWarps * 16 * nrows);
     unsigned long long* empty = full + a.n_stages;
+    unsigned long long* meet = empty + a.n_stages;     // where warps that share a tile meet (a bounded wait, like all)
 
     const int out_per_tile = a.epi == EPI_SWIGLU ? 8 : 16;
     const int n_tiles = (a.M + out_per_tile - 1) / out_per_tile;
     const int stages_per_tile = kpad / kStageK;
-    // this block's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...; the i-th of them goes to warp i % 8,
-    // in rounds of eight tiles
+    // A unit of work is (tile, slice of K): `ksplit` warps share a tile when a block has few tiles.
+    // This block's tiles are blockIdx.x, blockIdx.x + gridDim.x, ...; its work units go to the warps
+    // in turn, in rounds of eight.
+    const int ks = a.ksplit;
+    const int stages_per_slice = (stages_per_tile + ks - 1) / ks;
     const int my_tiles = n_tiles > (int)blockIdx.x ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-    const int n_rounds = (my_tiles + kConsumerWarps - 1) / kConsumerWarps;
-    // the ring is dealt out to the warps that work (fewer tiles than warps: fewer, deeper parts)
-    const int depth = a.n_stages / max(1, min(kConsumerWarps, my_tiles));
+    const int my_units = my_tiles * ks;
+    const int n_rounds = (my_units + kConsumerWarps - 1) / kConsumerWarps;
+    // the ring is dealt out to the warps that work (fewer units than warps: fewer, deeper parts); a warp
+    // sees every phase of the barriers of its part, which a parity wait needs
+    const int depth = a.n_stages / max(1, min(kConsumerWarps, my_units));
 
     if (tid == 0) {
         for (int s = 0; s < a.n_stages; ++s) {
             mbar_init(full + s, 1);
             mbar_init(empty + s, 1);
         }
+        mbar_init(meet, kConsumerWarps);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
 
     if (warp == kConsumerWarps) {
-        // ---------------- producer: one thread deals stages to the warps' tiles ----------------
-        if (lane != 0) return;
-        for (int round = 0; round < n_rounds; ++round) {
-            const int live = min(kConsumerWarps, my_tiles - round * kConsumerWarps);
-            for (int st = 0; st < stages_per_tile; ++st) {
-                const unsigned q = (unsigned)(round * stages_per_tile + st);      // the warp's q-th stage
-                for (int w = 0; w < live; ++w) {
+        // ---------------- producer: lane w of this warp feeds consumer warp w's part of the ring ----------------
+        // Eight lanes poll their own barriers without blocking one another (test_wait, not try_wait), so a
+        // stage is re-issued as soon as its warp has let go of it, whatever the other warps do.
+        const int w = lane;
+        int round = 0, st = 0;            // the next stage of warp w: stage `st` of its unit in `round`
+        unsigned q = 0;                   // how many stages warp w has been dealt
+        bool more = w < kConsumerWarps && w < my_units;
+        unsigned idle = 0;
+        while (__any_sync(0xffffffffu, more)) {
+            bool progressed = false;
+            if (more) {
+                const int unit = round * kConsumerWarps + w;
+                const int stage_of_tile = (unit % ks) * stages_per_slice + st;
+                if (unit >= my_units) {
+                    more = false;
+                } else if (stage_of_tile >= stages_per_tile) {      // a short last slice: on to the next round
+                    ++round;
+                    st = 0;
+                    progressed = true;
+                } else {
                     const int slot = w * depth + (int)(q % depth);
-                    if (q >= (unsigned)depth && !mbar_wait(empty + slot, ((q / depth) - 1) & 1)) {
-                        atomicCAS(a.status, GEMV_OK, GEMV_TIMEOUT_EMPTY);
-                        return;
+                    bool free_slot = q < (unsigned)depth;
+                    if (!free_slot) {
+                        unsigned done;
+                        asm volatile(
+                            "{\n.reg .pred p;\n"
+                            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                            "selp.u32 %0, 1, 0, p;\n}\n"
+                            : "=r"(done)
+                            : "r"(smem_u32(empty + slot)), "r"(((q / depth) - 1) & 1)
+                            : "memory");
+                        free_slot = done != 0;
                     }
-                    const int tile = blockIdx.x + (round * kConsumerWarps + w) * gridDim.x;
-                    mbar_expect_tx(full + slot, kStageBytes);
-                    tma_load_box(ring + (size_t)slot * kStageBytes, &wmap, tile * 16, st * (kStageK / 64), full + slot);
+                    if (free_slot) {
+                        const int tile = blockIdx.x + (unit / ks) * gridDim.x;
+                        mbar_expect_tx(full + slot, kStageBytes);
+                        tma_load_box(ring + (size_t)slot * kStageBytes, &wmap, tile * 16, stage_of_tile * (kStageK / 64), full + slot);
+                        ++q;
+                        if (++st == stages_per_slice) { st = 0; ++round; }
+                        progressed = true;
+                    }
                 }
+            }
+            if (__any_sync(0xffffffffu, progressed)) {
+                idle = 0;
+            } else {
+                __nanosleep(128);      // leave the shared-memory pipe to the consumers while there is nothing to issue
+            }
+            if (++idle > (kSpinLimit << 2)) {             // nobody could issue for seconds
+                if (lane == 0) atomicCAS(a.status, GEMV_OK, GEMV_TIMEOUT_EMPTY);
+                return;
             }
         }
         return;
@@ -239,30 +291,35 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
 
     const int g = lane >> 2, t = lane & 3;
     for (int round = 0; round < n_rounds; ++round) {
-        const int live = min(kConsumerWarps, my_tiles - round * kConsumerWarps);
+        const int live = min(kConsumerWarps, my_units - round * kConsumerWarps);
+        const int unit = round * kConsumerWarps + warp;
+        const int tile = blockIdx.x + (unit / ks) * gridDim.x;
+        float c[2][NBT][4];     // two sets, used in turn: two chains of dependent instructions instead of one
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int j = 0; j < NBT; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) c[h][j][e] = 0.f;
+        bool failed = false;
         if (warp < live) {
-            const int tile = blockIdx.x + (round * kConsumerWarps + warp) * gridDim.x;
-            float c[2][NBT][4];     // two sets, used in turn: two chains of dependent instructions instead of one
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int j = 0; j < NBT; ++j)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) c[h][j][e] = 0.f;
-            for (int st = 0; st < stages_per_tile; ++st) {
-                const unsigned q = (unsigned)(round * stages_per_tile + st);      // this warp's q-th stage
+            for (int st = 0; st < stages_per_slice; ++st) {
+                const int stage_of_tile = (unit % ks) * stages_per_slice + st;
+                if (stage_of_tile >= stages_per_tile) break;
+                const unsigned q = (unsigned)(round * stages_per_slice + st);      // this warp's q-th stage
                 const int slot = warp * depth + (int)(q % depth);
                 if (!mbar_wait(full + slot, (q / depth) & 1)) {
                     if (lane == 0) atomicCAS(a.status, GEMV_OK, GEMV_TIMEOUT_FULL);
-                    return;
+                    failed = true;       // the status word says so; go on to where the others wait for this warp
+                    break;
                 }
                 const unsigned char* stage = ring + (size_t)slot * kStageBytes;
+                // The stage is 8 units of 32 k: chunk u / 2, 64-byte half u % 2; the 16-byte slot of a line is
+                // XORed with the line's number mod 8 (the 128-byte swizzle), here the row's.
 #pragma unroll
                 for (int u = 0; u < kStageK / 32; ++u) {
-                    const int k = st * kStageK + u * 32;
+                    const int k = stage_of_tile * kStageK + u * 32;
                     if (k < a.K) {
-                        // unit u of the stage: chunk u / 2, 64-byte half u % 2; the 16-byte slot of a line is
-                        // XORed with the line's number mod 8 (the 128-byte swizzle), here the row's
                         const unsigned char* chunk = stage + (u >> 1) * (16 * 128);
                         const int s16 = (u & 1) * 4 + t;
                         const uint4 lo = *reinterpret_cast<const uint4*>(chunk + g * 128 + ((s16 ^ g) << 4));
@@ -278,33 +335,88 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty + slot);          // the stage is read: the producer may refill it
             }
-            // the tile is done: rows g and g + 8, tokens 2t and 2t + 1 of every token tile
+        }
+        if (ks > 1) {
+            // warps that share a tile: the partial sums meet in shared memory; the warp of slice 0 adds them
+            // in a fixed order.  With a split there is a single round (a block has at most 8 / ksplit tiles).
+            float* mine = red + (size_t)warp * 16 * nrows;
 #pragma unroll
             for (int j = 0; j < NBT; ++j) {
-                const float v00 = c[0][j][0] + c[1][j][0], v01 = c[0][j][1] + c[1][j][1];   // row g
-                const float v10 = c[0][j][2] + c[1][j][2], v11 = c[0][j][3] + c[1][j][3];   // row g + 8
-                const int b0 = j * 8 + 2 * t, b1 = b0 + 1;
-                if (a.epi == EPI_SWIGLU) {
-                    const int i = tile * 8 + g;      // rows 0..7 of the tile are gates, rows 8..15 their ups
-                    if (i < a.M) {
-                        __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(a.y);
-                        if (b0 < a.N) y[(size_t)b0 * a.ldy + i] = __float2bfloat16_rn(v00 / (1.0f + expf(-v00)) * v10);
-                        if (b1 < a.N) y[(size_t)b1 * a.ldy + i] = __float2bfloat16_rn(v01 / (1.0f + expf(-v01)) * v11);
-                    }
-                } else {
-                    const float v[2][2] = {{v00, v01}, {v10, v11}};
+                mine[(size_t)g * nrows + j * 8 + 2 * t] = c[0][j][0] + c[1][j][0];
+                mine[(size_t)g * nrows + j * 8 + 2 * t + 1] = c[0][j][1] + c[1][j][1];
+                mine[(size_t)(g + 8) * nrows + j * 8 + 2 * t] = c[0][j][2] + c[1][j][2];
+                mine[(size_t)(g + 8) * nrows + j * 8 + 2 * t + 1] = c[0][j][3] + c[1][j][3];
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(meet);
+            if (!mbar_wait(meet, 0)) {
+                if (lane == 0) atomicCAS(a.status, GEMV_OK, GEMV_TIMEOUT_FULL);
+                return;
+            }
+            if (failed || warp >= live || unit % ks != 0) return;
 #pragma unroll
-                    for (int rr = 0; rr < 2; ++rr) {
-                        const int m = tile * 16 + g + 8 * rr;
-                        if (m >= a.M) continue;
+            for (int j = 0; j < NBT; ++j)
 #pragma unroll
-                        for (int bb = 0; bb < 2; ++bb) {
-                            const int b = b0 + bb;
-                            if (b >= a.N) continue;
-                            if (a.epi == EPI_RESID_ADD) a.acc[(size_t)b * a.M + m] += v[rr][bb];
-                            else if (a.y_f32) reinterpret_cast<float*>(a.y)[(size_t)b * a.ldy + m] = v[rr][bb];
-                            else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)b * a.ldy + m] = __float2bfloat16_rn(v[rr][bb]);
-                        }
+                for (int e = 0; e < 4; ++e) { c[0][j][e] = 0.f; c[1][j][e] = 0.f; }
+            for (int z = 0; z < ks; ++z) {
+                const float* part = red + (size_t)(warp + z) * 16 * nrows;
+#pragma unroll
+                for (int j = 0; j < NBT; ++j) {
+                    c[0][j][0] += part[(size_t)g * nrows + j * 8 + 2 * t];
+                    c[0][j][1] += part[(size_t)g * nrows + j * 8 + 2 * t + 1];
+                    c[0][j][2] += part[(size_t)(g + 8) * nrows + j * 8 + 2 * t];
+                    c[0][j][3] += part[(size_t)(g + 8) * nrows + j * 8 + 2 * t + 1];
+                }
+            }
+        } else if (failed) {
+            return;
+        } else if (warp >= live) {
+            continue;
+        }
+        // the tile is done: rows g and g + 8, tokens 2t and 2t + 1 of every token tile
+        if (a.epi == EPI_RESID_ADD) {
+            // all loads of the stream first, then the sums: the round trips overlap
+            float old[NBT][4];
+#pragma unroll
+            for (int j = 0; j < NBT; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int m = tile * 16 + g + 8 * (e >> 1), b = j * 8 + 2 * t + (e & 1);
+                    old[j][e] = (m < a.M && b < a.N) ? a.acc[(size_t)b * a.M + m] : 0.f;
+                }
+#pragma unroll
+            for (int j = 0; j < NBT; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int m = tile * 16 + g + 8 * (e >> 1), b = j * 8 + 2 * t + (e & 1);
+                    if (m < a.M && b < a.N) a.acc[(size_t)b * a.M + m] = old[j][e] + (c[0][j][e] + c[1][j][e]);
+                }
+            continue;
+        }
+#pragma unroll
+        for (int j = 0; j < NBT; ++j) {
+            const float v00 = c[0][j][0] + c[1][j][0], v01 = c[0][j][1] + c[1][j][1];   // row g
+            const float v10 = c[0][j][2] + c[1][j][2], v11 = c[0][j][3] + c[1][j][3];   // row g + 8
+            const int b0 = j * 8 + 2 * t, b1 = b0 + 1;
+            if (a.epi == EPI_SWIGLU) {
+                const int i = tile * 8 + g;      // rows 0..7 of the tile are gates, rows 8..15 their ups
+                if (i < a.M) {
+                    __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(a.y);
+                    if (b0 < a.N) y[(size_t)b0 * a.ldy + i] = __float2bfloat16_rn(v00 / (1.0f + expf(-v00)) * v10);
+                    if (b1 < a.N) y[(size_t)b1 * a.ldy + i] = __float2bfloat16_rn(v01 / (1.0f + expf(-v01)) * v11);
+                }
+            } else {
+                const float v[2][2] = {{v00, v01}, {v10, v11}};
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int m = tile * 16 + g + 8 * rr;
+                    if (m >= a.M) continue;
+#pragma unroll
+                    for (int bb = 0; bb < 2; ++bb) {
+                        const int b = b0 + bb;
+                        if (b >= a.N) continue;
+                        if (a.y_f32) reinterpret_cast<float*>(a.y)[(size_t)b * a.ldy + m] = v[rr][bb];
+                        else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)b * a.ldy + m] = __float2bfloat16_rn(v[rr][bb]);
                     }
                 }
             }
@@ -320,11 +432,11 @@ static size_t gemv_plan(int N, int K, int* n_stages_out, int* nbt_out) {
     const int nrows = nbt * 8;
     const int kpad = (K + kStageK - 1) / kStageK * kStageK;
     const size_t tokens = (size_t)nrows * (kpad + 8) * 2;
-    const size_t red = 0;
+    const size_t red = (size_t)kConsumerWarps * 16 * nrows * 4;
     const size_t limit = 220 * 1024;
     int stages = 16;
-    while (stages > 8 && (size_t)stages * kStageBytes + tokens + red + (size_t)stages * 16 + 1024 > limit) --stages;
-    const size_t total = (size_t)stages * kStageBytes + tokens + red + (size_t)stages * 16 + 1024;
+    while (stages > 8 && (size_t)stages * kStageBytes + tokens + red + (size_t)stages * 16 + 64 + 1024 > limit) --stages;
+    const size_t total = (size_t)stages * kStageBytes + tokens + red + (size_t)stages * 16 + 64 + 1024;
     if (total > limit) return 0;
     *n_stages_out = stages;
     *nbt_out = nbt;
@@ -400,6 +512,11 @@ BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, 
     const int out_per_tile = epi == EPI_SWIGLU ? 8 : 16;
     const int tiles = (M + out_per_tile - 1) / out_per_tile;
     const int grid = tiles < 148 ? tiles : 148;
+    // few tiles per block: several warps share a tile, each on a slice of K
+    const int tiles_per_block = (tiles + grid - 1) / grid;
+    const int stages_per_tile = (K + kStageK - 1) / kStageK;
+    a.ksplit = 1;
+    while (a.ksplit * 2 * tiles_per_block <= kConsumerWarps && a.ksplit * 2 <= stages_per_tile) a.ksplit *= 2;
     static bool opted_in[3] = {false, false, false};     // per token-tile variant of the kernel
     auto launch = [&](auto kernel) -> int {
         if (!opted_in[nbt]) {
