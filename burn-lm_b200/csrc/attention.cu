@@ -10,6 +10,7 @@
 #include <math.h>
 
 #include "attention_decode.cuh"
+#include "attention_prefill.cuh"
 #include "common.cuh"
 
 BLM_API const char* blm_attention_last_error() { return g_blm_error; }
@@ -352,6 +353,16 @@ BLM_API int blm_attention(const void* q, long long q_stride, const void* pool, i
         d.scale_log2e = scale * 1.4426950408889634f;
         BLM_REQUIRE(n_splits <= 64, "attention: at most 64 splits, got %d", n_splits);
         if (launch_attn_decode(d, hd, group, n_seqs, stream)) return blm_check_launch("attention decode");
+    }
+    if (dtype == BLM_BF16 && max_q_len >= 16 && (hd == 64 || hd == 128) && !general_only) {
+        // prompts: the tensor-core kernel
+        AttnPrefillArgs f;
+        f.q = (const __nv_bfloat16*)q; f.q_stride = q_stride; f.pool = (const __nv_bfloat16*)pool;
+        f.block_table = block_table; f.table_stride = table_stride; f.cu_seqlens = cu_seqlens;
+        f.slot_of_seq = slot_of_seq; f.start_pos = start_pos; f.out = (__nv_bfloat16*)out;
+        f.n_heads = n_heads; f.n_kv = n_kv; f.window = window; f.scale_log2e = scale * 1.4426950408889634f;
+        BLM_REQUIRE(q_stride % 8 == 0 && ((size_t)q & 15) == 0, "attention: q rows must be 16-byte aligned");
+        if (launch_attn_prefill(f, hd, n_seqs, max_q_len, stream)) return blm_check_launch("attention prefill");
     }
     AttnArgs a;
     a.q = q; a.q_stride = q_stride; a.pool = pool; a.block_table = block_table; a.table_stride = table_stride;

@@ -32,7 +32,7 @@ MODULES = {
     "gemv": ["gemv.cu"],
     "sampling": ["sampling.cu"],
 }
-HEADERS = ["common.cuh", "attention_decode.cuh"]
+HEADERS = ["common.cuh", "attention_decode.cuh", "attention_prefill.cuh"]
 
 _lock = threading.Lock()
 _loaded: dict[str, ctypes.CDLL] = {}

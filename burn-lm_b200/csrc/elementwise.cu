@@ -63,9 +63,71 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restri
         o[d] = from_f32<TA>(row_buf[d] * inv * to_f32(gamma[d]));
 }
 
+// bf16 activations, width a multiple of 8: 16-byte accesses, the row kept in registers when it fits
+template <typename TG>
+__global__ void add_rmsnorm_bf16_vec_kernel(float* __restrict__ resid, const __nv_bfloat16* __restrict__ delta,
+                                            const TG* __restrict__ gamma, __nv_bfloat16* __restrict__ out,
+                                            const int* __restrict__ rows, int width, float eps) {
+    __shared__ float red[33];
+    constexpr int MAXV = 4;                 // 8-lane groups per thread: width <= blockDim * 8 * MAXV
+    const int src = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* r = resid + (size_t)src * width;
+    const __nv_bfloat16* dl = delta ? delta + (size_t)src * width : nullptr;
+    float h[MAXV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+        const int d = (v * blockDim.x + threadIdx.x) * 8;
+        if (d < width) {
+            const float4 a = *reinterpret_cast<const float4*>(r + d), b = *reinterpret_cast<const float4*>(r + d + 4);
+            h[v][0] = a.x; h[v][1] = a.y; h[v][2] = a.z; h[v][3] = a.w; h[v][4] = b.x; h[v][5] = b.y; h[v][6] = b.z; h[v][7] = b.w;
+            if (dl) {
+                const uint4 dv = *reinterpret_cast<const uint4*>(dl + d);
+                const __nv_bfloat162* dp = reinterpret_cast<const __nv_bfloat162*>(&dv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(dp[e]);
+                    h[v][2 * e] += f.x;
+                    h[v][2 * e + 1] += f.y;
+                }
+                if (!rows) {
+                    *reinterpret_cast<float4*>(r + d) = make_float4(h[v][0], h[v][1], h[v][2], h[v][3]);
+                    *reinterpret_cast<float4*>(r + d + 4) = make_float4(h[v][4], h[v][5], h[v][6], h[v][7]);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += h[v][e] * h[v][e];
+        }
+    }
+    const float total = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(total / (float)width + eps);
+    __nv_bfloat16* o = out + (size_t)blockIdx.x * width;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+        const int d = (v * blockDim.x + threadIdx.x) * 8;
+        if (d < width) {
+            uint4 ov;
+            __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                op[e] = __floats2bfloat162_rn(h[v][2 * e] * inv * to_f32(gamma[d + 2 * e]), h[v][2 * e + 1] * inv * to_f32(gamma[d + 2 * e + 1]));
+            *reinterpret_cast<uint4*>(o + d) = ov;
+        }
+    }
+}
+
 template <typename TA, typename TG>
 static int launch_add_rmsnorm(float* resid, const void* delta, const void* gamma, void* out,
                               const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
+    if (sizeof(TA) == 2 && width % 8 == 0 && width <= 256 * 8 * 4 && ((size_t)resid & 15) == 0 && ((size_t)out & 15) == 0 &&
+        (delta == nullptr || ((size_t)delta & 15) == 0)) {
+        const int threads = width >= 2048 ? 256 : 128;
+        if (width <= threads * 8 * 4) {
+            add_rmsnorm_bf16_vec_kernel<TG><<<n_rows, threads, 0, stream>>>(resid, (const __nv_bfloat16*)delta, (const TG*)gamma,
+                                                                              (__nv_bfloat16*)out, rows, width, eps);
+            return blm_check_launch("add_rmsnorm");
+        }
+    }
     const size_t smem = (size_t)(width + 33) * sizeof(float);
     BLM_REQUIRE(smem <= 200 * 1024, "rms norm: width %d is beyond the 51,000 this kernel holds in shared memory", width);
     auto k = add_rmsnorm_kernel<TA, TG>;
@@ -164,11 +226,64 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ 
     }
 }
 
+// bf16, the whole head rotated, pairs (i, i + hd/2), hd a multiple of 16, positions inside the table: eight
+// pairs per thread with 16-byte accesses
+__global__ void rope_append_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ token_seq,
+                                            const int* __restrict__ token_pos, const int* __restrict__ slot_of_seq,
+                                            const int* __restrict__ block_table, int table_stride,
+                                            __nv_bfloat16* __restrict__ pool, int n_heads, int n_kv, int hd, int page_size,
+                                            int write_cache, const float2* __restrict__ table) {
+    const int n = blockIdx.y;
+    const int item = blockIdx.x * blockDim.x + threadIdx.x;
+    const int half = hd >> 1, cpp = half >> 3;                  // chunks of 8 pairs per head
+    const int n_rot = (n_heads + n_kv) * cpp;
+    const int n_v = write_cache ? n_kv * (hd >> 3) : 0;
+    if (item >= n_rot + n_v) return;
+    const int pos = token_pos[n];
+    __nv_bfloat16* row = qkv + (size_t)n * (size_t)(n_heads + 2 * n_kv) * hd;
+    __nv_bfloat16* kdst = nullptr;
+    __nv_bfloat16* vdst = nullptr;
+    if (write_cache) {
+        const int slot = slot_of_seq[token_seq[n]];
+        const int page = block_table[(size_t)slot * table_stride + pos / page_size];
+        const size_t page_elems = (size_t)n_kv * page_size * hd;
+        kdst = pool + (size_t)page * 2 * page_elems + (size_t)(pos % page_size) * hd;
+        vdst = kdst + page_elems;
+    }
+    const size_t head_stride_cache = (size_t)page_size * hd;
+    if (item < n_rot) {
+        const int h = item / cpp, i = (item % cpp) * 8;
+        __nv_bfloat16* hp = row + (size_t)h * hd;
+        const uint4 av = *reinterpret_cast<const uint4*>(hp + i), bv = *reinterpret_cast<const uint4*>(hp + i + half);
+        const float4* cs = reinterpret_cast<const float4*>(table + (size_t)pos * half + i);
+        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&av);
+        const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&bv);
+        uint4 ra, rb;
+        __nv_bfloat162* rap = reinterpret_cast<__nv_bfloat162*>(&ra);
+        __nv_bfloat162* rbp = reinterpret_cast<__nv_bfloat162*>(&rb);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float4 t = cs[e];                  // (cos, sin) of pairs 2e and 2e + 1
+            const float2 a2 = __bfloat1622float2(ap[e]), b2 = __bfloat1622float2(bp[e]);
+            rap[e] = __floats2bfloat162_rn(a2.x * t.x - b2.x * t.y, a2.y * t.z - b2.y * t.w);
+            rbp[e] = __floats2bfloat162_rn(a2.x * t.y + b2.x * t.x, a2.y * t.w + b2.y * t.z);
+        }
+        __nv_bfloat16* dst = (h < n_heads || !kdst) ? hp : kdst + (size_t)(h - n_heads) * head_stride_cache;
+        *reinterpret_cast<uint4*>(dst + i) = ra;
+        *reinterpret_cast<uint4*>(dst + i + half) = rb;
+    } else {
+        const int j = item - n_rot;
+        const int h = j / (hd >> 3), l = (j % (hd >> 3)) * 8;
+        *reinterpret_cast<uint4*>(vdst + (size_t)h * head_stride_cache + l) =
+            *reinterpret_cast<const uint4*>(row + (size_t)(n_heads + n_kv + h) * hd + l);
+    }
+}
+
 BLM_API int blm_rope_append(void* qkv, int dtype, const int* token_seq, const int* token_pos,
                             const int* slot_of_seq, const int* block_table, int table_stride,
                             const double* inv_freq, int rot, int pairing, void* pool, int n_tokens,
                             int n_heads, int n_kv, int hd, int page_size, int write_cache,
-                            const float2* table, int table_len, cudaStream_t stream) {
+                            const float2* table, int table_len, int table_covers_step, cudaStream_t stream) {
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(rot >= 0 && rot <= hd && rot % 2 == 0, "rotary: %d rotated lanes of a head of %d", rot, hd);
     BLM_REQUIRE(rot == 0 || inv_freq != nullptr, "rotary: no frequencies");
@@ -180,6 +295,19 @@ BLM_API int blm_rope_append(void* qkv, int dtype, const int* token_seq, const in
     const dim3 grid((items + threads - 1) / threads, n_tokens);
     BLM_REQUIRE(grid.y <= 65535, "rotary: %d tokens in one step (at most 65535)", n_tokens);
     const size_t smem = 0;
+    if (dtype == BLM_BF16 && rot == hd && pairing == 0 && hd % 16 == 0 && table != nullptr && table_len > 0 &&
+        ((size_t)qkv & 15) == 0 && (!write_cache || ((size_t)pool & 15) == 0) && ((size_t)table & 15) == 0) {
+        // every position of the step must lie inside the table for this path; the host makes the table
+        // as long as the cache's longest sequence, and a step never goes beyond that
+        const int vitems = (n_heads + n_kv) * (hd / 16) + (write_cache ? n_kv * (hd / 8) : 0);
+        const dim3 vgrid((vitems + threads - 1) / threads, n_tokens);
+        if (table_covers_step) {
+            rope_append_bf16_vec_kernel<<<vgrid, threads, 0, stream>>>((__nv_bfloat16*)qkv, token_seq, token_pos, slot_of_seq,
+                                                                       block_table, table_stride, (__nv_bfloat16*)pool, n_heads,
+                                                                       n_kv, hd, page_size, write_cache, table);
+            return blm_check_launch("rope_append");
+        }
+    }
     if (dtype == BLM_F32)
         rope_append_kernel<float><<<grid, threads, smem, stream>>>((float*)qkv, token_seq, token_pos, slot_of_seq, block_table, table_stride, inv_freq, rot, pairing, (float*)pool, n_heads, n_kv, hd, page_size, write_cache, table, table_len);
     else if (dtype == BLM_BF16)
@@ -225,12 +353,42 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     }
 }
 
+// bf16, eight outputs per thread: 16-byte loads of the gates and of the ups, one 16-byte store
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int inner,
+                                     size_t total8, int tile) {
+    const int per_row = inner >> 3;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = idx / per_row;
+        const int i = (int)(idx % per_row) * 8;
+        const size_t gi = tile ? (size_t)(i / tile) * 2 * tile + i % tile : (size_t)i;
+        const size_t ui = tile ? gi + tile : (size_t)inner + i;
+        const uint4 gv = *reinterpret_cast<const uint4*>(gu + n * 2 * inner + gi);
+        const uint4 uv = *reinterpret_cast<const uint4*>(gu + n * 2 * inner + ui);
+        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uv);
+        uint4 ov;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 g = __bfloat1622float2(gp[e]), u = __bfloat1622float2(up[e]);
+            op[e] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+        }
+        *reinterpret_cast<uint4*>(out + n * inner + i) = ov;
+    }
+}
+
 BLM_API int blm_swiglu(const void* gu, void* out, int dtype, int n_rows, int inner, int tile, cudaStream_t stream) {
     if (n_rows == 0) return BLM_OK;
     BLM_REQUIRE(tile >= 0 && (tile == 0 || inner % tile == 0), "swiglu: tiles of %d do not divide %d", tile, inner);
     const size_t total = (size_t)n_rows * inner;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == BLM_BF16 && inner % 8 == 0 && (tile == 0 || tile % 8 == 0) && ((size_t)gu & 15) == 0 && ((size_t)out & 15) == 0) {
+        const size_t total8 = total / 8;
+        const int b8 = (int)((total8 + threads - 1) / threads < 148 * 16 ? (total8 + threads - 1) / threads : 148 * 16);
+        swiglu_bf16x8_kernel<<<b8, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inner, total8, tile);
+        return blm_check_launch("swiglu");
+    }
     if (dtype == BLM_F32)
         swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, inner, total, tile);
     else if (dtype == BLM_BF16)

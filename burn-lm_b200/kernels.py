@@ -53,7 +53,7 @@ _protos = {
         "blm_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                             c_float, c_void_p],
         "blm_rope_append": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                            c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+                            c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
         "blm_rope_table": [c_void_p, c_void_p, c_int, c_int, c_void_p],
         "blm_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "blm_convert": [c_void_p, c_int, c_void_p, c_int, c_size_t, c_void_p],
@@ -160,12 +160,13 @@ def rope_table(inv_freq, n_positions):
 
 
 def rope_append(qkv, token_seq, token_pos, slot_of_seq, block_table, inv_freq, rotary_dim, interleaved,
-                pool, n_heads, n_kv, head_dim, write_cache=True, table=None):
+                pool, n_heads, n_kv, head_dim, write_cache=True, table=None, max_position=None):
     """Rotate q (in place) and k of every token by its position, and append k, v to the paged cache.
 
     qkv [N, (n_heads + 2 n_kv) * head_dim]; pool [pages, 2, n_kv, PAGE, head_dim] of one cache line;
     inv_freq float64 [rotary_dim / 2] or None when rotary_dim == 0; `table` (from rope_table) spares
-    the per-token angles for positions it covers."""
+    the per-token angles for positions it covers.  `max_position`: an upper bound of the step's
+    positions known on the host; when the table covers it, the vector kernel may run."""
     _need_cuda(qkv, token_seq, token_pos, slot_of_seq, block_table, inv_freq, pool, table)
     if table is not None and (table.dtype != torch.float32 or tuple(table.shape[1:]) != (rotary_dim // 2, 2)):
         raise KernelError("rope_append: table must be float32 [positions, rotary_dim / 2, 2]")
@@ -181,7 +182,8 @@ def rope_append(qkv, token_seq, token_pos, slot_of_seq, block_table, inv_freq, r
     _call("elementwise", "blm_rope_append", _ptr(qkv), _code(qkv.dtype), _ptr(token_seq), _ptr(token_pos),
           _ptr(slot_of_seq), _ptr(block_table), block_table.shape[1], _ptr(inv_freq), rotary_dim,
           1 if interleaved else 0, _ptr(pool), n, n_heads, n_kv, head_dim, PAGE, 1 if write_cache else 0,
-          _ptr(table), table.shape[0] if table is not None else 0, _stream())
+          _ptr(table), table.shape[0] if table is not None else 0,
+          1 if (table is not None and max_position is not None and max_position < table.shape[0]) else 0, _stream())
 
 
 GATE_TILE = 8   # a fused [gate; up] weight for the skinny kernel: tiles of 8 gate rows, then their 8 up rows

@@ -103,7 +103,8 @@ class Attention(Part):
             qkv = self.q_only(x, out_dtype=rt.dtype)
             n_kv_in_row = 0
         K.rope_append(qkv, step.token_seq, step.token_pos, step.slot_of_seq, cache.block_table, inv_freq, rot,
-                      interleaved, cache.pool, s.n_heads, n_kv_in_row, s.head_dim, write_cache=cache.writes, table=table)
+                      interleaved, cache.pool, s.n_heads, n_kv_in_row, s.head_dim, write_cache=cache.writes, table=table,
+                      max_position=step.max_kv_len - 1)
         out = torch.empty((n, s.n_heads * s.head_dim), dtype=rt.dtype, device=qkv.device)
         n_splits = self._splits(step)
         scratch = None

@@ -192,7 +192,7 @@ def run_attention_case(dtype, H, KV, hd, lens_before, lens_new, window, n_splits
         scratch = torch.empty(k.attention_scratch_floats(n, H, hd, n_splits), device="cuda")
     k.attention(qkv, q_stride, st["pool"], st["table"], st["cu"], st["slots"], st["starts"], out, n, len(lens_new),
                 max(lens_new), H, KV, hd, scale, window=window, n_splits=n_splits, scratch=scratch)
-    if dtype == torch.bfloat16 and max(lens_new) == 1:
+    if dtype == torch.bfloat16 and (max(lens_new) == 1 or max(lens_new) >= 16):
         # whichever kernel took the step, the general one must say the same (up to bf16 rounding of the output)
         out_general = torch.empty_like(out)
         k.attention(qkv, q_stride, st["pool"], st["table"], st["cu"], st["slots"], st["starts"], out_general, n, len(lens_new),
@@ -403,6 +403,14 @@ def test_rope_table_equals_on_the_fly():
     k.rope_append(b, st["token_seq"], st["token_pos"], st["slots"], st["table"], inv_freq, hd, False, pool_b, H, KV, hd, table=table)
     assert torch.equal(a, b)
     assert torch.equal(torch.nan_to_num(st["pool"].float()), torch.nan_to_num(pool_b.float()))
+    # a table that covers the whole step: the vector kernel (same numbers up to the last bit of a product)
+    c, pool_c = qkv.clone(), torch.full_like(st["pool"], float("nan"))
+    full = k.rope_table(inv_freq, 256)
+    k.rope_append(c, st["token_seq"], st["token_pos"], st["slots"], st["table"], inv_freq, hd, False, pool_c, H, KV, hd,
+                  table=full, max_position=129)
+    torch.testing.assert_close(c.float(), a.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(torch.nan_to_num(pool_c.float()), torch.nan_to_num(st["pool"].float()), rtol=1e-2, atol=1e-2)
+    assert torch.equal(torch.isnan(pool_c.float()), torch.isnan(st["pool"].float()))
 
 
 def test_argmax_large_vocabulary():
@@ -415,3 +423,13 @@ def test_argmax_large_vocabulary():
     want = logits.argmax(-1)
     want[3] = 5000
     assert out.tolist() == want.tolist()
+
+
+@pytest.mark.parametrize("H,KV,hd", [(8, 2, 64), (4, 4, 128), (6, 1, 64)])
+def test_prompt_attention_on_tensor_cores(H, KV, hd):
+    """Prompts of head size 64 / 128 in bfloat16 take the tensor-core kernel: whole prompts of unequal
+    lengths, prompts that continue a cached prefix, and a window; each against the general kernel and
+    against the plain restatement (through run_attention_case)."""
+    run_attention_case(torch.bfloat16, H, KV, hd, [0, 0, 0, 0, 0], [16, 63, 64, 65, 333], 0, 1, seed=50)
+    run_attention_case(torch.bfloat16, H, KV, hd, [10, 100, 64, 700], [17, 40, 128, 70], 0, 1, seed=51)
+    run_attention_case(torch.bfloat16, H, KV, hd, [0, 130, 64], [200, 90, 31], 75, 1, seed=52)
