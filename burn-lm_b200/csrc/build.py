@@ -32,7 +32,7 @@ MODULES = {
     "gemv": ["gemv.cu"],
     "sampling": ["sampling.cu"],
 }
-HEADERS = ["common.cuh", "attention_decode.cuh", "attention_prefill.cuh"]
+HEADERS = ["common.cuh", "attention_decode.cuh", "attention_prefill.cuh", "sampling_no_alloc.h"]
 
 _lock = threading.Lock()
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -3,6 +3,7 @@
 // probabilities quantised to 2^-40, in integer arithmetic, so the result does not depend on the
 // order in which threads add things up.
 #include "common.cuh"
+#include "sampling_no_alloc.h"
 
 BLM_API const char* blm_sampling_last_error() { return g_blm_error; }
 
@@ -343,4 +344,41 @@ BLM_API int blm_sample(const float* logits, long long row_stride, int n_rows, in
     sample_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, row_stride, vocab, temperature, top_p, seeds,
                                                          stream_ids, counters, out);
     return blm_check_launch("sample");
+}
+
+// ---------------------------------------------------------------------------------------------
+// argmax for callers that must not allocate (see sampling_no_alloc.h; no counterpart in the reference)
+// ---------------------------------------------------------------------------------------------
+// The partial results of argmax_chunk_kernel: values first, then indices.  In host code this name is
+// only a stand-in for the array; the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) float g_argmax_no_alloc_scratch[2 * BLM_ARGMAX_NO_ALLOC_MAX_PARTIALS];
+
+constexpr int kNoAllocMaxDevices = 64;
+static float* g_argmax_no_alloc_ptr[kNoAllocMaxDevices] = {};   // per device, found at the first call there
+
+BLM_API int blm_argmax_no_alloc(const float* logits, long long row_stride, int n_rows, int vocab, int* out,
+                                cudaStream_t stream) {
+    if (n_rows == 0) return BLM_OK;
+    BLM_REQUIRE(n_rows > 0 && vocab > 0, "argmax_no_alloc: bad sizes");
+    const int chunks = (vocab + kArgmaxChunk - 1) / kArgmaxChunk;
+    BLM_REQUIRE((long long)n_rows * chunks <= BLM_ARGMAX_NO_ALLOC_MAX_PARTIALS,
+                "argmax_no_alloc: %d rows of %d logits need %lld partial results, the built-in scratch holds %d",
+                n_rows, vocab, (long long)n_rows * chunks, BLM_ARGMAX_NO_ALLOC_MAX_PARTIALS);
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "argmax_no_alloc: %s", cudaGetErrorString(e));
+    BLM_REQUIRE(device >= 0 && device < kNoAllocMaxDevices, "argmax_no_alloc: device %d", device);
+    if (g_argmax_no_alloc_ptr[device] == nullptr) {
+        // set-up, once per device, with that device current
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_argmax_no_alloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr)
+            return blm_fail(BLM_CUDA_ERROR, "argmax_no_alloc: no device address for the scratch array: %s", cudaGetErrorString(e));
+        g_argmax_no_alloc_ptr[device] = ptr;
+    }
+    float* part_val = g_argmax_no_alloc_ptr[device];
+    int* part_idx = reinterpret_cast<int*>(part_val + BLM_ARGMAX_NO_ALLOC_MAX_PARTIALS);
+    argmax_chunk_kernel<<<dim3(chunks, n_rows), 256, 0, stream>>>(logits, row_stride, vocab, part_val, part_idx);
+    argmax_merge_kernel<<<n_rows, 32, 0, stream>>>(part_val, part_idx, chunks, out);
+    return blm_check_launch("argmax_no_alloc");
 }
