@@ -22,7 +22,9 @@ def requests_for(cfg, seed, lengths):
 
 LENGTHS = {"tiny_a": [5, 11, 17, 64, 65, 128, 33, 100, 2, 97],
            "tiny_b": [1, 7, 30, 64, 200, 129, 256, 40],
-           "tiny_c": [300, 45, 640, 64, 129, 33]}
+           "tiny_c": [300, 45, 640, 64, 129, 33],
+           "tiny_d": [200, 16, 333, 64, 65, 40, 7],
+           "tiny_e": [129, 48, 260, 17, 64]}
 
 
 def check(got, want_by_id, tolerance, what):

@@ -34,7 +34,24 @@ TINY_C = {
     "hidden_act": "silu",
 }
 
-CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
+# head_dim 64 and 128: the sizes the tensor-core attention kernels and the skinny product are written for
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 128, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 320, "vocab_size": 515, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 256},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 1024, "hidden_act": "silu",
+}
+
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 3, "hidden_size": 256, "num_attention_heads": 4, "num_key_value_heads": 1,
+    "head_dim": 128, "intermediate_size": 384, "vocab_size": 640, "rope_theta": 10000.0, "rope_scaling": None,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 1024, "hidden_act": "silu",
+}
+
+CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D, "tiny_e": TINY_E}
 
 
 def make_folder(tmp_path, name, seed=0, dtype="float32"):
