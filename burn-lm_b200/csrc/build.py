@@ -30,6 +30,7 @@ MODULES = {
     "attention": ["attention.cu"],
     "gemm": ["gemm_f32.cu"],
     "gemv": ["gemv.cu"],
+    "gemm_tc": ["gemm_tc.cu"],
     "sampling": ["sampling.cu"],
 }
 HEADERS = ["common.cuh", "attention_decode.cuh", "attention_prefill.cuh", "sampling_no_alloc.h"]

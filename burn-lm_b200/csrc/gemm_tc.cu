@@ -1,0 +1,320 @@
+// Matrix product for prompts on the 5th-generation tensor cores: y[M, N] = x[M, K] . W[N, K]^T, bf16
+// operands, fp32 accumulation in tensor memory, with the gated activation fused into the epilogue.
+//
+// One block computes a 128 x 256 tile of y.  Warp 0 (one thread) is the producer: TMA tile loads
+// (cp.async.bulk.tensor.2d, 128-byte swizzle) of 128 x 64 of x and 256 x 64 of W per stage into a
+// ring of four stages, completion on mbarriers.  Warp 1 allocates 256 columns of tensor memory and
+// (one thread) issues tcgen05.mma.cta_group::1.kind::f16 (M 128, N 256, K 16) four times per stage
+// from shared-memory descriptors, and tcgen05.commit frees the stage when the tensor core has read it.
+// Warps 2..5 are the epilogue: when the last commit lands they read the accumulator with tcgen05.ld
+// (a warp reads the 32 lanes of its quarter, 16 columns at a time), and store bf16; for a fused
+// [gate; up] weight laid out in tiles of 8 gate rows followed by their 8 up rows, 16 columns are
+// exactly 8 gates and their 8 ups, so silu(gate) * up is formed in registers and the [M, 2 I]
+// intermediate never exists.  Edges: the TMA fills what lies outside x or W with zeros, the epilogue
+// stores only what lies inside y.
+//
+// Every mbarrier wait is bounded; a wait that runs out records a code in the caller's status word and
+// the block goes on to its end, where the tensor memory is given back.
+#include <cuda.h>
+
+#include <map>
+#include <tuple>
+
+#include "common.cuh"
+
+BLM_API const char* blm_gemm_tc_last_error() { return g_blm_error; }
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;      // block tile; BK bf16 = 128 bytes = one swizzle row
+constexpr int kStages = 4;
+constexpr int kThreads = 192;                   // producer warp, mma warp, 4 epilogue warps
+constexpr int kTmemCols = 256;                  // fp32 accumulator: one column per output column
+constexpr unsigned kABytes = BM * BK * 2, kBBytes = BN * BK * 2;
+constexpr unsigned kSpinLimit = 1u << 22;
+
+enum { EPI_STORE = 0, EPI_SWIGLU = 1 };
+enum { TC_OK = 0, TC_TIMEOUT_FULL = 11, TC_TIMEOUT_EMPTY = 12, TC_TIMEOUT_ACCUM = 13 };
+
+struct TcArgs {
+    __nv_bfloat16* y;
+    long long ldy;
+    int M, N, K;        // N: rows of W
+    int epi;
+    int* status;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    const unsigned addr = smem_u32(bar);
+    for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+        unsigned done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+// shared-memory operand descriptor: K-major tile of rows of 128 bytes, 128-byte swizzle; 8-row groups
+// 1024 bytes apart
+__device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_u32(tile) >> 4) & 0x3fff);      // start address
+    d |= (unsigned long long)1 << 16;                               // leading byte offset (unused with a swizzle)
+    d |= (unsigned long long)(1024 >> 4) << 32;                     // stride byte offset
+    d |= (unsigned long long)1 << 46;                               // descriptor version of this architecture
+    d |= (unsigned long long)2 << 61;                               // 128-byte swizzle
+    return d;
+}
+// instruction descriptor of kind::f16: fp32 accumulator, bf16 x bf16, both K-major, M 128, N 256
+constexpr unsigned kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc, unsigned accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
+    unsigned r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap xmap,
+                                                              const __grid_constant__ CUtensorMap wmap) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned char* As = smem;                                  // [kStages][BM][128 bytes]
+    unsigned char* Bs = smem + kStages * kABytes;              // [kStages][BN][128 bytes]
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(Bs + kStages * kBBytes);
+    unsigned long long* empty = full + kStages;
+    unsigned long long* accum = empty + kStages;
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(accum + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int k_iters = (a.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        // tensor memory for the accumulator: the whole warp asks, the address lands in shared memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- producer ----------------
+            for (int it = 0; it < k_iters; ++it) {
+                const int s = it % kStages;
+                if (it >= kStages && !mbar_wait(empty + s, ((it / kStages) - 1) & 1)) {
+                    atomicCAS(a.status, TC_OK, TC_TIMEOUT_EMPTY);
+                    break;
+                }
+                mbar_expect_tx(full + s, kABytes + kBBytes);
+                tma_load_2d(As + s * kABytes, &xmap, it * BK, m0, full + s);
+                tma_load_2d(Bs + s * kBBytes, &wmap, it * BK, n0, full + s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---------------- tensor core ----------------
+            bool ok = true;
+            for (int it = 0; it < k_iters && ok; ++it) {
+                const int s = it % kStages;
+                if (!mbar_wait(full + s, (it / kStages) & 1)) {
+                    atomicCAS(a.status, TC_OK, TC_TIMEOUT_FULL);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned long long ad = umma_desc(As + s * kABytes), bd = umma_desc(Bs + s * kBBytes);
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; ++kk)      // 16 bf16 = 32 bytes further along the swizzled row: +2 in the address field
+                    umma(tmem_base, ad + 2 * kk, bd + 2 * kk, (it > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(empty + s);                   // the stage is free when these products have read it
+            }
+            umma_commit(accum);                           // the accumulator is complete when everything issued is done
+        }
+    } else {
+        // ---------------- epilogue: warp w reads lanes 32 (w % 4) .. of the accumulator ----------------
+        const int quarter = warp & 3;
+        const int row = m0 + quarter * 32 + lane;
+        if (mbar_wait(accum, 0)) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16);
+            if (a.epi == EPI_SWIGLU) {
+                // columns 16 j .. 16 j + 7 are gates, 16 j + 8 .. 16 j + 15 their ups: outputs (n0 / 2) + 8 j ..
+                const int inner = a.N >> 1;
+#pragma unroll 1
+                for (int j = 0; j < BN / 16; ++j) {
+                    float v[16];
+                    tmem_ld16(taddr + j * 16, v);
+                    const int o0 = (n0 >> 1) + j * 8;
+                    if (row < a.M && o0 < inner) {
+                        unsigned packed[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float g0 = v[2 * e], g1 = v[2 * e + 1], u0 = v[8 + 2 * e], u1 = v[8 + 2 * e + 1];
+                            const __nv_bfloat162 p = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+                            packed[e] = *reinterpret_cast<const unsigned*>(&p);
+                        }
+                        __nv_bfloat16* dst = a.y + (size_t)row * a.ldy + o0;
+                        if (o0 + 8 <= inner && ((a.ldy & 7) == 0)) {
+                            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        } else {
+                            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(packed);
+                            for (int e = 0; e < 8 && o0 + e < inner; ++e) dst[e] = src[e];
+                        }
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int j = 0; j < BN / 16; ++j) {
+                    float v[16];
+                    tmem_ld16(taddr + j * 16, v);
+                    const int c0 = n0 + j * 16;
+                    if (row < a.M && c0 < a.N) {
+                        unsigned packed[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const __nv_bfloat162 p = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                            packed[e] = *reinterpret_cast<const unsigned*>(&p);
+                        }
+                        __nv_bfloat16* dst = a.y + (size_t)row * a.ldy + c0;
+                        if (c0 + 16 <= a.N && ((a.ldy & 7) == 0)) {
+                            reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        } else {
+                            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(packed);
+                            for (int e = 0; e < 16 && c0 + e < a.N; ++e) dst[e] = src[e];
+                        }
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            atomicCAS(a.status, TC_OK, TC_TIMEOUT_ACCUM);
+        }
+    }
+    // everybody meets; then the warp that took the tensor memory gives it back
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols));
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The TMA's view of a K-major bf16 matrix [rows, K] (row stride ld): boxes of box_rows x 64, 128-byte swizzle.
+int make_map(const void* base, long long ld, int rows, int K, int box_rows, bool cache, CUtensorMap* out) {
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+            return blm_fail(BLM_CUDA_ERROR, "gemm_tc: the driver has no cuTensorMapEncodeTiled");
+        encode = (EncodeTiledFn)fn;
+    }
+    static std::map<std::tuple<const void*, long long, int, int, int>, CUtensorMap> maps;
+    const auto key = std::make_tuple(base, ld, rows, K, box_rows);
+    if (cache) {
+        auto it = maps.find(key);
+        if (it != maps.end()) {
+            *out = it->second;
+            return BLM_OK;
+        }
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return blm_fail(BLM_CUDA_ERROR, "gemm_tc: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    if (cache) {
+        if (maps.size() > 4096) maps.clear();
+        maps.emplace(key, *out);
+    }
+    return BLM_OK;
+}
+
+}  // namespace
+
+// 1 when blm_gemm_tc takes the shape
+BLM_API int blm_gemm_tc_supported(int M, int N, int K) { return M >= 1 && N >= 16 && K >= 64 && K % 8 == 0; }
+
+// y[M, N] = x[M, K] . w[N, K]^T (epi 0), or y[M, N / 2] = silu(gate) * up for a weight in tiles of 8 gate rows
+// followed by their 8 up rows (epi 1).  x, w, y bfloat16; ldx, ldw, ldy in elements.
+BLM_API int blm_gemm_tc(const void* x, long long ldx, const void* w, long long ldw, void* y, long long ldy, int M, int N, int K,
+                        int epi, int* status, cudaStream_t stream) {
+    if (M == 0 || N == 0) return BLM_OK;
+    BLM_REQUIRE(blm_gemm_tc_supported(M, N, K), "gemm_tc: shape %d x %d x %d (K a multiple of 8, at least 64)", M, N, K);
+    BLM_REQUIRE(ldx % 8 == 0 && ldw % 8 == 0 && ((size_t)x & 15) == 0 && ((size_t)w & 15) == 0,
+                "gemm_tc: operand rows must be 16-byte aligned");
+    BLM_REQUIRE(epi == EPI_STORE || (epi == EPI_SWIGLU && N % 16 == 0), "gemm_tc: epilogue %d with %d weight rows", epi, N);
+    BLM_REQUIRE(status != nullptr, "gemm_tc: no status word");
+    CUtensorMap xmap, wmap;
+    int rc = make_map(x, ldx, M, K, BM, false, &xmap);
+    if (rc != BLM_OK) return rc;
+    rc = make_map(w, ldw, N, K, BN, true, &wmap);
+    if (rc != BLM_OK) return rc;
+    TcArgs a;
+    a.y = (__nv_bfloat16*)y; a.ldy = ldy; a.M = M; a.N = N; a.K = K; a.epi = epi; a.status = status;
+    const size_t smem = (size_t)kStages * (kABytes + kBBytes) + (2 * kStages + 1) * 8 + 16 + 1024;
+    static bool opted_in = false;
+    if (!opted_in) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
+        opted_in = true;
+    }
+    const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    BLM_REQUIRE(grid.y <= 65535, "gemm_tc: too many rows (%d)", M);
+    gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(a, xmap, wmap);
+    return blm_check_launch("gemm_tc");
+}

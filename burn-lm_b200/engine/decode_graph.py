@@ -59,6 +59,7 @@ class DecodeGraph:
         self.logits = None
         self._graph = None          # forward only
         self._loop_graph = None     # forward + argmax + advance
+        self._greedy_graph = None   # forward + argmax
         self._loop_history_steps = 0
         self._copied = None
         self.launches_per_step = 0
@@ -72,12 +73,9 @@ class DecodeGraph:
 
     def load(self, tokens, positions, slots) -> None:
         """Bring a step's inputs from (pinned) host memory to the graph's buffers."""
-        b = self.batch
         if self._copied is not None:
             self._copied.synchronize()       # the last copy has left the pinned buffer
-        self.host_meta[:b] = torch.tensor(tokens, dtype=torch.int32)
-        self.host_meta[b:2 * b] = torch.tensor(positions, dtype=torch.int32)
-        self.host_meta[2 * b:] = torch.tensor(slots, dtype=torch.int32)
+        self.host_meta.copy_(torch.tensor([*tokens, *positions, *slots], dtype=torch.int32))
         self.meta.copy_(self.host_meta, non_blocking=True)
         self._copied = torch.cuda.Event()
         self._copied.record()
@@ -99,6 +97,20 @@ class DecodeGraph:
             return self.logits
         self._graph.replay()
         return self._captured_logits
+
+    def step_greedy(self) -> torch.Tensor:
+        """One decode step on the loaded inputs with the argmax inside the captured graph; the
+        sampled tokens, int32 [B], in a buffer that the next step overwrites."""
+        if self._greedy_graph is None:
+            K.argmax(self._forward(), self.sampled)  # the first step runs plainly and warms everything up
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with _capturing(g):
+                K.argmax(self._forward(), self.sampled)
+            self._greedy_graph = g
+            return self.sampled
+        self._greedy_graph.replay()
+        return self.sampled
 
     def run(self, n_steps: int, keep_history: bool = True) -> torch.Tensor:
         """n_steps greedy decode steps without the host in between, starting from the loaded inputs.

@@ -116,6 +116,31 @@ class Engine:
             self.cache.set_length(s, st + n_steps)
         return history
 
+    def decode_greedy(self, slots, tokens) -> Optional[list]:
+        """One greedy decode step for the sequences in `slots`, each fed its token: the argmax runs in
+        the captured graph and the sampled ids come back as a list.  The short way through a step for
+        the generation loop; None when this engine does not capture its decode steps."""
+        if not self.use_graphs:
+            return None
+        cache = self.cache
+        starts = []
+        grow = None
+        for s, t in zip(slots, tokens):
+            if not 0 <= t < self.vocab_size:
+                raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
+            n = cache.seq_len[s]
+            starts.append(n)
+            if n % 64 == 0 or n >= cache.max_seq_len:       # a new page, or the limit: the careful path decides
+                grow = True
+        if grow or len(set(slots)) != len(slots):
+            cache.reserve([(s, n + 1) for s, n in zip(slots, starts)])
+        g = self.decode_graph(len(slots), max(starts) + 1)
+        g.load(tokens, starts, slots)
+        out = g.step_greedy().tolist()
+        for s, n in zip(slots, starts):
+            cache.seq_len[s] = n + 1
+        return out
+
     # -- the step ------------------------------------------------------------------------------------
     def _pack(self, entries):
         """Validate the entries and lay their metadata out in one int32 array (host)."""

@@ -134,6 +134,7 @@ class GenerationLoop:
         engine = self.engine
         max_len = engine.cache.max_seq_len
         slots = {i: engine.acquire() for i in batch}
+        fused = getattr(engine, "decode_greedy", None)
         # a request's draws are numbered from 0 in a stream of its own: (seed, request index)
         live = list(batch)
         try:
@@ -170,9 +171,13 @@ class GenerationLoop:
                 live = nxt
                 if not live:
                     break
-                entries = [StepEntry(slots[i], [results[i].tokens[-1]], [0]) for i in live]
-                logits = engine.step(entries)
-                tokens = self.sampler.sample(logits, params, live, [len(results[i].tokens) for i in live])
+                tokens = None
+                if params.greedy and fused is not None:      # the engine samples inside its captured step
+                    tokens = fused([slots[i] for i in live], [results[i].tokens[-1] for i in live])
+                if tokens is None:
+                    entries = [StepEntry(slots[i], [results[i].tokens[-1]], [0]) for i in live]
+                    logits = engine.step(entries)
+                    tokens = self.sampler.sample(logits, params, live, [len(results[i].tokens) for i in live])
                 stats.decode_steps += 1
             stats.decode_seconds += time.perf_counter() - t0
             verify = getattr(engine, "verify", None)

@@ -73,6 +73,11 @@ _protos = {
                      c_float, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p],
         "blm_gemv_supported": [c_int, c_int, c_int],
     },
+    "gemm_tc": {
+        "blm_gemm_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                        c_void_p, c_void_p],
+        "blm_gemm_tc_supported": [c_int, c_int, c_int],
+    },
     "sampling": {
         "blm_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "blm_argmax_scratch_floats": [c_int, c_int],
@@ -276,6 +281,25 @@ def gemv_supported(n_tokens, m, k) -> bool:
     return bool(_lib("gemv").blm_gemv_supported(n_tokens, m, k))
 
 
+def gemm_tc_supported(m, n, k) -> bool:
+    return bool(_lib("gemm_tc").blm_gemm_tc_supported(m, n, k))
+
+
+def gemm_tc(x, w, out, swiglu=False):
+    """x [M, K] times w [N, K] transposed on the tcgen05 tensor cores (bfloat16, fp32 accumulation in
+    tensor memory).  out [M, N]; with `swiglu`, w is a fused gate/up weight in tiles of GATE_TILE gate
+    rows followed by their up rows and out [M, N / 2] = silu(gate) * up, formed in the epilogue."""
+    _need_cuda(x, w, out)
+    m, k = x.shape
+    n = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or w.shape[1] != k:
+        raise KernelError("gemm_tc: bfloat16 x [M, K], w [N, K], out")
+    if tuple(out.shape) != (m, n // 2 if swiglu else n):
+        raise KernelError("gemm_tc: out must be [M, N] (or [M, N / 2] with the gated epilogue)")
+    _call("gemm_tc", "blm_gemm_tc", _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), m, n, k,
+          1 if swiglu else 0, _ptr(status_word(x.device)), _stream())
+
+
 _status: dict = {}
 
 
@@ -295,8 +319,10 @@ def check_status(device) -> None:
     code = int(w.item())
     if code:
         w.zero_()
-        what = {1: "a consumer waited in vain for a weight stage", 2: "the producer waited in vain for a free stage"}
-        raise KernelError(f"gemv: {what.get(code, 'status ' + str(code))}; the step's results are not valid")
+        what = {1: "gemv: a consumer waited in vain for a weight stage", 2: "gemv: the producer waited in vain for a free stage",
+                11: "gemm_tc: the tensor-core thread waited in vain for a stage", 12: "gemm_tc: the producer waited in vain for a free stage",
+                13: "gemm_tc: the epilogue waited in vain for the accumulator"}
+        raise KernelError(f"{what.get(code, 'status ' + str(code))}; the step's results are not valid")
 
 
 def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, out=None, add_into=None, swiglu=False):

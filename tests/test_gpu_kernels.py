@@ -433,3 +433,32 @@ def test_prompt_attention_on_tensor_cores(H, KV, hd):
     run_attention_case(torch.bfloat16, H, KV, hd, [0, 0, 0, 0, 0], [16, 63, 64, 65, 333], 0, 1, seed=50)
     run_attention_case(torch.bfloat16, H, KV, hd, [10, 100, 64, 700], [17, 40, 128, 70], 0, 1, seed=51)
     run_attention_case(torch.bfloat16, H, KV, hd, [0, 130, 64], [200, 90, 31], 75, 1, seed=52)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (300, 520, 200), (77, 48, 1000), (2048, 3072, 2048), (513, 2048, 8192)])
+def test_gemm_tc_store(m, n, k):
+    """The tcgen05 product against fp64: exact bf16 products summed in fp32, rounded once to bf16."""
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+    K().gemm_tc(x, w, out)
+    K().check_status("cuda")
+    want = x.double() @ w.double().T
+    assert not torch.isnan(out.float()).any()
+    assert (out.double() - want).abs().max().item() < 5e-3 * want.abs().max().item()
+
+
+@pytest.mark.parametrize("m,inner,k", [(128, 128, 64), (333, 520, 192), (2048, 8192, 2048)])
+def test_gemm_tc_gated(m, inner, k):
+    g = torch.Generator(device="cuda").manual_seed(m + inner)
+    x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    wgu = (torch.randn(2 * inner, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)         # [gate; up]
+    tiled = torch.stack([wgu[:inner].view(inner // 8, 8, k), wgu[inner:].view(inner // 8, 8, k)], dim=1).reshape(2 * inner, k).contiguous()
+    out = torch.full((m, inner), float("nan"), device="cuda", dtype=torch.bfloat16)
+    K().gemm_tc(x, tiled, out, swiglu=True)
+    K().check_status("cuda")
+    gu = x.double() @ wgu.double().T
+    want = gu[:, :inner] / (1 + torch.exp(-gu[:, :inner])) * gu[:, inner:]
+    assert not torch.isnan(out.float()).any()
+    assert (out.double() - want).abs().max().item() < 1e-2 * want.abs().max().item()
