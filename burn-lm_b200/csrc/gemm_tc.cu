@@ -1,13 +1,14 @@
 // Matrix product for prompts on the 5th-generation tensor cores: y[M, N] = x[M, K] . W[N, K]^T, bf16
 // operands, fp32 accumulation in tensor memory, with the gated activation fused into the epilogue.
 //
-// One block computes a 128 x 256 tile of y.  Warp 0 (one thread) is the producer: TMA tile loads
-// (cp.async.bulk.tensor.2d, 128-byte swizzle) of 128 x 64 of x and 256 x 64 of W per stage into a
-// ring of four stages, completion on mbarriers.  Warp 1 allocates 256 columns of tensor memory and
-// (one thread) issues tcgen05.mma.cta_group::1.kind::f16 (M 128, N 256, K 16) four times per stage
-// from shared-memory descriptors, and tcgen05.commit frees the stage when the tensor core has read it.
-// Warps 2..5 are the epilogue: when the last commit lands they read the accumulator with tcgen05.ld
-// (a warp reads the 32 lanes of its quarter, 16 columns at a time), and store bf16; for a fused
+// Persistent blocks, one per SM, walk 128 x 256 tiles of y.  Warp 0 (one thread) is the producer: TMA
+// tile loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of 128 x 64 of x and 256 x 64 of W per stage
+// into a ring of four stages, completion on mbarriers.  Warp 1 allocates all 512 columns of tensor
+// memory (two accumulators) and (one thread) issues tcgen05.mma.cta_group::1.kind::f16 (M 128, N 256,
+// K 16) four times per stage from shared-memory descriptors; tcgen05.commit frees the stage when the
+// tensor core has read it.  Warps 2..5 are the epilogue: when a tile's last commit lands they read its
+// accumulator with tcgen05.ld (a warp reads the 32 lanes of its quarter, 16 columns at a time) and
+// store bf16, while the tensor core already fills the other accumulator with the next tile; for a fused
 // [gate; up] weight laid out in tiles of 8 gate rows followed by their 8 up rows, 16 columns are
 // exactly 8 gates and their 8 ups, so silu(gate) * up is formed in registers and the [M, 2 I]
 // intermediate never exists.  Edges: the TMA fills what lies outside x or W with zeros, the epilogue
@@ -29,12 +30,12 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 64;      // block tile; BK bf16 = 128 bytes = one swizzle row
 constexpr int kStages = 4;
 constexpr int kThreads = 192;                   // producer warp, mma warp, 4 epilogue warps
-constexpr int kTmemCols = 256;                  // fp32 accumulator: one column per output column
+constexpr int kTmemCols = 512;                  // two fp32 accumulators of 256 columns: one per output column
 constexpr unsigned kABytes = BM * BK * 2, kBBytes = BN * BK * 2;
 constexpr unsigned kSpinLimit = 1u << 22;
 
 enum { EPI_STORE = 0, EPI_SWIGLU = 1 };
-enum { TC_OK = 0, TC_TIMEOUT_FULL = 11, TC_TIMEOUT_EMPTY = 12, TC_TIMEOUT_ACCUM = 13 };
+enum { TC_OK = 0, TC_TIMEOUT_FULL = 11, TC_TIMEOUT_EMPTY = 12, TC_TIMEOUT_ACCUM = 13, TC_TIMEOUT_DRAIN = 14 };
 
 struct TcArgs {
     __nv_bfloat16* y;
@@ -47,6 +48,9 @@ struct TcArgs {
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
@@ -109,6 +113,46 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Stores 16 accumulator columns of one row: plain (16 outputs) or gated (8 gates and their 8 ups -> 8 outputs).
+__device__ __forceinline__ void store_columns(const TcArgs& a, const float (&v)[16], int row, int n0, int j) {
+    if (row >= a.M) return;
+    if (a.epi == EPI_SWIGLU) {
+        const int inner = a.N >> 1, o0 = (n0 >> 1) + j * 8;
+        if (o0 >= inner) return;
+        unsigned packed[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float g0 = v[2 * e], g1 = v[2 * e + 1], u0 = v[8 + 2 * e], u1 = v[8 + 2 * e + 1];
+            const __nv_bfloat162 p = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+            packed[e] = *reinterpret_cast<const unsigned*>(&p);
+        }
+        __nv_bfloat16* dst = a.y + (size_t)row * a.ldy + o0;
+        if (o0 + 8 <= inner && ((a.ldy & 7) == 0)) {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        } else {
+            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(packed);
+            for (int e = 0; e < 8 && o0 + e < inner; ++e) dst[e] = src[e];
+        }
+    } else {
+        const int c0 = n0 + j * 16;
+        if (c0 >= a.N) return;
+        unsigned packed[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const __nv_bfloat162 p = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+            packed[e] = *reinterpret_cast<const unsigned*>(&p);
+        }
+        __nv_bfloat16* dst = a.y + (size_t)row * a.ldy + c0;
+        if (c0 + 16 <= a.N && ((a.ldy & 7) == 0)) {
+            reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(packed);
+            for (int e = 0; e < 16 && c0 + e < a.N; ++e) dst[e] = src[e];
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap xmap,
                                                               const __grid_constant__ CUtensorMap wmap) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -117,23 +161,29 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs a, co
     unsigned char* Bs = smem + kStages * kABytes;              // [kStages][BN][128 bytes]
     unsigned long long* full = reinterpret_cast<unsigned long long*>(Bs + kStages * kBBytes);
     unsigned long long* empty = full + kStages;
-    unsigned long long* accum = empty + kStages;
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(accum + 1);
+    unsigned long long* acc_full = empty + kStages;            // [2] the tensor core has finished an accumulator
+    unsigned long long* acc_empty = acc_full + 2;              // [2] the epilogue has read it
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int m_tiles = (a.M + BM - 1) / BM, n_tiles = (a.N + BN - 1) / BN;
+    const int tiles = m_tiles * n_tiles;
     const int k_iters = (a.K + BK - 1) / BK;
+    // tile t: rows (t % m_tiles), columns (t / m_tiles): the blocks that run together share W tiles in L2
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(full + s, 1);
             mbar_init(empty + s, 1);
         }
-        mbar_init(accum, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full + b, 1);
+            mbar_init(acc_empty + b, 4);       // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
-        // tensor memory for the accumulator: the whole warp asks, the address lands in shared memory
+        // tensor memory for the accumulators: the whole warp asks, the address lands in shared memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
@@ -145,95 +195,78 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs a, co
     if (warp == 0) {
         if (lane == 0) {
             // ---------------- producer ----------------
-            for (int it = 0; it < k_iters; ++it) {
-                const int s = it % kStages;
-                if (it >= kStages && !mbar_wait(empty + s, ((it / kStages) - 1) & 1)) {
-                    atomicCAS(a.status, TC_OK, TC_TIMEOUT_EMPTY);
-                    break;
+            unsigned it = 0;        // stages issued so far, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+                for (int k = 0; k < k_iters; ++k, ++it) {
+                    const int s = it % kStages;
+                    if (it >= (unsigned)kStages && !mbar_wait(empty + s, ((it / kStages) - 1) & 1)) {
+                        atomicCAS(a.status, TC_OK, TC_TIMEOUT_EMPTY);
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(full + s, kABytes + kBBytes);
+                    tma_load_2d(As + s * kABytes, &xmap, k * BK, m0, full + s);
+                    tma_load_2d(Bs + s * kBBytes, &wmap, k * BK, n0, full + s);
                 }
-                mbar_expect_tx(full + s, kABytes + kBBytes);
-                tma_load_2d(As + s * kABytes, &xmap, it * BK, m0, full + s);
-                tma_load_2d(Bs + s * kBBytes, &wmap, it * BK, n0, full + s);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // ---------------- tensor core ----------------
+            unsigned it = 0;
+            int n_tile = 0;
             bool ok = true;
-            for (int it = 0; it < k_iters && ok; ++it) {
-                const int s = it % kStages;
-                if (!mbar_wait(full + s, (it / kStages) & 1)) {
-                    atomicCAS(a.status, TC_OK, TC_TIMEOUT_FULL);
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++n_tile) {
+                const int b = n_tile & 1;
+                if (n_tile >= 2 && !mbar_wait(acc_empty + b, ((n_tile >> 1) - 1) & 1)) {      // the epilogue has read this accumulator
+                    atomicCAS(a.status, TC_OK, TC_TIMEOUT_DRAIN);
                     ok = false;
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const unsigned long long ad = umma_desc(As + s * kABytes), bd = umma_desc(Bs + s * kBBytes);
+                const unsigned tmem_d = tmem_base + (unsigned)(b * BN);
+                for (int k = 0; k < k_iters; ++k, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(full + s, (it / kStages) & 1)) {
+                        atomicCAS(a.status, TC_OK, TC_TIMEOUT_FULL);
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const unsigned long long ad = umma_desc(As + s * kABytes), bd = umma_desc(Bs + s * kBBytes);
 #pragma unroll
-                for (int kk = 0; kk < BK / 16; ++kk)      // 16 bf16 = 32 bytes further along the swizzled row: +2 in the address field
-                    umma(tmem_base, ad + 2 * kk, bd + 2 * kk, (it > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(empty + s);                   // the stage is free when these products have read it
+                    for (int kk = 0; kk < BK / 16; ++kk)      // 16 bf16 = 32 bytes further along the swizzled row: +2 in the address field
+                        umma(tmem_d, ad + 2 * kk, bd + 2 * kk, (k > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(empty + s);                   // the stage is free when these products have read it
+                }
+                umma_commit(acc_full + b);                    // the accumulator is complete when everything issued is done
             }
-            umma_commit(accum);                           // the accumulator is complete when everything issued is done
         }
     } else {
-        // ---------------- epilogue: warp w reads lanes 32 (w % 4) .. of the accumulator ----------------
+        // ---------------- epilogue: warp w reads lanes 32 (w % 4) .. of the accumulators ----------------
         const int quarter = warp & 3;
-        const int row = m0 + quarter * 32 + lane;
-        if (mbar_wait(accum, 0)) {
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16);
-            if (a.epi == EPI_SWIGLU) {
-                // columns 16 j .. 16 j + 7 are gates, 16 j + 8 .. 16 j + 15 their ups: outputs (n0 / 2) + 8 j ..
-                const int inner = a.N >> 1;
-#pragma unroll 1
-                for (int j = 0; j < BN / 16; ++j) {
-                    float v[16];
-                    tmem_ld16(taddr + j * 16, v);
-                    const int o0 = (n0 >> 1) + j * 8;
-                    if (row < a.M && o0 < inner) {
-                        unsigned packed[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float g0 = v[2 * e], g1 = v[2 * e + 1], u0 = v[8 + 2 * e], u1 = v[8 + 2 * e + 1];
-                            const __nv_bfloat162 p = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
-                            packed[e] = *reinterpret_cast<const unsigned*>(&p);
-                        }
-                        __nv_bfloat16* dst = a.y + (size_t)row * a.ldy + o0;
-                        if (o0 + 8 <= inner && ((a.ldy & 7) == 0)) {
-                            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        } else {
-                            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(packed);
-                            for (int e = 0; e < 8 && o0 + e < inner; ++e) dst[e] = src[e];
-                        }
-                    }
-                }
-            } else {
-#pragma unroll 1
-                for (int j = 0; j < BN / 16; ++j) {
-                    float v[16];
-                    tmem_ld16(taddr + j * 16, v);
-                    const int c0 = n0 + j * 16;
-                    if (row < a.M && c0 < a.N) {
-                        unsigned packed[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const __nv_bfloat162 p = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-                            packed[e] = *reinterpret_cast<const unsigned*>(&p);
-                        }
-                        __nv_bfloat16* dst = a.y + (size_t)row * a.ldy + c0;
-                        if (c0 + 16 <= a.N && ((a.ldy & 7) == 0)) {
-                            reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                            reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                        } else {
-                            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(packed);
-                            for (int e = 0; e < 16 && c0 + e < a.N; ++e) dst[e] = src[e];
-                        }
-                    }
-                }
+        int n_tile = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++n_tile) {
+            const int b = n_tile & 1;
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+            if (!mbar_wait(acc_full + b, (n_tile >> 1) & 1)) {
+                if (lane == 0) atomicCAS(a.status, TC_OK, TC_TIMEOUT_ACCUM);
+                break;
             }
-        } else if (lane == 0) {
-            atomicCAS(a.status, TC_OK, TC_TIMEOUT_ACCUM);
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(b * BN);
+            const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int j = 0; j < BN / 16; ++j) {
+                float v[16];
+                tmem_ld16(taddr + j * 16, v);
+                store_columns(a, v, row, n0, j);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + b);        // this warp has read its quarter
         }
     }
     // everybody meets; then the warp that took the tensor memory gives it back
@@ -306,15 +339,15 @@ BLM_API int blm_gemm_tc(const void* x, long long ldx, const void* w, long long l
     if (rc != BLM_OK) return rc;
     TcArgs a;
     a.y = (__nv_bfloat16*)y; a.ldy = ldy; a.M = M; a.N = N; a.K = K; a.epi = epi; a.status = status;
-    const size_t smem = (size_t)kStages * (kABytes + kBBytes) + (2 * kStages + 1) * 8 + 16 + 1024;
+    const size_t smem = (size_t)kStages * (kABytes + kBBytes) + (2 * kStages + 4) * 8 + 16 + 1024;
     static bool opted_in = false;
     if (!opted_in) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
         opted_in = true;
     }
-    const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    BLM_REQUIRE(grid.y <= 65535, "gemm_tc: too many rows (%d)", M);
+    const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    const int grid = (int)(tiles < 148 ? tiles : 148);        // persistent: one block per SM
     gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(a, xmap, wmap);
     return blm_check_launch("gemm_tc");
 }

@@ -3,9 +3,10 @@ number of tokens.
 
 bfloat16 weights: steps of up to 16 tokens run this package's skinny kernel (weights streamed once,
 tensor-core accumulation in fp32), which can also take the RMS norm in front of it and the gated
-activation or the residual add behind it; larger steps go through the library product (cuBLAS via
-torch.mm), as the reference's engine uses its library's `Linear`
-(crates/burn-lm-llama/src/nn/attention/mha.rs:124-126).  float32 weights go through this package's
+activation or the residual add behind it; for prompts the gated gate/up product runs this package's
+tcgen05 kernel (accumulator in tensor memory, activation in the epilogue) and the plain products go
+through the library product (cuBLAS via torch.mm), as the reference's engine uses its library's
+`Linear` (crates/burn-lm-llama/src/nn/attention/mha.rs:124-126).  float32 weights go through this package's
 own fp32 kernel, which has no reduced-precision mode: that is the 32-bit path, and also what a
 layer stored in 32-bit inside a bfloat16 model gets.
 """
@@ -20,6 +21,7 @@ from .. import kernels as K
 
 SKINNY_TOKENS = 16        # the skinny kernel takes up to this many tokens
 FUSED_NORM_TOKENS = 16    # ... and normalises them in its prologue (every block redoes it)
+TENSOR_CORE_TOKENS = 128  # from this many tokens the gated product runs this package's tcgen05 kernel
 
 
 @dataclass
@@ -102,6 +104,14 @@ class Linear:
         if out_dtype == torch.bfloat16 and self.gate_tile == K.GATE_TILE and self._skinny(n, inner):
             K.gemv(self.weight, n, out=act, swiglu=True, **self._source(x))
             return act
+        if (out_dtype == torch.bfloat16 and self.gate_tile == K.GATE_TILE and self.weight.dtype == torch.bfloat16
+                and n >= TENSOR_CORE_TOKENS and K.gemm_tc_supported(n, self.out_features, self.in_features)):
+            # prompts: the tcgen05 product with the gated activation in its epilogue
+            if isinstance(x, NormedStream):
+                x = x.materialize()
+            if x.dtype == torch.bfloat16 and x.is_contiguous():
+                K.gemm_tc(x, self.weight, act, swiglu=True)
+                return act
         K.swiglu(self(x, out_dtype), act, tile=self.gate_tile)
         return act
 
