@@ -1,10 +1,18 @@
 // Decode attention for bf16: one new token per sequence against its paged cache, grouped-query,
-// keys split over blocks.  A block owns one (sequence, kv head, split); its 4 warps walk the keys of
-// the split.  HD / 8 lanes share a key: each holds 8 lanes of the head (one 16-byte load of k, one of
-// v), the partial dot products of the G query heads of the group are summed over those lanes with
-// shuffles, and every lane keeps a running (max, sum, output slice) per head.  The running max is
-// only raised when a score exceeds it, so a key costs one exponential per head.
+// the pages of a sequence split over blocks.  A block owns one (sequence, kv head, split).  Its
+// producer thread streams the split's pages into a ring in shared memory: a page of one kv head is
+// 64 keys x HD, contiguous, so one bulk asynchronous copy (cp.async.bulk, completion on an mbarrier)
+// brings its keys and another its values.  Four consumer warps share each page: HD / 8 lanes hold a
+// key (8 lanes of the head each), the partial dot products of the G query heads of the group are
+// summed over those lanes with shuffles, and every lane keeps a running (max, sum, output slice) per
+// head.  The running max is only raised when a score exceeds it, so a key costs one exponential per
+// head.  Waits on mbarriers are bounded; one that runs out is recorded in the status word.
 #pragma once
+#include <cuda.h>
+
+#include <map>
+#include <tuple>
+
 #include "common.cuh"
 
 struct AttnDecodeArgs {
@@ -21,170 +29,281 @@ struct AttnDecodeArgs {
     float* part_ml;              // [N, n_heads, n_splits, 2]: (max in natural-log units, sum)
     int n_heads, n_kv, window, n_splits;
     float scale_log2e;           // softmax scale times log2(e): scores live in base-2 units
+    int* status;                 // 0, or 21 / 22 when a bounded wait ran out
 };
 
-// How many of the n_splits blocks of a (sequence, kv head) work: one for every 64 keys.
-__host__ __device__ inline int attn_decode_active_splits(int span, int n_splits) {
-    const int want = (span + 63) / 64;
-    return want < 1 ? 1 : (want > n_splits ? n_splits : want);
+// How many of the n_splits blocks of a (sequence, kv head) work: at most one per page the keys touch.
+__host__ __device__ inline int attn_decode_active_splits(int key_lo, int kv_len, int n_splits) {
+    const int n_pg = (kv_len - 1) / 64 - key_lo / 64 + 1;
+    return n_pg < 1 ? 1 : (n_pg > n_splits ? n_splits : n_pg);
 }
 
+namespace attn_decode {
+constexpr unsigned kSpinLimit = 1u << 22;
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    const unsigned addr = smem_u32(bar);
+    for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+        unsigned done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+}  // namespace attn_decode
+
+template <int HD>
+__host__ __device__ constexpr int attn_decode_stages() { return HD == 64 ? 4 : 3; }
+
+__device__ __forceinline__ void dec_ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void dec_ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void dec_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// The G query heads of a kv head are rows 0 .. G-1 of a 16-row tensor-core tile (the other rows are zero):
+// S = Q K^T and O += P V run as mma.sync.m16n8k16, so a page costs a warp a few dozen instructions
+// instead of hundreds.  A page arrives as TMA boxes of 64 keys x 64 lanes with the 128-byte swizzle, which
+// ldmatrix reads without bank conflicts; the four consumer warps take 16 keys of every page each and keep
+// their own running (max, sum, output), merged at the end.
 template <int HD, int G>
-__global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a) {
-    constexpr int LPK = HD / 8;        // lanes per key
-    constexpr int KPW = 32 / LPK;      // keys per warp per trip
-    constexpr int WARPS = 4;
+__global__ void __launch_bounds__(160) attn_decode_kernel(const AttnDecodeArgs a, const __grid_constant__ CUtensorMap pool_map) {
+    using namespace attn_decode;
+    constexpr int WARPS = 4;           // consumer warps; warp 4 is the producer
+    constexpr int S = attn_decode_stages<HD>();
+    constexpr int SUB = HD / 64;       // 64-lane boxes per row
+    constexpr int KS = HD / 16;        // k steps of Q K^T
+    constexpr int DT = HD / 8;         // 8-wide output tiles
+    constexpr unsigned BOX = 64 * 64 * 2;          // bytes of one box
+    constexpr unsigned PB = SUB * BOX;             // bytes of the keys (or of the values) of one page of one kv head
     constexpr float LN2 = 0.6931471805599453f;
-    __shared__ float sm_acc[WARPS][G][HD];
-    __shared__ float sm_m[WARPS][G], sm_l[WARPS][G];
+    extern __shared__ __align__(1024) unsigned char smem_dec_raw[];
+    unsigned char* smem_dec = smem_dec_raw + ((1024u - (smem_u32(smem_dec_raw) & 1023u)) & 1023u);
+    unsigned char* ring = smem_dec;                                                         // [S][k | v][SUB][64 x 128 bytes]
+    float* sm_acc = reinterpret_cast<float*>(smem_dec + (size_t)S * 2 * PB);                // [WARPS][G][HD]
+    float* sm_m = sm_acc + WARPS * G * HD;                                                  // [WARPS][G]
+    float* sm_l = sm_m + WARPS * G;
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(sm_l + WARPS * G);
+    unsigned long long* empty = full + S;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int sub = lane / LPK, li = lane % LPK;
+    const int g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
-    const int tok = a.cu_seqlens[seq];
+    const int tok = seq;                         // one token per sequence: the packed row is the sequence
     const int pos = a.start_pos[seq];            // the new token's position; keys 0..pos are visible
     const int kv_len = pos + 1;
-    const int* pages = a.block_table + (size_t)a.slot_of_seq[seq] * a.table_stride;
-    const size_t page_elems = (size_t)a.n_kv * 64 * HD;
-
-    float qf[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        const uint4 v = *reinterpret_cast<const uint4*>(a.q + (size_t)tok * a.q_stride + (size_t)(kvh * G + g) * HD + li * 8);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h[e]);
-            qf[g][2 * e] = f.x * a.scale_log2e;
-            qf[g][2 * e + 1] = f.y * a.scale_log2e;
-        }
-    }
-    float m[G], l[G], acc[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        m[g] = -INFINITY;
-        l[g] = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
-    }
-
-    // the keys of this split, in units of 16.  Only as many splits as the sequence has pages are
-    // active (the grid is sized for the longest sequence the cache can hold); the others leave at once
-    // and the combine kernel, which computes the same number, does not look at them.
     const int key_lo = a.window > 0 ? max(0, kv_len - a.window) : 0;
-    const int span = kv_len - key_lo;
-    const int active = attn_decode_active_splits(span, a.n_splits);
+    // Only as many splits as the keys touch pages are active (the grid is sized for the longest sequence
+    // the step may hold); the others leave at once and the combine kernel, which computes the same
+    // number, does not look at them.
+    const int active = attn_decode_active_splits(key_lo, kv_len, a.n_splits);
     if (split >= active) return;
-    const int per = (((span + 15) / 16 + active - 1) / active) * 16;
-    const int k_begin = key_lo + split * per;
-    const int k_end = min(kv_len, k_begin + per);
+    const int pg_first = key_lo / 64, n_pg = (kv_len - 1) / 64 - pg_first + 1;
+    const int per = (n_pg + active - 1) / active;
+    const int pg_lo = pg_first + split * per;
+    const int pg_hi = min(pg_first + n_pg, pg_lo + per);          // exclusive
+    const int* pages = a.block_table + (size_t)a.slot_of_seq[seq] * a.table_stride;
 
-    auto fetch = [&](int base, uint4& k4, uint4& v4) {
-        const int key = base + sub;
-        k4 = make_uint4(0u, 0u, 0u, 0u);
-        v4 = k4;
-        if (key < k_end) {
-            const int page = pages[key >> 6];
-            const __nv_bfloat16* kp = a.pool + (size_t)page * 2 * page_elems + ((size_t)kvh * 64 + (key & 63)) * HD + li * 8;
-            k4 = *reinterpret_cast<const uint4*>(kp);
-            v4 = *reinterpret_cast<const uint4*>(kp + page_elems);
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, WARPS);
         }
-    };
-    int base = k_begin + warp * KPW;
-    uint4 kv4, vv4;
-    fetch(base, kv4, vv4);
-    while (base < k_end) {
-        const int nbase = base + WARPS * KPW;
-        uint4 kn4, vn4;
-        fetch(nbase, kn4, vn4);        // the next trip's loads fly while this trip computes
-        const bool live = base + sub < k_end;
-        float kf[8], vf[8];
-        {
-            const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&kv4);
-            const __nv_bfloat162* vh = reinterpret_cast<const __nv_bfloat162*>(&vv4);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 kk = __bfloat1622float2(kh[e]), vv = __bfloat1622float2(vh[e]);
-                kf[2 * e] = kk.x; kf[2 * e + 1] = kk.y;
-                vf[2 * e] = vv.x; vf[2 * e + 1] = vv.y;
-            }
-        }
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            float s = 0.f;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) s += qf[g][e] * kf[e];
-#pragma unroll
-            for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (live) {
-                float p;
-                if (s > m[g]) {            // a new maximum: rescale what was gathered so far
-                    const float alpha = exp2f(m[g] - s);      // 0 the first time (m = -inf)
-                    l[g] *= alpha;
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[g][e] *= alpha;
-                    m[g] = s;
-                    p = 1.f;
-                } else {
-                    p = exp2f(s - m[g]);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == WARPS) {
+        // ---------------- producer: one thread streams the pages of this split ----------------
+        if (lane == 0) {
+            for (int i = 0, pg = pg_lo; pg < pg_hi; ++pg, ++i) {
+                const int s = i % S;
+                if (i >= S && !mbar_wait(empty + s, ((i / S) - 1) & 1)) {
+                    atomicCAS(a.status, 0, 22);
+                    break;
                 }
-                l[g] += p;
+                // rows of the pool seen as a matrix [pages * 2 * n_kv * 64, HD]: keys, then values, of a page
+                const int krow = ((pages[pg] * 2) * a.n_kv + kvh) * 64, vrow = krow + a.n_kv * 64;
+                mbar_expect_tx(full + s, 2 * PB);
+                unsigned char* dst = ring + (size_t)s * 2 * PB;
 #pragma unroll
-                for (int e = 0; e < 8; ++e) acc[g][e] += p * vf[e];
+                for (int h = 0; h < SUB; ++h) {
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                                     smem_u32(dst + h * BOX)),
+                                 "l"(&pool_map), "r"(h * 64), "r"(krow), "r"(smem_u32(full + s))
+                                 : "memory");
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                                     smem_u32(dst + PB + h * BOX)),
+                                 "l"(&pool_map), "r"(h * 64), "r"(vrow), "r"(smem_u32(full + s))
+                                 : "memory");
+                }
             }
         }
-        kv4 = kn4;
-        vv4 = vn4;
-        base = nbase;
-    }
+    } else {
+        // ---------------- consumers: warp w takes keys 16 w .. 16 w + 15 of every page ----------------
+        // Q as the A operand: row g is head g of the group (rows G.. and 8.. are zero)
+        unsigned qf[KS][4];
+        {
+            const __nv_bfloat16* qrow = a.q + (size_t)tok * a.q_stride + (size_t)(kvh * G + (g < G ? g : 0)) * HD;
+#pragma unroll
+            for (int kk = 0; kk < KS; ++kk) {
+                qf[kk][0] = g < G ? *reinterpret_cast<const unsigned*>(qrow + kk * 16 + 2 * t) : 0u;
+                qf[kk][2] = g < G ? *reinterpret_cast<const unsigned*>(qrow + kk * 16 + 8 + 2 * t) : 0u;
+                qf[kk][1] = 0u;
+                qf[kk][3] = 0u;
+            }
+        }
+        float o[DT][4];
+#pragma unroll
+        for (int d = 0; d < DT; ++d)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[d][e] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;        // of row g (head g); every lane of a quad holds the same max
+        auto swz = [](int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); };   // byte offset in a box
 
-    // merge the key slots of a warp (lanes that differ above the LPK bits)
-#pragma unroll
-    for (int o = LPK; o < 32; o <<= 1) {
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const float mo = __shfl_xor_sync(0xffffffffu, m[g], o);
-            const float lo = __shfl_xor_sync(0xffffffffu, l[g], o);
-            const float mn = fmaxf(m[g], mo);
-            const float sa = m[g] == -INFINITY ? 0.f : exp2f(m[g] - mn);
-            const float sb = mo == -INFINITY ? 0.f : exp2f(mo - mn);
-            l[g] = l[g] * sa + lo * sb;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const float ao = __shfl_xor_sync(0xffffffffu, acc[g][e], o);
-                acc[g][e] = acc[g][e] * sa + ao * sb;
+        for (int i = 0, pg = pg_lo; pg < pg_hi; ++pg, ++i) {
+            const int s = i % S;
+            if (!mbar_wait(full + s, (i / S) & 1)) {
+                if (lane == 0) atomicCAS(a.status, 0, 21);
+                break;
             }
-            m[g] = mn;
+            const unsigned char* Kt = ring + (size_t)s * 2 * PB;
+            const unsigned char* Vt = Kt + PB;
+            // scores of this warp's 16 keys: two tiles of 8 keys
+            float sc[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[nt][e] = 0.f;
+#pragma unroll
+                for (int kk = 0; kk < KS; kk += 2) {
+                    const int chunk = 2 * kk + (lane >> 3);           // 16-byte chunk of the row: k steps kk and kk + 1
+                    unsigned kb[4];
+                    dec_ldmatrix_x4(kb, Kt + (chunk >> 3) * BOX + swz(warp * 16 + nt * 8 + (lane & 7), chunk & 7));
+                    dec_mma(sc[nt], qf[kk], kb[0], kb[1]);
+                    dec_mma(sc[nt], qf[kk + 1], kb[2], kb[3]);
+                }
+            }
+            // scale, mask, online softmax of row g
+            float mx = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int key = pg * 64 + warp * 16 + nt * 8 + 2 * t + e;
+                    const float v = (key >= key_lo && key < kv_len) ? sc[nt][e] * a.scale_log2e : -INFINITY;
+                    sc[nt][e] = v;
+                    mx = fmaxf(mx, v);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run, mx);
+            const float alpha = m_run == -INFINITY ? 0.f : exp2f(m_run - m_new);
+            m_run = m_new;
+            float p[2][2];
+            float rs = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    p[nt][e] = (sc[nt][e] == -INFINITY || m_new == -INFINITY) ? 0.f : exp2f(sc[nt][e] - m_new);
+                    rs += p[nt][e];
+                }
+            l_run = l_run * alpha + rs;                 // this lane's share; summed over the quad at the end
+            unsigned pf[4];
+            {
+                const __nv_bfloat162 p0 = __floats2bfloat162_rn(p[0][0], p[0][1]), p1 = __floats2bfloat162_rn(p[1][0], p[1][1]);
+                pf[0] = *reinterpret_cast<const unsigned*>(&p0);     // row g, keys 2t, 2t + 1
+                pf[2] = *reinterpret_cast<const unsigned*>(&p1);     // row g, keys 8 + 2t, ...
+                pf[1] = 0u;
+                pf[3] = 0u;
+            }
+#pragma unroll
+            for (int d = 0; d < DT; ++d) {
+                o[d][0] *= alpha;
+                o[d][1] *= alpha;
+            }
+            // A masked key has weight zero, but 0 x NaN is NaN: rows of the value tile that hold no key of
+            // this sequence (a page's unwritten tail, keys before the window) are cleared before they are read.
+            if (pg * 64 + warp * 16 + 15 >= kv_len || pg * 64 + warp * 16 < key_lo) {
+                const int row = warp * 16 + (lane >> 1), key = pg * 64 + row;
+                if (key >= kv_len || key < key_lo)
+                    for (int c = lane & 1; c < HD / 8; c += 2)
+                        *reinterpret_cast<uint4*>(const_cast<unsigned char*>(Vt) + (c >> 3) * BOX + swz(row, c & 7)) = make_uint4(0u, 0u, 0u, 0u);
+                __syncwarp();
+            }
+            // O += P V over this warp's 16 keys
+#pragma unroll
+            for (int d = 0; d < DT; d += 2) {
+                const int chunk = d + (lane >> 4);
+                unsigned vb[4];
+                dec_ldmatrix_x4_trans(vb, Vt + (chunk >> 3) * BOX + swz(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, chunk & 7));
+                dec_mma(o[d], pf, vb[0], vb[1]);
+                dec_mma(o[d + 1], pf, vb[2], vb[3]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + s);      // this warp has read its keys of the page
         }
-    }
-    if (sub == 0) {
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+        if (g < G) {
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) sm_acc[warp][g][li * 8 + e] = acc[g][e];
-            if (li == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
+            for (int d = 0; d < DT; ++d) {
+                sm_acc[(warp * G + g) * HD + d * 8 + 2 * t] = o[d][0];
+                sm_acc[(warp * G + g) * HD + d * 8 + 2 * t + 1] = o[d][1];
+            }
+            if (t == 0) { sm_m[warp * G + g] = m_run; sm_l[warp * G + g] = l_run; }
         }
     }
     __syncthreads();
     // merge the warps and write
-    for (int idx = tid; idx < G * HD; idx += 128) {
-        const int g = idx / HD, d = idx % HD;
+    for (int idx = tid; idx < G * HD; idx += blockDim.x) {
+        const int gg = idx / HD, d = idx % HD;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, sm_m[w][g]);
-        float L = 0.f, o = 0.f;
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, sm_m[w * G + gg]);
+        float L = 0.f, ov = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
-            const float sc = sm_m[w][g] == -INFINITY ? 0.f : exp2f(sm_m[w][g] - M);
-            L += sm_l[w][g] * sc;
-            o += sm_acc[w][g][d] * sc;
+            const float scl = sm_m[w * G + gg] == -INFINITY ? 0.f : exp2f(sm_m[w * G + gg] - M);
+            L += sm_l[w * G + gg] * scl;
+            ov += sm_acc[(w * G + gg) * HD + d] * scl;
         }
-        const int head = kvh * G + g;
+        const int head = kvh * G + gg;
         if (active == 1) {
-            a.out[(size_t)tok * a.n_heads * HD + (size_t)head * HD + d] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+            a.out[(size_t)tok * a.n_heads * HD + (size_t)head * HD + d] = __float2bfloat16_rn(L > 0.f ? ov / L : 0.f);
         } else {
             const size_t pi = ((size_t)tok * a.n_heads + head) * a.n_splits + split;
-            a.part_acc[pi * HD + d] = o;
+            a.part_acc[pi * HD + d] = ov;
             if (d == 0) {
                 a.part_ml[pi * 2] = M == -INFINITY ? -INFINITY : M * LN2;
                 a.part_ml[pi * 2 + 1] = L;
@@ -203,8 +322,8 @@ __global__ void __launch_bounds__(128) attn_decode_combine_kernel(const AttnDeco
     if (row >= n_rows) return;
     const int tok = row / a.n_heads;                // one token per sequence: tok is the sequence
     const int kv_len = a.start_pos[tok] + 1;
-    const int span = a.window > 0 ? min(kv_len, a.window) : kv_len;
-    const int active = attn_decode_active_splits(span, a.n_splits);
+    const int key_lo = a.window > 0 ? max(0, kv_len - a.window) : 0;
+    const int active = attn_decode_active_splits(key_lo, kv_len, a.n_splits);
     if (active == 1) return;                        // the split kernel wrote the output itself
     const float* ml = a.part_ml + (size_t)row * a.n_splits * 2;
     float m0 = lane < active ? ml[lane * 2] : -INFINITY, m1 = lane + 32 < active ? ml[(lane + 32) * 2] : -INFINITY;
@@ -230,28 +349,79 @@ __global__ void __launch_bounds__(128) attn_decode_combine_kernel(const AttnDeco
     for (int e = 0; e < DPL; ++e) a.out[(size_t)row * HD + e * 32 + lane] = __float2bfloat16_rn(o[e] * inv);
 }
 
+typedef CUresult (*DecEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The TMA's view of one cache line's pool [pages][2][n_kv][64][HD]: a matrix of pages * 2 * n_kv * 64 rows
+// of HD lanes; boxes of 64 rows x 64 lanes with the 128-byte swizzle.
+static bool attn_decode_pool_map(const void* pool, int n_pages, int n_kv, int hd, CUtensorMap* out) {
+    static DecEncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess || !fn)
+            return false;
+        encode = (DecEncodeTiledFn)fn;
+    }
+    static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> maps;
+    const auto key = std::make_tuple(pool, n_pages, n_kv, hd);
+    auto it = maps.find(key);
+    if (it == maps.end()) {
+        CUtensorMap m;
+        const cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)n_pages * 2 * n_kv * 64};
+        const cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+        const cuuint32_t box[2] = {64, 64};
+        const cuuint32_t estr[2] = {1, 1};
+        if (encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+        if (maps.size() > 4096) maps.clear();
+        it = maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return true;
+}
+
+template <int HD, int G>
+static bool attn_decode_launch(const AttnDecodeArgs& a, dim3 grid, int n_pages, cudaStream_t stream) {
+    constexpr int S = attn_decode_stages<HD>();
+    const size_t smem = (size_t)S * 2 * 64 * HD * 2 + (size_t)4 * G * (HD + 2) * 4 + 2 * S * 8 + 16 + 1024;
+    CUtensorMap map;
+    if (!attn_decode_pool_map(a.pool, n_pages, a.n_kv, HD, &map)) return false;
+    static bool opted_in = false;
+    if (!opted_in) {
+        if (cudaFuncSetAttribute(attn_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+        opted_in = true;
+    }
+    attn_decode_kernel<HD, G><<<grid, 160, smem, stream>>>(a, map);
+    return true;
+}
+
 template <int HD>
-static bool launch_attn_decode_g(const AttnDecodeArgs& a, int group, dim3 grid, cudaStream_t stream) {
+static bool launch_attn_decode_g(const AttnDecodeArgs& a, int group, dim3 grid, int n_pages, cudaStream_t stream) {
     switch (group) {
-        case 1: attn_decode_kernel<HD, 1><<<grid, 128, 0, stream>>>(a); return true;
-        case 2: attn_decode_kernel<HD, 2><<<grid, 128, 0, stream>>>(a); return true;
-        case 4: attn_decode_kernel<HD, 4><<<grid, 128, 0, stream>>>(a); return true;
-        case 8: attn_decode_kernel<HD, 8><<<grid, 128, 0, stream>>>(a); return true;
+        case 1: return attn_decode_launch<HD, 1>(a, grid, n_pages, stream);
+        case 2: return attn_decode_launch<HD, 2>(a, grid, n_pages, stream);
+        case 4: return attn_decode_launch<HD, 4>(a, grid, n_pages, stream);
+        case 8: return attn_decode_launch<HD, 8>(a, grid, n_pages, stream);
         default: return false;
     }
 }
 
 // true when the specialised kernels were launched; false: the shape is left to the general kernel
-static bool launch_attn_decode(const AttnDecodeArgs& a, int hd, int group, int n_seqs, cudaStream_t stream) {
+static bool launch_attn_decode(const AttnDecodeArgs& a, int hd, int group, int n_seqs, int n_pages, cudaStream_t stream) {
     const dim3 grid(a.n_splits, a.n_kv, n_seqs);
     const int n_rows = n_seqs * a.n_heads;
     if (hd == 64) {
-        if (!launch_attn_decode_g<64>(a, group, grid, stream)) return false;
+        if (!launch_attn_decode_g<64>(a, group, grid, n_pages, stream)) return false;
         if (a.n_splits > 1) attn_decode_combine_kernel<64><<<(n_rows + 3) / 4, 128, 0, stream>>>(a, n_rows);
         return true;
     }
     if (hd == 128) {
-        if (!launch_attn_decode_g<128>(a, group, grid, stream)) return false;
+        if (!launch_attn_decode_g<128>(a, group, grid, n_pages, stream)) return false;
         if (a.n_splits > 1) attn_decode_combine_kernel<128><<<(n_rows + 3) / 4, 128, 0, stream>>>(a, n_rows);
         return true;
     }

@@ -62,7 +62,7 @@ _protos = {
     "attention": {
         "blm_attention": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                          c_int, c_int, c_float, c_int, c_void_p],
+                          c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p],
     },
     "gemm": {
         "blm_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
@@ -256,7 +256,8 @@ def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos
     _call("attention", "blm_attention", _ptr(q), q_stride, _ptr(pool), _code(q.dtype), _ptr(block_table),
           block_table.shape[1], _ptr(cu_seqlens), _ptr(slot_of_seq), _ptr(start_pos), _ptr(out), _ptr(scratch),
           n_tokens, n_seqs, max_q_len, n_heads, n_kv, head_dim, PAGE, int(window or 0), n_splits,
-          c_float(scale), 1 if general_only else 0, _stream(), kernels=2 if n_splits > 1 else 1)
+          c_float(scale), 1 if general_only else 0, _ptr(status_word(q.device)), pool.shape[0], _stream(),
+          kernels=2 if n_splits > 1 else 1)
 
 
 def gemm_f32(x, w, out=None):
@@ -319,7 +320,8 @@ def check_status(device) -> None:
     code = int(w.item())
     if code:
         w.zero_()
-        what = {1: "gemv: a consumer waited in vain for a weight stage", 2: "gemv: the producer waited in vain for a free stage",
+        what = {21: "decode attention: a consumer waited in vain for a page", 22: "decode attention: the producer waited in vain for a free stage",
+                1: "gemv: a consumer waited in vain for a weight stage", 2: "gemv: the producer waited in vain for a free stage",
                 11: "gemm_tc: the tensor-core thread waited in vain for a stage", 12: "gemm_tc: the producer waited in vain for a free stage",
                 13: "gemm_tc: the epilogue waited in vain for the accumulator"}
         raise KernelError(f"{what.get(code, 'status ' + str(code))}; the step's results are not valid")
