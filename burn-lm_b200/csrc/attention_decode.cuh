@@ -118,6 +118,8 @@ __global__ void __launch_bounds__(160) attn_decode_kernel(const AttnDecodeArgs a
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    pdl_launch_dependents();
+    pdl_wait();          // the queries and this step's keys are the work of the kernels before
     const int tok = seq;                         // one token per sequence: the packed row is the sequence
     const int pos = a.start_pos[seq];            // the new token's position; keys 0..pos are visible
     const int kv_len = pos + 1;
@@ -315,6 +317,8 @@ __global__ void __launch_bounds__(160) attn_decode_kernel(const AttnDecodeArgs a
 // Merges the partial results of the active splits: one warp per (token, head).
 template <int HD>
 __global__ void __launch_bounds__(128) attn_decode_combine_kernel(const AttnDecodeArgs a, int n_rows) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int DPL = HD / 32;       // dims per lane
     __shared__ float wts[4][64];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -396,8 +400,7 @@ static bool attn_decode_launch(const AttnDecodeArgs& a, dim3 grid, int n_pages, 
         if (cudaFuncSetAttribute(attn_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
         opted_in = true;
     }
-    attn_decode_kernel<HD, G><<<grid, 160, smem, stream>>>(a, map);
-    return true;
+    return blm_launch_dependent(attn_decode_kernel<HD, G>, grid, dim3(160), smem, stream, a, map) == cudaSuccess;
 }
 
 template <int HD>
@@ -417,12 +420,12 @@ static bool launch_attn_decode(const AttnDecodeArgs& a, int hd, int group, int n
     const int n_rows = n_seqs * a.n_heads;
     if (hd == 64) {
         if (!launch_attn_decode_g<64>(a, group, grid, n_pages, stream)) return false;
-        if (a.n_splits > 1) attn_decode_combine_kernel<64><<<(n_rows + 3) / 4, 128, 0, stream>>>(a, n_rows);
+        if (a.n_splits > 1) blm_launch_dependent(attn_decode_combine_kernel<64>, dim3((n_rows + 3) / 4), dim3(128), 0, stream, a, n_rows);
         return true;
     }
     if (hd == 128) {
         if (!launch_attn_decode_g<128>(a, group, grid, n_pages, stream)) return false;
-        if (a.n_splits > 1) attn_decode_combine_kernel<128><<<(n_rows + 3) / 4, 128, 0, stream>>>(a, n_rows);
+        if (a.n_splits > 1) blm_launch_dependent(attn_decode_combine_kernel<128>, dim3((n_rows + 3) / 4), dim3(128), 0, stream, a, n_rows);
         return true;
     }
     return false;

@@ -34,6 +34,30 @@ static inline int blm_check_launch(const char* what) {
         if (!(cond)) return blm_fail(BLM_BAD_ARGUMENT, __VA_ARGS__); \
     } while (0)
 
+// Programmatic dependent launch: a kernel launched through blm_launch_dependent may start while the kernel
+// before it on the stream is still running.  What it does before pdl_wait() must touch nothing that an
+// earlier kernel writes (barrier setup, prefetching weights); pdl_wait() returns when the earlier kernels
+// are complete and their writes visible.  pdl_launch_dependents() lets the kernel after this one start its
+// own preamble.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t blm_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                               Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // dtype tags shared with the Python side
 enum { BLM_F32 = 0, BLM_BF16 = 1 };
 

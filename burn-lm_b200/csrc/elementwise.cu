@@ -11,6 +11,8 @@ BLM_API const char* blm_elementwise_last_error() { return g_blm_error; }
 template <typename TT>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TT* __restrict__ table,
                              float* __restrict__ out, int width, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int n = blockIdx.x;
     int tok = tokens[n];
     if ((unsigned)tok >= (unsigned)vocab) tok = 0;  // ids are validated on the host; never read wild
@@ -25,9 +27,9 @@ BLM_API int blm_embed(const int* tokens, const void* table, int table_dtype, flo
     BLM_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0, "embed: bad sizes");
     const int threads = width >= 1024 ? 256 : 128;
     if (table_dtype == BLM_F32)
-        embed_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, width, vocab);
+        blm_launch_dependent(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, width, vocab);
     else if (table_dtype == BLM_BF16)
-        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, out, width, vocab);
+        blm_launch_dependent(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, width, vocab);
     else
         return blm_fail(BLM_BAD_ARGUMENT, "embed: table dtype %d", table_dtype);
     return blm_check_launch("embed");
@@ -233,6 +235,8 @@ __global__ void rope_append_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, con
                                             const int* __restrict__ block_table, int table_stride,
                                             __nv_bfloat16* __restrict__ pool, int n_heads, int n_kv, int hd, int page_size,
                                             int write_cache, const float2* __restrict__ table) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int n = blockIdx.y;
     const int item = blockIdx.x * blockDim.x + threadIdx.x;
     const int half = hd >> 1, cpp = half >> 3;                  // chunks of 8 pairs per head
@@ -302,9 +306,9 @@ BLM_API int blm_rope_append(void* qkv, int dtype, const int* token_seq, const in
         const int vitems = (n_heads + n_kv) * (hd / 16) + (write_cache ? n_kv * (hd / 8) : 0);
         const dim3 vgrid((vitems + threads - 1) / threads, n_tokens);
         if (table_covers_step) {
-            rope_append_bf16_vec_kernel<<<vgrid, threads, 0, stream>>>((__nv_bfloat16*)qkv, token_seq, token_pos, slot_of_seq,
-                                                                       block_table, table_stride, (__nv_bfloat16*)pool, n_heads,
-                                                                       n_kv, hd, page_size, write_cache, table);
+            blm_launch_dependent(rope_append_bf16_vec_kernel, vgrid, dim3(threads), 0, stream, (__nv_bfloat16*)qkv, token_seq, token_pos,
+                                 slot_of_seq, block_table, table_stride, (__nv_bfloat16*)pool, n_heads, n_kv, hd, page_size,
+                                 write_cache, table);
             return blm_check_launch("rope_append");
         }
     }
@@ -428,6 +432,8 @@ BLM_API int blm_convert(const void* in, int in_dtype, void* out, int out_dtype, 
 __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict__ pos, const int* __restrict__ sampled,
                                       int* __restrict__ history, int* __restrict__ step_no, long long* __restrict__ counters,
                                       int batch, int history_steps) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     const int s = *step_no;
     if (b < batch) {
@@ -439,13 +445,18 @@ __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict_
     }
 }
 // a launch of its own, so that every block of the kernel above has read the old value
-__global__ void bump_kernel(int* step_no) { *step_no += 1; }
+__global__ void bump_kernel(int* step_no) {
+    pdl_launch_dependents();
+    pdl_wait();
+    *step_no += 1;
+}
 
 BLM_API int blm_decode_advance(int* tokens, int* pos, const int* sampled, int* history, int* step_no,
                                long long* counters, int batch, int history_steps, cudaStream_t stream) {
     if (batch == 0) return BLM_OK;
     BLM_REQUIRE(step_no != nullptr, "decode_advance: no step counter");
-    decode_advance_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(tokens, pos, sampled, history, step_no, counters, batch, history_steps);
-    bump_kernel<<<1, 1, 0, stream>>>(step_no);
+    blm_launch_dependent(decode_advance_kernel, dim3((batch + 127) / 128), dim3(128), 0, stream, tokens, pos, sampled, history, step_no,
+                         counters, batch, history_steps);
+    blm_launch_dependent(bump_kernel, dim3(1), dim3(1), 0, stream, step_no);
     return blm_check_launch("decode_advance");
 }

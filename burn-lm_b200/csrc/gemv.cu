@@ -227,6 +227,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
+    // The weights are nobody's output: the producer streams them at once, also while the kernel before this
+    // one still runs; the consumers wait for it before they touch the tokens.
+    pdl_launch_dependents();
 
     if (warp == kConsumerWarps) {
         // ---------------- producer: lane w of this warp feeds consumer warp w's part of the ring ----------------
@@ -286,6 +289,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
     }
 
     // ---------------- consumers ----------------
+    pdl_wait();
     gemv_stage_tokens<NBT>(a, xs, xstride, kpad, tid, lane, warp);
     consumer_barrier();
 
@@ -524,7 +528,8 @@ BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, 
             if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "gemv: %s", cudaGetErrorString(e));
             opted_in[nbt] = true;
         }
-        kernel<<<grid, kGemvThreads, smem, stream>>>(a, wmap);
+        cudaError_t e = blm_launch_dependent(kernel, dim3(grid), dim3(kGemvThreads), smem, stream, a, wmap);
+        if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "gemv: %s", cudaGetErrorString(e));
         return blm_check_launch("gemv");
     };
     return nbt == 1 ? launch(gemv_kernel<1>) : launch(gemv_kernel<2>);

@@ -51,6 +51,8 @@ constexpr int kArgmaxChunk = 4096;
 
 __global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
                                                            float* __restrict__ part_val, int* __restrict__ part_idx) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float bv[8];
     __shared__ int bi[8];
     const float* row = logits + (size_t)blockIdx.y * row_stride;
@@ -79,6 +81,8 @@ __global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* __restri
 
 __global__ void argmax_merge_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int chunks,
                                     int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     float best = -INFINITY;
     int idx = 0x7fffffff;
     for (int i = threadIdx.x; i < chunks; i += 32) {
@@ -112,8 +116,8 @@ BLM_API int blm_argmax(const float* logits, long long row_stride, int n_rows, in
     const int chunks = (vocab + kArgmaxChunk - 1) / kArgmaxChunk;
     float* part_val = scratch;
     int* part_idx = reinterpret_cast<int*>(scratch + (size_t)n_rows * chunks);
-    argmax_chunk_kernel<<<dim3(chunks, n_rows), 256, 0, stream>>>(logits, row_stride, vocab, part_val, part_idx);
-    argmax_merge_kernel<<<n_rows, 32, 0, stream>>>(part_val, part_idx, chunks, out);
+    blm_launch_dependent(argmax_chunk_kernel, dim3(chunks, n_rows), dim3(256), 0, stream, logits, row_stride, vocab, part_val, part_idx);
+    blm_launch_dependent(argmax_merge_kernel, dim3(n_rows), dim3(32), 0, stream, (const float*)part_val, (const int*)part_idx, chunks, out);
     return blm_check_launch("argmax");
 }
 
