@@ -119,7 +119,9 @@ __global__ void __launch_bounds__(160) attn_decode_kernel(const AttnDecodeArgs a
     const int g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     pdl_launch_dependents();
+    blm_trace(0x400);
     pdl_wait();          // the queries and this step's keys are the work of the kernels before
+    blm_trace(0x410);
     const int tok = seq;                         // one token per sequence: the packed row is the sequence
     const int pos = a.start_pos[seq];            // the new token's position; keys 0..pos are visible
     const int kv_len = pos + 1;
@@ -319,6 +321,7 @@ template <int HD>
 __global__ void __launch_bounds__(128) attn_decode_combine_kernel(const AttnDecodeArgs a, int n_rows) {
     pdl_launch_dependents();
     pdl_wait();
+    blm_trace(0x420);
     constexpr int DPL = HD / 32;       // dims per lane
     __shared__ float wts[4][64];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

@@ -24,6 +24,9 @@ NVCC_FLAGS = [
     "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
 
+# extra compiler flags from the environment, e.g. -DBLM_TRACE for the device-side timeline
+NVCC_FLAGS += os.environ.get("BURN_LM_B200_NVCC_FLAGS", "").split()
+
 # module name -> its sources (headers every module includes are hashed too)
 MODULES = {
     "elementwise": ["elementwise.cu"],

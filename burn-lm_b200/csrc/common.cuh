@@ -58,6 +58,38 @@ static inline cudaError_t blm_launch_dependent(void (*kernel)(KArgs...), dim3 gr
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Device-side timeline, compiled in with -DBLM_TRACE only: thread 0 of a block records (globaltimer, tag,
+// block) at the places that call blm_trace(); blm_trace_dump copies the records of this library to the host.
+#ifdef BLM_TRACE
+constexpr unsigned kTraceCapacity = 1u << 18;
+__device__ unsigned long long g_blm_trace[kTraceCapacity][2];
+__device__ unsigned g_blm_trace_n;
+__device__ __forceinline__ void blm_trace(unsigned tag) {
+    if (threadIdx.x != 0) return;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    const unsigned i = atomicAdd(&g_blm_trace_n, 1u);
+    if (i < kTraceCapacity) {
+        g_blm_trace[i][0] = t;
+        g_blm_trace[i][1] = ((unsigned long long)tag << 32) | (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+    }
+}
+// copies up to `capacity` records (two 64-bit words each) to `host`, returns how many there were, and clears them
+BLM_API long long blm_trace_dump(unsigned long long* host, long long capacity) {
+    unsigned n = 0;
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(&n, g_blm_trace_n, sizeof(n));
+    const long long have = n < kTraceCapacity ? n : kTraceCapacity;
+    const long long take = have < capacity ? have : capacity;
+    if (take > 0) cudaMemcpyFromSymbol(host, g_blm_trace, (size_t)take * 16);
+    n = 0;
+    cudaMemcpyToSymbol(g_blm_trace_n, &n, sizeof(n));
+    return have;
+}
+#else
+#define blm_trace(tag) ((void)0)
+#endif
+
 // dtype tags shared with the Python side
 enum { BLM_F32 = 0, BLM_BF16 = 1 };
 

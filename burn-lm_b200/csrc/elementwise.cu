@@ -13,6 +13,7 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TT* __restric
                              float* __restrict__ out, int width, int vocab) {
     pdl_launch_dependents();
     pdl_wait();
+    blm_trace(0x220);
     const int n = blockIdx.x;
     int tok = tokens[n];
     if ((unsigned)tok >= (unsigned)vocab) tok = 0;  // ids are validated on the host; never read wild
@@ -237,6 +238,7 @@ __global__ void rope_append_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, con
                                             int write_cache, const float2* __restrict__ table) {
     pdl_launch_dependents();
     pdl_wait();
+    blm_trace(0x210);
     const int n = blockIdx.y;
     const int item = blockIdx.x * blockDim.x + threadIdx.x;
     const int half = hd >> 1, cpp = half >> 3;                  // chunks of 8 pairs per head
@@ -434,6 +436,7 @@ __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict_
                                       int batch, int history_steps) {
     pdl_launch_dependents();
     pdl_wait();
+    blm_trace(0x230);
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     const int s = *step_no;
     if (b < batch) {

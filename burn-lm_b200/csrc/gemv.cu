@@ -61,6 +61,17 @@ struct GemvArgs {
     int epi;
     int n_stages;            // ring depth
     int ksplit;              // warps that share a tile, each walking 1/ksplit of K (1, 2, 4 or 8)
+    // A norm handed over by the kernel that wrote the stream: x is bf16(stream * gamma), not yet divided by
+    // the root mean square; ssq_in[part][16] holds, for each stream row, sums of squares whose total over
+    // the parts is the row's; the result is scaled by 1 / sqrt(total / K + eps) per row.
+    const float* ssq_in;
+    int ssq_parts;
+    // EPI_RESID_ADD can hand such a norm over: besides the sum it leaves bf16(stream * next_gamma) in
+    // xg_out [N, M] and its tile's sums of squares in ssq_out[tile][16].
+    const void* next_gamma;
+    int next_gamma_f32;
+    __nv_bfloat16* xg_out;
+    float* ssq_out;
     int* status;             // device word: 0, or the first failure (a bounded wait ran out)
 };
 
@@ -124,7 +135,8 @@ __device__ __forceinline__ void gemv_stage_tokens(const GemvArgs& a, __nv_bfloat
             const int r = idx / vec, k = (idx % vec) * 8;
             __nv_bfloat16* dst = xs + (size_t)r * xstride + k;
             if (r < a.N && k < a.K) {
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(a.x + (size_t)r * a.ldx + k));
+                const size_t src_row = a.rows ? a.rows[r] : r;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(a.x + src_row * a.ldx + k));
             } else {
                 *reinterpret_cast<uint4*>(dst) = zero4;
             }
@@ -202,6 +214,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
     unsigned long long* full = reinterpret_cast<unsigned long long*>(red + kConsumerWarps * 16 * nrows);
     unsigned long long* empty = full + a.n_stages;
     unsigned long long* meet = empty + a.n_stages;     // where warps that share a tile meet (a bounded wait, like all)
+    float* row_scale = reinterpret_cast<float*>(meet + 1);          // [16]: 1 / rms of a handed-over norm's rows
 
     const int out_per_tile = a.epi == EPI_SWIGLU ? 8 : 16;
     const int n_tiles = (a.M + out_per_tile - 1) / out_per_tile;
@@ -289,9 +302,24 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
     }
 
     // ---------------- consumers ----------------
+    blm_trace(0x100 | a.epi);
     pdl_wait();
+    blm_trace(0x110 | a.epi);
     gemv_stage_tokens<NBT>(a, xs, xstride, kpad, tid, lane, warp);
+    if (a.ssq_in != nullptr) {
+        // a warp per row: the parts in a fixed order (lane p, p + 32, ..., then the butterfly)
+        for (int r = warp; r < nrows; r += kConsumerWarps) {
+            float ssq = 0.f;
+            if (r < a.N) {
+                const int src_row = a.rows ? a.rows[r] : r;
+                for (int part = lane; part < a.ssq_parts; part += 32) ssq += a.ssq_in[(size_t)part * 16 + src_row];
+            }
+            ssq = warp_sum(ssq);
+            if (lane == 0) row_scale[r] = r < a.N ? 1.0f / sqrtf(ssq / (float)a.K + a.eps) : 0.f;
+        }
+    }
     consumer_barrier();
+    blm_trace(0x120 | a.epi);
 
     const int g = lane >> 2, t = lane & 3;
     for (int round = 0; round < n_rounds; ++round) {
@@ -378,6 +406,15 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
             continue;
         }
         // the tile is done: rows g and g + 8, tokens 2t and 2t + 1 of every token tile
+        if (a.ssq_in != nullptr) {
+#pragma unroll
+            for (int j = 0; j < NBT; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    c[0][j][e] = (c[0][j][e] + c[1][j][e]) * row_scale[j * 8 + 2 * t + (e & 1)];
+                    c[1][j][e] = 0.f;
+                }
+        }
         if (a.epi == EPI_RESID_ADD) {
             // all loads of the stream first, then the sums: the round trips overlap
             float old[NBT][4];
@@ -388,13 +425,48 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
                     const int m = tile * 16 + g + 8 * (e >> 1), b = j * 8 + 2 * t + (e & 1);
                     old[j][e] = (m < a.M && b < a.N) ? a.acc[(size_t)b * a.M + m] : 0.f;
                 }
+            float gm[2] = {0.f, 0.f};          // the next norm's gamma of rows g and g + 8
+            if (a.xg_out != nullptr) {
 #pragma unroll
-            for (int j = 0; j < NBT; ++j)
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int m = tile * 16 + g + 8 * rr;
+                    if (m < a.M)
+                        gm[rr] = a.next_gamma_f32 ? reinterpret_cast<const float*>(a.next_gamma)[m]
+                                                  : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.next_gamma)[m]);
+                }
+            }
+            float sq[NBT][2];                  // this thread's share of the sums of squares of tokens 2t, 2t + 1
+#pragma unroll
+            for (int j = 0; j < NBT; ++j) {
+                sq[j][0] = 0.f;
+                sq[j][1] = 0.f;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int m = tile * 16 + g + 8 * (e >> 1), b = j * 8 + 2 * t + (e & 1);
-                    if (m < a.M && b < a.N) a.acc[(size_t)b * a.M + m] = old[j][e] + (c[0][j][e] + c[1][j][e]);
+                    if (m < a.M && b < a.N) {
+                        const float v = old[j][e] + (c[0][j][e] + c[1][j][e]);
+                        a.acc[(size_t)b * a.M + m] = v;
+                        if (a.xg_out != nullptr) {
+                            a.xg_out[(size_t)b * a.M + m] = __float2bfloat16_rn(v * gm[e >> 1]);
+                            sq[j][e & 1] += v * v;
+                        }
+                    }
                 }
+            }
+            if (a.xg_out != nullptr) {
+                // over the tile's 16 rows: the lanes of equal t, in a fixed order
+#pragma unroll
+                for (int j = 0; j < NBT; ++j)
+#pragma unroll
+                    for (int bb = 0; bb < 2; ++bb) {
+                        float v = sq[j][bb];
+                        v += __shfl_xor_sync(0xffffffffu, v, 4);
+                        v += __shfl_xor_sync(0xffffffffu, v, 8);
+                        v += __shfl_xor_sync(0xffffffffu, v, 16);
+                        const int b = j * 8 + 2 * t + bb;
+                        if (g == 0 && b < a.N) a.ssq_out[(size_t)tile * 16 + b] = v;
+                    }
+            }
             continue;
         }
 #pragma unroll
@@ -426,6 +498,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
             }
         }
     }
+    blm_trace(0x130 | a.epi);
 }
 
 // Shared memory for a shape and the ring depth it leaves room for; 0 when the tokens do not fit.
@@ -439,8 +512,8 @@ static size_t gemv_plan(int N, int K, int* n_stages_out, int* nbt_out) {
     const size_t red = (size_t)kConsumerWarps * 16 * nrows * 4;
     const size_t limit = 220 * 1024;
     int stages = 16;
-    while (stages > 8 && (size_t)stages * kStageBytes + tokens + red + (size_t)stages * 16 + 64 + 1024 > limit) --stages;
-    const size_t total = (size_t)stages * kStageBytes + tokens + red + (size_t)stages * 16 + 64 + 1024;
+    while (stages > 8 && (size_t)stages * kStageBytes + tokens + red + (size_t)stages * 16 + 128 + 1024 > limit) --stages;
+    const size_t total = (size_t)stages * kStageBytes + tokens + red + (size_t)stages * 16 + 128 + 1024;
     if (total > limit) return 0;
     *n_stages_out = stages;
     *nbt_out = nbt;
@@ -490,7 +563,9 @@ static int weight_map(const void* w, long long ldw, int rows, int K, CUtensorMap
 
 BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, long long ldx,
                      const float* resid, const void* gamma, int gamma_f32, float eps, const int* rows, int N,
-                     void* y, long long ldy, int y_f32, float* acc, int epi, int* status, cudaStream_t stream) {
+                     void* y, long long ldy, int y_f32, float* acc, int epi, const float* ssq_in, int ssq_parts,
+                     const void* next_gamma, int next_gamma_f32, void* xg_out, float* ssq_out, int* status,
+                     cudaStream_t stream) {
     if (N == 0 || M == 0) return BLM_OK;
     BLM_REQUIRE(N >= 1 && N <= 16, "gemv: %d tokens (1..16)", N);
     BLM_REQUIRE(K % 64 == 0 && K >= 64, "gemv: K = %d must be a multiple of 64", K);
@@ -503,10 +578,15 @@ BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, 
     BLM_REQUIRE(epi == EPI_RESID_ADD || y != nullptr, "gemv: no output");
     BLM_REQUIRE(resid == nullptr || ((size_t)resid & 15) == 0, "gemv: the stream must be 16-byte aligned");
     BLM_REQUIRE(status != nullptr, "gemv: no status word");
+    BLM_REQUIRE(ssq_in == nullptr || (x != nullptr && ssq_parts >= 1), "gemv: a handed-over norm comes with x and its sums of squares");
+    BLM_REQUIRE(xg_out == nullptr || (epi == EPI_RESID_ADD && next_gamma != nullptr && ssq_out != nullptr),
+                "gemv: only the product that adds into the stream can hand a norm over, with gamma and room for the sums");
     GemvArgs a;
     a.w = (const __nv_bfloat16*)w; a.ldw = ldw; a.M = M; a.K = K;
     a.x = (const __nv_bfloat16*)x; a.ldx = ldx; a.resid = resid; a.gamma = gamma; a.gamma_f32 = gamma_f32; a.eps = eps;
     a.rows = rows; a.N = N; a.y = y; a.ldy = ldy; a.y_f32 = y_f32; a.acc = acc; a.epi = epi; a.status = status;
+    a.ssq_in = ssq_in; a.ssq_parts = ssq_parts; a.next_gamma = next_gamma; a.next_gamma_f32 = next_gamma_f32;
+    a.xg_out = (__nv_bfloat16*)xg_out; a.ssq_out = ssq_out;
     int nbt;
     const size_t smem = gemv_plan(N, K, &a.n_stages, &nbt);
     BLM_REQUIRE(smem > 0, "gemv: the shape N=%d K=%d does not fit shared memory", N, K);

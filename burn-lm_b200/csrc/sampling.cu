@@ -53,6 +53,7 @@ __global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* __restri
                                                            float* __restrict__ part_val, int* __restrict__ part_idx) {
     pdl_launch_dependents();
     pdl_wait();
+    blm_trace(0x310);
     __shared__ float bv[8];
     __shared__ int bi[8];
     const float* row = logits + (size_t)blockIdx.y * row_stride;
@@ -83,6 +84,7 @@ __global__ void argmax_merge_kernel(const float* __restrict__ part_val, const in
                                     int* __restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
+    blm_trace(0x320);
     float best = -INFINITY;
     int idx = 0x7fffffff;
     for (int i = threadIdx.x; i < chunks; i += 32) {

@@ -70,7 +70,8 @@ _protos = {
     },
     "gemv": {
         "blm_gemv": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
-                     c_float, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p],
+                     c_float, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int,
+                     c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
         "blm_gemv_supported": [c_int, c_int, c_int],
     },
     "gemm_tc": {
@@ -327,22 +328,48 @@ def check_status(device) -> None:
         raise KernelError(f"{what.get(code, 'status ' + str(code))}; the step's results are not valid")
 
 
-def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, out=None, add_into=None, swiglu=False):
+SQUARES_ROWS = 16     # row length of the sums of squares that go with a handed-over norm
+
+
+def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, out=None, add_into=None, swiglu=False,
+         squares=None, hand_over=None):
     """Skinny product of n_tokens <= 16 tokens with a bfloat16 weight [M, K], with fused ends.
 
     Input: `x` bfloat16 [N, K], or the fp32 residual stream `stream_rows` [*, K] to be RMS-normalised
-    with `gamma`, `eps` (optionally gathering `rows`).  Output: `out` [N, M] bfloat16 or float32;
+    with `gamma`, `eps` (optionally gathering `rows`), or a norm that the writer of the stream handed
+    over: `x` = bfloat16(stream * gamma) with `squares` (fp32 [parts, SQUARES_ROWS], the stream rows'
+    sums of squares in parts) and `eps`; the result is then divided by the rows' root mean square.
+    Output: `out` [N, M] bfloat16 or float32;
     with `swiglu` the weight is [2 I, K] in tiles of GATE_TILE gate rows followed by the up rows of the
     same outputs, and out [N, I] = silu(gate) * up; with
-    `add_into` (fp32 [N, M]) the product is added into it and nothing else is written."""
-    _need_cuda(w, x, stream_rows, gamma, rows, out, add_into)
+    `add_into` (fp32 [N, M]) the product is added into it and nothing else is written, unless
+    `hand_over` = (gamma, scaled, squares) asks for the next norm's input as well: scaled
+    (bfloat16 [N, M]) = the new stream times gamma, squares (fp32 [ceil(M / 16), SQUARES_ROWS]) its
+    sums of squares by tiles of 16 lanes."""
+    _need_cuda(w, x, stream_rows, gamma, rows, out, add_into, squares)
     m_rows, k = w.shape
     if w.dtype != torch.bfloat16:
         raise KernelError("gemv: the weight must be bfloat16")
     m = m_rows // 2 if swiglu else m_rows
     epi = EPI_SWIGLU if swiglu else (EPI_RESID_ADD if add_into is not None else EPI_STORE)
-    if x is not None and (x.dtype != torch.bfloat16 or tuple(x.shape) != (n_tokens, k)):
+    if x is not None and (x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != k
+                          or (rows is None and x.shape[0] != n_tokens)):
         raise KernelError("gemv: x must be bfloat16 [N, K]")
+    if rows is not None and rows.numel() != n_tokens:
+        raise KernelError("gemv: one row index per token")
+    if squares is not None and (x is None or squares.dtype != torch.float32 or squares.dim() != 2
+                                or squares.shape[1] != SQUARES_ROWS or not squares.is_contiguous()
+                                or x.shape[0] > SQUARES_ROWS):
+        raise KernelError("gemv: squares go with x and are float32 [parts, 16]")
+    next_gamma = scaled = squares_out = None
+    if hand_over is not None:
+        next_gamma, scaled, squares_out = hand_over
+        _need_cuda(next_gamma, scaled, squares_out)
+        if (epi != EPI_RESID_ADD or scaled.dtype != torch.bfloat16 or tuple(scaled.shape) != (n_tokens, m)
+                or not scaled.is_contiguous() or squares_out.dtype != torch.float32 or not squares_out.is_contiguous()
+                or tuple(squares_out.shape) != ((m + 15) // 16, SQUARES_ROWS) or next_gamma.numel() != m):
+            raise KernelError("gemv: hand_over = (gamma [M], scaled bfloat16 [N, M], squares float32 [ceil(M / 16), 16]) "
+                              "with add_into")
     if stream_rows is not None and (stream_rows.dtype != torch.float32 or stream_rows.shape[1] != k or gamma is None):
         raise KernelError("gemv: the stream must be float32 [*, K] with a gamma")
     if epi == EPI_RESID_ADD:
@@ -355,7 +382,9 @@ def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, 
           _ptr(stream_rows), _ptr(gamma), 1 if (gamma is not None and gamma.dtype == torch.float32) else 0, c_float(eps),
           _ptr(rows), n_tokens, _ptr(out), out.stride(0) if out is not None else 0,
           1 if (out is not None and out.dtype == torch.float32) else 0, _ptr(add_into), epi,
-          _ptr(status_word(w.device)), _stream())
+          _ptr(squares), squares.shape[0] if squares is not None else 0,
+          _ptr(next_gamma), 1 if (next_gamma is not None and next_gamma.dtype == torch.float32) else 0,
+          _ptr(scaled), _ptr(squares_out), _ptr(status_word(w.device)), _stream())
 
 
 def argmax(logits, out):

@@ -97,11 +97,23 @@ class Model:
         resid = torch.empty((step.n_tokens, self.plan.hidden_size), dtype=torch.float32, device=self.runtime.device)
         self.embedding.forward(step.tokens, resid)
         delta = None
-        for run, entry in enumerate(self.plan.schedule):
-            delta = self.layers[entry.layer].block.forward(resid, delta, step, cache.view(run))
+        schedule = self.plan.schedule
+        for run, entry in enumerate(schedule):
+            block = self.layers[entry.layer].block
+            if hasattr(block, "first_norm"):
+                # the norm that reads the stream after this block: the next run's first, or the last norm
+                after = self.layers[schedule[run + 1].layer].block if run + 1 < len(schedule) else None
+                next_norm = self.final_norm if after is None else (after.first_norm() if hasattr(after, "first_norm") else None)
+                delta = block.forward(resid, delta, step, cache.view(run), next_norm=next_norm)
+            else:
+                delta = block.forward(resid, delta, step, cache.view(run))
         if step.n_want == 0:
             return None
-        x = self.final_norm.add_norm(resid, delta, rows=step.want_rows, lazy=getattr(self.head, "takes_pending_norm", False))
+        lazy = getattr(self.head, "takes_pending_norm", False)
+        if getattr(self.final_norm, "takes_handed_norm", False):
+            x = self.final_norm.add_norm(resid, delta, rows=step.want_rows, lazy=lazy, handoff=step.handoff)
+        else:
+            x = self.final_norm.add_norm(resid, delta, rows=step.want_rows, lazy=lazy)
         return self.head.forward(x)
 
     def prepare(self, max_positions: int) -> None:

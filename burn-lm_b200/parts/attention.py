@@ -116,4 +116,4 @@ class Attention(Part):
         K.attention(qkv, qkv.shape[1], cache.pool, cache.block_table, step.cu_seqlens, step.slot_of_seq,
                     step.start_pos, out, n, step.n_seqs, step.max_q_len, s.n_heads, s.n_kv_heads, s.head_dim,
                     self.scale, window=s.window or 0, n_splits=n_splits, scratch=scratch)
-        return self.o.into_stream(out, stream, rt.dtype)
+        return self.o.into_stream(out, stream, rt.dtype, handoff=getattr(step, "handoff", None))

@@ -74,6 +74,7 @@ class StepContext:
     n_want: int
     workspace: "object" = None   # the engine's scratch provider: scratch(name, n_floats) -> fp32 tensor
     host: dict = field(default_factory=dict)   # host copies for parts that plan on the CPU
+    handoff: "object" = None     # parts.linear.NormHandoff of the step, when the block uses one
 
 
 class Part:

@@ -8,6 +8,13 @@ the block before it (`delta`) and returns its own.
 from __future__ import annotations
 
 from ..registry import register_part
+from .linear import NormHandoff
+
+
+def _add_norm(norm, resid, delta, lazy, handoff):
+    if getattr(norm, "takes_handed_norm", False):
+        return norm.add_norm(resid, delta, lazy=lazy, handoff=handoff)
+    return norm.add_norm(resid, delta, lazy=lazy)
 
 
 @register_part("block", "prenorm")
@@ -21,17 +28,28 @@ class PreNormBlock:
     def parts(self):
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
 
-    def forward(self, resid, delta, step, cache_view):
+    def first_norm(self):
+        """The norm that reads the stream first in this block: the block before may prepare its input."""
+        return self.mixer_norm
+
+    def forward(self, resid, delta, step, cache_view, next_norm=None):
         # Two optional abilities of a mixer or feed-forward shorten the path: `takes_pending_norm`
         # (its first product normalises on the fly) and `adds_to_stream` (its last product adds its
-        # result into the residual stream itself and returns None).
+        # result into the residual stream itself and returns None).  A part that adds into the stream
+        # is told, through the step's handoff, which norm reads the stream next (`next_norm` after this
+        # block), and may leave that norm's input beside its sum.
         mixer, ff = self.mixer, self.feed_forward
-        x = self.mixer_norm.add_norm(resid, delta, lazy=getattr(mixer, "takes_pending_norm", False))
+        if step.handoff is None:
+            step.handoff = NormHandoff()
+        handoff = step.handoff
+        x = _add_norm(self.mixer_norm, resid, delta, getattr(mixer, "takes_pending_norm", False), handoff)
         if getattr(mixer, "adds_to_stream", False):
+            handoff.expect(self.feed_forward_norm)
             a = mixer.forward(x, step, cache_view, stream=resid)
         else:
             a = mixer.forward(x, step, cache_view)
-        x = self.feed_forward_norm.add_norm(resid, a, lazy=getattr(ff, "takes_pending_norm", False))
+        x = _add_norm(self.feed_forward_norm, resid, a, getattr(ff, "takes_pending_norm", False), handoff)
         if getattr(ff, "adds_to_stream", False):
+            handoff.expect(next_norm)
             return ff.forward(x, step, stream=resid)
         return ff.forward(x, step)

@@ -55,4 +55,4 @@ class SwiGLU(Part):
     def forward(self, x, step, stream=None):
         rt = self.runtime
         act = self.gate_up.gated(x, rt.dtype)
-        return self.down.into_stream(act, stream, rt.dtype)
+        return self.down.into_stream(act, stream, rt.dtype, handoff=getattr(step, "handoff", None))

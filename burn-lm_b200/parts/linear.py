@@ -25,6 +25,40 @@ TENSOR_CORE_TOKENS = 128  # from this many tokens the gated product runs this pa
 
 
 @dataclass
+class HandedNorm:
+    """What the writer of the stream left for the norm that reads it next: `scaled` = bfloat16(stream * gamma)
+    [N, width] and `squares` [parts, 16], the rows' sums of squares in parts.  Only the division by the root
+    mean square is left, and that commutes with the product that follows."""
+    scaled: torch.Tensor
+    squares: torch.Tensor
+
+
+class NormHandoff:
+    """A step's letterbox between the part that adds into the residual stream last and the norm that reads
+    the stream next.  The block says which norm comes next (`expect`); a product that can leaves the norm's
+    input with its sum (`leave`); the norm picks it up (`claim`).  Nothing left, nothing claimed: the norm
+    is computed from the stream as ever."""
+
+    def __init__(self):
+        self.wanted = None
+        self.left = None
+
+    def expect(self, norm) -> None:
+        """`norm`: a part with `gamma` and `spec.eps` that can take a handed-over input, or None."""
+        self.wanted = norm if getattr(norm, "takes_handed_norm", False) else None
+        self.left = None
+
+    def leave(self, stream, gamma, handed: HandedNorm) -> None:
+        self.left = (stream, gamma, handed)
+
+    def claim(self, stream, gamma) -> Optional[HandedNorm]:
+        left, self.left, self.wanted = self.left, None, None
+        if left is not None and left[0] is stream and left[1] is gamma:
+            return left[2]
+        return None
+
+
+@dataclass
 class NormedStream:
     """An RMS norm not yet computed: rows of the fp32 residual stream, to be normalised with gamma.
     A consumer that can normalise on the fly takes it as it is; `materialize()` runs the norm."""
@@ -33,6 +67,7 @@ class NormedStream:
     eps: float
     rows: Optional[torch.Tensor]
     dtype: torch.dtype
+    handed: Optional[HandedNorm] = None
 
     @property
     def n_tokens(self) -> int:
@@ -66,6 +101,8 @@ class Linear:
     def _source(self, x):
         """Keyword arguments that hand x (a tensor or a pending norm) to the skinny kernel."""
         if isinstance(x, NormedStream):
+            if x.handed is not None and x.n_tokens <= SKINNY_TOKENS:
+                return dict(x=x.handed.scaled, squares=x.handed.squares, eps=x.eps, rows=x.rows)
             if x.n_tokens <= FUSED_NORM_TOKENS:
                 return dict(stream_rows=x.resid, gamma=x.gamma, eps=x.eps, rows=x.rows)
             x = x.materialize()
@@ -87,12 +124,22 @@ class Linear:
             x = x.materialize()
         return self._library(x, out_dtype or x.dtype)
 
-    def into_stream(self, x, stream: Optional[torch.Tensor], out_dtype: torch.dtype):
+    def into_stream(self, x, stream: Optional[torch.Tensor], out_dtype: torch.dtype, handoff: Optional[NormHandoff] = None):
         """The product added into the fp32 residual stream when the skinny kernel can do that itself
-        (returns None); otherwise the product, for the next norm to add."""
+        (returns None); otherwise the product, for the next norm to add.  With a `handoff` that expects a
+        norm, the kernel also leaves that norm's input there."""
         n = self._tokens(x)
         if stream is not None and self._skinny(n, self.out_features):
-            K.gemv(self.weight, n, add_into=stream, **self._source(x))
+            hand_over = None
+            norm = handoff.wanted if handoff is not None else None
+            if norm is not None and n <= K.SQUARES_ROWS and norm.gamma.numel() == self.out_features:
+                handed = HandedNorm(torch.empty((n, self.out_features), dtype=torch.bfloat16, device=stream.device),
+                                    torch.empty(((self.out_features + 15) // 16, K.SQUARES_ROWS), dtype=torch.float32,
+                                                device=stream.device))
+                hand_over = (norm.gamma, handed.scaled, handed.squares)
+            K.gemv(self.weight, n, add_into=stream, hand_over=hand_over, **self._source(x))
+            if hand_over is not None:
+                handoff.leave(stream, norm.gamma, handed)
             return None
         return self(x, out_dtype)
 

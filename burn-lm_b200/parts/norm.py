@@ -35,11 +35,15 @@ class RMSNorm(Part):
     def bind(self, loaded):
         self.gamma = loaded[self.tensor_names["weight"]]
 
-    def add_norm(self, resid, delta, rows=None, lazy=False):
+    takes_handed_norm = True      # a product that writes the stream may leave this norm's input (parts.linear.NormHandoff)
+
+    def add_norm(self, resid, delta, rows=None, lazy=False, handoff=None):
         """`lazy`: the caller can take a norm that is not computed yet (parts.linear.NormedStream);
-        it gets one when nothing has to be added into the stream first."""
+        it gets one when nothing has to be added into the stream first.  `handoff`: where the writer of
+        the stream may have left this norm's input."""
+        handed = handoff.claim(resid, self.gamma) if handoff is not None else None
         if lazy and delta is None:
-            return NormedStream(resid, self.gamma, self.spec.eps, rows, self.runtime.dtype)
+            return NormedStream(resid, self.gamma, self.spec.eps, rows, self.runtime.dtype, handed)
         n = rows.numel() if rows is not None else resid.shape[0]
         out = torch.empty((n, self.spec.size), dtype=self.runtime.dtype, device=resid.device)
         K.add_rmsnorm(resid, delta, self.gamma, self.spec.eps, out, rows)

@@ -372,6 +372,50 @@ def test_gemv_norm_prologue_swiglu_and_stream_add(n, gdt):
     assert (out.double() - want3).abs().max().item() < 1e-3 * want3.abs().max().item()
 
 
+@pytest.mark.parametrize("n", [1, 5, 8, 16])
+@pytest.mark.parametrize("gdt", DTYPES)
+@pytest.mark.parametrize("width,inner", [(192, 320), (2048, 512), (200 * 16 + 8, 64)])
+def test_gemv_hands_the_next_norm_over(n, gdt, width, inner):
+    """The product that adds into the stream also leaves bfloat16(stream * gamma) and the rows' sums of
+    squares by tiles; the product after it takes those instead of normalising the stream itself."""
+    g = torch.Generator(device="cuda").manual_seed(n + width)
+    act = torch.randn(n, inner, device="cuda", generator=g).to(torch.bfloat16)
+    wd = (torch.randn(width, inner, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    gamma = (1 + 0.1 * torch.randn(width, device="cuda", generator=g)).to(gdt)
+    stream = torch.randn(n, width, device="cuda", generator=g) * 3
+    stream[n // 2, 7] = 40.0           # one lane that dominates its row's sum of squares
+    before = stream.clone()
+    scaled = torch.full((n, width), float("nan"), device="cuda", dtype=torch.bfloat16)
+    squares = torch.full(((width + 15) // 16, 16), float("nan"), device="cuda")
+    K().gemv(wd, n, x=act, add_into=stream, hand_over=(gamma, scaled, squares))
+    new = before.double() + gemv_reference(wd, act)
+    assert (stream.double() - new).abs().max().item() < 2e-5 * new.abs().max().item()
+    want_scaled = stream.double() * gamma.double()
+    assert (scaled.double() - want_scaled).abs().max().item() <= 2 ** -8 * want_scaled.abs().max().item()
+    assert (squares[:, :n].double().sum(0) - (stream.double() ** 2).sum(-1)).abs().max().item() < 1e-5 * (stream.double() ** 2).sum(-1).max().item()
+    # the consumer: gathers rows, divides by the root mean square
+    eps = 1e-5
+    m = 136
+    w2 = (torch.randn(m, width, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    if width % 64:
+        return          # the producer takes any width; the consumer's K must be a multiple of 64
+    rows = torch.randperm(n, device="cuda", generator=g).to(torch.int32)
+    out = torch.empty(n, m, device="cuda")
+    K().gemv(w2, n, x=scaled, squares=squares, eps=eps, rows=rows, out=out)
+    h = stream.double()[rows.long()]
+    want = gemv_reference(w2, scaled[rows.long()]) / torch.sqrt((h * h).mean(-1, keepdim=True) + eps)
+    assert (out.double() - want).abs().max().item() < 1e-4 * want.abs().max().item()
+    # and it is the norm: against the stream normalised in one piece, up to bfloat16 rounding of the input
+    xn = h / torch.sqrt((h * h).mean(-1, keepdim=True) + eps) * gamma.double()
+    want_norm = xn @ w2.double().T
+    assert (out.double() - want_norm).abs().max().item() < 2e-2 * want_norm.abs().max().item()
+    # one token alone gives the same bits as in the batch
+    one = torch.empty(1, m, device="cuda")
+    K().gemv(w2, 1, x=scaled, squares=squares, eps=eps, rows=rows[:1].contiguous(), out=one)
+    assert torch.equal(one[0], out[0])
+    K().check_status("cuda")
+
+
 def test_gemv_refuses_what_it_cannot_do():
     k = K()
     assert not k.gemv_supported(17, 10, 64) and not k.gemv_supported(4, 10, 96)
