@@ -72,6 +72,9 @@ struct GemvArgs {
     int next_gamma_f32;
     __nv_bfloat16* xg_out;
     float* ssq_out;
+    // When every block has one tile, a token lane is used once per block: the tokens then travel with the
+    // weights, a box of [token rows x 256 k] behind the weight box of every stage, and nothing is staged.
+    int x_in_ring;
     int* status;             // device word: 0, or the first failure (a bounded wait ran out)
 };
 
@@ -117,6 +120,14 @@ __device__ __forceinline__ void tma_load_box(void* dst, const CUtensorMap* map, 
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(
             smem_u32(dst)),
         "l"(map), "r"(0), "r"(row0), "r"(chunk0), "r"(smem_u32(bar))
+        : "memory");
+}
+// the tokens' part of a stage: chunks [chunk0, chunk0 + 4) of all token rows (rows beyond N arrive as zeros)
+__device__ __forceinline__ void tma_load_tokens(void* dst, const CUtensorMap* map, int chunk0, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(0), "r"(0), "r"(chunk0), "r"(smem_u32(bar))
         : "memory");
 }
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerWarps * 32) : "memory"); }
@@ -201,7 +212,7 @@ __device__ __forceinline__ void gemv_stage_tokens(const GemvArgs& a, __nv_bfloat
 }
 
 template <int NBT>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap wmap) {
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap) {
     extern __shared__ __align__(1024) unsigned char smem[];
     constexpr int nrows = NBT * 8;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -209,8 +220,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
     const int xstride = kpad + 8;                                   // bf16 elements; 16 bytes of padding
     // layout: ring | tokens | partial sums of warps that share a tile | barriers
     unsigned char* ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);   // the swizzle wants 1024-byte alignment
-    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ring + (size_t)a.n_stages * kStageBytes);
-    float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs) + (size_t)nrows * xstride * 2);   // [warp][16][nrows]
+    constexpr int kTokenBytes = nrows * kStageK * 2;                 // the tokens' part of a stage: [4 chunks][nrows][128 bytes]
+    const int stage_bytes = kStageBytes + (a.x_in_ring ? kTokenBytes : 0);
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ring + (size_t)a.n_stages * stage_bytes);
+    float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs) +
+                                          (a.x_in_ring ? 0 : (size_t)nrows * xstride * 2));   // [warp][16][nrows]
     unsigned long long* full = reinterpret_cast<unsigned long long*>(red + kConsumerWarps * 16 * nrows);
     unsigned long long* empty = full + a.n_stages;
     unsigned long long* meet = empty + a.n_stages;     // where warps that share a tile meet (a bounded wait, like all)
@@ -253,6 +267,31 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
         unsigned q = 0;                   // how many stages warp w has been dealt
         bool more = w < kConsumerWarps && w < my_units;
         unsigned idle = 0;
+        if (a.x_in_ring) {
+            // The weights of the first stages go out at once; the tokens are the work of the kernel before,
+            // so their boxes follow after the wait, onto the same barriers.  (One tile per block: a warp
+            // has the one unit `w` of round 0.)
+            int pre = 0;
+            if (more) {
+                for (; pre < depth && pre < stages_per_slice; ++pre) {
+                    const int stage_of_tile = (w % ks) * stages_per_slice + pre;
+                    if (stage_of_tile >= stages_per_tile) break;
+                    const int slot = w * depth + pre;
+                    mbar_expect_tx(full + slot, stage_bytes);
+                    tma_load_box(ring + (size_t)slot * stage_bytes, &wmap, ((int)blockIdx.x + (w / ks) * (int)gridDim.x) * 16,
+                                 stage_of_tile * (kStageK / 64), full + slot);
+                }
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                const int slot = w * depth + i;
+                tma_load_tokens(ring + (size_t)slot * stage_bytes + kStageBytes, &xmap,
+                                ((w % ks) * stages_per_slice + i) * (kStageK / 64), full + slot);
+            }
+            q = pre;
+            st = pre;
+            if (more && (st == stages_per_slice || (w % ks) * stages_per_slice + st >= stages_per_tile)) { st = 0; ++round; }
+        }
         while (__any_sync(0xffffffffu, more)) {
             bool progressed = false;
             if (more) {
@@ -280,8 +319,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
                     }
                     if (free_slot) {
                         const int tile = blockIdx.x + (unit / ks) * gridDim.x;
-                        mbar_expect_tx(full + slot, kStageBytes);
-                        tma_load_box(ring + (size_t)slot * kStageBytes, &wmap, tile * 16, stage_of_tile * (kStageK / 64), full + slot);
+                        mbar_expect_tx(full + slot, stage_bytes);
+                        tma_load_box(ring + (size_t)slot * stage_bytes, &wmap, tile * 16, stage_of_tile * (kStageK / 64), full + slot);
+                        if (a.x_in_ring)
+                            tma_load_tokens(ring + (size_t)slot * stage_bytes + kStageBytes, &xmap, stage_of_tile * (kStageK / 64), full + slot);
                         ++q;
                         if (++st == stages_per_slice) { st = 0; ++round; }
                         progressed = true;
@@ -305,7 +346,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
     blm_trace(0x100 | a.epi);
     pdl_wait();
     blm_trace(0x110 | a.epi);
-    gemv_stage_tokens<NBT>(a, xs, xstride, kpad, tid, lane, warp);
+    if (!a.x_in_ring) gemv_stage_tokens<NBT>(a, xs, xstride, kpad, tid, lane, warp);
     if (a.ssq_in != nullptr) {
         // a warp per row: the parts in a fixed order (lane p, p + 32, ..., then the butterfly)
         for (int r = warp; r < nrows; r += kConsumerWarps) {
@@ -345,7 +386,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
                     failed = true;       // the status word says so; go on to where the others wait for this warp
                     break;
                 }
-                const unsigned char* stage = ring + (size_t)slot * kStageBytes;
+                const unsigned char* stage = ring + (size_t)slot * stage_bytes;
                 // The stage is 8 units of 32 k: chunk u / 2, 64-byte half u % 2; the 16-byte slot of a line is
                 // XORed with the line's number mod 8 (the 128-byte swizzle), here the row's.
 #pragma unroll
@@ -358,7 +399,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
                         const uint4 hi = *reinterpret_cast<const uint4*>(chunk + (g + 8) * 128 + ((s16 ^ g) << 4));
 #pragma unroll
                         for (int j = 0; j < NBT; ++j) {
-                            const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)(j * 8 + g) * xstride + k + 8 * t);
+                            // tokens: staged rows, or the stage's own box [chunk][token row][128 bytes], swizzled like the weights
+                            const uint4 xv = a.x_in_ring
+                                ? *reinterpret_cast<const uint4*>(stage + kStageBytes + (u >> 1) * (nrows * 128) + (j * 8 + g) * 128 + ((s16 ^ g) << 4))
+                                : *reinterpret_cast<const uint4*>(xs + (size_t)(j * 8 + g) * xstride + k + 8 * t);
                             mma16816(c[0][j], lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
                             mma16816(c[1][j], lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
                         }
@@ -502,18 +546,19 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
 }
 
 // Shared memory for a shape and the ring depth it leaves room for; 0 when the tokens do not fit.
-static size_t gemv_plan(int N, int K, int* n_stages_out, int* nbt_out) {
+static size_t gemv_plan(int N, int K, bool x_in_ring, int* n_stages_out, int* nbt_out) {
     int nbt = 1;
     while (nbt * 8 < N) nbt *= 2;
     if (nbt > 2) return 0;
     const int nrows = nbt * 8;
     const int kpad = (K + kStageK - 1) / kStageK * kStageK;
-    const size_t tokens = (size_t)nrows * (kpad + 8) * 2;
+    const size_t tokens = x_in_ring ? 0 : (size_t)nrows * (kpad + 8) * 2;
+    const size_t stage = kStageBytes + (x_in_ring ? (size_t)nrows * kStageK * 2 : 0);
     const size_t red = (size_t)kConsumerWarps * 16 * nrows * 4;
     const size_t limit = 220 * 1024;
     int stages = 16;
-    while (stages > 8 && (size_t)stages * kStageBytes + tokens + red + (size_t)stages * 16 + 128 + 1024 > limit) --stages;
-    const size_t total = (size_t)stages * kStageBytes + tokens + red + (size_t)stages * 16 + 128 + 1024;
+    while (stages > 8 && (size_t)stages * stage + tokens + red + (size_t)stages * 16 + 128 + 1024 > limit) --stages;
+    const size_t total = (size_t)stages * stage + tokens + red + (size_t)stages * 16 + 128 + 1024;
     if (total > limit) return 0;
     *n_stages_out = stages;
     *nbt_out = nbt;
@@ -523,7 +568,7 @@ static size_t gemv_plan(int N, int K, int* n_stages_out, int* nbt_out) {
 // 1 when blm_gemv takes the shape, else 0 (the caller then uses the library product).
 BLM_API int blm_gemv_supported(int N, int M, int K) {
     int st, nbt;
-    return N >= 1 && N <= 16 && K % 64 == 0 && M >= 1 && gemv_plan(N, K, &st, &nbt) > 0;
+    return N >= 1 && N <= 16 && K % 64 == 0 && M >= 1 && gemv_plan(N, K, false, &st, &nbt) > 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -561,6 +606,37 @@ static int weight_map(const void* w, long long ldw, int rows, int K, CUtensorMap
     return BLM_OK;
 }
 
+// The TMA's view of the tokens [N, K] (row stride ldx): dims (64 k, N, K / 64); box (64, token rows, 4).
+static int token_map(const void* x, long long ldx, int N, int K, int nrows, CUtensorMap* out) {
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+            return blm_fail(BLM_CUDA_ERROR, "gemv: the driver has no cuTensorMapEncodeTiled");
+        encode = (EncodeTiledFn)fn;
+    }
+    static std::map<std::tuple<const void*, long long, int, int, int>, CUtensorMap> cache;
+    const auto key = std::make_tuple(x, ldx, N, K, nrows);
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+        CUtensorMap m;
+        const cuuint64_t dims[3] = {64, (cuuint64_t)N, (cuuint64_t)(K / 64)};
+        const cuuint64_t strides[2] = {(cuuint64_t)ldx * 2, 128};
+        const cuuint32_t box[3] = {64, (cuuint32_t)nrows, kStageK / 64};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(x), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return blm_fail(BLM_CUDA_ERROR, "gemv: cuTensorMapEncodeTiled failed for the tokens (%d)", (int)r);
+        if (cache.size() > 4096) cache.clear();
+        it = cache.emplace(key, m).first;
+    }
+    *out = it->second;
+    return BLM_OK;
+}
+
 BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, long long ldx,
                      const float* resid, const void* gamma, int gamma_f32, float eps, const int* rows, int N,
                      void* y, long long ldy, int y_f32, float* acc, int epi, const float* ssq_in, int ssq_parts,
@@ -587,15 +663,27 @@ BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, 
     a.rows = rows; a.N = N; a.y = y; a.ldy = ldy; a.y_f32 = y_f32; a.acc = acc; a.epi = epi; a.status = status;
     a.ssq_in = ssq_in; a.ssq_parts = ssq_parts; a.next_gamma = next_gamma; a.next_gamma_f32 = next_gamma_f32;
     a.xg_out = (__nv_bfloat16*)xg_out; a.ssq_out = ssq_out;
-    int nbt;
-    const size_t smem = gemv_plan(N, K, &a.n_stages, &nbt);
-    BLM_REQUIRE(smem > 0, "gemv: the shape N=%d K=%d does not fit shared memory", N, K);
-    CUtensorMap wmap;
-    int rc = weight_map(w, ldw, epi == EPI_SWIGLU ? 2 * M : M, K, &wmap);
-    if (rc != BLM_OK) return rc;
     const int out_per_tile = epi == EPI_SWIGLU ? 8 : 16;
     const int tiles = (M + out_per_tile - 1) / out_per_tile;
     const int grid = tiles < 148 ? tiles : 148;
+    // one tile per block and plain tokens: the tokens travel with the weights
+    a.x_in_ring = tiles <= 148 && x != nullptr && rows == nullptr && ssq_in == nullptr && K >= 2 * kStageK;
+    int nbt;
+    size_t smem = gemv_plan(N, K, a.x_in_ring != 0, &a.n_stages, &nbt);
+    if (smem == 0 && a.x_in_ring) {
+        a.x_in_ring = 0;
+        smem = gemv_plan(N, K, false, &a.n_stages, &nbt);
+    }
+    BLM_REQUIRE(smem > 0, "gemv: the shape N=%d K=%d does not fit shared memory", N, K);
+    CUtensorMap wmap, xmap;
+    int rc = weight_map(w, ldw, epi == EPI_SWIGLU ? 2 * M : M, K, &wmap);
+    if (rc != BLM_OK) return rc;
+    if (a.x_in_ring) {
+        rc = token_map(x, ldx, N, K, nbt * 8, &xmap);
+        if (rc != BLM_OK) return rc;
+    } else {
+        xmap = wmap;      // not used
+    }
     // few tiles per block: several warps share a tile, each on a slice of K
     const int tiles_per_block = (tiles + grid - 1) / grid;
     const int stages_per_tile = (K + kStageK - 1) / kStageK;
@@ -608,7 +696,7 @@ BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, 
             if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "gemv: %s", cudaGetErrorString(e));
             opted_in[nbt] = true;
         }
-        cudaError_t e = blm_launch_dependent(kernel, dim3(grid), dim3(kGemvThreads), smem, stream, a, wmap);
+        cudaError_t e = blm_launch_dependent(kernel, dim3(grid), dim3(kGemvThreads), smem, stream, a, wmap, xmap);
         if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "gemv: %s", cudaGetErrorString(e));
         return blm_check_launch("gemv");
     };
