@@ -84,9 +84,10 @@ class Attention(Part):
         group = s.n_heads // s.n_kv_heads
         pages = (step.max_kv_len + K.PAGE - 1) // K.PAGE
         if K.attention_decode_is_specialised(self.runtime.dtype, s.head_dim, group):
-            # pages are shared out over enough blocks to fill the SMs about four times; with many sequences
-            # one block walks all pages of a (sequence, kv head) and nothing has to be combined
-            want = (4 * 148 + step.n_seqs * s.n_kv_heads - 1) // (step.n_seqs * s.n_kv_heads)
+            # pages are shared out over enough blocks to fill the SMs about twice (measured best at batch 8
+            # and 64); with many sequences one block walks all pages of a (sequence, kv head) and nothing
+            # has to be combined
+            want = (2 * 148 + step.n_seqs * s.n_kv_heads - 1) // (step.n_seqs * s.n_kv_heads)
             return max(1, min(pages, want, 64))
         blocks = step.n_seqs * s.n_kv_heads * ((group + 31) // 32)
         return max(1, min(pages, (_TARGET_BLOCKS + blocks - 1) // blocks, 64))
