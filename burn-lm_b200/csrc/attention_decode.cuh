@@ -28,6 +28,8 @@ struct AttnDecodeArgs {
     float* part_acc;             // [N, n_heads, n_splits, HD]
     float* part_ml;              // [N, n_heads, n_splits, 2]: (max in natural-log units, sum)
     int n_heads, n_kv, window, n_splits;
+    int n_stages;                // pages the ring of a block holds (a multiple of n_groups)
+    int n_groups;                // groups of four consumer warps; group g takes pages g, g + n_groups, ... of the block's
     float scale_log2e;           // softmax scale times log2(e): scores live in base-2 units
     int* status;                 // 0, or 21 / 22 when a bounded wait ran out
 };
@@ -72,8 +74,23 @@ __device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned b
 }
 }  // namespace attn_decode
 
-template <int HD>
-__host__ __device__ constexpr int attn_decode_stages() { return HD == 64 ? 4 : 3; }
+// How many pages the ring of a block holds.  With few blocks (one per SM or less) a block keeps all its
+// pages in flight at once, up to what shared memory takes; with many blocks several share an SM and the
+// rings are short.
+static inline int attn_decode_stages(int hd, int blocks, int pages_per_block) {
+    const int page_kb = 2 * 64 * hd * 2 / 1024;                    // keys and values of a page of one kv head
+    const int room_kb = blocks <= 148 ? 192 : (blocks <= 296 ? 96 : 64);
+    int s = room_kb / page_kb;
+    if (s > pages_per_block) s = pages_per_block;
+    return s < 2 ? 2 : s;
+}
+// Groups of consumer warps.  One warp per scheduler waits out every latency of its chain of dependent
+// instructions; when a block is (almost) alone on its SM, several groups work on different pages at once.
+static inline int attn_decode_groups(int blocks, int pages_per_block, int stages) {
+    int ng = blocks <= 148 ? 4 : (blocks <= 444 ? 2 : 1);
+    while (ng > 1 && (ng > pages_per_block || ng > stages)) ng /= 2;
+    return ng;
+}
 
 __device__ __forceinline__ void dec_ldmatrix_x4(unsigned (&r)[4], const void* p) {
     const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
@@ -95,11 +112,11 @@ __device__ __forceinline__ void dec_mma(float (&c)[4], const unsigned (&a)[4], u
 // instead of hundreds.  A page arrives as TMA boxes of 64 keys x 64 lanes with the 128-byte swizzle, which
 // ldmatrix reads without bank conflicts; the four consumer warps take 16 keys of every page each and keep
 // their own running (max, sum, output), merged at the end.
-template <int HD, int G>
-__global__ void __launch_bounds__(160) attn_decode_kernel(const AttnDecodeArgs a, const __grid_constant__ CUtensorMap pool_map) {
+template <int HD, int G, int NG>
+__global__ void __launch_bounds__((4 * NG + 1) * 32) attn_decode_kernel(const AttnDecodeArgs a, const __grid_constant__ CUtensorMap pool_map) {
     using namespace attn_decode;
-    constexpr int WARPS = 4;           // consumer warps; warp 4 is the producer
-    constexpr int S = attn_decode_stages<HD>();
+    constexpr int WARPS = 4 * NG;      // consumer warps (NG groups of four); the warp after them is the producer
+    const int S = a.n_stages;
     constexpr int SUB = HD / 64;       // 64-lane boxes per row
     constexpr int KS = HD / 16;        // k steps of Q K^T
     constexpr int DT = HD / 8;         // 8-wide output tiles
@@ -140,23 +157,33 @@ __global__ void __launch_bounds__(160) attn_decode_kernel(const AttnDecodeArgs a
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(full + s, 1);
-            mbar_init(empty + s, WARPS);
+            mbar_init(empty + s, 4);          // the four warps of the group that reads the stage
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
 
     if (warp == WARPS) {
-        // ---------------- producer: one thread streams the pages of this split ----------------
-        if (lane == 0) {
-            for (int i = 0, pg = pg_lo; pg < pg_hi; ++pg, ++i) {
-                const int s = i % S;
-                if (i >= S && !mbar_wait(empty + s, ((i / S) - 1) & 1)) {
+        // ---------------- producer: streams the pages of this split ----------------
+        // The warp reads the page numbers together, 32 at a time (one round trip instead of one per page);
+        // lane 0 issues the copies.
+        bool failed = false;
+        int s = -1;                       // the stage of page i and the parity of its barriers' current phase
+        unsigned phase = 0;
+        for (int base = pg_lo, i = 0; base < pg_hi; base += 32) {
+            const int mine = base + lane < pg_hi ? pages[base + lane] : 0;
+            const int n = min(32, pg_hi - base);
+            for (int j = 0; j < n; ++j, ++i) {
+                const int page = __shfl_sync(0xffffffffu, mine, j);
+                if (++s == S) { s = 0; phase ^= 1; }
+                if (lane != 0 || failed) continue;
+                if (i >= S && !mbar_wait(empty + s, phase ^ 1)) {
                     atomicCAS(a.status, 0, 22);
-                    break;
+                    failed = true;
+                    continue;
                 }
                 // rows of the pool seen as a matrix [pages * 2 * n_kv * 64, HD]: keys, then values, of a page
-                const int krow = ((pages[pg] * 2) * a.n_kv + kvh) * 64, vrow = krow + a.n_kv * 64;
+                const int krow = ((page * 2) * a.n_kv + kvh) * 64, vrow = krow + a.n_kv * 64;
                 mbar_expect_tx(full + s, 2 * PB);
                 unsigned char* dst = ring + (size_t)s * 2 * PB;
 #pragma unroll
@@ -173,7 +200,7 @@ __global__ void __launch_bounds__(160) attn_decode_kernel(const AttnDecodeArgs a
             }
         }
     } else {
-        // ---------------- consumers: warp w takes keys 16 w .. 16 w + 15 of every page ----------------
+        // ---------------- consumers: the warps of a group take 16 keys each of the group's pages ----------------
         // Q as the A operand: row g is head g of the group (rows G.. and 8.. are zero)
         unsigned qf[KS][4];
         {
@@ -194,12 +221,19 @@ __global__ void __launch_bounds__(160) attn_decode_kernel(const AttnDecodeArgs a
         float m_run = -INFINITY, l_run = 0.f;        // of row g (head g); every lane of a quad holds the same max
         auto swz = [](int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); };   // byte offset in a box
 
-        for (int i = 0, pg = pg_lo; pg < pg_hi; ++pg, ++i) {
-            const int s = i % S;
-            if (!mbar_wait(full + s, (i / S) & 1)) {
+        // This warp's group takes every NG-th page; the ring's depth is a multiple of NG, so a stage always
+        // serves the same group, which thus sees every phase of the stage's barriers.
+        const int group = warp >> 2, quarter = warp & 3;
+        int s = group - NG;
+        unsigned phase = 0;
+        for (int i = group, pg = pg_lo + group; pg < pg_hi; pg += NG, i += NG) {
+            s += NG;
+            if (s >= S) { s -= S; phase ^= 1; }
+            if (!mbar_wait(full + s, phase)) {
                 if (lane == 0) atomicCAS(a.status, 0, 21);
                 break;
             }
+            if (i == 0) blm_trace(0x430);
             const unsigned char* Kt = ring + (size_t)s * 2 * PB;
             const unsigned char* Vt = Kt + PB;
             // scores of this warp's 16 keys: two tiles of 8 keys
@@ -212,7 +246,7 @@ __global__ void __launch_bounds__(160) attn_decode_kernel(const AttnDecodeArgs a
                 for (int kk = 0; kk < KS; kk += 2) {
                     const int chunk = 2 * kk + (lane >> 3);           // 16-byte chunk of the row: k steps kk and kk + 1
                     unsigned kb[4];
-                    dec_ldmatrix_x4(kb, Kt + (chunk >> 3) * BOX + swz(warp * 16 + nt * 8 + (lane & 7), chunk & 7));
+                    dec_ldmatrix_x4(kb, Kt + (chunk >> 3) * BOX + swz(quarter * 16 + nt * 8 + (lane & 7), chunk & 7));
                     dec_mma(sc[nt], qf[kk], kb[0], kb[1]);
                     dec_mma(sc[nt], qf[kk + 1], kb[2], kb[3]);
                 }
@@ -223,7 +257,7 @@ __global__ void __launch_bounds__(160) attn_decode_kernel(const AttnDecodeArgs a
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    const int key = pg * 64 + warp * 16 + nt * 8 + 2 * t + e;
+                    const int key = pg * 64 + quarter * 16 + nt * 8 + 2 * t + e;
                     const float v = (key >= key_lo && key < kv_len) ? sc[nt][e] * a.scale_log2e : -INFINITY;
                     sc[nt][e] = v;
                     mx = fmaxf(mx, v);
@@ -258,8 +292,8 @@ __global__ void __launch_bounds__(160) attn_decode_kernel(const AttnDecodeArgs a
             }
             // A masked key has weight zero, but 0 x NaN is NaN: rows of the value tile that hold no key of
             // this sequence (a page's unwritten tail, keys before the window) are cleared before they are read.
-            if (pg * 64 + warp * 16 + 15 >= kv_len || pg * 64 + warp * 16 < key_lo) {
-                const int row = warp * 16 + (lane >> 1), key = pg * 64 + row;
+            if (pg * 64 + quarter * 16 + 15 >= kv_len || pg * 64 + quarter * 16 < key_lo) {
+                const int row = quarter * 16 + (lane >> 1), key = pg * 64 + row;
                 if (key >= kv_len || key < key_lo)
                     for (int c = lane & 1; c < HD / 8; c += 2)
                         *reinterpret_cast<uint4*>(const_cast<unsigned char*>(Vt) + (c >> 3) * BOX + swz(row, c & 7)) = make_uint4(0u, 0u, 0u, 0u);
@@ -270,13 +304,14 @@ __global__ void __launch_bounds__(160) attn_decode_kernel(const AttnDecodeArgs a
             for (int d = 0; d < DT; d += 2) {
                 const int chunk = d + (lane >> 4);
                 unsigned vb[4];
-                dec_ldmatrix_x4_trans(vb, Vt + (chunk >> 3) * BOX + swz(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, chunk & 7));
+                dec_ldmatrix_x4_trans(vb, Vt + (chunk >> 3) * BOX + swz(quarter * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, chunk & 7));
                 dec_mma(o[d], pf, vb[0], vb[1]);
                 dec_mma(o[d + 1], pf, vb[2], vb[3]);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty + s);      // this warp has read its keys of the page
         }
+        blm_trace(0x440);
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
         if (g < G) {
@@ -314,6 +349,7 @@ __global__ void __launch_bounds__(160) attn_decode_kernel(const AttnDecodeArgs a
             }
         }
     }
+    blm_trace(0x450);
 }
 
 // Merges the partial results of the active splits: one warp per (token, head).
@@ -392,18 +428,32 @@ static bool attn_decode_pool_map(const void* pool, int n_pages, int n_kv, int hd
     return true;
 }
 
-template <int HD, int G>
-static bool attn_decode_launch(const AttnDecodeArgs& a, dim3 grid, int n_pages, cudaStream_t stream) {
-    constexpr int S = attn_decode_stages<HD>();
-    const size_t smem = (size_t)S * 2 * 64 * HD * 2 + (size_t)4 * G * (HD + 2) * 4 + 2 * S * 8 + 16 + 1024;
+template <int HD, int G, int NG>
+static bool attn_decode_launch_ng(AttnDecodeArgs a, dim3 grid, int n_pages, cudaStream_t stream) {
+    auto bytes = [&](int stages) {
+        return (size_t)stages * 2 * 64 * HD * 2 + (size_t)4 * a.n_groups * G * (HD + 2) * 4 + 2 * stages * 8 + 16 + 1024;
+    };
+    while (bytes(a.n_stages) > 220 * 1024 && a.n_stages > a.n_groups) a.n_stages -= a.n_groups;   // the warps' results need room too
+    if (bytes(a.n_stages) > 220 * 1024) return false;
+    const size_t smem = bytes(a.n_stages);
     CUtensorMap map;
     if (!attn_decode_pool_map(a.pool, n_pages, a.n_kv, HD, &map)) return false;
     static bool opted_in = false;
     if (!opted_in) {
-        if (cudaFuncSetAttribute(attn_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+        if (cudaFuncSetAttribute(attn_decode_kernel<HD, G, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess) return false;
         opted_in = true;
     }
-    return blm_launch_dependent(attn_decode_kernel<HD, G>, grid, dim3(160), smem, stream, a, map) == cudaSuccess;
+    return blm_launch_dependent(attn_decode_kernel<HD, G, NG>, grid, dim3((4 * NG + 1) * 32), smem, stream, a, map) == cudaSuccess;
+}
+
+template <int HD, int G>
+static bool attn_decode_launch(const AttnDecodeArgs& a, dim3 grid, int n_pages, cudaStream_t stream) {
+    switch (a.n_groups) {
+        case 1: return attn_decode_launch_ng<HD, G, 1>(a, grid, n_pages, stream);
+        case 2: return attn_decode_launch_ng<HD, G, 2>(a, grid, n_pages, stream);
+        case 4: return attn_decode_launch_ng<HD, G, 4>(a, grid, n_pages, stream);
+        default: return false;
+    }
 }
 
 template <int HD>
@@ -418,8 +468,15 @@ static bool launch_attn_decode_g(const AttnDecodeArgs& a, int group, dim3 grid, 
 }
 
 // true when the specialised kernels were launched; false: the shape is left to the general kernel
-static bool launch_attn_decode(const AttnDecodeArgs& a, int hd, int group, int n_seqs, int n_pages, cudaStream_t stream) {
+static bool launch_attn_decode(AttnDecodeArgs a, int hd, int group, int n_seqs, int n_pages, int max_kv_len, cudaStream_t stream) {
     const dim3 grid(a.n_splits, a.n_kv, n_seqs);
+    // the longest walk of a block: the pages of the longest sequence (all the cache could hold, when the
+    // caller does not say), shared out over the splits
+    const int most_pages = max_kv_len > 0 ? (max_kv_len + 63) / 64 : 4 * a.n_splits;
+    const int blocks = a.n_splits * a.n_kv * n_seqs, pages_per_block = (most_pages + a.n_splits - 1) / a.n_splits;
+    a.n_stages = attn_decode_stages(hd, blocks, pages_per_block);
+    a.n_groups = attn_decode_groups(blocks, pages_per_block, a.n_stages);
+    a.n_stages -= a.n_stages % a.n_groups;
     const int n_rows = n_seqs * a.n_heads;
     if (hd == 64) {
         if (!launch_attn_decode_g<64>(a, group, grid, n_pages, stream)) return false;

@@ -62,7 +62,7 @@ _protos = {
     "attention": {
         "blm_attention": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                          c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p],
+                          c_int, c_int, c_float, c_int, c_void_p, c_int, c_int, c_void_p],
     },
     "gemm": {
         "blm_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
@@ -235,7 +235,8 @@ def attention_scratch_floats(n_tokens, n_heads, head_dim, n_splits):
 
 
 def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos, out, n_tokens, n_seqs,
-              max_q_len, n_heads, n_kv, head_dim, scale, window=0, n_splits=1, scratch=None, general_only=False):
+              max_q_len, n_heads, n_kv, head_dim, scale, window=0, n_splits=1, scratch=None, general_only=False,
+              max_kv_len=0):
     """Causal grouped-query attention of the step's tokens over the paged cache (after the append).
 
     q: tensor whose token n, head h starts at element n * q_stride + h * head_dim (the qkv buffer).
@@ -244,7 +245,8 @@ def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos
     blocks and combines the partial results; it needs `scratch` (float32,
     attention_scratch_floats(...) elements).  bfloat16 steps of one token per sequence with a head
     size of 64 or 128 and 1, 2, 4 or 8 query heads per kv head run a specialised kernel unless
-    `general_only`."""
+    `general_only`; `max_kv_len` (the longest sequence after the step, when known) lets it size its
+    rings of pages."""
     _need_cuda(q, pool, block_table, cu_seqlens, slot_of_seq, start_pos, out, scratch)
     if tuple(out.shape) != (n_tokens, n_heads * head_dim) or out.dtype != q.dtype or pool.dtype != q.dtype:
         raise KernelError("attention: out must be [N, heads * head_dim] in q's dtype, as the pool")
@@ -257,7 +259,7 @@ def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos
     _call("attention", "blm_attention", _ptr(q), q_stride, _ptr(pool), _code(q.dtype), _ptr(block_table),
           block_table.shape[1], _ptr(cu_seqlens), _ptr(slot_of_seq), _ptr(start_pos), _ptr(out), _ptr(scratch),
           n_tokens, n_seqs, max_q_len, n_heads, n_kv, head_dim, PAGE, int(window or 0), n_splits,
-          c_float(scale), 1 if general_only else 0, _ptr(status_word(q.device)), pool.shape[0], _stream(),
+          c_float(scale), 1 if general_only else 0, _ptr(status_word(q.device)), pool.shape[0], int(max_kv_len), _stream(),
           kernels=2 if n_splits > 1 else 1)
 
 

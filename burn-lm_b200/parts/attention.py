@@ -84,11 +84,13 @@ class Attention(Part):
         group = s.n_heads // s.n_kv_heads
         pages = (step.max_kv_len + K.PAGE - 1) // K.PAGE
         if K.attention_decode_is_specialised(self.runtime.dtype, s.head_dim, group):
-            # pages are shared out over enough blocks to fill the SMs about twice (measured best at batch 8
-            # and 64); with many sequences one block walks all pages of a (sequence, kv head) and nothing
-            # has to be combined
-            want = (2 * 148 + step.n_seqs * s.n_kv_heads - 1) // (step.n_seqs * s.n_kv_heads)
-            return max(1, min(pages, want, 64))
+            # One block walks all pages of a (sequence, kv head) while they fit its ring of about twelve
+            # pages (sixteen still stream well): its groups of warps work on several pages at once and nothing is combined
+            # (measured best at batch 1, 8 and 64 with 9 pages).  Longer sequences are cut into a ring's
+            # worth per block, as far as that still helps to fill the SMs about twice.
+            by_length = (pages + 15) // 16
+            to_fill = (2 * 148 + step.n_seqs * s.n_kv_heads - 1) // (step.n_seqs * s.n_kv_heads)
+            return max(1, min(by_length, to_fill, pages, 64))
         blocks = step.n_seqs * s.n_kv_heads * ((group + 31) // 32)
         return max(1, min(pages, (_TARGET_BLOCKS + blocks - 1) // blocks, 64))
 
@@ -116,5 +118,5 @@ class Attention(Part):
             scratch = step.workspace.scratch("attention", K.attention_scratch_floats(n, s.n_heads, s.head_dim, n_splits))
         K.attention(qkv, qkv.shape[1], cache.pool, cache.block_table, step.cu_seqlens, step.slot_of_seq,
                     step.start_pos, out, n, step.n_seqs, step.max_q_len, s.n_heads, s.n_kv_heads, s.head_dim,
-                    self.scale, window=s.window or 0, n_splits=n_splits, scratch=scratch)
+                    self.scale, window=s.window or 0, n_splits=n_splits, scratch=scratch, max_kv_len=step.max_kv_len)
         return self.o.into_stream(out, stream, rt.dtype, handoff=getattr(step, "handoff", None))
