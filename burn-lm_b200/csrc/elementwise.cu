@@ -166,7 +166,9 @@ BLM_API int blm_add_rmsnorm(float* resid, const void* delta, const void* gamma, 
 //   cache pool of one layer: [pages][2 (k, v)][KV][page_size][hd].
 //   The angle pos * inv_freq[i] and its sine and cosine are computed in fp64 and applied in fp32,
 //   so no position is too far for the table and long contexts lose nothing to the angle.
-//   pairing 0: lanes (i, i + rot/2); pairing 1: lanes (2i, 2i + 1).  rot == 0: no rotation.
+//   pairing 0: lanes (i, i + rot/2); pairing 1: lanes (2i, 2i + 1); pairing 2: pair i sits at lanes
+//   (16 (i / 8) + i % 8, that + 8), the order in which a 16-row tile of a matrix product holds the pairs
+//   of a head whose rows were dealt out that way.  rot == 0: no rotation.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ token_seq,
@@ -208,7 +210,8 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ 
             c = (float)cd;
             s = (float)sd;
         }
-        const int la = pairing ? 2 * i : i, lb = pairing ? 2 * i + 1 : i + half;
+        const int la = pairing == 1 ? 2 * i : (pairing == 2 ? 16 * (i >> 3) + (i & 7) : i);
+        const int lb = pairing == 1 ? la + 1 : (pairing == 2 ? la + 8 : i + half);
         T* hp = row + (size_t)h * hd;
         const float a = to_f32(hp[la]), b = to_f32(hp[lb]);
         const T ra = from_f32<T>(a * c - b * s), rb = from_f32<T>(a * s + b * c);
@@ -229,13 +232,13 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ 
     }
 }
 
-// bf16, the whole head rotated, pairs (i, i + hd/2), hd a multiple of 16, positions inside the table: eight
-// pairs per thread with 16-byte accesses
+// bf16, the whole head rotated, pairs (i, i + hd/2) or tiled (`tiled`: pairing 2 above), hd a multiple of 16,
+// positions inside the table: eight pairs per thread with 16-byte accesses
 __global__ void rope_append_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ token_seq,
                                             const int* __restrict__ token_pos, const int* __restrict__ slot_of_seq,
                                             const int* __restrict__ block_table, int table_stride,
                                             __nv_bfloat16* __restrict__ pool, int n_heads, int n_kv, int hd, int page_size,
-                                            int write_cache, const float2* __restrict__ table) {
+                                            int write_cache, const float2* __restrict__ table, int tiled) {
     pdl_launch_dependents();
     pdl_wait();
     blm_trace(0x210);
@@ -260,7 +263,8 @@ __global__ void rope_append_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, con
     if (item < n_rot) {
         const int h = item / cpp, i = (item % cpp) * 8;
         __nv_bfloat16* hp = row + (size_t)h * hd;
-        const uint4 av = *reinterpret_cast<const uint4*>(hp + i), bv = *reinterpret_cast<const uint4*>(hp + i + half);
+        const int la = tiled ? 2 * i : i, lb = tiled ? 2 * i + 8 : i + half;      // where the eight pairs' two halves lie
+        const uint4 av = *reinterpret_cast<const uint4*>(hp + la), bv = *reinterpret_cast<const uint4*>(hp + lb);
         const float4* cs = reinterpret_cast<const float4*>(table + (size_t)pos * half + i);
         const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&av);
         const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&bv);
@@ -275,8 +279,8 @@ __global__ void rope_append_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, con
             rbp[e] = __floats2bfloat162_rn(a2.x * t.y + b2.x * t.x, a2.y * t.w + b2.y * t.z);
         }
         __nv_bfloat16* dst = (h < n_heads || !kdst) ? hp : kdst + (size_t)(h - n_heads) * head_stride_cache;
-        *reinterpret_cast<uint4*>(dst + i) = ra;
-        *reinterpret_cast<uint4*>(dst + i + half) = rb;
+        *reinterpret_cast<uint4*>(dst + la) = ra;
+        *reinterpret_cast<uint4*>(dst + lb) = rb;
     } else {
         const int j = item - n_rot;
         const int h = j / (hd >> 3), l = (j % (hd >> 3)) * 8;
@@ -293,7 +297,8 @@ BLM_API int blm_rope_append(void* qkv, int dtype, const int* token_seq, const in
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(rot >= 0 && rot <= hd && rot % 2 == 0, "rotary: %d rotated lanes of a head of %d", rot, hd);
     BLM_REQUIRE(rot == 0 || inv_freq != nullptr, "rotary: no frequencies");
-    BLM_REQUIRE(pairing == 0 || pairing == 1, "rotary: pairing %d", pairing);
+    BLM_REQUIRE(pairing >= 0 && pairing <= 2, "rotary: pairing %d", pairing);
+    BLM_REQUIRE(pairing != 2 || rot % 16 == 0, "rotary: tiled pairs need a multiple of 16 rotated lanes, got %d", rot);
     BLM_REQUIRE(hd % 2 == 0, "rotary: odd head size %d", hd);
     const int threads = 128;
     const int items = (n_heads + n_kv) * (rot / 2) + (write_cache ? n_kv * (hd - rot) + n_kv * (hd / 2) : 0);
@@ -301,7 +306,7 @@ BLM_API int blm_rope_append(void* qkv, int dtype, const int* token_seq, const in
     const dim3 grid((items + threads - 1) / threads, n_tokens);
     BLM_REQUIRE(grid.y <= 65535, "rotary: %d tokens in one step (at most 65535)", n_tokens);
     const size_t smem = 0;
-    if (dtype == BLM_BF16 && rot == hd && pairing == 0 && hd % 16 == 0 && table != nullptr && table_len > 0 &&
+    if (dtype == BLM_BF16 && rot == hd && pairing != 1 && hd % 16 == 0 && table != nullptr && table_len > 0 &&
         ((size_t)qkv & 15) == 0 && (!write_cache || ((size_t)pool & 15) == 0) && ((size_t)table & 15) == 0) {
         // every position of the step must lie inside the table for this path; the host makes the table
         // as long as the cache's longest sequence, and a step never goes beyond that
@@ -310,7 +315,7 @@ BLM_API int blm_rope_append(void* qkv, int dtype, const int* token_seq, const in
         if (table_covers_step) {
             blm_launch_dependent(rope_append_bf16_vec_kernel, vgrid, dim3(threads), 0, stream, (__nv_bfloat16*)qkv, token_seq, token_pos,
                                  slot_of_seq, block_table, table_stride, (__nv_bfloat16*)pool, n_heads, n_kv, hd, page_size,
-                                 write_cache, table);
+                                 write_cache, table, pairing == 2 ? 1 : 0);
             return blm_check_launch("rope_append");
         }
     }

@@ -38,7 +38,22 @@ constexpr int kStageK = 256;                              // k elements per stag
 constexpr int kStageBytes = 16 * kStageK * 2;             // [4 chunks][16 rows][128 bytes], swizzled
 constexpr unsigned kSpinLimit = 1u << 20;   // polls of a wait before it gives up (seconds; a real wait is microseconds)
 
-enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESID_ADD = 2 };
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESID_ADD = 2, EPI_ROPE = 3 };
+
+// EPI_ROPE: the product is a step's q, k and v (heads in that order); q and k are rotated by their token's
+// position and the rotated k and the v go straight to the token's place in the paged cache, q to y.  The
+// rows of every q and k head are dealt out so that a 16-row tile holds eight pairs: rows 0..7 the lanes
+// 8j .. 8j + 7 of the head, rows 8..15 their partners (lanes + hd / 2); a thread then has both halves of
+// its pairs in registers.  q and k keep that order of lanes (a dot product does not mind), v the stored one.
+struct GemvRope {
+    const int* token_pos;        // [N] position of every token
+    const int* token_seq;        // [N] the token's sequence in the step
+    const int* slot_of_seq;      // cache slot of every sequence
+    const int* block_table;      // [slots][table_stride] pages of every slot
+    const float2* table;         // (cos, sin) [positions][hd / 2]; covers every position of the step
+    __nv_bfloat16* pool;         // [pages][2][n_kv][page_size][hd] of this cache line
+    int table_stride, n_heads, n_kv, hd, page_size, write_cache;
+};
 enum { GEMV_OK = 0, GEMV_TIMEOUT_FULL = 1, GEMV_TIMEOUT_EMPTY = 2 };
 
 struct GemvArgs {
@@ -75,6 +90,7 @@ struct GemvArgs {
     // When every block has one tile, a token lane is used once per block: the tokens then travel with the
     // weights, a box of [token rows x 256 k] behind the weight box of every stage, and nothing is staged.
     int x_in_ring;
+    GemvRope rope;           // EPI_ROPE
     int* status;             // device word: 0, or the first failure (a bounded wait ran out)
 };
 
@@ -513,6 +529,40 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
             }
             continue;
         }
+        if (a.epi == EPI_ROPE) {
+            const GemvRope& r = a.rope;
+            const int tiles_per_head = r.hd >> 4, head = tile / tiles_per_head, jt = tile % tiles_per_head;
+            const int half = r.hd >> 1;
+            const size_t head_stride_cache = (size_t)r.page_size * r.hd, page_elems = (size_t)r.n_kv * head_stride_cache;
+#pragma unroll
+            for (int j = 0; j < NBT; ++j)
+#pragma unroll
+                for (int bb = 0; bb < 2; ++bb) {
+                    const int b = j * 8 + 2 * t + bb;
+                    if (b >= a.N || tile * 16 >= a.M) continue;
+                    float lo = c[0][j][bb] + c[1][j][bb], hi = c[0][j][2 + bb] + c[1][j][2 + bb];   // rows g and g + 8
+                    const int pos = r.token_pos[b];
+                    if (head < r.n_heads + r.n_kv) {
+                        const float2 cs = r.table[(size_t)pos * half + 8 * jt + g];
+                        const float rl = lo * cs.x - hi * cs.y, rh = lo * cs.y + hi * cs.x;
+                        lo = rl;
+                        hi = rh;
+                    }
+                    __nv_bfloat16* dst;
+                    if (head < r.n_heads) {
+                        dst = reinterpret_cast<__nv_bfloat16*>(a.y) + (size_t)b * a.ldy + (size_t)head * r.hd;
+                    } else {
+                        const int slot = r.slot_of_seq[r.token_seq[b]];
+                        const int page = r.block_table[(size_t)slot * r.table_stride + pos / r.page_size];
+                        const int kvh = head - r.n_heads;          // k heads, then v heads
+                        dst = r.pool + (size_t)page * 2 * page_elems + (size_t)(pos % r.page_size) * r.hd +
+                              (kvh < r.n_kv ? (size_t)kvh * head_stride_cache : page_elems + (size_t)(kvh - r.n_kv) * head_stride_cache);
+                    }
+                    dst[16 * jt + g] = __float2bfloat16_rn(lo);
+                    dst[16 * jt + g + 8] = __float2bfloat16_rn(hi);
+                }
+            continue;
+        }
 #pragma unroll
         for (int j = 0; j < NBT; ++j) {
             const float v00 = c[0][j][0] + c[1][j][0], v01 = c[0][j][1] + c[1][j][1];   // row g
@@ -640,15 +690,23 @@ static int token_map(const void* x, long long ldx, int N, int K, int nrows, CUte
 BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, long long ldx,
                      const float* resid, const void* gamma, int gamma_f32, float eps, const int* rows, int N,
                      void* y, long long ldy, int y_f32, float* acc, int epi, const float* ssq_in, int ssq_parts,
-                     const void* next_gamma, int next_gamma_f32, void* xg_out, float* ssq_out, int* status,
-                     cudaStream_t stream) {
+                     const void* next_gamma, int next_gamma_f32, void* xg_out, float* ssq_out, const GemvRope* rope,
+                     int* status, cudaStream_t stream) {
     if (N == 0 || M == 0) return BLM_OK;
     BLM_REQUIRE(N >= 1 && N <= 16, "gemv: %d tokens (1..16)", N);
     BLM_REQUIRE(K % 64 == 0 && K >= 64, "gemv: K = %d must be a multiple of 64", K);
     BLM_REQUIRE((x != nullptr) != (resid != nullptr), "gemv: give either x or the stream to normalise");
     BLM_REQUIRE(x == nullptr || (ldx % 8 == 0 && ((size_t)x & 15) == 0), "gemv: x rows must be 16-byte aligned");
     BLM_REQUIRE(ldw % 8 == 0 && ((size_t)w & 15) == 0, "gemv: weight rows must be 16-byte aligned");
-    BLM_REQUIRE(epi == EPI_STORE || epi == EPI_SWIGLU || epi == EPI_RESID_ADD, "gemv: epilogue %d", epi);
+    BLM_REQUIRE(epi == EPI_STORE || epi == EPI_SWIGLU || epi == EPI_RESID_ADD || epi == EPI_ROPE, "gemv: epilogue %d", epi);
+    if (epi == EPI_ROPE) {
+        BLM_REQUIRE(rope != nullptr && rope->token_pos && rope->table && y_f32 == 0, "gemv: the rotary epilogue needs positions, a table and a bfloat16 q");
+        BLM_REQUIRE(rope->hd % 16 == 0 && rope->hd >= 16, "gemv: the rotary epilogue takes head sizes in steps of 16, got %d", rope->hd);
+        BLM_REQUIRE(M == (rope->n_heads + (rope->write_cache ? 2 * rope->n_kv : 0)) * rope->hd,
+                    "gemv: %d outputs are not %d q heads%s of %d lanes", M, rope->n_heads, rope->write_cache ? " and the k and v heads" : "", rope->hd);
+        BLM_REQUIRE(!rope->write_cache || (rope->pool && rope->token_seq && rope->slot_of_seq && rope->block_table && rope->page_size > 0),
+                    "gemv: the rotary epilogue writes the cache and needs its pool and tables");
+    }
     BLM_REQUIRE(epi != EPI_SWIGLU || M % 8 == 0, "gemv: the gated epilogue needs an inner size that is a multiple of 8, got %d", M);
     BLM_REQUIRE(epi != EPI_RESID_ADD || acc != nullptr, "gemv: no stream to add into");
     BLM_REQUIRE(epi == EPI_RESID_ADD || y != nullptr, "gemv: no output");
@@ -663,6 +721,8 @@ BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, 
     a.rows = rows; a.N = N; a.y = y; a.ldy = ldy; a.y_f32 = y_f32; a.acc = acc; a.epi = epi; a.status = status;
     a.ssq_in = ssq_in; a.ssq_parts = ssq_parts; a.next_gamma = next_gamma; a.next_gamma_f32 = next_gamma_f32;
     a.xg_out = (__nv_bfloat16*)xg_out; a.ssq_out = ssq_out;
+    if (epi == EPI_ROPE) a.rope = *rope;
+    else a.rope = GemvRope{};
     const int out_per_tile = epi == EPI_SWIGLU ? 8 : 16;
     const int tiles = (M + out_per_tile - 1) / out_per_tile;
     const int grid = tiles < 148 ? tiles : 148;

@@ -71,7 +71,7 @@ _protos = {
     "gemv": {
         "blm_gemv": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
                      c_float, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int,
-                     c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+                     c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "blm_gemv_supported": [c_int, c_int, c_int],
     },
     "gemm_tc": {
@@ -165,9 +165,16 @@ def rope_table(inv_freq, n_positions):
     return table
 
 
+PAIRS_HALVES, PAIRS_INTERLEAVED, PAIRS_TILED = 0, 1, 2
+
+
 def rope_append(qkv, token_seq, token_pos, slot_of_seq, block_table, inv_freq, rotary_dim, interleaved,
                 pool, n_heads, n_kv, head_dim, write_cache=True, table=None, max_position=None):
     """Rotate q (in place) and k of every token by its position, and append k, v to the paged cache.
+
+    `interleaved`: False or PAIRS_HALVES: pair i is lanes (i, i + rotary_dim / 2); True or
+    PAIRS_INTERLEAVED: lanes (2i, 2i + 1); PAIRS_TILED: lanes (16 (i // 8) + i % 8, that + 8), the order
+    of a head whose weight rows were dealt out with tiled_pair_order().
 
     qkv [N, (n_heads + 2 n_kv) * head_dim]; pool [pages, 2, n_kv, PAGE, head_dim] of one cache line;
     inv_freq float64 [rotary_dim / 2] or None when rotary_dim == 0; `table` (from rope_table) spares
@@ -187,9 +194,16 @@ def rope_append(qkv, token_seq, token_pos, slot_of_seq, block_table, inv_freq, r
             raise KernelError("rope_append: inv_freq must be float64 [rotary_dim / 2]")
     _call("elementwise", "blm_rope_append", _ptr(qkv), _code(qkv.dtype), _ptr(token_seq), _ptr(token_pos),
           _ptr(slot_of_seq), _ptr(block_table), block_table.shape[1], _ptr(inv_freq), rotary_dim,
-          1 if interleaved else 0, _ptr(pool), n, n_heads, n_kv, head_dim, PAGE, 1 if write_cache else 0,
+          int(interleaved), _ptr(pool), n, n_heads, n_kv, head_dim, PAGE, 1 if write_cache else 0,
           _ptr(table), table.shape[0] if table is not None else 0,
           1 if (table is not None and max_position is not None and max_position < table.shape[0]) else 0, _stream())
+
+
+def tiled_pair_order(head_dim: int) -> list:
+    """For PAIRS_TILED: which lane of a head (in the stored order, pairs (i, i + head_dim / 2)) goes to each
+    place: every 16 places hold lanes 8j .. 8j + 7 and then their partners."""
+    half = head_dim // 2
+    return [(8 * (p // 16) + p % 16) if p % 16 < 8 else (half + 8 * (p // 16) + p % 16 - 8) for p in range(head_dim)]
 
 
 GATE_TILE = 8   # a fused [gate; up] weight for the skinny kernel: tiles of 8 gate rows, then their 8 up rows
@@ -278,7 +292,13 @@ def gemm_f32(x, w, out=None):
     return out
 
 
-EPI_STORE, EPI_SWIGLU, EPI_RESID_ADD = 0, 1, 2
+EPI_STORE, EPI_SWIGLU, EPI_RESID_ADD, EPI_ROPE = 0, 1, 2, 3
+
+
+class _GemvRope(ctypes.Structure):
+    _fields_ = [("token_pos", c_void_p), ("token_seq", c_void_p), ("slot_of_seq", c_void_p), ("block_table", c_void_p),
+                ("table", c_void_p), ("pool", c_void_p), ("table_stride", c_int), ("n_heads", c_int), ("n_kv", c_int),
+                ("hd", c_int), ("page_size", c_int), ("write_cache", c_int)]
 
 
 def gemv_supported(n_tokens, m, k) -> bool:
@@ -334,7 +354,7 @@ SQUARES_ROWS = 16     # row length of the sums of squares that go with a handed-
 
 
 def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, out=None, add_into=None, swiglu=False,
-         squares=None, hand_over=None):
+         squares=None, hand_over=None, rope=None):
     """Skinny product of n_tokens <= 16 tokens with a bfloat16 weight [M, K], with fused ends.
 
     Input: `x` bfloat16 [N, K], or the fp32 residual stream `stream_rows` [*, K] to be RMS-normalised
@@ -347,13 +367,35 @@ def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, 
     `add_into` (fp32 [N, M]) the product is added into it and nothing else is written, unless
     `hand_over` = (gamma, scaled, squares) asks for the next norm's input as well: scaled
     (bfloat16 [N, M]) = the new stream times gamma, squares (fp32 [ceil(M / 16), SQUARES_ROWS]) its
-    sums of squares by tiles of 16 lanes."""
+    sums of squares by tiles of 16 lanes.
+    With `rope` (a dict: token_pos, token_seq, slot_of_seq, block_table, table from rope_table, pool,
+    n_heads, n_kv, head_dim, write_cache, max_position) the weight is a step's [q; k; v] (or q alone without
+    write_cache) whose q and k heads have their rows in tiled_pair_order(): q and k are rotated by their
+    token's position, q goes to `out` [N, n_heads * head_dim] (lanes in that order), the rotated k and the
+    v to the token's place in `pool`."""
     _need_cuda(w, x, stream_rows, gamma, rows, out, add_into, squares)
     m_rows, k = w.shape
     if w.dtype != torch.bfloat16:
         raise KernelError("gemv: the weight must be bfloat16")
     m = m_rows // 2 if swiglu else m_rows
-    epi = EPI_SWIGLU if swiglu else (EPI_RESID_ADD if add_into is not None else EPI_STORE)
+    epi = EPI_SWIGLU if swiglu else (EPI_RESID_ADD if add_into is not None else (EPI_ROPE if rope is not None else EPI_STORE))
+    rope_arg = None
+    if rope is not None:
+        if swiglu or add_into is not None:
+            raise KernelError("gemv: one epilogue at a time")
+        r = rope
+        hd, table, pool = r["head_dim"], r["table"], r["pool"]
+        _need_cuda(r["token_pos"], r["token_seq"], r["slot_of_seq"], r["block_table"], table, pool)
+        if table is None or table.dtype != torch.float32 or tuple(table.shape[1:]) != (hd // 2, 2) \
+                or r.get("max_position") is None or r["max_position"] >= table.shape[0]:
+            raise KernelError("gemv: the rotary epilogue needs a table [positions, head_dim / 2, 2] that covers the step")
+        if r["write_cache"] and (pool.dtype != torch.bfloat16 or tuple(pool.shape[1:]) != (2, r["n_kv"], PAGE, hd)):
+            raise KernelError(f"gemv: pool must be bfloat16 [pages, 2, {r['n_kv']}, {PAGE}, {hd}]")
+        if out is None or out.dtype != torch.bfloat16 or tuple(out.shape) != (n_tokens, r["n_heads"] * hd):
+            raise KernelError("gemv: the rotary epilogue writes q to a bfloat16 out [N, n_heads * head_dim]")
+        rope_arg = _GemvRope(r["token_pos"].data_ptr(), r["token_seq"].data_ptr(), r["slot_of_seq"].data_ptr(),
+                             r["block_table"].data_ptr(), table.data_ptr(), pool.data_ptr() if pool is not None else 0,
+                             r["block_table"].shape[1], r["n_heads"], r["n_kv"], hd, PAGE, 1 if r["write_cache"] else 0)
     if x is not None and (x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != k
                           or (rows is None and x.shape[0] != n_tokens)):
         raise KernelError("gemv: x must be bfloat16 [N, K]")
@@ -377,6 +419,8 @@ def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, 
     if epi == EPI_RESID_ADD:
         if add_into.dtype != torch.float32 or tuple(add_into.shape) != (n_tokens, m):
             raise KernelError("gemv: add_into must be float32 [N, M]")
+    elif epi == EPI_ROPE:
+        pass
     elif out is None or tuple(out.shape) != (n_tokens, m) or out.dtype not in (torch.bfloat16, torch.float32) \
             or (swiglu and out.dtype != torch.bfloat16):
         raise KernelError("gemv: out must be [N, M] bfloat16 (or float32 for a plain store)")
@@ -386,7 +430,8 @@ def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, 
           1 if (out is not None and out.dtype == torch.float32) else 0, _ptr(add_into), epi,
           _ptr(squares), squares.shape[0] if squares is not None else 0,
           _ptr(next_gamma), 1 if (next_gamma is not None and next_gamma.dtype == torch.float32) else 0,
-          _ptr(scaled), _ptr(squares_out), _ptr(status_word(w.device)), _stream())
+          _ptr(scaled), _ptr(squares_out), ctypes.byref(rope_arg) if rope_arg is not None else None,
+          _ptr(status_word(w.device)), _stream())
 
 
 def argmax(logits, out):

@@ -63,6 +63,18 @@ class Attention(Part):
         q, k, v = loaded[t["q"]], loaded[t["k"]], loaded[t["v"]]
         if not (q.dtype == k.dtype == v.dtype):
             raise ValueError(f"{t['q']}, {t['k']}, {t['v']} are stored in different dtypes")
+        # bfloat16 heads that are rotated whole, in pairs (i, i + head_dim / 2): the rows of every q and k head
+        # are dealt out in tiles of eight lanes and their eight partners, so that the skinny product can
+        # rotate in its epilogue (kernels.tiled_pair_order).  q and k then carry their lanes in that order
+        # everywhere, in the cache too; their dot products do not notice.
+        s = self.spec
+        _, rot, interleaved = self.position.rotation() if hasattr(self.position, "rotation") else (None, 0, False)
+        self.pairs = K.PAIRS_INTERLEAVED if interleaved else K.PAIRS_HALVES
+        if q.dtype == torch.bfloat16 and rot == s.head_dim and not interleaved:
+            order = torch.tensor(K.tiled_pair_order(s.head_dim), device=q.device)
+            q = q.view(s.n_heads, s.head_dim, -1)[:, order].reshape(q.shape)
+            k = k.view(s.n_kv_heads, s.head_dim, -1)[:, order].reshape(k.shape)
+            self.pairs = K.PAIRS_TILED
         fused = torch.cat([q, k, v], dim=0).contiguous()
         self.qkv = Linear(fused)
         self.q_only = Linear(fused[: self.spec.n_heads * self.spec.head_dim])
@@ -102,15 +114,21 @@ class Attention(Part):
         inv_freq, rot, interleaved = self.position.rotation()
         table = self.position.table() if hasattr(self.position, "table") else None
         n = step.n_tokens
-        if cache.writes:
-            qkv = self.qkv(x, out_dtype=rt.dtype)
-            n_kv_in_row = s.n_kv_heads
-        else:  # this run reads the cache line another run has written: only q is needed
-            qkv = self.q_only(x, out_dtype=rt.dtype)
-            n_kv_in_row = 0
-        K.rope_append(qkv, step.token_seq, step.token_pos, step.slot_of_seq, cache.block_table, inv_freq, rot,
-                      interleaved, cache.pool, s.n_heads, n_kv_in_row, s.head_dim, write_cache=cache.writes, table=table,
-                      max_position=step.max_kv_len - 1)
+        product = self.qkv if cache.writes else self.q_only     # a run that reads another run's cache line needs q only
+        qkv = None
+        if self.pairs == K.PAIRS_TILED and table is not None and step.max_kv_len <= table.shape[0]:
+            # few tokens: the skinny product rotates and appends in its epilogue and leaves q
+            q = torch.empty((n, s.n_heads * s.head_dim), dtype=rt.dtype, device=cache.pool.device)
+            rope = dict(token_pos=step.token_pos, token_seq=step.token_seq, slot_of_seq=step.slot_of_seq,
+                        block_table=cache.block_table, table=table, pool=cache.pool, n_heads=s.n_heads,
+                        n_kv=s.n_kv_heads, head_dim=s.head_dim, write_cache=cache.writes, max_position=step.max_kv_len - 1)
+            if product.with_rotary(x, q, rope):
+                qkv = q
+        if qkv is None:
+            qkv = product(x, out_dtype=rt.dtype)
+            K.rope_append(qkv, step.token_seq, step.token_pos, step.slot_of_seq, cache.block_table, inv_freq, rot,
+                          self.pairs, cache.pool, s.n_heads, s.n_kv_heads if cache.writes else 0, s.head_dim,
+                          write_cache=cache.writes, table=table, max_position=step.max_kv_len - 1)
         out = torch.empty((n, s.n_heads * s.head_dim), dtype=rt.dtype, device=qkv.device)
         n_splits = self._splits(step)
         scratch = None

@@ -143,6 +143,16 @@ class Linear:
             return None
         return self(x, out_dtype)
 
+    def with_rotary(self, x, q_out: torch.Tensor, rope: dict) -> bool:
+        """For a [q; k; v] weight whose q and k rows are in kernels.tiled_pair_order(): when the skinny kernel
+        takes the step, it rotates q and k and appends k and v to the cache in its epilogue, writes q to
+        `q_out` and this returns True; else nothing is done."""
+        n = self._tokens(x)
+        if q_out.dtype != torch.bfloat16 or not self._skinny(n, self.out_features):
+            return False
+        K.gemv(self.weight, n, out=q_out, rope=rope, **self._source(x))
+        return True
+
     def gated(self, x, out_dtype: torch.dtype) -> torch.Tensor:
         """silu(x Wgate^T) * (x Wup^T) for a fused [gate; up] weight."""
         n = self._tokens(x)

@@ -416,6 +416,84 @@ def test_gemv_hands_the_next_norm_over(n, gdt, width, inner):
     K().check_status("cuda")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd", [32, 64, 112])
+def test_rope_tiled_pairs(dtype, hd):
+    """Pairs dealt out in tiles (eight lanes, then their eight partners) rotate like the pairs
+    (i, i + hd / 2) they came from: both kernels, with and without a table."""
+    k = K()
+    H, KV = 3, 2
+    lens_before, lens_new = [0, 70, 5], [9, 1, 66]
+    order = torch.tensor(k.tiled_pair_order(hd), device="cuda")
+    inv_freq = torch.tensor([1e4 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(hd)
+    n = sum(lens_new)
+    qkv = torch.randn(n, (H + 2 * KV) * hd, device="cuda", generator=g).to(dtype)
+    dealt = qkv.clone().view(n, H + 2 * KV, hd)
+    dealt[:, : H + KV] = dealt[:, : H + KV][:, :, order]
+    dealt = dealt.reshape(n, -1).contiguous()
+    for table_len in (0, 40, 200):          # no table; one that covers some positions; one that covers the step
+        a, b = qkv.clone(), dealt.clone()
+        sa = paged_setup(lens_before, lens_new, KV, hd, dtype, seed=3)
+        sb = paged_setup(lens_before, lens_new, KV, hd, dtype, seed=3)
+        table = k.rope_table(inv_freq, table_len) if table_len else None
+        mp = max(x + y for x, y in zip(lens_before, lens_new)) - 1
+        k.rope_append(a, sa["token_seq"], sa["token_pos"], sa["slots"], sa["table"], inv_freq, hd, k.PAIRS_HALVES, sa["pool"], H, KV, hd,
+                      table=table, max_position=mp)
+        k.rope_append(b, sb["token_seq"], sb["token_pos"], sb["slots"], sb["table"], inv_freq, hd, k.PAIRS_TILED, sb["pool"], H, KV, hd,
+                      table=table, max_position=mp)
+        want = a.view(n, H + 2 * KV, hd).clone()
+        want[:, : H + KV] = want[:, : H + KV][:, :, order]
+        tol = dict(rtol=0, atol=0) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)   # the vector kernel fuses a product
+        torch.testing.assert_close(b.view(n, H + 2 * KV, hd)[:, :H].float(), want[:, :H].float(), **tol)
+        pa, pb = torch.nan_to_num(sa["pool"].float()), torch.nan_to_num(sb["pool"].float())
+        torch.testing.assert_close(pb[:, 0], pa[:, 0][..., order], **tol)
+        assert torch.equal(pb[:, 1], pa[:, 1])
+        assert torch.equal(torch.isnan(sa["pool"].float()), torch.isnan(sb["pool"].float()))
+
+
+@pytest.mark.parametrize("n", [1, 7, 16])
+@pytest.mark.parametrize("H,KV,hd,width", [(4, 2, 64, 256), (3, 1, 32, 192), (6, 3, 128, 512)])
+@pytest.mark.parametrize("write_cache", [True, False])
+def test_gemv_rotary_epilogue(n, H, KV, hd, width, write_cache):
+    """The skinny product that rotates q and k and appends k and v in its epilogue, against the plain
+    product followed by the rotary kernel."""
+    k = K()
+    g = torch.Generator(device="cuda").manual_seed(n * 7 + hd)
+    heads = H + (2 * KV if write_cache else 0)
+    w = (torch.randn(heads * hd, width, device="cuda", generator=g) * 0.08).to(torch.bfloat16)
+    x = torch.randn(n, width, device="cuda", generator=g).to(torch.bfloat16)
+    order = torch.tensor(k.tiled_pair_order(hd), device="cuda")
+    dealt = w.clone().view(heads, hd, width)
+    dealt[: H + (KV if write_cache else 0)] = dealt[: H + (KV if write_cache else 0)][:, order]
+    dealt = dealt.reshape(heads * hd, width).contiguous()
+    lens_before = [5 + 37 * i for i in range(n)]                 # one token per sequence, pages 0..n
+    inv_freq = torch.tensor([5e5 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64, device="cuda")
+    table = k.rope_table(inv_freq, max(lens_before) + 2)
+    sa = paged_setup(lens_before, [1] * n, KV, hd, torch.bfloat16, seed=5)
+    sb = paged_setup(lens_before, [1] * n, KV, hd, torch.bfloat16, seed=5)
+    # the plain way, in the stored order of lanes
+    qkv = torch.empty(n, heads * hd, device="cuda", dtype=torch.bfloat16)
+    k.gemv(w, n, x=x, out=qkv)
+    k.rope_append(qkv, sa["token_seq"], sa["token_pos"], sa["slots"], sa["table"], inv_freq, hd, k.PAIRS_HALVES, sa["pool"], H,
+                  KV if write_cache else 0, hd, write_cache=write_cache, table=table, max_position=max(lens_before))
+    q_want = qkv[:, : H * hd].reshape(n, H, hd)[:, :, order].float()
+    # fused
+    q = torch.full((n, H * hd), float("nan"), device="cuda", dtype=torch.bfloat16)
+    rope = dict(token_pos=sb["token_pos"], token_seq=sb["token_seq"], slot_of_seq=sb["slots"], block_table=sb["table"], table=table,
+                pool=sb["pool"], n_heads=H, n_kv=KV, head_dim=hd, write_cache=write_cache, max_position=max(lens_before))
+    k.gemv(dealt, n, x=x, out=q, rope=rope)
+    scale = q_want.abs().max().item()
+    assert (q.view(n, H, hd).float() - q_want).abs().max().item() < 1.5e-2 * scale      # one rounding to bfloat16 less
+    pa, pb = sa["pool"].float(), sb["pool"].float()
+    assert torch.equal(torch.isnan(pa), torch.isnan(pb))                                # the same places written, no other
+    if write_cache:
+        pa, pb = torch.nan_to_num(pa), torch.nan_to_num(pb)
+        assert (pb[:, 0] - pa[:, 0][..., order]).abs().max().item() < 1.5e-2 * pa[:, 0].abs().max().item()
+        assert torch.equal(pb[:, 1], pa[:, 1])
+    k.check_status("cuda")
+
+
 def test_gemv_refuses_what_it_cannot_do():
     k = K()
     assert not k.gemv_supported(17, 10, 64) and not k.gemv_supported(4, 10, 96)
