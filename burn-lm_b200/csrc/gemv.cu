@@ -55,6 +55,7 @@ struct GemvRope {
     int table_stride, n_heads, n_kv, hd, page_size, write_cache;
 };
 enum { GEMV_OK = 0, GEMV_TIMEOUT_FULL = 1, GEMV_TIMEOUT_EMPTY = 2 };
+enum { X_STAGED = 0, X_IN_RING = 1, X_BY_TMA = 2 };
 
 struct GemvArgs {
     const __nv_bfloat16* w;
@@ -87,9 +88,13 @@ struct GemvArgs {
     int next_gamma_f32;
     __nv_bfloat16* xg_out;
     float* ssq_out;
-    // When every block has one tile, a token lane is used once per block: the tokens then travel with the
-    // weights, a box of [token rows x 256 k] behind the weight box of every stage, and nothing is staged.
-    int x_in_ring;
+    // How plain tokens reach shared memory.  X_STAGED: the consumers copy them (or normalise the stream)
+    // before they start.  X_IN_RING: every block has one tile, so a token lane is used once per block and
+    // the tokens travel with the weights, a box of [token rows x 256 k] behind the weight box of every
+    // stage.  X_BY_TMA: the producer fetches them once, in chunks of 256 k with a barrier each, and a
+    // consumer only waits for the chunk it is about to use: the first weights are worked on while the
+    // later tokens are still on their way.
+    int x_mode;
     GemvRope rope;           // EPI_ROPE
     int* status;             // device word: 0, or the first failure (a bounded wait ran out)
 };
@@ -237,14 +242,16 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
     // layout: ring | tokens | partial sums of warps that share a tile | barriers
     unsigned char* ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);   // the swizzle wants 1024-byte alignment
     constexpr int kTokenBytes = nrows * kStageK * 2;                 // the tokens' part of a stage: [4 chunks][nrows][128 bytes]
-    const int stage_bytes = kStageBytes + (a.x_in_ring ? kTokenBytes : 0);
+    const int stage_bytes = kStageBytes + (a.x_mode == X_IN_RING ? kTokenBytes : 0);
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ring + (size_t)a.n_stages * stage_bytes);
-    float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs) +
-                                          (a.x_in_ring ? 0 : (size_t)nrows * xstride * 2));   // [warp][16][nrows]
+    // X_STAGED: [nrows][xstride]; X_BY_TMA: [chunks of 256 k][4][nrows][128 bytes], swizzled like a stage
+    const size_t xs_bytes = a.x_mode == X_IN_RING ? 0 : (a.x_mode == X_BY_TMA ? (size_t)nrows * kpad * 2 : (size_t)nrows * xstride * 2);
+    float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs) + xs_bytes);   // [warp][16][nrows]
     unsigned long long* full = reinterpret_cast<unsigned long long*>(red + kConsumerWarps * 16 * nrows);
     unsigned long long* empty = full + a.n_stages;
     unsigned long long* meet = empty + a.n_stages;     // where warps that share a tile meet (a bounded wait, like all)
     float* row_scale = reinterpret_cast<float*>(meet + 1);          // [16]: 1 / rms of a handed-over norm's rows
+    unsigned long long* xfull = reinterpret_cast<unsigned long long*>(row_scale + 16);   // X_BY_TMA: one per chunk of 256 k
 
     const int out_per_tile = a.epi == EPI_SWIGLU ? 8 : 16;
     const int n_tiles = (a.M + out_per_tile - 1) / out_per_tile;
@@ -267,6 +274,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
             mbar_init(empty + s, 1);
         }
         mbar_init(meet, kConsumerWarps);
+        if (a.x_mode == X_BY_TMA)
+            for (int ch = 0; ch < kpad / kStageK; ++ch) mbar_init(xfull + ch, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
@@ -283,10 +292,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
         unsigned q = 0;                   // how many stages warp w has been dealt
         bool more = w < kConsumerWarps && w < my_units;
         unsigned idle = 0;
-        if (a.x_in_ring) {
-            // The weights of the first stages go out at once; the tokens are the work of the kernel before,
-            // so their boxes follow after the wait, onto the same barriers.  (One tile per block: a warp
-            // has the one unit `w` of round 0.)
+        if (a.x_mode != X_STAGED) {
+            // The weights of the first stages (of the warps' units of round 0) go out at once; the tokens
+            // are the work of the kernel before, so they follow after the wait: with the weights, onto
+            // the same barriers, or in chunks of their own, one lane a chunk.
             int pre = 0;
             if (more) {
                 for (; pre < depth && pre < stages_per_slice; ++pre) {
@@ -299,10 +308,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
                 }
             }
             pdl_wait();
-            for (int i = 0; i < pre; ++i) {
-                const int slot = w * depth + i;
-                tma_load_tokens(ring + (size_t)slot * stage_bytes + kStageBytes, &xmap,
-                                ((w % ks) * stages_per_slice + i) * (kStageK / 64), full + slot);
+            if (a.x_mode == X_IN_RING) {
+                for (int i = 0; i < pre; ++i) {
+                    const int slot = w * depth + i;
+                    tma_load_tokens(ring + (size_t)slot * stage_bytes + kStageBytes, &xmap,
+                                    ((w % ks) * stages_per_slice + i) * (kStageK / 64), full + slot);
+                }
+            } else if (my_units > 0) {
+                for (int ch = lane; ch < stages_per_tile; ch += 32) {
+                    mbar_expect_tx(xfull + ch, kTokenBytes);
+                    tma_load_tokens(reinterpret_cast<unsigned char*>(xs) + (size_t)ch * kTokenBytes, &xmap, ch * (kStageK / 64), xfull + ch);
+                }
             }
             q = pre;
             st = pre;
@@ -337,7 +353,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
                         const int tile = blockIdx.x + (unit / ks) * gridDim.x;
                         mbar_expect_tx(full + slot, stage_bytes);
                         tma_load_box(ring + (size_t)slot * stage_bytes, &wmap, tile * 16, stage_of_tile * (kStageK / 64), full + slot);
-                        if (a.x_in_ring)
+                        if (a.x_mode == X_IN_RING)
                             tma_load_tokens(ring + (size_t)slot * stage_bytes + kStageBytes, &xmap, stage_of_tile * (kStageK / 64), full + slot);
                         ++q;
                         if (++st == stages_per_slice) { st = 0; ++round; }
@@ -362,7 +378,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
     blm_trace(0x100 | a.epi);
     pdl_wait();
     blm_trace(0x110 | a.epi);
-    if (!a.x_in_ring) gemv_stage_tokens<NBT>(a, xs, xstride, kpad, tid, lane, warp);
+    if (a.x_mode == X_STAGED) gemv_stage_tokens<NBT>(a, xs, xstride, kpad, tid, lane, warp);
     if (a.ssq_in != nullptr) {
         // a warp per row: the parts in a fixed order (lane p, p + 32, ..., then the butterfly)
         for (int r = warp; r < nrows; r += kConsumerWarps) {
@@ -403,6 +419,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
                     break;
                 }
                 const unsigned char* stage = ring + (size_t)slot * stage_bytes;
+                if (a.x_mode == X_BY_TMA && !mbar_wait(xfull + stage_of_tile, 0)) {      // this chunk of the tokens (it arrives once)
+                    if (lane == 0) atomicCAS(a.status, GEMV_OK, GEMV_TIMEOUT_FULL);
+                    failed = true;
+                    break;
+                }
+                // where this stage's tokens lie when they are swizzled boxes [4][nrows][128 bytes]
+                const unsigned char* xbox = a.x_mode == X_IN_RING ? stage + kStageBytes
+                                                                  : reinterpret_cast<const unsigned char*>(xs) + (size_t)stage_of_tile * kTokenBytes;
                 // The stage is 8 units of 32 k: chunk u / 2, 64-byte half u % 2; the 16-byte slot of a line is
                 // XORed with the line's number mod 8 (the 128-byte swizzle), here the row's.
 #pragma unroll
@@ -416,8 +440,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
 #pragma unroll
                         for (int j = 0; j < NBT; ++j) {
                             // tokens: staged rows, or the stage's own box [chunk][token row][128 bytes], swizzled like the weights
-                            const uint4 xv = a.x_in_ring
-                                ? *reinterpret_cast<const uint4*>(stage + kStageBytes + (u >> 1) * (nrows * 128) + (j * 8 + g) * 128 + ((s16 ^ g) << 4))
+                            const uint4 xv = a.x_mode != X_STAGED
+                                ? *reinterpret_cast<const uint4*>(xbox + (u >> 1) * (nrows * 128) + (j * 8 + g) * 128 + ((s16 ^ g) << 4))
                                 : *reinterpret_cast<const uint4*>(xs + (size_t)(j * 8 + g) * xstride + k + 8 * t);
                             mma16816(c[0][j], lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
                             mma16816(c[1][j], lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
@@ -596,19 +620,20 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
 }
 
 // Shared memory for a shape and the ring depth it leaves room for; 0 when the tokens do not fit.
-static size_t gemv_plan(int N, int K, bool x_in_ring, int* n_stages_out, int* nbt_out) {
+static size_t gemv_plan(int N, int K, int x_mode, int* n_stages_out, int* nbt_out) {
     int nbt = 1;
     while (nbt * 8 < N) nbt *= 2;
     if (nbt > 2) return 0;
     const int nrows = nbt * 8;
     const int kpad = (K + kStageK - 1) / kStageK * kStageK;
-    const size_t tokens = x_in_ring ? 0 : (size_t)nrows * (kpad + 8) * 2;
-    const size_t stage = kStageBytes + (x_in_ring ? (size_t)nrows * kStageK * 2 : 0);
+    const size_t tokens = x_mode == X_IN_RING ? 0 : (x_mode == X_BY_TMA ? (size_t)nrows * kpad * 2 : (size_t)nrows * (kpad + 8) * 2);
+    const size_t stage = kStageBytes + (x_mode == X_IN_RING ? (size_t)nrows * kStageK * 2 : 0);
+    const size_t fixed = 128 + 1024 + (size_t)(kpad / kStageK) * 8;      // the other barriers, the row scales, alignment
     const size_t red = (size_t)kConsumerWarps * 16 * nrows * 4;
     const size_t limit = 220 * 1024;
     int stages = 16;
-    while (stages > 8 && (size_t)stages * stage + tokens + red + (size_t)stages * 16 + 128 + 1024 > limit) --stages;
-    const size_t total = (size_t)stages * stage + tokens + red + (size_t)stages * 16 + 128 + 1024;
+    while (stages > 8 && (size_t)stages * stage + tokens + red + (size_t)stages * 16 + fixed > limit) --stages;
+    const size_t total = (size_t)stages * stage + tokens + red + (size_t)stages * 16 + fixed;
     if (total > limit) return 0;
     *n_stages_out = stages;
     *nbt_out = nbt;
@@ -618,7 +643,7 @@ static size_t gemv_plan(int N, int K, bool x_in_ring, int* n_stages_out, int* nb
 // 1 when blm_gemv takes the shape, else 0 (the caller then uses the library product).
 BLM_API int blm_gemv_supported(int N, int M, int K) {
     int st, nbt;
-    return N >= 1 && N <= 16 && K % 64 == 0 && M >= 1 && gemv_plan(N, K, false, &st, &nbt) > 0;
+    return N >= 1 && N <= 16 && K % 64 == 0 && M >= 1 && gemv_plan(N, K, X_STAGED, &st, &nbt) > 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -727,18 +752,20 @@ BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, 
     const int tiles = (M + out_per_tile - 1) / out_per_tile;
     const int grid = tiles < 148 ? tiles : 148;
     // one tile per block and plain tokens: the tokens travel with the weights
-    a.x_in_ring = tiles <= 148 && x != nullptr && rows == nullptr && ssq_in == nullptr && K >= 2 * kStageK;
+    a.x_mode = X_STAGED;
+    if (x != nullptr && rows == nullptr)
+        a.x_mode = (tiles <= 148 && ssq_in == nullptr && K >= 2 * kStageK) ? X_IN_RING : X_BY_TMA;
     int nbt;
-    size_t smem = gemv_plan(N, K, a.x_in_ring != 0, &a.n_stages, &nbt);
-    if (smem == 0 && a.x_in_ring) {
-        a.x_in_ring = 0;
-        smem = gemv_plan(N, K, false, &a.n_stages, &nbt);
+    size_t smem = gemv_plan(N, K, a.x_mode, &a.n_stages, &nbt);
+    if (smem == 0 && a.x_mode != X_STAGED) {
+        a.x_mode = X_STAGED;
+        smem = gemv_plan(N, K, X_STAGED, &a.n_stages, &nbt);
     }
     BLM_REQUIRE(smem > 0, "gemv: the shape N=%d K=%d does not fit shared memory", N, K);
     CUtensorMap wmap, xmap;
     int rc = weight_map(w, ldw, epi == EPI_SWIGLU ? 2 * M : M, K, &wmap);
     if (rc != BLM_OK) return rc;
-    if (a.x_in_ring) {
+    if (a.x_mode != X_STAGED) {
         rc = token_map(x, ldx, N, K, nbt * 8, &xmap);
         if (rc != BLM_OK) return rc;
     } else {
