@@ -76,7 +76,6 @@ struct GemvArgs {
     float* acc;              // EPI_RESID_ADD: fp32 [N, M] (ld = M)
     int epi;
     int n_stages;            // ring depth
-    int ksplit;              // warps that share a tile, each walking 1/ksplit of K (1, 2, 4 or 8)
     // A norm handed over by the kernel that wrote the stream: x is bf16(stream * gamma), not yet divided by
     // the root mean square; ssq_in[part][16] holds, for each stream row, sums of squares whose total over
     // the parts is the row's; the result is scaled by 1 / sqrt(total / K + eps) per row.
@@ -252,16 +251,20 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
     unsigned long long* meet = empty + a.n_stages;     // where warps that share a tile meet (a bounded wait, like all)
     float* row_scale = reinterpret_cast<float*>(meet + 1);          // [16]: 1 / rms of a handed-over norm's rows
     unsigned long long* xfull = reinterpret_cast<unsigned long long*>(row_scale + 16);   // X_BY_TMA: one per chunk of 256 k
+    long long* rope_cache = reinterpret_cast<long long*>(xfull + kpad / kStageK);          // EPI_ROPE [16]: where a token's k row of kv head 0 starts in the pool
+    int* rope_pos = reinterpret_cast<int*>(rope_cache + 16);                              // EPI_ROPE [16]: the tokens' positions
 
     const int out_per_tile = a.epi == EPI_SWIGLU ? 8 : 16;
     const int n_tiles = (a.M + out_per_tile - 1) / out_per_tile;
     const int stages_per_tile = kpad / kStageK;
-    // A unit of work is (tile, slice of K): `ksplit` warps share a tile when a block has few tiles.
+    // A unit of work is (tile, slice of K): `ks` warps share a tile when a block has few tiles.
     // This block's tiles are blockIdx.x, blockIdx.x + gridDim.x, ...; its work units go to the warps
     // in turn, in rounds of eight.
-    const int ks = a.ksplit;
-    const int stages_per_slice = (stages_per_tile + ks - 1) / ks;
     const int my_tiles = n_tiles > (int)blockIdx.x ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    // few tiles in this block: several warps share a tile, each on a slice of K (1, 2, 4 or 8 of them)
+    int ks = 1;
+    while (ks * 2 * my_tiles <= kConsumerWarps && ks * 2 <= stages_per_tile) ks *= 2;
+    const int stages_per_slice = (stages_per_tile + ks - 1) / ks;
     const int my_units = my_tiles * ks;
     const int n_rounds = (my_units + kConsumerWarps - 1) / kConsumerWarps;
     // the ring is dealt out to the warps that work (fewer units than warps: fewer, deeper parts); a warp
@@ -391,6 +394,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
             if (lane == 0) row_scale[r] = r < a.N ? 1.0f / sqrtf(ssq / (float)a.K + a.eps) : 0.f;
         }
     }
+    if (a.epi == EPI_ROPE && tid < a.N) {
+        // the chain token -> sequence -> slot -> page, walked once here instead of by every thread of the epilogue
+        const GemvRope& r = a.rope;
+        const int pos = r.token_pos[tid];
+        rope_pos[tid] = pos;
+        if (r.write_cache) {
+            const int slot = r.slot_of_seq[r.token_seq[tid]];
+            const int page = r.block_table[(size_t)slot * r.table_stride + pos / r.page_size];
+            rope_cache[tid] = ((long long)page * 2 * r.n_kv * r.page_size + pos % r.page_size) * r.hd;
+        }
+    }
     consumer_barrier();
     blm_trace(0x120 | a.epi);
 
@@ -454,7 +468,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
         }
         if (ks > 1) {
             // warps that share a tile: the partial sums meet in shared memory; the warp of slice 0 adds them
-            // in a fixed order.  With a split there is a single round (a block has at most 8 / ksplit tiles).
+            // in a fixed order.  With a split there is a single round (a block has at most 8 / ks tiles).
             float* mine = red + (size_t)warp * 16 * nrows;
 #pragma unroll
             for (int j = 0; j < NBT; ++j) {
@@ -565,7 +579,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
                     const int b = j * 8 + 2 * t + bb;
                     if (b >= a.N || tile * 16 >= a.M) continue;
                     float lo = c[0][j][bb] + c[1][j][bb], hi = c[0][j][2 + bb] + c[1][j][2 + bb];   // rows g and g + 8
-                    const int pos = r.token_pos[b];
+                    const int pos = rope_pos[b];
                     if (head < r.n_heads + r.n_kv) {
                         const float2 cs = r.table[(size_t)pos * half + 8 * jt + g];
                         const float rl = lo * cs.x - hi * cs.y, rh = lo * cs.y + hi * cs.x;
@@ -576,10 +590,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
                     if (head < r.n_heads) {
                         dst = reinterpret_cast<__nv_bfloat16*>(a.y) + (size_t)b * a.ldy + (size_t)head * r.hd;
                     } else {
-                        const int slot = r.slot_of_seq[r.token_seq[b]];
-                        const int page = r.block_table[(size_t)slot * r.table_stride + pos / r.page_size];
                         const int kvh = head - r.n_heads;          // k heads, then v heads
-                        dst = r.pool + (size_t)page * 2 * page_elems + (size_t)(pos % r.page_size) * r.hd +
+                        dst = r.pool + rope_cache[b] +
                               (kvh < r.n_kv ? (size_t)kvh * head_stride_cache : page_elems + (size_t)(kvh - r.n_kv) * head_stride_cache);
                     }
                     dst[16 * jt + g] = __float2bfloat16_rn(lo);
@@ -628,7 +640,7 @@ static size_t gemv_plan(int N, int K, int x_mode, int* n_stages_out, int* nbt_ou
     const int kpad = (K + kStageK - 1) / kStageK * kStageK;
     const size_t tokens = x_mode == X_IN_RING ? 0 : (x_mode == X_BY_TMA ? (size_t)nrows * kpad * 2 : (size_t)nrows * (kpad + 8) * 2);
     const size_t stage = kStageBytes + (x_mode == X_IN_RING ? (size_t)nrows * kStageK * 2 : 0);
-    const size_t fixed = 128 + 1024 + (size_t)(kpad / kStageK) * 8;      // the other barriers, the row scales, alignment
+    const size_t fixed = 128 + 1024 + (size_t)(kpad / kStageK) * 8 + 256;      // the other barriers, the row scales, the rotary epilogue's tables, alignment
     const size_t red = (size_t)kConsumerWarps * 16 * nrows * 4;
     const size_t limit = 220 * 1024;
     int stages = 16;
@@ -771,11 +783,6 @@ BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, 
     } else {
         xmap = wmap;      // not used
     }
-    // few tiles per block: several warps share a tile, each on a slice of K
-    const int tiles_per_block = (tiles + grid - 1) / grid;
-    const int stages_per_tile = (K + kStageK - 1) / kStageK;
-    a.ksplit = 1;
-    while (a.ksplit * 2 * tiles_per_block <= kConsumerWarps && a.ksplit * 2 <= stages_per_tile) a.ksplit *= 2;
     static bool opted_in[3] = {false, false, false};     // per token-tile variant of the kernel
     auto launch = [&](auto kernel) -> int {
         if (!opted_in[nbt]) {
