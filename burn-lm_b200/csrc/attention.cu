@@ -11,6 +11,7 @@
 
 #include "attention_decode.cuh"
 #include "attention_prefill.cuh"
+#include "attention_prefill_tc.cuh"
 #include "common.cuh"
 
 BLM_API const char* blm_attention_last_error() { return g_blm_error; }
@@ -366,6 +367,16 @@ BLM_API int blm_attention(const void* q, long long q_stride, const void* pool, i
         f.slot_of_seq = slot_of_seq; f.start_pos = start_pos; f.out = (__nv_bfloat16*)out;
         f.n_heads = n_heads; f.n_kv = n_kv; f.window = window; f.scale_log2e = scale * 1.4426950408889634f;
         BLM_REQUIRE(q_stride % 8 == 0 && ((size_t)q & 15) == 0, "attention: q rows must be 16-byte aligned");
+        if (max_q_len >= 64 && status != nullptr && n_pages > 0 && ((size_t)pool & 15) == 0) {
+            // long prompts: the products on tcgen05, accumulators in tensor memory
+            AttnPrefillTcArgs t;
+            t.block_table = block_table; t.table_stride = table_stride; t.cu_seqlens = cu_seqlens; t.slot_of_seq = slot_of_seq;
+            t.start_pos = start_pos; t.out = (__nv_bfloat16*)out; t.n_heads = n_heads; t.n_kv = n_kv; t.window = window;
+            t.scale_log2e = f.scale_log2e; t.status = status;
+            const int rc = launch_attn_prefill_tc(t, q, q_stride, pool, n_pages, hd, n_tokens, n_seqs, max_q_len, stream);
+            if (rc == BLM_OK) return blm_check_launch("attention prefill (tcgen05)");
+            if (rc > 0) return rc;
+        }
         if (launch_attn_prefill(f, hd, n_seqs, max_q_len, stream)) return blm_check_launch("attention prefill");
     }
     AttnArgs a;

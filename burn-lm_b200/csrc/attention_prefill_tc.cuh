@@ -1,0 +1,465 @@
+// Prompt attention on the 5th-generation tensor cores (bf16, head size 64 or 128): causal grouped-query
+// attention of a step's new tokens over the paged cache, the products on tcgen05 with their accumulators
+// in tensor memory.
+//
+// A block owns 128 query rows of one head of one sequence and walks the keys in blocks of 128 (two cache
+// pages).  Warp 0 (one thread) is the producer: TMA tile loads with the 128-byte swizzle of the query
+// tile (once, from the step's q rows), of the keys (a ring of two stages) and of the values (one stage),
+// completion on mbarriers.  Warp 1 (one thread) issues the products: S = Q K^T (M 128, N 128, both
+// operands K-major in shared memory) into tensor memory, and, once the softmax warps have written the
+// probabilities, PV = P V (A = P from shared memory, B = V as it lies in the cache, keys by lanes, read
+// MN-major) into other columns; tcgen05.commit frees the stages and tells the softmax warps.  Warps 2..5
+// are the softmax: a thread owns one query row (its lane of tensor memory), reads the row of S with
+// tcgen05.ld twice (maximum, then exponentials), writes the probabilities as bf16 into the swizzled P
+// tile, and keeps the running maximum, sum and the output row in registers: O = O * alpha + PV after
+// every block, so nothing in tensor memory is ever rescaled.  Two blocks share an SM (256 columns of
+// tensor memory each), one's softmax under the other's products.
+//
+// Rows of a value tile that no key of the sequence has written (a page's tail) are cleared by the softmax
+// threads before the product: a probability of zero does not silence a NaN.  Every mbarrier wait is
+// bounded; one that runs out records a code in the status word and the block goes to its end, where the
+// tensor memory is given back.
+#pragma once
+#include <cuda.h>
+
+#include <map>
+#include <tuple>
+
+#include "common.cuh"
+
+struct AttnPrefillTcArgs {
+    const int* block_table;
+    int table_stride;
+    const int* cu_seqlens;
+    const int* slot_of_seq;
+    const int* start_pos;
+    __nv_bfloat16* out;          // [N, n_heads * HD]
+    int n_heads, n_kv, window;
+    float scale_log2e;
+    int* status;                 // 0, or 31..35 when a bounded wait ran out
+};
+
+namespace attn_tc {
+constexpr unsigned kSpinLimit = 1u << 22;
+constexpr int kThreads = 192;        // producer warp, tensor-core warp, four softmax warps
+constexpr int BQ = 128, BKV = 128;   // query rows of a block, keys of a step
+enum { TC_ATTN_Q = 31, TC_ATTN_K = 32, TC_ATTN_V = 33, TC_ATTN_S = 34, TC_ATTN_P = 35, TC_ATTN_PV = 36, TC_ATTN_FREE = 37 };
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    const unsigned addr = smem_u32(bar);
+    for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+        unsigned done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+// Shared-memory operand descriptors; tiles are rows of 128 bytes with the 128-byte swizzle, eight rows
+// 1024 bytes apart.  K-major (Q, K, P): the rows are the operand's M or N index, a row holds 64 of its k.
+// MN-major (V): the rows are the k index (keys), a row holds 64 of the operand's N (lanes of the head);
+// groups of eight k rows are 1024 bytes apart (the stride offset), the next 64 lanes `lanes_step` bytes
+// further (the leading offset).
+__device__ __forceinline__ unsigned long long desc_k_major(const void* tile) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_u32(tile) >> 4) & 0x3fff);
+    d |= (unsigned long long)1 << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+__device__ __forceinline__ unsigned long long desc_mn_major(const void* tile, unsigned lanes_step) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_u32(tile) >> 4) & 0x3fff);
+    d |= (unsigned long long)((lanes_step >> 4) & 0x3fff) << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+// instruction descriptor of kind::f16: fp32 accumulator, bf16 x bf16, M 128
+__host__ __device__ constexpr unsigned idesc(int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((unsigned)(n >> 3) << 17) | ((unsigned)(128 >> 4) << 24);
+}
+__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc, unsigned id, unsigned accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(id), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// 2^x on the special-function unit (x = -inf gives 0)
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
+    unsigned r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+}  // namespace attn_tc
+
+template <int HD>
+__global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(const AttnPrefillTcArgs a, const __grid_constant__ CUtensorMap qmap,
+                                                                            const __grid_constant__ CUtensorMap pool_map) {
+    using namespace attn_tc;
+    constexpr int SUB = HD / 64;                         // 64-lane sub-tiles of a row
+    constexpr unsigned kTile = 128 * 128;                // bytes of a sub-tile: 128 rows of 128 bytes
+    constexpr unsigned kQBytes = SUB * kTile, kKBytes = SUB * kTile, kVBytes = SUB * kTile, kPBytes = 2 * kTile;
+    constexpr int kTmemCols = 256;                       // S: columns 0..127; PV: columns 128..128 + HD
+    extern __shared__ __align__(1024) unsigned char smem_tc_raw[];
+    unsigned char* smem = smem_tc_raw + ((1024u - (smem_u32(smem_tc_raw) & 1023u)) & 1023u);
+    unsigned char* Qs = smem;                            // [SUB][128 rows][128 bytes]
+    unsigned char* Ks = Qs + kQBytes;                    // [2 stages][SUB][128 keys][128 bytes]
+    unsigned char* Vs = Ks + 2 * kKBytes;                // [SUB][128 keys][128 bytes]
+    unsigned char* Ps = Vs + kVBytes;                    // [2 halves of 64 keys][128 rows][128 bytes]
+    unsigned long long* q_full = reinterpret_cast<unsigned long long*>(Ps + kPBytes);
+    unsigned long long* k_full = q_full + 1;             // [2]
+    unsigned long long* k_empty = k_full + 2;            // [2]
+    unsigned long long* v_full = k_empty + 2;
+    unsigned long long* v_empty = v_full + 1;
+    unsigned long long* s_full = v_empty + 1;
+    unsigned long long* p_full = s_full + 1;
+    unsigned long long* pv_full = p_full + 1;
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(pv_full + 1);
+
+    pdl_wait();          // q and the keys are the work of the kernels before
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // blocks start in the order x, y, z: all heads of the longest query tile first, then the next tile, so
+    // that the long walks begin early and the short ones fill the end
+    const int head = blockIdx.x, seq = blockIdx.z;
+    const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;
+    const int tok0 = a.cu_seqlens[seq], q_len = a.cu_seqlens[seq + 1] - tok0;
+    const int q0 = qt * BQ;
+    if (q0 >= q_len) return;                                      // the whole block: nothing was set up yet
+    pdl_launch_dependents();
+    const int start = a.start_pos[seq];
+    const int kv_total = start + q_len;                           // keys of this sequence in the cache after the step's append
+    const int rows = min(BQ, q_len - q0);
+    const int key_hi = start + q0 + rows - 1;                     // the last key any row of the block sees
+    const int key_lo = a.window > 0 ? max(0, start + q0 - a.window + 1) : 0;
+    const int kb_lo = key_lo / BKV, kb_hi = key_hi / BKV, n_blocks = kb_hi - kb_lo + 1;
+    const int kvh = head / (a.n_heads / a.n_kv);
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
+        mbar_init(v_full, 1);
+        mbar_init(v_empty, 1);
+        mbar_init(s_full, 1);
+        mbar_init(p_full, 4);            // one arrival per softmax warp
+        mbar_init(pv_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- producer ----------------
+            const int* pages = a.block_table + (size_t)a.slot_of_seq[seq] * a.table_stride;
+            const int last_page = (kv_total - 1) / 64;
+            mbar_expect_tx(q_full, kQBytes);
+#pragma unroll
+            for (int h = 0; h < SUB; ++h) tma_load_2d(Qs + h * kTile, &qmap, head * HD + h * 64, tok0 + q0, q_full);
+            bool ok = true;
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                const int kb = kb_lo + j;
+                // the block's two pages; a second page the sequence does not have is read from the first (its
+                // keys are masked and its value rows cleared)
+                const int pa = pages[2 * kb], pb = 2 * kb + 1 <= last_page ? pages[2 * kb + 1] : pa;
+                const int ka = ((pa * 2) * a.n_kv + kvh) * 64, kbr = ((pb * 2) * a.n_kv + kvh) * 64;
+                const int s = j & 1;
+                if (j >= 2 && !mbar_wait(k_empty + s, ((j >> 1) - 1) & 1)) { atomicCAS(a.status, 0, TC_ATTN_FREE); ok = false; break; }
+                mbar_expect_tx(k_full + s, kKBytes);
+#pragma unroll
+                for (int h = 0; h < SUB; ++h) {
+                    tma_load_2d(Ks + s * kKBytes + h * kTile, &pool_map, h * 64, ka, k_full + s);
+                    tma_load_2d(Ks + s * kKBytes + h * kTile + 64 * 128, &pool_map, h * 64, kbr, k_full + s);
+                }
+                if (j >= 1 && !mbar_wait(v_empty, (j - 1) & 1)) { atomicCAS(a.status, 0, TC_ATTN_FREE); ok = false; break; }
+                mbar_expect_tx(v_full, kVBytes);
+#pragma unroll
+                for (int h = 0; h < SUB; ++h) {
+                    tma_load_2d(Vs + h * kTile, &pool_map, h * 64, ka + a.n_kv * 64, v_full);
+                    tma_load_2d(Vs + h * kTile + 64 * 128, &pool_map, h * 64, kbr + a.n_kv * 64, v_full);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---------------- tensor core ----------------
+            constexpr unsigned kIdescS = idesc(BKV, false), kIdescPV = idesc(HD, true);
+            bool ok = mbar_wait(q_full, 0);
+            if (!ok) atomicCAS(a.status, 0, TC_ATTN_Q);
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                const int s = j & 1;
+                if (!mbar_wait(k_full + s, (j >> 1) & 1)) { atomicCAS(a.status, 0, TC_ATTN_K); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                // S = Q K^T: HD / 16 steps of k; a step is 32 bytes along the swizzled row (+2 in the address
+                // field), the second half of a 128-lane head lies in the next sub-tile
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const unsigned long long ad = desc_k_major(Qs + (kk >> 2) * kTile) + 2 * (kk & 3);
+                    const unsigned long long bd = desc_k_major(Ks + s * kKBytes + (kk >> 2) * kTile) + 2 * (kk & 3);
+                    umma(tmem_base, ad, bd, kIdescS, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(k_empty + s);
+                umma_commit(s_full);
+                // PV = P V once the probabilities are written (which also says that S and the last PV were read)
+                if (!mbar_wait(p_full, j & 1)) { atomicCAS(a.status, 0, TC_ATTN_P); break; }
+                if (!mbar_wait(v_full, j & 1)) { atomicCAS(a.status, 0, TC_ATTN_V); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+                for (int kk = 0; kk < BKV / 16; ++kk) {
+                    const unsigned long long ad = desc_k_major(Ps + (kk >> 2) * kTile) + 2 * (kk & 3);
+                    // 16 keys further: two groups of eight rows, 2048 bytes
+                    const unsigned long long bd = desc_mn_major(Vs, kTile) + (unsigned long long)(kk * (2048 >> 4));
+                    umma(tmem_base + 128, ad, bd, kIdescPV, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(v_empty);
+                umma_commit(pv_full);
+            }
+        }
+    } else {
+        // ---------------- softmax: thread <-> query row ----------------
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                       // row of the tile, lane of tensor memory
+        const bool live = r < rows;
+        const int pos = start + q0 + r;                          // this row's position: it sees keys lo .. pos
+        const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+        const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16);
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; ++d) o[d] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_blocks && ok; ++j) {
+            const int key0 = (kb_lo + j) * BKV;
+            if (r == 0) blm_trace_here(0x500);
+            if (!mbar_wait(s_full, j & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_S); ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (r == 0) blm_trace_here(0x510);
+            // A block whose every key every row sees (all but the diagonal and the window's edge) needs no masks.
+            const bool open_block = key0 + BKV - 1 <= start + q0 && (a.window <= 0 || key0 >= start + q0 + BQ - a.window);
+            // the row's maximum (of the raw scores: the scale is positive)
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; ++c) {
+                float v[32];
+                tmem_ld32(taddr + c * 32, v);
+                if (open_block) {
+                    float m4[4] = {v[0], v[1], v[2], v[3]};
+#pragma unroll
+                    for (int i = 4; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], v[i]);
+                    mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = key0 + c * 32 + i;
+                        if (live && key >= lo && key <= pos) mx = fmaxf(mx, v[i]);
+                    }
+                }
+            }
+            if (r == 0) blm_trace_here(0x520);
+            const float m_new = fmaxf(m_run, mx * a.scale_log2e);
+            const float alpha = m_run == -INFINITY ? 0.f : ex2(m_run - m_new);
+            m_run = m_new;
+            const float neg_m = m_new == -INFINITY ? 0.f : -m_new;      // a row without a visible key: every probability is masked anyway
+            // probabilities, as bf16 into the P tile: 16-byte chunk c of the row's half h at h * kTile + r * 128 + ((c ^ (r & 7)) << 4)
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; ++c) {
+                float v[32];
+                tmem_ld32(taddr + c * 32, v);
+                unsigned packed[16];
+                if (open_block) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = ex2(fmaf(v[i], a.scale_log2e, neg_m)), p1 = ex2(fmaf(v[i + 1], a.scale_log2e, neg_m));
+                        rs4[(i >> 1) & 3] += p0 + p1;
+                        const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                        packed[i >> 1] = *reinterpret_cast<const unsigned*>(&pk);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const int key = key0 + c * 32 + i;
+                        const float p0 = (live && key >= lo && key <= pos) ? ex2(fmaf(v[i], a.scale_log2e, neg_m)) : 0.f;
+                        const float p1 = (live && key + 1 >= lo && key + 1 <= pos) ? ex2(fmaf(v[i + 1], a.scale_log2e, neg_m)) : 0.f;
+                        rs4[(i >> 1) & 3] += p0 + p1;
+                        const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                        packed[i >> 1] = *reinterpret_cast<const unsigned*>(&pk);
+                    }
+                }
+                unsigned char* prow = Ps + (c >> 1) * kTile + r * 128;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int chunk = (c & 1) * 4 + q4;
+                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
+                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                }
+            }
+            const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            if (r == 0) blm_trace_here(0x530);
+            l_run = l_run * alpha + rs;
+            // value rows no key of the sequence has written (beyond its last key) may hold anything: cleared
+            if (key0 + BKV > kv_total) {
+                if (!mbar_wait(v_full, j & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_V); ok = false; break; }
+                if (key0 + r >= kv_total) {
+#pragma unroll
+                    for (int h = 0; h < SUB; ++h)
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(Vs + h * kTile + r * 128 + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            // the writes to shared memory become visible to the tensor core; S has been read
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+            if (r == 0) blm_trace_here(0x540);
+            // O = O * alpha + P V
+            if (!mbar_wait(pv_full, j & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_PV); ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (r == 0) blm_trace_here(0x550);
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                float v[32];
+                tmem_ld32(taddr + 128 + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + v[i];
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        }
+        if (ok && live) {
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            __nv_bfloat16* dst = a.out + (size_t)(tok0 + q0 + r) * a.n_heads * HD + (size_t)head * HD;
+#pragma unroll
+            for (int d = 0; d < HD; d += 8) {
+                unsigned pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const __nv_bfloat162 two = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
+                    pk[e] = *reinterpret_cast<const unsigned*>(&two);
+                }
+                *reinterpret_cast<uint4*>(dst + d) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+        }
+    }
+    // everybody meets; then the warp that took the tensor memory gives it back
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols));
+    }
+}
+
+typedef CUresult (*TcAttnEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                        const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                        CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// A bf16 matrix [rows, width] with row stride ld (elements) as the TMA sees it: boxes of box_rows x 64, 128-byte swizzle.
+static bool attn_tc_map(const void* base, long long ld, long long rows, int width, int box_rows, CUtensorMap* out) {
+    static TcAttnEncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess || !fn)
+            return false;
+        encode = (TcAttnEncodeTiledFn)fn;
+    }
+    static std::map<std::tuple<const void*, long long, long long, int, int>, CUtensorMap> maps;
+    const auto key = std::make_tuple(base, ld, rows, width, box_rows);
+    auto it = maps.find(key);
+    if (it == maps.end()) {
+        CUtensorMap m;
+        const cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
+        const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+        const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+        const cuuint32_t estr[2] = {1, 1};
+        if (encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+        if (maps.size() > 4096) maps.clear();
+        it = maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return true;
+}
+
+template <int HD>
+static int attn_prefill_tc_launch(const AttnPrefillTcArgs& a, const CUtensorMap& qmap, const CUtensorMap& pmap, dim3 grid, cudaStream_t stream) {
+    constexpr int SUB = HD / 64;
+    const size_t smem = (size_t)(SUB + 2 * SUB + SUB + 2) * 128 * 128 + 16 * 8 + 16 + 1024;
+    static bool opted_in = false;
+    if (!opted_in) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "attention prefill (tcgen05): %s", cudaGetErrorString(e));
+        opted_in = true;
+    }
+    cudaError_t e = blm_launch_dependent(attn_prefill_tc_kernel<HD>, grid, dim3(attn_tc::kThreads), smem, stream, a, qmap, pmap);
+    if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "attention prefill (tcgen05): %s", cudaGetErrorString(e));
+    return BLM_OK;
+}
+
+// BLM_OK when the kernel took the step, -1 when the shape is not its own, else an error.
+// q: the step's rows, token n's head h at q + n * q_stride + h * hd.
+static int launch_attn_prefill_tc(const AttnPrefillTcArgs& a, const void* q, long long q_stride, const void* pool, int n_pages,
+                                  int hd, int n_tokens, int n_seqs, int max_q_len, cudaStream_t stream) {
+    const dim3 grid(a.n_heads, (max_q_len + attn_tc::BQ - 1) / attn_tc::BQ, n_seqs);
+    if (grid.y > 65535 || grid.z > 65535 || (hd != 64 && hd != 128)) return -1;
+    CUtensorMap qmap, pmap;
+    if (!attn_tc_map(q, q_stride, n_tokens, a.n_heads * hd, attn_tc::BQ, &qmap) ||
+        !attn_tc_map(pool, hd, (long long)n_pages * 2 * a.n_kv * 64, hd, 64, &pmap))
+        return blm_fail(BLM_CUDA_ERROR, "attention prefill (tcgen05): cuTensorMapEncodeTiled failed");
+    return hd == 64 ? attn_prefill_tc_launch<64>(a, qmap, pmap, grid, stream) : attn_prefill_tc_launch<128>(a, qmap, pmap, grid, stream);
+}

@@ -36,7 +36,7 @@ MODULES = {
     "gemm_tc": ["gemm_tc.cu"],
     "sampling": ["sampling.cu"],
 }
-HEADERS = ["common.cuh", "attention_decode.cuh", "attention_prefill.cuh", "sampling_no_alloc.h"]
+HEADERS = ["common.cuh", "attention_decode.cuh", "attention_prefill.cuh", "attention_prefill_tc.cuh", "sampling_no_alloc.h"]
 
 _lock = threading.Lock()
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -64,8 +64,12 @@ static inline cudaError_t blm_launch_dependent(void (*kernel)(KArgs...), dim3 gr
 constexpr unsigned kTraceCapacity = 1u << 18;
 __device__ unsigned long long g_blm_trace[kTraceCapacity][2];
 __device__ unsigned g_blm_trace_n;
+__device__ __forceinline__ void blm_trace_here(unsigned tag);
 __device__ __forceinline__ void blm_trace(unsigned tag) {
-    if (threadIdx.x != 0) return;
+    if (threadIdx.x == 0) blm_trace_here(tag);
+}
+// for the one thread the caller picked
+__device__ __forceinline__ void blm_trace_here(unsigned tag) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
     const unsigned i = atomicAdd(&g_blm_trace_n, 1u);
@@ -88,6 +92,7 @@ BLM_API long long blm_trace_dump(unsigned long long* host, long long capacity) {
 }
 #else
 #define blm_trace(tag) ((void)0)
+#define blm_trace_here(tag) ((void)0)
 #endif
 
 // dtype tags shared with the Python side
