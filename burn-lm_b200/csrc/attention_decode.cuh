@@ -87,7 +87,7 @@ static inline int attn_decode_stages(int hd, int blocks, int pages_per_block) {
 // Groups of consumer warps.  One warp per scheduler waits out every latency of its chain of dependent
 // instructions; when a block is (almost) alone on its SM, several groups work on different pages at once.
 static inline int attn_decode_groups(int blocks, int pages_per_block, int stages) {
-    int ng = blocks <= 148 ? 4 : (blocks <= 444 ? 2 : 1);
+    int ng = blocks <= 148 ? 4 : 2;
     while (ng > 1 && (ng > pages_per_block || ng > stages)) ng /= 2;
     return ng;
 }
