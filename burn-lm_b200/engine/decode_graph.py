@@ -44,6 +44,9 @@ class DecodeGraph:
         # tokens | positions | slots: what a step brings, in one buffer, one copy
         self.meta = torch.zeros(3 * b, dtype=torch.int32, device=dev)
         self.host_meta = torch.zeros(3 * b, dtype=torch.int32, pin_memory=True)
+        self._host_meta_np = self.host_meta.numpy()             # the same pinned bytes, filled without a tensor in between
+        self.host_sampled = torch.zeros(b, dtype=torch.int32, pin_memory=True)
+        self._host_sampled_np = self.host_sampled.numpy()
         self.tokens, self.pos, self.slots = self.meta[:b], self.meta[b:2 * b], self.meta[2 * b:]
         ar = torch.arange(b + 1, dtype=torch.int32, device=dev)
         self.ctx = StepContext(
@@ -75,7 +78,7 @@ class DecodeGraph:
         """Bring a step's inputs from (pinned) host memory to the graph's buffers."""
         if self._copied is not None:
             self._copied.synchronize()       # the last copy has left the pinned buffer
-        self.host_meta.copy_(torch.tensor([*tokens, *positions, *slots], dtype=torch.int32))
+        self._host_meta_np[:] = [*tokens, *positions, *slots]
         self.meta.copy_(self.host_meta, non_blocking=True)
         self._copied = torch.cuda.Event()
         self._copied.record()
@@ -111,6 +114,13 @@ class DecodeGraph:
             return self.sampled
         self._greedy_graph.replay()
         return self.sampled
+
+    def step_greedy_host(self) -> list:
+        """step_greedy(), and the sampled tokens read back through pinned memory as a list."""
+        sampled = self.step_greedy()
+        self.host_sampled.copy_(sampled, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._host_sampled_np.tolist()
 
     def run(self, n_steps: int, keep_history: bool = True) -> torch.Tensor:
         """n_steps greedy decode steps without the host in between, starting from the loaded inputs.

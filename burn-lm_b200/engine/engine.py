@@ -136,7 +136,7 @@ class Engine:
             cache.reserve([(s, n + 1) for s, n in zip(slots, starts)])
         g = self.decode_graph(len(slots), max(starts) + 1)
         g.load(tokens, starts, slots)
-        out = g.step_greedy().tolist()
+        out = g.step_greedy_host()
         for s, n in zip(slots, starts):
             cache.seq_len[s] = n + 1
         return out

@@ -54,6 +54,7 @@ class Model:
     def __init__(self, plan: ModelPlan, runtime: Runtime, config=None):
         self.plan, self.runtime, self.config = plan, runtime, config
         self.embedding = _build(plan.embedding, "embedding", runtime)
+        self.stream_position = _build(plan.stream_position, "position", runtime) if plan.stream_position is not None else None
         self.layers = [Layer(lp, runtime) for lp in plan.layers]
         self.final_norm = _build(plan.final_norm, "norm", runtime)
         self.head = _build(plan.head, "head", runtime)
@@ -61,7 +62,7 @@ class Model:
 
     # -- weights ---------------------------------------------------------------------------------
     def parts(self):
-        out = [self.embedding]
+        out = [self.embedding] + ([self.stream_position] if self.stream_position is not None else [])
         for layer in self.layers:
             out.extend(layer.parts())
         out.extend([self.final_norm, self.head])
@@ -96,6 +97,8 @@ class Model:
             raise RuntimeError("the model has no weights yet")
         resid = torch.empty((step.n_tokens, self.plan.hidden_size), dtype=torch.float32, device=self.runtime.device)
         self.embedding.forward(step.tokens, resid)
+        if self.stream_position is not None:
+            self.stream_position.on_embedding(resid, step)      # an encoding that is added to the stream
         delta = None
         schedule = self.plan.schedule
         for run, entry in enumerate(schedule):

@@ -51,6 +51,7 @@ class ModelPlan:
     max_positions: int
     stop_ids: tuple = ()
     ignorable_tensors: tuple = ()   # regular expressions of stored names that may be left unread
+    stream_position: Optional[PartPlan] = None   # family "position": an encoding added to the stream after the embedding
 
     def __post_init__(self):
         for n, e in enumerate(self.schedule):

@@ -1,6 +1,7 @@
 """Each part of a layer alone against its plain twin, built directly from its spec with random
-tensors, and a toy architecture with a toy mixer (state of its own), a layer that runs twice and a
-run that reads another run's cache: all registered from here, without touching the package."""
+tensors, and two toy architectures registered from here, without touching the package: one with a toy
+mixer (state of its own), a layer that runs twice and a run that reads another run's cache; one with a
+feed-forward that routes tokens to experts and a position encoding that is added to the stream."""
 import dataclasses
 import json
 import os
@@ -299,3 +300,173 @@ def test_toy_architecture_registers_builds_and_steps(tmp_path):
         for rid in reqs:
             err = row_error(got[rid], want[rid])
             assert err.max() < 1e-4, (what, rid, float(err.max()), int(err.argmax()))
+
+
+# --------------------------------------------------------------------------------------------------
+# a second toy: a feed-forward with routing and a position encoding added to the stream, both written
+# here with torch operations and registered from here
+# --------------------------------------------------------------------------------------------------
+@dataclasses.dataclass(frozen=True)
+class RoutedSpec:
+    hidden_size: int
+    inner: int
+    experts: int
+
+
+@dataclasses.dataclass(frozen=True)
+class LearnedPositionSpec:
+    hidden_size: int
+    positions: int
+
+
+def register_routed_toy():
+    from burn_lm_b200 import register_architecture, register_part, Architecture, TensorSpec
+    from burn_lm_b200.config import KeyReader
+    from burn_lm_b200.parts import CacheNeed, Part, RMSNormSpec, AttentionSpec, NoPositionSpec, EmbeddingSpec, HeadSpec
+    from burn_lm_b200.plan import LayerPlan, ModelPlan, PartPlan, ScheduleEntry
+    from burn_lm_b200 import registry
+
+    if "ToyRoutedLM" in [a.name for a in registry.architectures()]:
+        return
+
+    @register_part("feed_forward", "toy_routed")
+    class RoutedFeedForward(Part):
+        """Every token goes to the expert with the largest router logit (fp32) and is weighted by that
+        expert's softmax probability; an expert is a gated feed-forward."""
+        family = "feed_forward"
+
+        def tensor_specs(self):
+            s, t = self.spec, self.tensor_names
+            return [TensorSpec(t["router"], (s.experts, s.hidden_size), init="normal:0.5"),
+                    TensorSpec(t["gate"], (s.experts * s.inner, s.hidden_size), init="normal:0.1"),
+                    TensorSpec(t["up"], (s.experts * s.inner, s.hidden_size), init="normal:0.1"),
+                    TensorSpec(t["down"], (s.experts * s.hidden_size, s.inner), init="normal:0.1")]
+
+        def bind(self, loaded):
+            s, t = self.spec, self.tensor_names
+            self.router = loaded[t["router"]].float()
+            self.gate = loaded[t["gate"]].float().view(s.experts, s.inner, s.hidden_size)
+            self.up = loaded[t["up"]].float().view(s.experts, s.inner, s.hidden_size)
+            self.down = loaded[t["down"]].float().view(s.experts, s.hidden_size, s.inner)
+
+        def forward(self, x, step):
+            xf = x.float()
+            prob = torch.softmax(xf @ self.router.T, dim=-1)
+            weight, expert = prob.max(dim=-1)
+            out = torch.zeros_like(xf)
+            for e in range(self.spec.experts):
+                rows = (expert == e).nonzero().flatten()
+                if rows.numel():
+                    xe = xf[rows]
+                    g = xe @ self.gate[e].T
+                    out[rows] = ((g / (1 + torch.exp(-g))) * (xe @ self.up[e].T)) @ self.down[e].T * weight[rows, None]
+            return out.to(x.dtype)
+
+    @register_part("position", "toy_learned")
+    class LearnedPosition(Part):
+        """A stored vector per position, added to the stream after the embedding."""
+        family = "position"
+
+        def tensor_specs(self):
+            return [TensorSpec(self.tensor_names["table"], (self.spec.positions, self.spec.hidden_size), init="normal:0.3")]
+
+        def bind(self, loaded):
+            self.table = loaded[self.tensor_names["table"]].float()
+
+        def on_embedding(self, resid, step):
+            resid += self.table[step.token_pos.long()]
+
+    @dataclasses.dataclass(frozen=True)
+    class RoutedConfig:
+        width: int
+        depth: int
+        words: int
+        experts: int
+        inner: int
+        heads: int
+        positions: int
+
+        @classmethod
+        def from_dict(cls, d):
+            r = KeyReader(d)
+            return cls(r.integer("r_width"), r.integer("r_depth"), r.integer("r_words"), r.integer("r_experts"),
+                       r.integer("r_inner"), r.integer("r_heads"), r.integer("r_positions"))
+
+    def plan(cfg):
+        norm = RMSNormSpec(cfg.width, 1e-6)
+        layers = []
+        for n in range(cfg.depth):
+            p = f"r.{n}."
+            layers.append(LayerPlan(
+                "prenorm", PartPlan("rmsnorm", norm, {"weight": p + "n1"}),
+                PartPlan("attention", AttentionSpec(cfg.width, cfg.heads, cfg.heads, cfg.width // cfg.heads, PartPlan("none", NoPositionSpec())),
+                         {"q": p + "q", "k": p + "k", "v": p + "v", "o": p + "o"}),
+                PartPlan("rmsnorm", norm, {"weight": p + "n2"}),
+                PartPlan("toy_routed", RoutedSpec(cfg.width, cfg.inner, cfg.experts),
+                         {"router": p + "router", "gate": p + "g", "up": p + "u", "down": p + "d"})))
+        return ModelPlan("ToyRoutedLM", cfg.words, cfg.width,
+                         PartPlan("table", EmbeddingSpec(cfg.words, cfg.width), {"table": "r.embed"}),
+                         tuple(layers), tuple(ScheduleEntry(n) for n in range(cfg.depth)),
+                         PartPlan("rmsnorm", norm, {"weight": "r.norm"}),
+                         PartPlan("linear", HeadSpec(cfg.words, cfg.width), {"weight": "r.head"}), max_positions=cfg.positions,
+                         stream_position=PartPlan("toy_learned", LearnedPositionSpec(cfg.width, cfg.positions), {"table": "r.pos"}))
+
+    register_architecture(Architecture("ToyRoutedLM", RoutedConfig, plan, description="test-only"))
+
+
+ROUTED = {"architectures": ["ToyRoutedLM"], "r_width": 64, "r_depth": 3, "r_words": 70, "r_experts": 5, "r_inner": 40,
+          "r_heads": 2, "r_positions": 160}
+
+
+def routed_plain(t, tokens):
+    """The routed toy on one whole sequence, float64, written out plainly."""
+    T = len(tokens)
+    h = P.embedding(t["r.embed"], tokens) + t["r.pos"][:T]
+    for n in range(3):
+        p = f"r.{n}."
+        xn = P.rms_norm(h, t[p + "n1"], 1e-6)
+        q = (xn @ t[p + "q"].T).reshape(T, 2, 32)
+        k = (xn @ t[p + "k"].T).reshape(T, 2, 32)
+        v = (xn @ t[p + "v"].T).reshape(T, 2, 32)
+        o = np.zeros((T, 2, 32))
+        for hh in range(2):
+            s = q[:, hh] @ k[:, hh].T / np.sqrt(32.0)
+            s = np.where(np.triu(np.ones((T, T), bool), 1), -np.inf, s)
+            o[:, hh] = P.softmax(s) @ v[:, hh]
+        h = h + o.reshape(T, 64) @ t[p + "o"].T
+        xn = P.rms_norm(h, t[p + "n2"], 1e-6)
+        prob = P.softmax(xn @ t[p + "router"].T)
+        out = np.zeros_like(xn)
+        for i in range(T):
+            e = int(prob[i].argmax())
+            g = xn[i] @ t[p + "g"].reshape(5, 40, 64)[e].T
+            u = xn[i] @ t[p + "u"].reshape(5, 40, 64)[e].T
+            out[i] = ((g / (1 + np.exp(-g))) * u) @ t[p + "d"].reshape(5, 64, 40)[e].T * prob[i, e]
+        h = h + out
+    return P.rms_norm(h, t["r.norm"], 1e-6) @ t["r.head"].T
+
+
+def test_toy_routed_feed_forward_and_stream_position(tmp_path):
+    """A feed-forward with routing and a position encoding added to the stream, defined above, registered,
+    built from a model folder and stepped whole, token by token and in unequal batches."""
+    import traces
+    from burn_lm_b200 import Engine, write_random_model
+    from tiny import random_tokens, row_error
+    register_routed_toy()
+    folder = write_random_model(str(tmp_path / "routed"), ROUTED, seed=4, dtype="float32")
+    cfg, tensors = P.read_model_folder(folder)
+    reqs = {"a": random_tokens(5, 90, 70), "b": random_tokens(6, 33, 70), "c": random_tokens(7, 140, 70)}
+    want = {rid: routed_plain(tensors, toks) for rid, toks in reqs.items()}
+    used = set()
+    for what, steps in (("whole", traces.whole(reqs)), ("tail", traces.tail(reqs, 32)), ("batched", traces.batched(reqs, 2, [5, 32]))):
+        eng = Engine.from_folder(folder, dtype="float32", max_tokens=traces.max_live_tokens(steps), max_seqs=2)
+        got = traces.run_in_process(eng, steps, str(tmp_path / what), 70)
+        for rid in reqs:
+            err = row_error(got[rid], want[rid])
+            assert err.max() < 1e-4, (what, rid, float(err.max()), int(err.argmax()))
+    # the router is not a constant: the first layer alone sends tokens to several experts
+    t = tensors
+    for rid, toks in reqs.items():
+        h = P.embedding(t["r.embed"], toks) + t["r.pos"][: len(toks)]
+        used |= set(P.softmax(P.rms_norm(h, t["r.0.n1"], 1e-6) @ t["r.0.router"].T).argmax(-1).tolist())
+    assert len(used) >= 3
