@@ -11,9 +11,10 @@
 // MN-major) into other columns; tcgen05.commit frees the stages and tells the softmax warps.  Warps 2..5
 // are the softmax: a thread owns one query row (its lane of tensor memory), reads the row of S with
 // tcgen05.ld twice (maximum, then exponentials), writes the probabilities as bf16 into the swizzled P
-// tile, and keeps the running maximum, sum and the output row in registers: O = O * alpha + PV after
-// every block, so nothing in tensor memory is ever rescaled.  Two blocks share an SM (256 columns of
-// tensor memory each), one's softmax under the other's products.
+// tile, and keeps the row's reference maximum and sum in registers.  O accumulates in tensor memory over
+// the blocks; a row of it is rescaled there (tcgen05.ld, multiply, tcgen05.st) only when a block's
+// maximum exceeds the row's reference by more than 2^8, which after the first blocks is rare.  Two
+// blocks share an SM (256 columns of tensor memory each), one's softmax under the other's products.
 //
 // Rows of a value tile that no key of the sequence has written (a page's tail) are cleared by the softmax
 // threads before the product: a probability of zero does not silence a NaN.  Every mbarrier wait is
@@ -134,6 +135,43 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// The same in two halves, so that a load is in flight while the columns before it are worked on: issue, and
+// later wait; the wait names the registers, so nothing that uses them is moved before it.
+__device__ __forceinline__ void tmem_ld32_issue(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld32_wait(unsigned (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]),
+                   "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]),
+                   "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]),
+                   "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+constexpr float kLazy = 8.0f;     // the reference maximum of a row moves only when a block exceeds it by more than 2^kLazy
 }  // namespace attn_tc
 
 template <int HD>
@@ -258,7 +296,7 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
                     const unsigned long long ad = desc_k_major(Ps + (kk >> 2) * kTile) + 2 * (kk & 3);
                     // 16 keys further: two groups of eight rows, 2048 bytes
                     const unsigned long long bd = desc_mn_major(Vs, kTile) + (unsigned long long)(kk * (2048 >> 4));
-                    umma(tmem_base + 128, ad, bd, kIdescPV, kk > 0 ? 1u : 0u);
+                    umma(tmem_base + 128, ad, bd, kIdescPV, (j > 0 || kk > 0) ? 1u : 0u);      // O accumulates over the blocks
                 }
                 umma_commit(v_empty);
                 umma_commit(pv_full);
@@ -272,9 +310,9 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
         const int pos = start + q0 + r;                          // this row's position: it sees keys lo .. pos
         const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
         const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16);
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.f;
+        // O accumulates in tensor memory over the blocks, against a reference maximum m_run per row that only
+        // moves when a block's maximum exceeds it by more than 2^kLazy: then the row of O is rescaled in tensor
+        // memory (read, multiply, write back).  Otherwise probabilities may exceed one, by at most that factor.
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < n_blocks && ok; ++j) {
@@ -287,10 +325,16 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
             const bool open_block = key0 + BKV - 1 <= start + q0 && (a.window <= 0 || key0 >= start + q0 + BQ - a.window);
             // the row's maximum (of the raw scores: the scale is positive)
             float mx = -INFINITY;
-#pragma unroll 1
+            unsigned buf[2][32];           // two loads of 32 columns: one in flight, one being worked on
+            tmem_ld32_issue(taddr, buf[0]);
+#pragma unroll
             for (int c = 0; c < BKV / 32; ++c) {
+                tmem_ld32_wait(buf[c & 1]);
+                // the next columns of this pass, or the first of the next pass
+                tmem_ld32_issue(taddr + ((c + 1) & 3) * 32, buf[(c + 1) & 1]);
                 float v[32];
-                tmem_ld32(taddr + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(buf[c & 1][i]);
                 if (open_block) {
                     float m4[4] = {v[0], v[1], v[2], v[3]};
 #pragma unroll
@@ -305,16 +349,38 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
                 }
             }
             if (r == 0) blm_trace_here(0x520);
-            const float m_new = fmaxf(m_run, mx * a.scale_log2e);
-            const float alpha = m_run == -INFINITY ? 0.f : ex2(m_run - m_new);
-            m_run = m_new;
-            const float neg_m = m_new == -INFINITY ? 0.f : -m_new;      // a row without a visible key: every probability is masked anyway
+            const float m_blk = mx * a.scale_log2e;
+            const bool move = m_blk > m_run + kLazy;                     // also the first block that shows the row a key
+            if (__any_sync(0xffffffffu, move)) {
+                const float alpha = move ? (m_run == -INFINITY ? 0.f : ex2(m_run - m_blk)) : 1.0f;
+                if (j > 0) {
+                    // the last product into O must have landed before its rows are touched
+                    if (!mbar_wait(pv_full, (j - 1) & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_PV); ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+                    for (int c = 0; c < HD / 32; ++c) {
+                        float v[32];
+                        tmem_ld32(taddr + 128 + c * 32, v);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] *= alpha;
+                        tmem_st32(taddr + 128 + c * 32, v);
+                    }
+                }
+                if (move) {
+                    l_run *= alpha;
+                    m_run = m_blk;
+                }
+            }
+            const float neg_m = m_run == -INFINITY ? 0.f : -m_run;      // a row without a visible key: every probability is masked anyway
             // probabilities, as bf16 into the P tile: 16-byte chunk c of the row's half h at h * kTile + r * 128 + ((c ^ (r & 7)) << 4)
             float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
+#pragma unroll
             for (int c = 0; c < BKV / 32; ++c) {
+                tmem_ld32_wait(buf[c & 1]);
+                if (c + 1 < BKV / 32) tmem_ld32_issue(taddr + (c + 1) * 32, buf[(c + 1) & 1]);
                 float v[32];
-                tmem_ld32(taddr + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(buf[c & 1][i]);
                 unsigned packed[16];
                 if (open_block) {
 #pragma unroll
@@ -345,7 +411,7 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
             }
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             if (r == 0) blm_trace_here(0x530);
-            l_run = l_run * alpha + rs;
+            l_run += rs;
             // value rows no key of the sequence has written (beyond its last key) may hold anything: cleared
             if (key0 + BKV > kv_total) {
                 if (!mbar_wait(v_full, j & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_V); ok = false; break; }
@@ -362,16 +428,20 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
             if (r == 0) blm_trace_here(0x540);
-            // O = O * alpha + P V
-            if (!mbar_wait(pv_full, j & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_PV); ok = false; break; }
+        }
+        // the last product into O, then the row: O / l
+        float o[HD];
+        if (ok) {
+            if (!mbar_wait(pv_full, (n_blocks - 1) & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_PV); ok = false; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            if (r == 0) blm_trace_here(0x550);
+        }
+        if (ok) {
 #pragma unroll
             for (int c = 0; c < HD / 32; ++c) {
                 float v[32];
                 tmem_ld32(taddr + 128 + c * 32, v);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + v[i];
+                for (int i = 0; i < 32; ++i) o[c * 32 + i] = v[i];
             }
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
         }
