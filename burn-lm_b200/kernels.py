@@ -345,6 +345,10 @@ def check_status(device) -> None:
         w.zero_()
         what = {21: "decode attention: a consumer waited in vain for a page", 22: "decode attention: the producer waited in vain for a free stage",
                 1: "gemv: a consumer waited in vain for a weight stage", 2: "gemv: the producer waited in vain for a free stage",
+                31: "prompt attention: the query tile did not arrive", 32: "prompt attention: a key tile did not arrive",
+                33: "prompt attention: a value tile did not arrive", 34: "prompt attention: the scores did not arrive",
+                35: "prompt attention: the probabilities were not written", 36: "prompt attention: the product with the values did not arrive",
+                37: "prompt attention: the producer waited in vain for a free stage",
                 11: "gemm_tc: the tensor-core thread waited in vain for a stage", 12: "gemm_tc: the producer waited in vain for a free stage",
                 13: "gemm_tc: the epilogue waited in vain for the accumulator"}
         raise KernelError(f"{what.get(code, 'status ' + str(code))}; the step's results are not valid")
