@@ -35,6 +35,7 @@ MODULES = {
     "gemv": ["gemv.cu"],
     "gemm_tc": ["gemm_tc.cu"],
     "sampling": ["sampling.cu"],
+    "runtime": ["runtime.cu"],
 }
 HEADERS = ["common.cuh", "attention_decode.cuh", "attention_prefill.cuh", "attention_prefill_tc.cuh", "sampling_no_alloc.h"]
 

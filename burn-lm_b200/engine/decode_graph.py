@@ -63,6 +63,7 @@ class DecodeGraph:
         self._graph = None          # forward only
         self._loop_graph = None     # forward + argmax + advance
         self._greedy_graph = None   # forward + argmax
+        self._greedy_exec = None    # its cudaGraphExec_t (an integer) once known; False when torch does not give it out
         self._loop_history_steps = 0
         self._copied = None
         self.launches_per_step = 0
@@ -115,11 +116,26 @@ class DecodeGraph:
         self._greedy_graph.replay()
         return self.sampled
 
-    def step_greedy_host(self) -> list:
-        """step_greedy(), and the sampled tokens read back through pinned memory as a list."""
+    def step_greedy_host(self, tokens, positions, slots) -> list:
+        """A greedy step from host inputs to host outputs: the inputs go from pinned memory to the graph's
+        buffers, the captured step runs, the sampled tokens come back through pinned memory as a list.
+        Once the graph exists, native code issues the copies, the launch and the wait in one call."""
+        if self._greedy_exec:
+            self._host_meta_np[:] = [*tokens, *positions, *slots]
+            self.ctx.host["slots"], self.ctx.host["start_pos"] = list(slots), list(positions)
+            K.graph_step(self._greedy_exec, self.meta, self.host_meta, self.host_sampled, self.sampled)
+            return self._host_sampled_np.tolist()
+        self.load(tokens, positions, slots)
         sampled = self.step_greedy()
         self.host_sampled.copy_(sampled, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        if self._greedy_graph is not None and self._greedy_exec is None:
+            try:        # the instantiated graph's handle, where this torch gives it out
+                self._greedy_exec = int(self._greedy_graph.raw_cuda_graph_exec()) or None
+            except Exception:
+                self._greedy_exec = None
+            if self._greedy_exec is None:
+                self._greedy_exec = False      # asked once; stay on the interpreter's path
         return self._host_sampled_np.tolist()
 
     def run(self, n_steps: int, keep_history: bool = True) -> torch.Tensor:

@@ -135,8 +135,7 @@ class Engine:
         if grow or len(set(slots)) != len(slots):
             cache.reserve([(s, n + 1) for s, n in zip(slots, starts)])
         g = self.decode_graph(len(slots), max(starts) + 1)
-        g.load(tokens, starts, slots)
-        out = g.step_greedy_host()
+        out = g.step_greedy_host(tokens, starts, slots)
         for s, n in zip(slots, starts):
             cache.seq_len[s] = n + 1
         return out

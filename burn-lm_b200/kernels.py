@@ -74,6 +74,9 @@ _protos = {
                      c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "blm_gemv_supported": [c_int, c_int, c_int],
     },
+    "runtime": {
+        "blm_graph_step": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p],
+    },
     "gemm_tc": {
         "blm_gemm_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
                         c_void_p, c_void_p],
@@ -322,6 +325,15 @@ def gemm_tc(x, w, out, swiglu=False):
         raise KernelError("gemm_tc: out must be [M, N] (or [M, N / 2] with the gated epilogue)")
     _call("gemm_tc", "blm_gemm_tc", _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), m, n, k,
           1 if swiglu else 0, _ptr(status_word(x.device)), _stream())
+
+
+def graph_step(graph_exec: int, dev_in, host_in, host_out, dev_out, kernels: int = 0) -> None:
+    """One captured step driven from native code: host_in (pinned) -> dev_in, the instantiated graph
+    `graph_exec` (a cudaGraphExec_t as an integer), dev_out -> host_out (pinned), and the wait, on the
+    current stream."""
+    _call("runtime", "blm_graph_step", c_void_p(graph_exec), _ptr(dev_in), c_void_p(host_in.data_ptr()),
+          host_in.numel() * host_in.element_size(), c_void_p(host_out.data_ptr()), _ptr(dev_out),
+          host_out.numel() * host_out.element_size(), _stream(), kernels=kernels)
 
 
 _status: dict = {}
