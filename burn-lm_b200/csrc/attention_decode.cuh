@@ -75,11 +75,12 @@ __device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned b
 }  // namespace attn_decode
 
 // How many pages the ring of a block holds.  With few blocks (one per SM or less) a block keeps all its
-// pages in flight at once, up to what shared memory takes; with many blocks several share an SM and the
-// rings are short.
+// pages in flight at once, up to what shared memory takes; with many blocks the rings are short, so that
+// all blocks are resident at once (at batch 64, 512 blocks: two pages a ring and six blocks an SM measured
+// best, ahead of three or four pages).
 static inline int attn_decode_stages(int hd, int blocks, int pages_per_block) {
     const int page_kb = 2 * 64 * hd * 2 / 1024;                    // keys and values of a page of one kv head
-    const int room_kb = blocks <= 148 ? 192 : (blocks <= 296 ? 96 : 64);
+    const int room_kb = blocks <= 148 ? 192 : (blocks <= 296 ? 96 : 32);
     int s = room_kb / page_kb;
     if (s > pages_per_block) s = pages_per_block;
     return s < 2 ? 2 : s;
@@ -87,7 +88,7 @@ static inline int attn_decode_stages(int hd, int blocks, int pages_per_block) {
 // Groups of consumer warps.  One warp per scheduler waits out every latency of its chain of dependent
 // instructions; when a block is (almost) alone on its SM, several groups work on different pages at once.
 static inline int attn_decode_groups(int blocks, int pages_per_block, int stages) {
-    int ng = blocks <= 148 ? 4 : 2;
+    int ng = blocks <= 148 ? 4 : (blocks <= 296 ? 2 : 1);
     while (ng > 1 && (ng > pages_per_block || ng > stages)) ng /= 2;
     return ng;
 }
