@@ -193,27 +193,72 @@ __device__ __forceinline__ unsigned long long block_exclusive_scan_u64(unsigned 
 
 constexpr double kQuant = 1099511627776.0;  // 2^40
 
-// The probability of token i.  Every pass below recomputes it through this one function, with the
-// roundings spelled out, so that all passes see the same bits.
-__device__ __forceinline__ float prob_of(const float* __restrict__ row, int i, float inv_t, float mx, float inv_z) {
-    return __fmul_rn(expf(__fsub_rn(__fmul_rn(row[i], inv_t), mx)), inv_z);
+// A 64-bit add into a histogram in shared memory out of two native 32-bit atomic adds (a 64-bit atomic add
+// to shared memory is a compare-and-swap loop): the low word's add returns what it found, which tells
+// whether it carried; the carry goes with the high word.
+__device__ __forceinline__ void hist_add(unsigned int* lo, unsigned int* hi, int bin, unsigned long long v) {
+    const unsigned int vl = (unsigned int)v;
+    const unsigned int old = atomicAdd(lo + bin, vl);
+    const unsigned int carry = old + vl < old ? 1u : 0u;
+    const unsigned int vh = (unsigned int)(v >> 32) + carry;
+    if (vh) atomicAdd(hi + bin, vh);
 }
-__device__ __forceinline__ unsigned long long quantise(float p) { return (unsigned long long)((double)p * kQuant); }
+
+// The probability of token i: its exponential, computed once and kept in the row of `work`, times 1 / Z.
+// Every pass below goes through this one function, so that all passes see the same bits.
+__device__ __forceinline__ float prob_of(const float* __restrict__ e, int i, float inv_z) { return __fmul_rn(e[i], inv_z); }
+
+// Calls f(i, probability of token i) for i = lo .. hi - 1 in order.  A thread's chunk is contiguous (the
+// order of the vocabulary matters to the draw), so its loads do not coalesce with its neighbours'; sixteen
+// are asked for at once, so that the round trips to L2 overlap instead of following one another.
+// Calls f(probability of token i) for every token, in no particular order: the threads stride through the
+// row together, 16 bytes each, so the loads coalesce.  For the passes whose sums do not care for the order.
+template <typename F>
+__device__ __forceinline__ void for_all(const float* __restrict__ e, int vocab, float inv_z, F f) {
+    if ((vocab & 3) == 0 && ((size_t)e & 15) == 0) {
+        const float4* e4 = reinterpret_cast<const float4*>(e);
+        for (int i = threadIdx.x; i < (vocab >> 2); i += blockDim.x) {
+            const float4 v = e4[i];
+            f(__fmul_rn(v.x, inv_z));
+            f(__fmul_rn(v.y, inv_z));
+            f(__fmul_rn(v.z, inv_z));
+            f(__fmul_rn(v.w, inv_z));
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) f(__fmul_rn(e[i], inv_z));
+    }
+}
+
+template <typename F>
+__device__ __forceinline__ void for_chunk(const float* __restrict__ e, int lo, int hi, float inv_z, F f) {
+    constexpr int kBatch = 16;
+    for (int i0 = lo; i0 < hi; i0 += kBatch) {
+        float v[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) v[u] = i0 + u < hi ? e[i0 + u] : 0.f;
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u)
+            if (i0 + u < hi) f(i0 + u, __fmul_rn(v[u], inv_z));
+    }
+}
+// floor(p * 2^40): scaling a float by a power of two is exact, so this needs no double
+__device__ __forceinline__ unsigned long long quantise(float p) { return __float2ull_rz(__fmul_rn(p, (float)kQuant)); }
 
 __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     const float* __restrict__ logits, long long row_stride, int vocab, const float* __restrict__ temperature,
     const float* __restrict__ top_p, const unsigned long long* __restrict__ seeds,
     const unsigned long long* __restrict__ stream_ids, const unsigned long long* __restrict__ counters,
-    int* __restrict__ out) {
+    int* __restrict__ out, float* __restrict__ work) {
     __shared__ float redf[33];
     __shared__ unsigned long long red[33];
-    __shared__ unsigned long long hist[256];
+    __shared__ unsigned int hist_lo[256], hist_hi[256];      // a bin's 64-bit sum in two words (see hist_add)
     __shared__ unsigned int s_prefix;
     __shared__ unsigned long long s_above;
     __shared__ int s_result;
 
     const int b = blockIdx.x;
     const float* row = logits + (size_t)b * row_stride;
+    float* e = work + (size_t)b * vocab;          // exp(logit / temperature - max), written once below
     const float inv_t = 1.0f / temperature[b];
     const int tid = threadIdx.x;
 
@@ -232,8 +277,12 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     mx = redf[32];
     __syncthreads();
     float z = 0.f;
-    for (int i = tid; i < vocab; i += blockDim.x) z += expf(__fsub_rn(__fmul_rn(row[i], inv_t), mx));
-    z = block_sum(z, redf);
+    for (int i = tid; i < vocab; i += blockDim.x) {
+        const float ei = expf(__fsub_rn(__fmul_rn(row[i], inv_t), mx));
+        e[i] = ei;
+        z += ei;
+    }
+    z = block_sum(z, redf);          // (its barriers also make every thread's e visible to the others)
     const float inv_z = 1.0f / z;
 
     // contiguous chunk of the vocabulary per thread (index order matters below)
@@ -241,7 +290,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     const int lo = min(vocab, tid * per), hi = min(vocab, lo + per);
 
     unsigned long long total = 0;
-    for (int i = lo; i < hi; ++i) total += quantise(prob_of(row, i, inv_t, mx, inv_z));
+    for_all(e, vocab, inv_z, [&](float p) { total += quantise(p); });
     total = block_sum_u64(total, red);
 
     // nucleus: the key tau (float bits of a probability) with mass(> tau) < target <= mass(>= tau)
@@ -255,25 +304,80 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
         if (target < 1) target = 1;
         if (tid == 0) { s_prefix = 0; s_above = 0; }
         __syncthreads();
-        for (int round = 0; round < 4; ++round) {
-            const int shift = 24 - 8 * round;
-            for (int i = tid; i < 256; i += blockDim.x) hist[i] = 0ull;
+        // The digits of a probability's bits, from the top: its exponent (the sign is 0), then its mantissa in
+        // pieces of 8, 8 and 7 bits.
+        //
+        // First digit.  The whole vocabulary takes part and shares a dozen exponents, so a histogram in shared
+        // memory would have a thousand threads adding to the same few words.  Instead every thread sums, in
+        // registers, the sixteen exponents from the largest probability's down (that one is 1 / Z exactly)
+        // and what lies below them; the block adds the threads' sums up.  Only if the nucleus reaches below
+        // those sixteen exponents (2^-16 of the largest probability) does the general histogram run.
+        int first_round = 0;
+        {
+            constexpr int kTop = 16;
+            const int top = (int)((__float_as_uint(inv_z) >> 23) & 255u), base = top - (kTop - 1);
+            unsigned long long wacc[kTop + 1];          // [kTop]: everything below the window
+#pragma unroll
+            for (int k = 0; k <= kTop; ++k) wacc[k] = 0ull;
+            for_all(e, vocab, inv_z, [&](float p) {
+                const int d = (int)(__float_as_uint(p) >> 23) - base;
+                const unsigned long long w = quantise(p);
+#pragma unroll
+                for (int k = 0; k < kTop; ++k) wacc[k] += d == k ? w : 0ull;
+                wacc[kTop] += d < 0 ? w : 0ull;
+            });
+            for (int i = tid; i < 256; i += blockDim.x) { hist_lo[i] = 0u; hist_hi[i] = 0u; }
+            __syncthreads();
+#pragma unroll
+            for (int k = 0; k <= kTop; ++k) {
+                unsigned long long v = wacc[k];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if ((tid & 31) == 0 && v) hist_add(hist_lo, hist_hi, k, v);       // 32 adds a word
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned long long run = 0;
+                int k = kTop - 1;
+                for (; k >= 0; --k) {
+                    const unsigned long long h = ((unsigned long long)hist_hi[k] << 32) | hist_lo[k];
+                    if (run + h >= target) break;
+                    run += h;
+                }
+                if (k >= 0 && base + k >= 0) {       // found inside the window
+                    s_above = run;
+                    s_prefix = (unsigned int)(base + k) << 23;
+                    s_result = 1;
+                } else {
+                    s_result = 0;
+                }
+            }
+            __syncthreads();
+            first_round = s_result;                   // 1: the exponent is known, go on with the mantissa
+            __syncthreads();
+        }
+        for (int round = first_round; round < 4; ++round) {
+            const int shift = round == 0 ? 23 : (round == 1 ? 15 : (round == 2 ? 7 : 0));
+            const int width = round == 3 ? 7 : 8;
+            for (int i = tid; i < 256; i += blockDim.x) { hist_lo[i] = 0u; hist_hi[i] = 0u; }
             __syncthreads();
             const unsigned int prefix = s_prefix;
-            const unsigned int mask = round == 0 ? 0u : (0xffffffffu << (shift + 8));
-            for (int i = lo; i < hi; ++i) {
-                const float p = prob_of(row, i, inv_t, mx, inv_z);
+            const unsigned int mask = round == 0 ? 0u : (0xffffffffu << (shift + width));
+            const unsigned int digit = (1u << width) - 1u;
+            // the tokens that share the digits found so far, spread over the bins of the next one (integer sums:
+            // the order does not matter)
+            for_all(e, vocab, inv_z, [&](float p) {
                 const unsigned int bits = __float_as_uint(p);
-                if ((bits & mask) == prefix)
-                    atomicAdd(&hist[(bits >> shift) & 255u], quantise(p));
-            }
+                if ((bits & mask) == prefix) hist_add(hist_lo, hist_hi, (int)((bits >> shift) & digit), quantise(p));
+            });
             __syncthreads();
             if (tid == 0) {
                 unsigned long long run = s_above;
                 int bin = 255;
                 for (; bin > 0; --bin) {
-                    if (run + hist[bin] >= target) break;
-                    run += hist[bin];
+                    const unsigned long long h = ((unsigned long long)hist_hi[bin] << 32) | hist_lo[bin];
+                    if (run + h >= target) break;
+                    run += h;
                 }
                 s_above = run;
                 s_prefix = prefix | ((unsigned int)bin << shift);
@@ -288,25 +392,35 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
         else ties_kept = (target - above + tie_w - 1) / tie_w;  // smallest j with above + j * w >= target
     }
 
-    // rank of this thread's first tie, in index order
-    unsigned long long my_ties = 0;
-    if (pp < 1.0f)
-        for (int i = lo; i < hi; ++i) {
-            const float p = prob_of(row, i, inv_t, mx, inv_z);
-            if (__float_as_uint(p) == tau) ++my_ties;
+    // Tokens at tau.  How many there are is a sum in any order; only when not all of them are kept does their
+    // order in the vocabulary matter, and the rank of this thread's first one is counted over its chunk.
+    unsigned long long ties_before = 0;
+    if (pp < 1.0f) {
+        unsigned long long n_ties = 0;
+        for_all(e, vocab, inv_z, [&](float p) {
+            if (__float_as_uint(p) == tau) ++n_ties;
+        });
+        n_ties = block_sum_u64(n_ties, red);
+        if (n_ties <= ties_kept) {
+            ties_kept = ~0ull;          // all of them: no ranks needed
+        } else {
+            unsigned long long my_ties = 0;
+            for_chunk(e, lo, hi, inv_z, [&](int, float p) {
+                if (__float_as_uint(p) == tau) ++my_ties;
+            });
+            unsigned long long all_ties;
+            ties_before = block_exclusive_scan_u64(my_ties, red, &all_ties);
         }
-    unsigned long long all_ties;
-    const unsigned long long ties_before = block_exclusive_scan_u64(my_ties, red, &all_ties);
+    }
 
     // kept mass of the chunk, then its prefix
     unsigned long long mass = 0, t_rank = ties_before;
-    for (int i = lo; i < hi; ++i) {
-        const float p = prob_of(row, i, inv_t, mx, inv_z);
+    for_chunk(e, lo, hi, inv_z, [&](int, float p) {
         const unsigned int bits = __float_as_uint(p);
         const unsigned long long w = quantise(p);
         if (pp >= 1.0f || bits > tau) mass += w;
         else if (bits == tau) { if (t_rank < ties_kept) mass += w; ++t_rank; }
-    }
+    });
     unsigned long long kept_total;
     const unsigned long long before = block_exclusive_scan_u64(mass, red, &kept_total);
 
@@ -319,7 +433,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
         unsigned long long run = before;
         t_rank = ties_before;
         for (int i = lo; i < hi; ++i) {
-            const float p = prob_of(row, i, inv_t, mx, inv_z);
+            const float p = prob_of(e, i, inv_z);
             const unsigned int bits = __float_as_uint(p);
             const unsigned long long w = quantise(p);
             bool kept = false;
@@ -344,11 +458,12 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
 
 BLM_API int blm_sample(const float* logits, long long row_stride, int n_rows, int vocab, const float* temperature,
                        const float* top_p, const unsigned long long* seeds, const unsigned long long* stream_ids,
-                       const unsigned long long* counters, int* out, cudaStream_t stream) {
+                       const unsigned long long* counters, int* out, float* work, cudaStream_t stream) {
     if (n_rows == 0) return BLM_OK;
     BLM_REQUIRE(vocab > 0, "sample: empty vocabulary");
+    BLM_REQUIRE(work != nullptr, "sample: no room for the rows' exponentials (n_rows x vocab floats)");
     sample_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, row_stride, vocab, temperature, top_p, seeds,
-                                                         stream_ids, counters, out);
+                                                         stream_ids, counters, out, work);
     return blm_check_launch("sample");
 }
 

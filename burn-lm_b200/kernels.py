@@ -86,7 +86,7 @@ _protos = {
         "blm_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "blm_argmax_scratch_floats": [c_int, c_int],
         "blm_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                       c_void_p, c_void_p],
+                       c_void_p, c_void_p, c_void_p],
     },
 }
 _bound: dict[str, ctypes.CDLL] = {}
@@ -475,8 +475,9 @@ def sample(logits, temperature, top_p, seeds, stream_ids, counters, out):
                   (stream_ids, torch.int64), (counters, torch.int64)):
         if t.dtype != dt or t.numel() < b:
             raise KernelError("sample: per-row arguments must be float32/int64 of length B")
+    work = torch.empty((b, logits.shape[1]), dtype=torch.float32, device=logits.device)     # the rows' exponentials
     _call("sampling", "blm_sample", _ptr(logits), logits.stride(0), b, logits.shape[1], _ptr(temperature),
-          _ptr(top_p), _ptr(seeds), _ptr(stream_ids), _ptr(counters), _ptr(out), _stream())
+          _ptr(top_p), _ptr(seeds), _ptr(stream_ids), _ptr(counters), _ptr(out), _ptr(work), _stream())
 
 
 def uniform32(seed, stream_id, counter) -> int:

@@ -36,17 +36,34 @@ class SamplingParams:
 class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
+        self._plan = None       # what does not change from step to step, on the device, for the batch last seen
 
     def sample(self, logits: torch.Tensor, params: SamplingParams, stream_ids, counters) -> list:
         """One token id per row of logits [B, V]; stream_ids[b] and counters[b] name the draw."""
         b = logits.shape[0]
-        out = torch.empty(b, dtype=torch.int32, device=logits.device)
         if params.greedy:
+            out = torch.empty(b, dtype=torch.int32, device=logits.device)
             K.argmax(logits, out)
-        else:
+            return out.tolist()
+        # temperature, top-p, seed and stream ids stay the same while a batch decodes: they are uploaded once;
+        # a step brings its draw counters through pinned memory and takes its tokens back the same way
+        mask = (1 << 63) - 1
+        key = (b, params, tuple(stream_ids), logits.device)
+        plan = self._plan
+        if plan is None or plan["key"] != key:
             f = torch.tensor([[params.temperature] * b, [params.top_p] * b], dtype=torch.float32).to(logits.device)
-            mask = (1 << 63) - 1
-            ids = torch.tensor([[params.seed & mask] * b, [s & mask for s in stream_ids], [c & mask for c in counters]],
-                               dtype=torch.int64).to(logits.device)
-            K.sample(logits, f[0], f[1], ids[0], ids[1], ids[2], out)
-        return out.tolist()
+            ids = torch.tensor([[params.seed & mask] * b, [s & mask for s in stream_ids]], dtype=torch.int64).to(logits.device)
+            plan = self._plan = {
+                "key": key, "f": f, "ids": ids,
+                "counters": torch.zeros(b, dtype=torch.int64, device=logits.device),
+                "host_counters": torch.zeros(b, dtype=torch.int64, pin_memory=True),
+                "out": torch.zeros(b, dtype=torch.int32, device=logits.device),
+                "host_out": torch.zeros(b, dtype=torch.int32, pin_memory=True)}
+            plan["host_counters_np"] = plan["host_counters"].numpy()
+            plan["host_out_np"] = plan["host_out"].numpy()
+        plan["host_counters_np"][:] = [c & mask for c in counters]
+        plan["counters"].copy_(plan["host_counters"], non_blocking=True)
+        K.sample(logits, plan["f"][0], plan["f"][1], plan["ids"][0], plan["ids"][1], plan["counters"], plan["out"])
+        plan["host_out"].copy_(plan["out"], non_blocking=True)
+        torch.cuda.current_stream(logits.device).synchronize()
+        return plan["host_out_np"].tolist()

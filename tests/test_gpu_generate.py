@@ -1,5 +1,7 @@
 """Generation through the Python entry point, sampling kernels against the plain sampler, long
 decoding, and the first tokens of a sequence."""
+import math
+
 import numpy as np
 import pytest
 import torch
@@ -78,6 +80,41 @@ def test_sampling_matches_plain_on_the_same_logits():
         alone = smp.sample(logits[5:6].contiguous(), params, streams[5:6], counters[5:6])
         assert alone == got[5:6]
     assert smp.sample(logits, SamplingParams(0.0), [0] * B, [0] * B) == logits.argmax(-1).tolist()
+
+
+def test_sampling_nucleus_far_below_the_largest_probability():
+    """One token holds half of the mass and a large vocabulary shares the rest in crumbs 2^-17 of it and
+    smaller: the nucleus reaches far below the sixteen exponents under the largest probability that the
+    kernel sums in registers, so its general histogram has to find the threshold.  Against the plain
+    nucleus: the drawn token is kept, and it is the one (up to fp32 rounding of four hundred thousand
+    terms) at which the running kept mass passes u times the kept mass."""
+    from burn_lm_b200 import kernels as K
+    from burn_lm_b200.sampling import Sampler, SamplingParams
+    g = torch.Generator(device="cuda").manual_seed(3)
+    B, V = 12, 400000
+    logits = 0.1 * torch.randn(B, V, device="cuda", generator=g)
+    logits[:, 77] = math.log(V) + 0.05                      # about half of the mass
+    smp = Sampler("cuda")
+    for top_p in (0.9, 0.6):
+        params = SamplingParams(1.0, top_p, seed=99)
+        streams, counters = list(range(B)), [3 * b for b in range(B)]
+        got = smp.sample(logits, params, streams, counters)
+        crumbs = 0
+        for b in range(B):
+            probs = P.temperature_softmax(logits[b].cpu().numpy(), 1.0)
+            assert probs[77] > 0.4 and np.sort(probs)[-2] < probs[77] * 2.0 ** -16
+            keep = P.top_p_keep(probs, top_p)
+            assert abs(np.where(keep, probs, 0.0).sum() - top_p) < 1e-4          # the nucleus ends among the crumbs
+            assert keep[got[b]] or probs[got[b]] >= probs[keep].min() * 0.999
+            kept = np.where(keep, probs, 0.0)
+            run = np.cumsum(kept)
+            target = K.uniform32(99, streams[b], counters[b]) / 2.0 ** 32 * run[-1]
+            tol = 2e-5 * run[-1]
+            assert run[got[b]] - kept[got[b]] - tol <= target < run[got[b]] + tol, (top_p, b, got[b])
+            crumbs += int(got[b] != 77)
+        if top_p == 0.9:
+            assert crumbs >= 2                                  # some draws do land among the crumbs
+    K.check_status("cuda")
 
 
 def test_sampling_frequencies_follow_the_nucleus():
