@@ -206,3 +206,23 @@ def test_a_far_key_decides_the_logits(tmp_path):
         for rid in reqs:
             err = row_error(got[rid], want[rid])
             assert err.max() < 1e-4, (what, rid, float(err.max()), int(err.argmax()))
+
+
+def test_repeated_runs_and_captured_steps_give_the_same_tokens(tmp_path):
+    """Kernels of a decode step start before the kernel before them has ended (programmatic dependent
+    launch): a missing wait would show as tokens that change from run to run, or between the captured
+    graph and the same step launched plainly."""
+    import burn_lm_b200 as blm
+    folder = make_folder(tmp_path, "tiny_c", seed=21, dtype="bfloat16")
+    cfg = CONFIGS["tiny_c"]
+    lm = blm.load(folder, dtype="bfloat16", max_seq_len=512, max_batch=8)
+    prompts = [random_tokens(90 + n, length, cfg["vocab_size"]) for n, length in enumerate([3, 70, 64, 129, 17, 200, 1, 33])]
+    runs = [lm.generate(prompts, sample_len=150, ignore_stop=True).tokens for _ in range(3)]
+    assert runs[0] == runs[1] == runs[2]
+    lm.engine.use_graphs = False
+    plain = lm.generate(prompts, sample_len=150, ignore_stop=True).tokens
+    lm.engine.use_graphs = True
+    assert plain == runs[0]
+    sampled = [lm.generate(prompts, sample_len=40, ignore_stop=True, temperature=0.9, seed=8).tokens for _ in range(2)]
+    assert sampled[0] == sampled[1]
+    lm.engine.verify()
