@@ -1,5 +1,5 @@
 // Sampling from fp32 logits on the device: greedy, and temperature with an optional nucleus
-// (top-p).  One block per sequence.  Every decision of the nucleus and of the draw is made on
+// (top-p).  One block per sequence, or a cluster of blocks for a large vocabulary.  Every decision of the nucleus and of the draw is made on
 // probabilities quantised to 2^-40, in integer arithmetic, so the result does not depend on the
 // order in which threads add things up.
 #include "common.cuh"
@@ -244,6 +244,72 @@ __device__ __forceinline__ void for_chunk(const float* __restrict__ e, int lo, i
 // floor(p * 2^40): scaling a float by a power of two is exact, so this needs no double
 __device__ __forceinline__ unsigned long long quantise(float p) { return __float2ull_rz(__fmul_rn(p, (float)kQuant)); }
 
+// ---- a row over the blocks of a cluster ----
+// The blocks of a cluster share a row: block r takes the r-th piece of the vocabulary in every pass.  What
+// a block-wide sum was becomes: the block's sum into a word of its shared memory, a cluster barrier, every
+// block reads all the words (distributed shared memory) and adds them in the order of the ranks.  The
+// words are used in turn (two sets), so one barrier per sum is enough: a block can only overwrite a word
+// after the barrier of the sum in between, which every block passes after it has read.
+__device__ __forceinline__ unsigned cl_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r)); return r; }
+__device__ __forceinline__ unsigned cl_size() { unsigned r; asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(r)); return r; }
+__device__ __forceinline__ void cl_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ unsigned long long cl_ld_u64(const unsigned long long* local, unsigned rank) {
+    unsigned remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"((unsigned)__cvta_generic_to_shared(local)), "r"(rank));
+    unsigned long long v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];\n" : "=l"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned cl_ld_u32(const unsigned* local, unsigned rank) {
+    unsigned remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"((unsigned)__cvta_generic_to_shared(local)), "r"(rank));
+    unsigned v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];\n" : "=r"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+struct ClusterWords {
+    unsigned long long word[2];     // used in turn
+    int turn;
+};
+// every thread of every block of the cluster calls these with its block's value (the same in all its threads)
+__device__ __forceinline__ unsigned long long cl_sum_u64(unsigned long long block_value, ClusterWords* w, unsigned long long* before) {
+    const int t = w->turn;
+    __syncthreads();
+    if (threadIdx.x == 0) { w->word[t] = block_value; w->turn = t ^ 1; }
+    cl_sync();
+    unsigned long long total = 0, pre = 0;
+    const unsigned me = cl_rank(), n = cl_size();
+    for (unsigned r = 0; r < n; ++r) {
+        const unsigned long long v = cl_ld_u64(&w->word[t], r);
+        if (r < me) pre += v;
+        total += v;
+    }
+    if (before) *before = pre;
+    return total;
+}
+__device__ __forceinline__ float cl_max_f32(float block_value, ClusterWords* w) {
+    const int t = w->turn;
+    __syncthreads();
+    if (threadIdx.x == 0) { w->word[t] = (unsigned long long)__float_as_uint(block_value); w->turn = t ^ 1; }
+    cl_sync();
+    float m = -INFINITY;
+    for (unsigned r = 0, n = cl_size(); r < n; ++r) m = fmaxf(m, __uint_as_float((unsigned)cl_ld_u64(&w->word[t], r)));
+    return m;
+}
+// sums of floats across blocks are taken in the order of the ranks, from the blocks' own sums
+__device__ __forceinline__ float cl_sum_f32(float block_value, ClusterWords* w) {
+    const int t = w->turn;
+    __syncthreads();
+    if (threadIdx.x == 0) { w->word[t] = (unsigned long long)__float_as_uint(block_value); w->turn = t ^ 1; }
+    cl_sync();
+    float sum = 0.f;
+    for (unsigned r = 0, n = cl_size(); r < n; ++r) sum += __uint_as_float((unsigned)cl_ld_u64(&w->word[t], r));
+    return sum;
+}
+
 __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     const float* __restrict__ logits, long long row_stride, int vocab, const float* __restrict__ temperature,
     const float* __restrict__ top_p, const unsigned long long* __restrict__ seeds,
@@ -255,16 +321,23 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     __shared__ unsigned int s_prefix;
     __shared__ unsigned long long s_above;
     __shared__ int s_result;
+    __shared__ ClusterWords words;
 
-    const int b = blockIdx.x;
+    const unsigned rank = cl_rank(), n_blocks = cl_size();
+    const int b = blockIdx.x / n_blocks;             // the cluster's row
     const float* row = logits + (size_t)b * row_stride;
-    float* e = work + (size_t)b * vocab;          // exp(logit / temperature - max), written once below
+    float* e = work + (size_t)b * vocab;             // exp(logit / temperature - max), written once below
     const float inv_t = 1.0f / temperature[b];
     const int tid = threadIdx.x;
+    if (tid == 0) words.turn = 0;
+    // this block's piece of the vocabulary (a multiple of 4 tokens, so that 16-byte loads stay aligned)
+    const int piece = ((vocab + (int)n_blocks - 1) / (int)n_blocks + 3) & ~3;
+    const int p_lo = min(vocab, (int)rank * piece), p_hi = min(vocab, p_lo + piece), p_len = p_hi - p_lo;
+    const float* ep = e + p_lo;
 
     // max and normaliser of softmax(logits / temperature)
     float mx = -INFINITY;
-    for (int i = tid; i < vocab; i += blockDim.x) mx = fmaxf(mx, __fmul_rn(row[i], inv_t));
+    for (int i = p_lo + tid; i < p_hi; i += blockDim.x) mx = fmaxf(mx, __fmul_rn(row[i], inv_t));
     mx = warp_max(mx);
     if ((tid & 31) == 0) redf[tid >> 5] = mx;
     __syncthreads();
@@ -274,24 +347,24 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
         if (tid == 0) redf[32] = t;
     }
     __syncthreads();
-    mx = redf[32];
-    __syncthreads();
+    mx = cl_max_f32(redf[32], &words);
     float z = 0.f;
-    for (int i = tid; i < vocab; i += blockDim.x) {
+    for (int i = p_lo + tid; i < p_hi; i += blockDim.x) {
         const float ei = expf(__fsub_rn(__fmul_rn(row[i], inv_t), mx));
         e[i] = ei;
         z += ei;
     }
-    z = block_sum(z, redf);          // (its barriers also make every thread's e visible to the others)
+    z = block_sum(z, redf);          // (its barriers also make every thread's e visible to the others of the block)
+    z = cl_sum_f32(z, &words);
     const float inv_z = 1.0f / z;
 
-    // contiguous chunk of the vocabulary per thread (index order matters below)
-    const int per = (vocab + blockDim.x - 1) / blockDim.x;
-    const int lo = min(vocab, tid * per), hi = min(vocab, lo + per);
+    // contiguous chunk of the block's piece per thread (index order matters below)
+    const int per = (p_len + blockDim.x - 1) / blockDim.x;
+    const int lo = min(p_hi, p_lo + tid * per), hi = min(p_hi, lo + per);
 
     unsigned long long total = 0;
-    for_all(e, vocab, inv_z, [&](float p) { total += quantise(p); });
-    total = block_sum_u64(total, red);
+    for_all(ep, p_len, inv_z, [&](float p) { total += quantise(p); });
+    total = cl_sum_u64(block_sum_u64(total, red), &words, nullptr);
 
     // nucleus: the key tau (float bits of a probability) with mass(> tau) < target <= mass(>= tau)
     const float pp = top_p[b];
@@ -299,6 +372,18 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     unsigned long long above = 0;         // mass strictly above tau
     unsigned long long tie_w = 0;         // quantised mass of one token at tau
     unsigned long long ties_kept = ~0ull; // how many tokens at tau are kept, in index order
+    // after a block has filled its histogram: every block adds the blocks' histograms up for itself (thread t
+    // takes bin t, in the order of the ranks) and then all of them scan the same numbers
+    auto merge_hist = [&]() {
+        cl_sync();
+        unsigned long long h = 0;
+        if (tid < 256)
+            for (unsigned r = 0; r < n_blocks; ++r)
+                h += ((unsigned long long)cl_ld_u32(hist_hi + tid, r) << 32) | cl_ld_u32(hist_lo + tid, r);
+        cl_sync();                        // everybody has read everybody's bins
+        if (tid < 256) { hist_lo[tid] = (unsigned int)h; hist_hi[tid] = (unsigned int)(h >> 32); }
+        __syncthreads();
+    };
     if (pp < 1.0f) {
         unsigned long long target = (unsigned long long)((double)pp * (double)total);
         if (target < 1) target = 1;
@@ -319,7 +404,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
             unsigned long long wacc[kTop + 1];          // [kTop]: everything below the window
 #pragma unroll
             for (int k = 0; k <= kTop; ++k) wacc[k] = 0ull;
-            for_all(e, vocab, inv_z, [&](float p) {
+            for_all(ep, p_len, inv_z, [&](float p) {
                 const int d = (int)(__float_as_uint(p) >> 23) - base;
                 const unsigned long long w = quantise(p);
 #pragma unroll
@@ -335,7 +420,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
                 for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
                 if ((tid & 31) == 0 && v) hist_add(hist_lo, hist_hi, k, v);       // 32 adds a word
             }
-            __syncthreads();
+            merge_hist();
             if (tid == 0) {
                 unsigned long long run = 0;
                 int k = kTop - 1;
@@ -366,11 +451,12 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
             const unsigned int digit = (1u << width) - 1u;
             // the tokens that share the digits found so far, spread over the bins of the next one (integer sums:
             // the order does not matter)
-            for_all(e, vocab, inv_z, [&](float p) {
+            for_all(ep, p_len, inv_z, [&](float p) {
                 const unsigned int bits = __float_as_uint(p);
                 if ((bits & mask) == prefix) hist_add(hist_lo, hist_hi, (int)((bits >> shift) & digit), quantise(p));
             });
             __syncthreads();
+            merge_hist();
             if (tid == 0) {
                 unsigned long long run = s_above;
                 int bin = 255;
@@ -397,10 +483,10 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     unsigned long long ties_before = 0;
     if (pp < 1.0f) {
         unsigned long long n_ties = 0;
-        for_all(e, vocab, inv_z, [&](float p) {
+        for_all(ep, p_len, inv_z, [&](float p) {
             if (__float_as_uint(p) == tau) ++n_ties;
         });
-        n_ties = block_sum_u64(n_ties, red);
+        n_ties = cl_sum_u64(block_sum_u64(n_ties, red), &words, nullptr);
         if (n_ties <= ties_kept) {
             ties_kept = ~0ull;          // all of them: no ranks needed
         } else {
@@ -408,12 +494,14 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
             for_chunk(e, lo, hi, inv_z, [&](int, float p) {
                 if (__float_as_uint(p) == tau) ++my_ties;
             });
-            unsigned long long all_ties;
-            ties_before = block_exclusive_scan_u64(my_ties, red, &all_ties);
+            unsigned long long block_ties, blocks_before;
+            ties_before = block_exclusive_scan_u64(my_ties, red, &block_ties);
+            cl_sum_u64(block_ties, &words, &blocks_before);
+            ties_before += blocks_before;
         }
     }
 
-    // kept mass of the chunk, then its prefix
+    // kept mass of the chunk, then its prefix over the threads of the block and the blocks of the cluster
     unsigned long long mass = 0, t_rank = ties_before;
     for_chunk(e, lo, hi, inv_z, [&](int, float p) {
         const unsigned int bits = __float_as_uint(p);
@@ -421,8 +509,10 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
         if (pp >= 1.0f || bits > tau) mass += w;
         else if (bits == tau) { if (t_rank < ties_kept) mass += w; ++t_rank; }
     });
-    unsigned long long kept_total;
-    const unsigned long long before = block_exclusive_scan_u64(mass, red, &kept_total);
+    unsigned long long block_mass, blocks_before;
+    unsigned long long before = block_exclusive_scan_u64(mass, red, &block_mass);
+    const unsigned long long kept_total = cl_sum_u64(block_mass, &words, &blocks_before);
+    before += blocks_before;
 
     // draw: the first kept token, in vocabulary order, whose running kept mass exceeds u * kept_total
     const unsigned int u = blm_uniform32(seeds[b], stream_ids[b], counters[b]);
@@ -446,14 +536,17 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
         }
     }
     __syncthreads();
-    if (tid == 0) {
-        int r = s_result;
+    // exactly one thread of the cluster can have found the token; the blocks tell one another
+    const unsigned long long found = cl_sum_u64(s_result >= 0 ? (unsigned long long)(s_result + 1) : 0ull, &words, nullptr);
+    if (rank == 0 && tid == 0) {
+        int r = (int)found - 1;
         if (r < 0) {  // every probability underflowed the quantum: fall back to the largest logit
             float best = -INFINITY; r = 0;
             for (int i = 0; i < vocab; ++i) if (row[i] > best) { best = row[i]; r = i; }
         }
         out[b] = r;
     }
+    cl_sync();       // nobody leaves while its shared memory may still be read
 }
 
 BLM_API int blm_sample(const float* logits, long long row_stride, int n_rows, int vocab, const float* temperature,
@@ -462,8 +555,21 @@ BLM_API int blm_sample(const float* logits, long long row_stride, int n_rows, in
     if (n_rows == 0) return BLM_OK;
     BLM_REQUIRE(vocab > 0, "sample: empty vocabulary");
     BLM_REQUIRE(work != nullptr, "sample: no room for the rows' exponentials (n_rows x vocab floats)");
-    sample_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, row_stride, vocab, temperature, top_p, seeds,
-                                                         stream_ids, counters, out, work);
+    // a row is shared by the blocks of a cluster: eight for a large vocabulary, fewer for a small one
+    unsigned blocks = vocab >= 65536 ? 8u : (vocab >= 16384 ? 4u : (vocab >= 4096 ? 2u : 1u));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks * (unsigned)n_rows);
+    cfg.blockDim = dim3(kSampleThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = blocks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, sample_kernel, logits, row_stride, vocab, temperature, top_p, seeds, stream_ids, counters, out, work);
+    if (err != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "sample: %s", cudaGetErrorString(err));
     return blm_check_launch("sample");
 }
 
