@@ -104,3 +104,30 @@ def test_one_b_shape_three_ways(tmp_path, one_b, dtype, tolerance):
             assert err.max() < tolerance, (what, rid, float(err.max()), int(err.argmax()))
         del eng
         torch.cuda.empty_cache()
+
+
+# The layer sizes of the 8B model of the same family (width 4096, 32 heads on 8 kv heads of 128, inner 14336),
+# one layer, a small vocabulary: wider rows than the 1B shape, a head size of 128 and an inner size whose
+# tokens do not fit the skinny kernel's shared memory (that product then goes to the library).
+LLAMA_8B_ONE_LAYER = dict(LLAMA_1B_TWO_LAYERS, num_hidden_layers=1, hidden_size=4096, head_dim=128, intermediate_size=14336,
+                          vocab_size=3000, tie_word_embeddings=False,
+                          rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                        "original_max_position_embeddings": 8192})
+
+
+@pytest.mark.parametrize("dtype,tolerance", [("float32", 1e-4), ("bfloat16", 3e-2)])
+def test_eight_b_layer_shape(tmp_path, dtype, tolerance):
+    from burn_lm_b200 import Engine, write_random_model
+    folder = write_random_model(str(tmp_path / "8b1l"), LLAMA_8B_ONE_LAYER, seed=4, dtype="bfloat16", device="cuda")
+    cfg, tensors = P.read_model_folder(folder)
+    reqs = {f"w{n}": random_tokens(50 + n, length, 3000) for n, length in enumerate([80, 5, 140])}
+    want = {rid: P.forward(cfg, tensors, toks) for rid, toks in reqs.items()}
+    for what, steps in (("whole", traces.whole(reqs)), ("tail", traces.tail(reqs, 32)), ("batched", traces.batched(reqs, 3, [32, 2, 9]))):
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=traces.max_live_tokens(steps))
+        got = traces.run_in_process(eng, steps, str(tmp_path / what), 3000)
+        for rid in reqs:
+            err = row_error(got[rid], want[rid])
+            assert err.max() < tolerance, (what, rid, float(err.max()), int(err.argmax()))
+        eng.verify()
+        del eng
+        torch.cuda.empty_cache()
