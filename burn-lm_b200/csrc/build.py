@@ -123,6 +123,18 @@ def build(module: str, verbose: bool = True) -> str:
     return out
 
 
+def build_many(modules, verbose: bool = True) -> list[str]:
+    """Compile several modules side by side (a compiler process each); returns their libraries' paths."""
+    todo = [m for m in modules if not os.path.exists(library_path(m))]
+    if len(todo) > 1:
+        threads = [threading.Thread(target=build, args=(m, verbose)) for m in todo]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+    return [build(m, verbose) for m in modules]      # reports a failed build's error; built ones are found
+
+
 def build_all(verbose: bool = True) -> list[str]:
     return [build(m, verbose) for m in MODULES]
 

@@ -17,6 +17,7 @@ import torch
 
 from ..cache import Cache, CacheError
 from ..model import Model, load_model
+from .. import kernels as K
 from ..parts.base import StepContext
 
 
@@ -63,6 +64,7 @@ class Engine:
         self.cache = Cache(model.cache_needs(), model.plan.schedule, max_tokens, max_seqs, max_seq_len,
                            rt.dtype, rt.device)
         self.workspace = Workspace(rt.device)
+        K.prebuild(rt.dtype)
         model.prepare(self.cache.max_seq_len)
         self.vocab_size = model.plan.vocab_size
         self._staging = None    # pinned int32 staging for the step's metadata
