@@ -65,7 +65,20 @@ def _digest(module: str) -> str:
     return h.hexdigest()[:12]
 
 
+_dir: str | None = None
+_dir_lock = threading.Lock()
+
+
 def _build_dir() -> str:
+    """Where the libraries go: decided once per process (the probe below is not safe to run from two threads)."""
+    global _dir
+    with _dir_lock:
+        if _dir is None:
+            _dir = _find_build_dir()
+        return _dir
+
+
+def _find_build_dir() -> str:
     d = os.path.join(HERE, "_build")
     try:
         os.makedirs(d, exist_ok=True)
