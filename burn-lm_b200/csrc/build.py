@@ -10,6 +10,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -126,7 +127,7 @@ def build(module: str, verbose: bool = True) -> str:
         raise BuildError(f"nvcc failed for module {module!r}:\n{log}")
     os.replace(tmp, out)
     for old in os.listdir(os.path.dirname(out)):    # libraries of older sources of this module
-        if old.startswith(f"libblm_{module}_") and old.endswith(".so") and old != os.path.basename(out):
+        if re.fullmatch(rf"libblm_{module}_[0-9a-f]{{12}}\.so", old) and old != os.path.basename(out):
             try:
                 os.remove(os.path.join(os.path.dirname(out), old))
             except OSError:
