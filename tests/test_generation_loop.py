@@ -141,3 +141,44 @@ def test_plan_batches_respects_pages_slots_and_batch_size():
     assert b == [[0, 1, 2, 3], [4]]
     b, rej = plan_batches([10, 500, 0], sample_len=10, free_pages=4, free_slots=8, max_seq_len=1000)
     assert b == [[0]] and set(rej) == {1, 2}
+
+
+def test_norm_handoff_is_only_claimed_by_the_norm_it_was_left_for():
+    """The letterbox between the product that adds into the stream last and the norm that reads it next
+    (parts.linear.NormHandoff): what was left is claimed once, by the expected norm's gamma on the same
+    stream, and never by another."""
+    import torch
+    from burn_lm_b200.parts.linear import HandedNorm, NormHandoff
+
+    class Norm:
+        takes_handed_norm = True
+
+        def __init__(self):
+            self.gamma = torch.ones(4)
+
+    class PlainNorm:
+        def __init__(self):
+            self.gamma = torch.ones(4)
+
+    h = NormHandoff()
+    a, b, plain = Norm(), Norm(), PlainNorm()
+    stream, other = torch.zeros(2, 4), torch.zeros(2, 4)
+    handed = HandedNorm(torch.zeros(2, 4), torch.zeros(1, 16))
+    h.expect(plain)
+    assert h.wanted is None                       # a norm that cannot take one is not expected
+    h.expect(a)
+    assert h.wanted is a
+    h.leave(stream, a.gamma, handed)
+    assert h.claim(stream, b.gamma) is None       # another norm: nothing, and what was left is gone
+    assert h.claim(stream, a.gamma) is None
+    h.expect(a)
+    h.leave(stream, a.gamma, handed)
+    assert h.claim(other, a.gamma) is None        # another stream
+    h.expect(a)
+    h.leave(stream, a.gamma, handed)
+    assert h.claim(stream, a.gamma) is handed
+    assert h.claim(stream, a.gamma) is None       # once
+    h.expect(a)
+    h.leave(stream, a.gamma, handed)
+    h.expect(b)                                   # a new expectation forgets what was left for the old one
+    assert h.claim(stream, a.gamma) is None
