@@ -652,10 +652,14 @@ static size_t gemv_plan(int N, int K, int x_mode, int* n_stages_out, int* nbt_ou
     return total;
 }
 
-// 1 when blm_gemv takes the shape, else 0 (the caller then uses the library product).
-BLM_API int blm_gemv_supported(int N, int M, int K) {
+// 1 when blm_gemv takes the shape, else 0 (the caller then uses the library product).  `plain_tokens`: the
+// input is a bfloat16 matrix used row by row (not a stream to normalise, no gathered rows); such tokens
+// can travel with the weights, so their K is not bounded by shared memory.
+BLM_API int blm_gemv_supported(int N, int M, int K, int plain_tokens) {
     int st, nbt;
-    return N >= 1 && N <= 16 && K % 64 == 0 && M >= 1 && gemv_plan(N, K, X_STAGED, &st, &nbt) > 0;
+    if (!(N >= 1 && N <= 16 && K % 64 == 0 && M >= 1)) return 0;
+    if (gemv_plan(N, K, X_STAGED, &st, &nbt) > 0) return 1;
+    return plain_tokens && gemv_plan(N, K, X_IN_RING, &st, &nbt) > 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -763,13 +767,21 @@ BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, 
     const int out_per_tile = epi == EPI_SWIGLU ? 8 : 16;
     const int tiles = (M + out_per_tile - 1) / out_per_tile;
     const int grid = tiles < 148 ? tiles : 148;
-    // one tile per block and plain tokens: the tokens travel with the weights
+    // Plain tokens: with one tile per block they travel with the weights; else they are fetched once by TMA;
+    // and when they are too many for that (a very wide input) they travel with the weights after all, once
+    // per tile.  A stream to normalise or gathered rows are staged by the consumers.
     a.x_mode = X_STAGED;
-    if (x != nullptr && rows == nullptr)
-        a.x_mode = (tiles <= 148 && ssq_in == nullptr && K >= 2 * kStageK) ? X_IN_RING : X_BY_TMA;
     int nbt;
-    size_t smem = gemv_plan(N, K, a.x_mode, &a.n_stages, &nbt);
-    if (smem == 0 && a.x_mode != X_STAGED) {
+    size_t smem = 0;
+    if (x != nullptr && rows == nullptr) {
+        a.x_mode = (tiles <= 148 && ssq_in == nullptr && K >= 2 * kStageK) ? X_IN_RING : X_BY_TMA;
+        smem = gemv_plan(N, K, a.x_mode, &a.n_stages, &nbt);
+        if (smem == 0 && a.x_mode == X_BY_TMA) {
+            a.x_mode = X_IN_RING;
+            smem = gemv_plan(N, K, X_IN_RING, &a.n_stages, &nbt);
+        }
+    }
+    if (smem == 0) {
         a.x_mode = X_STAGED;
         smem = gemv_plan(N, K, X_STAGED, &a.n_stages, &nbt);
     }

@@ -72,7 +72,7 @@ _protos = {
         "blm_gemv": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
                      c_float, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int,
                      c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
-        "blm_gemv_supported": [c_int, c_int, c_int],
+        "blm_gemv_supported": [c_int, c_int, c_int, c_int],
     },
     "runtime": {
         "blm_graph_step": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p],
@@ -310,8 +310,10 @@ class _GemvRope(ctypes.Structure):
                 ("hd", c_int), ("page_size", c_int), ("write_cache", c_int)]
 
 
-def gemv_supported(n_tokens, m, k) -> bool:
-    return bool(_lib("gemv").blm_gemv_supported(n_tokens, m, k))
+def gemv_supported(n_tokens, m, k, plain_tokens=False) -> bool:
+    """Whether gemv() takes the shape.  `plain_tokens`: the input is a bfloat16 [N, K] tensor used row by row
+    (no stream to normalise, no gathered rows): then a very wide K is taken too."""
+    return bool(_lib("gemv").blm_gemv_supported(n_tokens, m, k, 1 if plain_tokens else 0))
 
 
 def gemm_tc_supported(m, n, k) -> bool:

@@ -89,10 +89,11 @@ class Linear:
         self.gate_tile = gate_tile
         self.out_features, self.in_features = weight.shape
 
-    def _skinny(self, n_tokens: int, m: int) -> bool:
+    def _skinny(self, n_tokens: int, m: int, x=None) -> bool:
         w = self.weight
+        plain = isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16
         return (w.dtype == torch.bfloat16 and w.is_cuda and n_tokens <= SKINNY_TOKENS
-                and K.gemv_supported(n_tokens, m, self.in_features))
+                and K.gemv_supported(n_tokens, m, self.in_features, plain_tokens=plain))
 
     @staticmethod
     def _tokens(x) -> int:
@@ -114,7 +115,7 @@ class Linear:
 
     def __call__(self, x, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         n = self._tokens(x)
-        if self._skinny(n, self.out_features):
+        if self._skinny(n, self.out_features, x):
             out_dtype = out_dtype or torch.bfloat16
             if out_dtype in (torch.bfloat16, torch.float32):
                 out = torch.empty((n, self.out_features), dtype=out_dtype, device=self.weight.device)
@@ -129,7 +130,7 @@ class Linear:
         (returns None); otherwise the product, for the next norm to add.  With a `handoff` that expects a
         norm, the kernel also leaves that norm's input there."""
         n = self._tokens(x)
-        if stream is not None and self._skinny(n, self.out_features):
+        if stream is not None and self._skinny(n, self.out_features, x):
             hand_over = None
             norm = handoff.wanted if handoff is not None else None
             if norm is not None and n <= K.SQUARES_ROWS and norm.gamma.numel() == self.out_features:
@@ -148,7 +149,7 @@ class Linear:
         takes the step, it rotates q and k and appends k and v to the cache in its epilogue, writes q to
         `q_out` and this returns True; else nothing is done."""
         n = self._tokens(x)
-        if q_out.dtype != torch.bfloat16 or not self._skinny(n, self.out_features):
+        if q_out.dtype != torch.bfloat16 or not self._skinny(n, self.out_features, x):
             return False
         K.gemv(self.weight, n, out=q_out, rope=rope, **self._source(x))
         return True
@@ -158,7 +159,7 @@ class Linear:
         n = self._tokens(x)
         inner = self.out_features // 2
         act = torch.empty((n, inner), dtype=out_dtype, device=self.weight.device)
-        if out_dtype == torch.bfloat16 and self.gate_tile == K.GATE_TILE and self._skinny(n, inner):
+        if out_dtype == torch.bfloat16 and self.gate_tile == K.GATE_TILE and self._skinny(n, inner, x):
             K.gemv(self.weight, n, out=act, swiglu=True, **self._source(x))
             return act
         if (out_dtype == torch.bfloat16 and self.gate_tile == K.GATE_TILE and self.weight.dtype == torch.bfloat16

@@ -312,12 +312,13 @@ def gemv_reference(w, x):
 
 @pytest.mark.parametrize("n", [1, 3, 8, 9, 16])
 # (18944, 2048): eight tiles for every block, all warps busy; (40016, 512): several rounds, the last one partial
-@pytest.mark.parametrize("m,k", [(40, 64), (200, 192), (3072, 2048), (1000, 8192), (77, 4160), (2500, 512), (18944, 2048), (40016, 512)])
+@pytest.mark.parametrize("m,k", [(40, 64), (200, 192), (3072, 2048), (1000, 8192), (77, 4160), (2500, 512), (18944, 2048), (40016, 512),
+                                 (4096, 14336)])
 def test_gemv_store(n, m, k):
     g = torch.Generator(device="cuda").manual_seed(n * 1000 + m)
     w = (torch.randn(m, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
     x = torch.randn(n, k, device="cuda", generator=g).to(torch.bfloat16)
-    if not K().gemv_supported(n, m, k):
+    if not K().gemv_supported(n, m, k, plain_tokens=True):
         assert n > 8 and k >= 8192          # only: too many tokens of too wide rows for shared memory
         pytest.skip("the tokens do not fit shared memory; the library product takes this shape")
     want = gemv_reference(w, x)
