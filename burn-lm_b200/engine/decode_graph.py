@@ -64,6 +64,10 @@ class DecodeGraph:
         self._loop_graph = None     # forward + argmax + advance
         self._greedy_graph = None   # forward + argmax
         self._greedy_exec = None    # its cudaGraphExec_t (an integer) once known; False when torch does not give it out
+        self._sample_graph = None   # forward + temperature / nucleus draw
+        self._sample_exec = None
+        self._sample_key = None     # (sampling parameters, stream ids) now in the graph's buffers
+        self._sample_f = self._sample_ids = self._sample_counters = None
         self._loop_history_steps = 0
         self._copied = None
         self.launches_per_step = 0
@@ -136,6 +140,57 @@ class DecodeGraph:
                 self._greedy_exec = None
             if self._greedy_exec is None:
                 self._greedy_exec = False      # asked once; stay on the interpreter's path
+        return self._host_sampled_np.tolist()
+
+    def step_sampled_host(self, tokens, positions, slots, params, stream_ids, counters) -> list:
+        """A step that draws its tokens by temperature and nucleus inside the captured graph, from host
+        inputs to host outputs.  temperature, top-p, seed and the sequences' stream ids sit in device
+        buffers of the graph (rewritten when they change); a step brings its draw counters beside its
+        tokens, positions and slots."""
+        mask = (1 << 63) - 1
+        b = self.batch
+        key = (params, tuple(stream_ids))
+        if self._sample_key != key:
+            if self._sample_f is None:
+                dev = self.meta.device
+                self._sample_f = torch.zeros((2, b), dtype=torch.float32, device=dev)
+                self._sample_ids = torch.zeros((2, b), dtype=torch.int64, device=dev)
+                self._sample_counters = torch.zeros(b, dtype=torch.int64, device=dev)
+                self._host_counters = torch.zeros(b, dtype=torch.int64, pin_memory=True)
+                self._host_counters_np = self._host_counters.numpy()
+            self._sample_f.copy_(torch.tensor([[params.temperature] * b, [params.top_p] * b], dtype=torch.float32))
+            self._sample_ids.copy_(torch.tensor([[params.seed & mask] * b, [s & mask for s in stream_ids]], dtype=torch.int64))
+            self._sample_key = key
+        self._host_counters_np[:] = [c & mask for c in counters]
+        self.ctx.host["slots"], self.ctx.host["start_pos"] = list(slots), list(positions)
+
+        def draw():
+            K.sample(self._forward(), self._sample_f[0], self._sample_f[1], self._sample_ids[0], self._sample_ids[1],
+                     self._sample_counters, self.sampled)
+
+        if self._sample_exec:
+            self._host_meta_np[:] = [*tokens, *positions, *slots]
+            K.graph_step(self._sample_exec, self.meta, self.host_meta, self.host_sampled, self.sampled,
+                         dev_in2=self._sample_counters, host_in2=self._host_counters)
+            return self._host_sampled_np.tolist()
+        self.load(tokens, positions, slots)
+        self._sample_counters.copy_(self._host_counters, non_blocking=True)
+        if self._sample_graph is None:
+            draw()                                   # the first step runs plainly and warms everything up
+            torch.cuda.synchronize()
+            result = self.sampled.tolist()
+            g = torch.cuda.CUDAGraph()
+            with _capturing(g):
+                draw()
+            self._sample_graph = g
+            try:
+                self._sample_exec = int(g.raw_cuda_graph_exec()) or False
+            except Exception:
+                self._sample_exec = False            # stay on the interpreter's path
+            return result
+        self._sample_graph.replay()
+        self.host_sampled.copy_(self.sampled, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
         return self._host_sampled_np.tolist()
 
     def run(self, n_steps: int, keep_history: bool = True) -> torch.Tensor:

@@ -142,6 +142,29 @@ class Engine:
             cache.seq_len[s] = n + 1
         return out
 
+    def decode_sampled(self, slots, tokens, params, stream_ids, counters) -> Optional[list]:
+        """One decode step that draws every sequence's next token (temperature, nucleus) inside the captured
+        graph; `stream_ids` and `counters` name the draws.  None when this engine does not capture its steps."""
+        if not self.use_graphs:
+            return None
+        cache = self.cache
+        starts = []
+        grow = None
+        for s, t in zip(slots, tokens):
+            if not 0 <= t < self.vocab_size:
+                raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
+            n = cache.seq_len[s]
+            starts.append(n)
+            if n % 64 == 0 or n >= cache.max_seq_len:
+                grow = True
+        if grow or len(set(slots)) != len(slots):
+            cache.reserve([(s, n + 1) for s, n in zip(slots, starts)])
+        g = self.decode_graph(len(slots), max(starts) + 1)
+        out = g.step_sampled_host(tokens, starts, slots, params, stream_ids, counters)
+        for s, n in zip(slots, starts):
+            cache.seq_len[s] = n + 1
+        return out
+
     # -- the step ------------------------------------------------------------------------------------
     def _pack(self, entries):
         """Validate the entries and lay their metadata out in one int32 array (host)."""

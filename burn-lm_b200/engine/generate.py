@@ -135,6 +135,7 @@ class GenerationLoop:
         max_len = engine.cache.max_seq_len
         slots = {i: engine.acquire() for i in batch}
         fused = getattr(engine, "decode_greedy", None)
+        fused_draw = getattr(engine, "decode_sampled", None)
         # a request's draws are numbered from 0 in a stream of its own: (seed, request index)
         live = list(batch)
         try:
@@ -174,6 +175,9 @@ class GenerationLoop:
                 tokens = None
                 if params.greedy and fused is not None:      # the engine samples inside its captured step
                     tokens = fused([slots[i] for i in live], [results[i].tokens[-1] for i in live])
+                elif not params.greedy and fused_draw is not None:
+                    tokens = fused_draw([slots[i] for i in live], [results[i].tokens[-1] for i in live], params, live,
+                                        [len(results[i].tokens) for i in live])
                 if tokens is None:
                     entries = [StepEntry(slots[i], [results[i].tokens[-1]], [0]) for i in live]
                     logits = engine.step(entries)

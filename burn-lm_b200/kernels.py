@@ -75,7 +75,8 @@ _protos = {
         "blm_gemv_supported": [c_int, c_int, c_int, c_int],
     },
     "runtime": {
-        "blm_graph_step": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p],
+        "blm_graph_step": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
+                           c_void_p],
     },
     "gemm_tc": {
         "blm_gemm_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
@@ -335,13 +336,14 @@ def gemm_tc(x, w, out, swiglu=False):
           1 if swiglu else 0, _ptr(status_word(x.device)), _stream())
 
 
-def graph_step(graph_exec: int, dev_in, host_in, host_out, dev_out, kernels: int = 0) -> None:
-    """One captured step driven from native code: host_in (pinned) -> dev_in, the instantiated graph
-    `graph_exec` (a cudaGraphExec_t as an integer), dev_out -> host_out (pinned), and the wait, on the
-    current stream."""
-    _call("runtime", "blm_graph_step", c_void_p(graph_exec), _ptr(dev_in), c_void_p(host_in.data_ptr()),
-          host_in.numel() * host_in.element_size(), c_void_p(host_out.data_ptr()), _ptr(dev_out),
-          host_out.numel() * host_out.element_size(), _stream(), kernels=kernels)
+def graph_step(graph_exec: int, dev_in, host_in, host_out, dev_out, dev_in2=None, host_in2=None) -> None:
+    """One captured step driven from native code: host_in (pinned) -> dev_in (and host_in2 -> dev_in2), the
+    instantiated graph `graph_exec` (a cudaGraphExec_t as an integer), dev_out -> host_out (pinned), and the
+    wait, on the current stream."""
+    nbytes = lambda t: t.numel() * t.element_size() if t is not None else 0
+    _call("runtime", "blm_graph_step", c_void_p(graph_exec), _ptr(dev_in), c_void_p(host_in.data_ptr()), nbytes(host_in),
+          _ptr(dev_in2), c_void_p(host_in2.data_ptr()) if host_in2 is not None else c_void_p(0), nbytes(host_in2),
+          c_void_p(host_out.data_ptr()), _ptr(dev_out), nbytes(host_out), _stream(), kernels=0)
 
 
 _status: dict = {}
