@@ -1,12 +1,14 @@
-// Decode attention for bf16: one new token per sequence against its paged cache, grouped-query,
-// the pages of a sequence split over blocks.  A block owns one (sequence, kv head, split).  Its
-// producer thread streams the split's pages into a ring in shared memory: a page of one kv head is
-// 64 keys x HD, contiguous, so one bulk asynchronous copy (cp.async.bulk, completion on an mbarrier)
-// brings its keys and another its values.  Four consumer warps share each page: HD / 8 lanes hold a
-// key (8 lanes of the head each), the partial dot products of the G query heads of the group are
-// summed over those lanes with shuffles, and every lane keeps a running (max, sum, output slice) per
-// head.  The running max is only raised when a score exceeds it, so a key costs one exponential per
-// head.  Waits on mbarriers are bounded; one that runs out is recorded in the status word.
+// Decode attention for bf16: one new token per sequence against its paged cache, grouped-query.  A block
+// owns one (sequence, kv head, split of the sequence's pages).  Its producer warp reads the page numbers
+// (32 at a time) and streams the pages into a ring in shared memory: TMA boxes of 64 keys x 64 lanes with
+// the 128-byte swizzle (cp.async.bulk.tensor over the pool seen as a matrix), completion on mbarriers.
+// The G query heads of the kv head are rows of a 16-row tensor-core tile, so scores and outputs are
+// mma.sync.m16n8k16 products; the four warps of a consumer group take 16 keys of a page each, and one, two
+// or four groups work on different pages at once (a warp alone on its scheduler waits out every latency
+// of its chain).  The ring is as deep as the block's walk when few blocks run, two pages when many share
+// an SM.  Warps and groups keep their own running (max, sum, output) and merge at the end; splits of a
+// long sequence are merged by a second kernel.  Waits on mbarriers are bounded; one that runs out is
+// recorded in the status word.
 #pragma once
 #include <cuda.h>
 

@@ -1,26 +1,34 @@
 // Skinny matrix products for decode steps: y[N, M] = x[N, K] . W[M, K]^T with N <= 16 tokens, bf16
 // weights streamed once from HBM, fp32 accumulation on the tensor cores.
 //
-// One persistent block per SM.  A producer thread feeds a ring of shared-memory stages with TMA
-// tile copies (cp.async.bulk.tensor, one 8 KB box of 16 weight rows by 256 k per stage, 128-byte
-// swizzle, completion counted on mbarriers), so ~100 KB of weights are in flight per SM whatever
-// the consumers do.  Each of the eight consumer warps owns a tile of 16 weight rows at a time and
-// walks its whole K, stage after stage, through a part of the ring that is its own (so that it sees
-// every phase of its barriers, which a parity wait needs); the producer deals the stages of the
-// warps' tiles in turn,
-// multiplying with mma.sync.m16n8k16: the weight rows are the "A" operand, the tokens (staged once
-// per block in shared memory) the "B" operand.  A thread reads 16 contiguous bytes of a weight row;
-// the k index inside an instruction is permuted the same way for both operands, which a dot
-// product does not notice, so the rows need no transpose.  A warp sums its tile alone, in one fixed
-// order, and writes it from registers: no reduction between warps, no barrier after the start.
+// One persistent block per SM.  A producer warp feeds a ring of shared-memory stages with TMA tile copies
+// (cp.async.bulk.tensor, one 8 KB box of 16 weight rows by 256 k per stage, 128-byte swizzle, completion
+// counted on mbarriers), eight of its lanes each polling the barriers of one consumer warp, so ~100 KB of
+// weights are in flight per SM whatever the consumers do.  Each of the eight consumer warps owns a tile
+// of 16 weight rows at a time (or a slice of its K, when the block has few tiles) and walks it stage after
+// stage through a part of the ring that is its own (so that it sees every phase of its barriers, which a
+// parity wait needs), multiplying with mma.sync.m16n8k16: the weight rows are the "A" operand, the tokens
+// the "B" operand.  A thread reads 16 contiguous bytes of a weight row; the k index inside an instruction
+// is permuted the same way for both operands, which a dot product does not notice, so the rows need no
+// transpose.  Sums are taken in one fixed order; slices of K meet in shared memory.
 // The weight is seen by the TMA as [K / 64][rows][64]: a box is 4 chunks of 64 k for 16 rows, which
 // lands in shared memory as [chunk][row][128 bytes].
 //
+// The tokens reach shared memory in one of three ways: with the weights, a box behind every stage's
+// weight box (one tile per block, or tokens too wide to keep); fetched once by TMA in chunks of 256 k with
+// a barrier each, so that the first weights are worked on while later tokens are on their way; or staged
+// by the consumers, which then also compute the RMS norm of the fp32 stream.
+//
 // Fused around the product, to save launches and activation traffic:
-//   prologue  x = rmsnorm(resid[rows]) * gamma computed by every block from the fp32 residual stream
+//   prologue  x = rmsnorm(resid[rows]) * gamma from the fp32 residual stream, or a norm handed over by the
+//             product that wrote the stream (x = stream * gamma in bf16 and the rows' sums of squares in
+//             parts): the result's rows are then scaled by 1 / rms
 //   epilogue  store (bf16 or fp32) | silu(gate) * up (a fused weight whose 16-row tiles hold 8 gate
 //             rows, then the 8 up rows of the same outputs)
-//             | resid += y (the residual add of the stream, exactly one writer per element)
+//             | resid += y (exactly one writer per element), optionally handing the next norm over
+//             | rotary embedding of q and k and the append of k and v to the paged cache
+// The kernel is launched as a programmatic dependent: its blocks start while the kernel before still
+// runs, set up and prefetch weights, and wait (griddepcontrol.wait) only where they first touch its output.
 // Every wait on an mbarrier is bounded: after kSpinLimit polls the thread records the failure in
 // the status word the caller gave and leaves the kernel.
 #include <cuda.h>
