@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
         bool more = w < kConsumerWarps && w < my_units;
         unsigned idle = 0;
         if (a.x_mode != X_STAGED) {
-            // The weights of the first stages (of the warps' units of round 0) go out at once; the tokens
+            // The weights of the first stages (of the warps' first units) go out at once; the tokens
             // are the work of the kernel before, so they follow after the wait: with the weights, onto
             // the same barriers, or in chunks of their own, one lane a chunk.
             int pre = 0;

@@ -14,7 +14,8 @@ import pytest
 
 from plain import llama_plain as P
 
-REF = os.environ.get("BURN_LM_REFERENCE", "/root/reference")
+# the reference's tree: where BURN_LM_REFERENCE says, else a folder `reference` beside this repository
+REF = os.environ.get("BURN_LM_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 LLAMA = os.path.join(REF, "crates", "burn-lm-llama", "src")
 
 pytestmark = pytest.mark.skipif(not os.path.isdir(LLAMA), reason="reference tree not mounted")
