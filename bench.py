@@ -159,11 +159,12 @@ def random_prompts(n, length, vocab, seed):
     return [[int(x) for x in rng.integers(0, vocab, size=length)] for _ in range(n)]
 
 
-def device_decode(engine, batch, steps, warmup, cfg, sample_clocks=False):
+def device_decode(engine, batch, steps, warmup, cfg, sample_clocks=False, prompt_len=None):
     """Prefill `batch` prompts, then time `steps` decode steps that run back to back on the device."""
     import torch
     from burn_lm_b200 import StepEntry, kernels
-    prompts = random_prompts(batch, PROMPT, cfg["vocab_size"], seed=batch)
+    plen = prompt_len or PROMPT
+    prompts = random_prompts(batch, plen, cfg["vocab_size"], seed=batch)
     slots = [engine.acquire() for _ in range(batch)]
     try:
         # prompts go in a few at a time to keep the prefill's activations small
@@ -172,7 +173,7 @@ def device_decode(engine, batch, steps, warmup, cfg, sample_clocks=False):
         first = [p[-1] for p in prompts]
         engine.decode_run(slots, first, max(warmup, 3))          # warm-up: captures the graph, W steps
         for s in slots:                                          # rewind: the timed run decodes from the prompt's end
-            engine.cache.set_length(s, PROMPT)
+            engine.cache.set_length(s, plen)
         torch.cuda.synchronize()
         before = kernels.launch_count()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -187,7 +188,7 @@ def device_decode(engine, batch, steps, warmup, cfg, sample_clocks=False):
         if sampler:
             sampler.__exit__()
         ms = start.elapsed_time(stop)
-        g = engine.decode_graph(batch, PROMPT + steps)
+        g = engine.decode_graph(batch, plen + steps)
         launches = g.launches_per_step * steps + (kernels.launch_count() - before)
         assert history.shape == (steps, batch)
         engine.verify()        # no kernel gave up a bounded wait
@@ -198,23 +199,48 @@ def device_decode(engine, batch, steps, warmup, cfg, sample_clocks=False):
             engine.release(s)
 
 
-def time_prefill(engine, cfg, reps=5):
+def time_prefill(engine, cfg, reps=5, tokens=PREFILL_TOKENS, n_prompts=1):
+    """Median time of one prefill step: `n_prompts` prompts of `tokens` tokens each, the last logits wanted."""
     import torch
     from burn_lm_b200 import StepEntry
-    prompt = random_prompts(1, PREFILL_TOKENS, cfg["vocab_size"], seed=99)[0]
+    prompts = random_prompts(n_prompts, tokens, cfg["vocab_size"], seed=99)
     times = []
     for r in range(reps + 2):
-        slot = engine.acquire()
+        slots = [engine.acquire() for _ in prompts]
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         start.record()
-        engine.step([StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+        engine.step([StepEntry(s, p, [tokens - 1]) for s, p in zip(slots, prompts)])
         stop.record()
         torch.cuda.synchronize()
-        engine.release(slot)
+        for s in slots:
+            engine.release(s)
         if r >= 2:
             times.append(start.elapsed_time(stop))
     return statistics.median(times)
+
+
+def sweep(engine, cfg, pk):
+    """Decode and prefill at further batch sizes and context lengths, one JSON line each, with the
+    fraction of the measured peak (bytes a step has to read, or flops) beside the time."""
+    for prompt_len in (512, 2048, 3840):
+        for b in (1, 8, 64):
+            steps = 128
+            r = device_decode(engine, b, steps, 3, cfg, prompt_len=prompt_len)
+            step_bytes = weight_bytes(cfg) + b * (prompt_len + steps / 2.0) * kv_bytes_per_token(cfg)
+            gbs = step_bytes / (r["ms_per_step"] / 1e3) / 1e9
+            print(json.dumps({"decode": {"batch": b, "context": prompt_len, "ms_per_step": round(r["ms_per_step"], 4),
+                                         "tokens_per_s": round(r["tokens_per_s"], 1), "gb_per_s": round(gbs, 1),
+                                         "frac_hbm": round(gbs / pk["hbm_gbs"], 3)}}), flush=True)
+    h, hd, layers = cfg["num_attention_heads"], cfg["head_dim"], cfg["num_hidden_layers"]
+    for n_prompts, tokens in ((1, 128), (1, 512), (1, 2048), (1, 4096), (8, 512), (16, 1024)):
+        ms = time_prefill(engine, cfg, reps=3, tokens=tokens, n_prompts=n_prompts)
+        total = n_prompts * tokens
+        # products over all tokens, attention within each prompt
+        flops = prefill_flops(cfg, total) - layers * 2.0 * h * hd * (total * total - n_prompts * tokens * tokens)
+        print(json.dumps({"prefill": {"prompts": n_prompts, "tokens_each": tokens, "ms": round(ms, 3),
+                                      "tokens_per_s": round(total / (ms / 1e3), 1),
+                                      "frac_bf16": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3)}}), flush=True)
 
 
 def run_ours(args):
@@ -240,6 +266,9 @@ def run_ours(args):
         return 0
     if args.only == "prefill":
         print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(time_prefill(engine, cfg, reps=1), 3)}))
+        return 0
+    if args.only == "sweep":
+        sweep(engine, cfg, pk)
         return 0
     main = device_decode(engine, batch, steps, warmup, cfg, sample_clocks=True)
     points = {}
@@ -300,7 +329,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--only", default=None, choices=["decode", "prefill"], help="run one workload briefly (for profilers)")
+    ap.add_argument("--only", default=None, choices=["decode", "prefill", "sweep"],
+                    help="run one workload briefly (for profilers), or a sweep over batch sizes and context lengths")
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration's 16 (named in config)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -190,7 +190,9 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const int* __restrict__ 
     T* kdst = nullptr;
     T* vdst = nullptr;
     if (write_cache) {
-        const int slot = slot_of_seq[token_seq[n]];
+        const int seq = token_seq[n];
+        if (seq < 0) return;         // a row of no sequence (padding): nothing of it reaches the cache
+        const int slot = slot_of_seq[seq];
         const int page = block_table[(size_t)slot * table_stride + pos / page_size];
         const size_t page_elems = (size_t)n_kv * page_size * hd;
         kdst = pool + (size_t)page * 2 * page_elems + (size_t)(pos % page_size) * hd;
@@ -253,7 +255,9 @@ __global__ void rope_append_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, con
     __nv_bfloat16* kdst = nullptr;
     __nv_bfloat16* vdst = nullptr;
     if (write_cache) {
-        const int slot = slot_of_seq[token_seq[n]];
+        const int seq = token_seq[n];
+        if (seq < 0) return;         // a row of no sequence (padding): nothing of it reaches the cache
+        const int slot = slot_of_seq[seq];
         const int page = block_table[(size_t)slot * table_stride + pos / page_size];
         const size_t page_elems = (size_t)n_kv * page_size * hd;
         kdst = pool + (size_t)page * 2 * page_elems + (size_t)(pos % page_size) * hd;

@@ -408,9 +408,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
         const int pos = r.token_pos[tid];
         rope_pos[tid] = pos;
         if (r.write_cache) {
-            const int slot = r.slot_of_seq[r.token_seq[tid]];
-            const int page = r.block_table[(size_t)slot * r.table_stride + pos / r.page_size];
-            rope_cache[tid] = ((long long)page * 2 * r.n_kv * r.page_size + pos % r.page_size) * r.hd;
+            const int seq = r.token_seq[tid];
+            long long where = -1;       // a row of no sequence (padding): nothing of it reaches the cache
+            if (seq >= 0) {
+                const int slot = r.slot_of_seq[seq];
+                const int page = r.block_table[(size_t)slot * r.table_stride + pos / r.page_size];
+                where = ((long long)page * 2 * r.n_kv * r.page_size + pos % r.page_size) * r.hd;
+            }
+            rope_cache[tid] = where;
         }
     }
     consumer_barrier();
@@ -599,6 +604,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
                         dst = reinterpret_cast<__nv_bfloat16*>(a.y) + (size_t)b * a.ldy + (size_t)head * r.hd;
                     } else {
                         const int kvh = head - r.n_heads;          // k heads, then v heads
+                        if (rope_cache[b] < 0) continue;
                         dst = r.pool + rope_cache[b] +
                               (kvh < r.n_kv ? (size_t)kvh * head_stride_cache : page_elems + (size_t)(kvh - r.n_kv) * head_stride_cache);
                     }

@@ -21,14 +21,15 @@ from .engine import Workspace
 
 
 @contextlib.contextmanager
-def _capturing(graph):
+def _capturing(graph, pool=None):
     """Capture with the garbage collector held back: a collection in the middle of a capture may
-    destroy an older CUDA graph, which CUDA does not permit while a stream is capturing."""
+    destroy an older CUDA graph, which CUDA does not permit while a stream is capturing.  `pool`: the
+    memory pool of graphs that run one after another and may share their buffers."""
     gc.collect()
     was_enabled = gc.isenabled()
     gc.disable()
     try:
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, pool=pool):
             yield
     finally:
         if was_enabled:

@@ -72,6 +72,8 @@ class Engine:
         self.use_graphs = all(getattr(p, "graph_safe", False) for p in model.parts())
         self._staging_free = None
         self._decode_graphs: dict = {}
+        from .prefill_graph import PrefillGraphs
+        self._prefill_graphs = PrefillGraphs(self)
 
     @classmethod
     def from_folder(cls, folder, dtype="bfloat16", max_tokens=4096, max_seqs=None, max_seq_len=None, device="cuda"):
@@ -240,6 +242,16 @@ class Engine:
             for slot, new_len in growth:
                 self.cache.set_length(slot, new_len)
             return logits
+        if self.use_graphs:
+            # short prompt steps: the same launches at a bucket's sizes, replayed as a graph from its second use
+            from .prefill_graph import bucket_of
+            bucket = bucket_of(len(tokens), len(entries), max_q, len(want_rows))
+            if bucket is not None:
+                graphs = self._prefill_graphs
+                logits = graphs.get(bucket).run(tokens, token_seq, token_pos, cu, slots, starts, want_rows, graphs.pool)
+                for slot, new_len in growth:
+                    self.cache.set_length(slot, new_len)
+                return logits
         d_tokens, d_seq, d_pos, d_cu, d_slots, d_starts, d_want = self._upload(
             [tokens, token_seq, token_pos, cu, slots, starts, want_rows])
         ctx = StepContext(

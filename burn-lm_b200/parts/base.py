@@ -65,7 +65,9 @@ class StepContext:
     max_q_len: int               # longest run of new tokens of one sequence in this step
     max_kv_len: int              # longest sequence after this step
     tokens: torch.Tensor         # int32 [N]
-    token_seq: torch.Tensor      # int32 [N] index of the token's sequence in this step
+    token_seq: torch.Tensor      # int32 [N] index of the token's sequence in this step; -1: a row of no sequence
+                                 # (padding up to a captured graph's size), computed like any row but kept out of
+                                 # the cache, and outside every sequence's cu_seqlens range
     token_pos: torch.Tensor      # int32 [N] absolute position
     cu_seqlens: torch.Tensor     # int32 [n_seqs + 1]
     slot_of_seq: torch.Tensor    # int32 [n_seqs] cache slot of every sequence

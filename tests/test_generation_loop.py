@@ -182,3 +182,26 @@ def test_norm_handoff_is_only_claimed_by_the_norm_it_was_left_for():
     h.leave(stream, a.gamma, handed)
     h.expect(b)                                   # a new expectation forgets what was left for the old one
     assert h.claim(stream, a.gamma) is None
+
+
+def test_prompt_step_buckets_hold_their_steps():
+    """A prompt step's bucket is no smaller than the step in any size, close to it in tokens, and decode
+    steps, long steps and steps with many wanted rows have none."""
+    from burn_lm_b200.engine.prefill_graph import MAX_TOKENS, MAX_WANTED, bucket_of
+    assert bucket_of(8, 8, 1, 8) is None                    # a decode step
+    assert bucket_of(MAX_TOKENS + 1, 1, MAX_TOKENS + 1, 1) is None
+    assert bucket_of(100, 1, 100, MAX_WANTED + 1) is None
+    seen = set()
+    for n_seqs in (1, 2, 3, 5, 8, 33):
+        for longest in (2, 17, 64, 129, 700, 2048):
+            for rest in (0, 1, 63, 500):
+                n_tokens = longest + rest + (n_seqs - 1)
+                if n_tokens > MAX_TOKENS:
+                    continue
+                for n_want in (0, 1, n_seqs):
+                    t, s, q, w = bucket_of(n_tokens, n_seqs, longest, n_want)
+                    assert n_tokens <= t < n_tokens * 1.25 + 64 and t % 64 == 0
+                    assert n_seqs <= s < 2 * n_seqs and longest <= q <= t and q % 64 == 0
+                    assert (w == 0) == (n_want == 0) and n_want <= w < max(2 * n_want, 1)
+                    seen.add((t, s, q, w))
+    assert len(seen) < 400

@@ -495,6 +495,66 @@ def test_gemv_rotary_epilogue(n, H, KV, hd, width, write_cache):
     k.check_status("cuda")
 
 
+@pytest.mark.parametrize("dtype,hd,table_len", [(torch.float32, 24, 0), (torch.bfloat16, 64, 0), (torch.bfloat16, 64, 256)])
+def test_rope_append_skips_rows_of_no_sequence(dtype, hd, table_len):
+    """Rows with sequence index -1 (padding up to a captured graph's size) write nothing to the cache: the
+    pool after a padded call equals the pool after the call without the padding (both rope kernels)."""
+    k = K()
+    H, KV = 3, 2
+    lens_before, lens_new = [0, 70], [9, 66]
+    n, pad = sum(lens_new), 11
+    inv_freq = torch.tensor([1e4 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64, device="cuda")
+    table = k.rope_table(inv_freq, table_len) if table_len else None
+    g = torch.Generator(device="cuda").manual_seed(hd)
+    qkv = torch.randn(n + pad, (H + 2 * KV) * hd, device="cuda", generator=g).to(dtype)
+    sa = paged_setup(lens_before, lens_new, KV, hd, dtype, seed=3)
+    sb = paged_setup(lens_before, lens_new, KV, hd, dtype, seed=3)
+    a, b = qkv[:n].clone(), qkv.clone()
+    minus = torch.full((pad,), -1, dtype=torch.int32, device="cuda")
+    zeros = torch.zeros(pad, dtype=torch.int32, device="cuda")
+    mp = max(x + y for x, y in zip(lens_before, lens_new)) - 1
+    k.rope_append(a, sa["token_seq"], sa["token_pos"], sa["slots"], sa["table"], inv_freq, hd, False, sa["pool"], H, KV, hd,
+                  table=table, max_position=mp)
+    k.rope_append(b, torch.cat([sb["token_seq"], minus]), torch.cat([sb["token_pos"], zeros]), sb["slots"], sb["table"],
+                  inv_freq, hd, False, sb["pool"], H, KV, hd, table=table, max_position=mp)
+    assert torch.equal(a, b[:n])
+    pa, pb = sa["pool"].float(), sb["pool"].float()
+    assert torch.equal(torch.isnan(pa), torch.isnan(pb))
+    assert torch.equal(torch.nan_to_num(pa), torch.nan_to_num(pb))
+
+
+def test_gemv_rotary_epilogue_skips_rows_of_no_sequence():
+    k = K()
+    n, H, KV, hd, width = 6, 4, 2, 64, 256
+    g = torch.Generator(device="cuda").manual_seed(77)
+    w = (torch.randn((H + 2 * KV) * hd, width, device="cuda", generator=g) * 0.08).to(torch.bfloat16)
+    x = torch.randn(n, width, device="cuda", generator=g).to(torch.bfloat16)
+    lens_before = [5 + 37 * i for i in range(n)]
+    inv_freq = torch.tensor([5e5 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64, device="cuda")
+    table = k.rope_table(inv_freq, max(lens_before) + 2)
+    pools = []
+    for skipped in ((), (1, 4)):
+        st = paged_setup(lens_before, [1] * n, KV, hd, torch.bfloat16, seed=5)
+        seq = st["token_seq"].clone()
+        for i in skipped:
+            seq[i] = -1
+        q = torch.empty((n, H * hd), device="cuda", dtype=torch.bfloat16)
+        rope = dict(token_pos=st["token_pos"], token_seq=seq, slot_of_seq=st["slots"], block_table=st["table"], table=table,
+                    pool=st["pool"], n_heads=H, n_kv=KV, head_dim=hd, write_cache=True, max_position=max(lens_before))
+        k.gemv(w, n, x=x, out=q, rope=rope)
+        pools.append((st, st["pool"].float()))
+    (st, full), (_, part) = pools
+    for s in range(n):          # sequence s holds one new token at position lens_before[s]
+        page = int(st["host_table"][st["host_slots"][s], lens_before[s] // k.PAGE])
+        entry_full, entry_part = full[page, :, :, lens_before[s] % k.PAGE], part[page, :, :, lens_before[s] % k.PAGE]
+        assert not torch.isnan(entry_full).any()
+        if s in (1, 4):
+            assert torch.isnan(entry_part).all()
+        else:
+            assert torch.equal(entry_full, entry_part)
+    k.check_status("cuda")
+
+
 def test_gemv_refuses_what_it_cannot_do():
     k = K()
     assert not k.gemv_supported(17, 10, 64) and not k.gemv_supported(4, 10, 96)

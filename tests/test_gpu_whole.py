@@ -36,3 +36,45 @@ def test_whole_prompts(tmp_path, name, dtype, stored, tolerance):
         want = P.forward(cfg, tensors, toks)
         err = row_error(got, want)
         assert err.max() < tolerance, (name, dtype, length, err.max(), int(err.argmax()))
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("dtype,tolerance", [("float32", FP32_TOL), ("bfloat16", BF16_TOL)])
+def test_prompt_steps_of_one_bucket_plain_captured_and_replayed(tmp_path, name, dtype, tolerance):
+    """Prompt steps are fitted into buckets of sizes and replayed as CUDA graphs from a bucket's second use.
+    Batches of different prompts that fall into one bucket: the first runs plainly, the second is captured,
+    the third replayed; each against the plain implementation, then the same batch again (replayed) to the
+    same bits; and the cache they leave gives the right next token's logits."""
+    from burn_lm_b200 import StepEntry
+    from burn_lm_b200.engine.prefill_graph import bucket_of
+    folder = make_folder(tmp_path, name, seed=5, dtype="bfloat16")
+    cfg, tensors = P.read_model_folder(folder)
+    eng = engine_for(folder, dtype)
+    assert eng.use_graphs
+    limit = cfg["max_position_embeddings"]
+    batches = [[33, 7, 20], [5, 40, 9], [17, 3, 38], [6, 36, 2, 11]]
+    batches = [[min(n, limit - 2) for n in b] for b in batches]
+    assert len({bucket_of(sum(b), len(b), max(b), len(b)) for b in batches}) == 1
+    first = None
+    for rep, lens in enumerate(batches + [batches[0]]):
+        prompts = [random_tokens(100 * (rep % len(batches)) + i, n, cfg["vocab_size"]) for i, n in enumerate(lens)]
+        slots = [eng.acquire() for _ in prompts]
+        got = eng.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)]).cpu().numpy()
+        for i, p in enumerate(prompts):
+            want = P.forward(cfg, tensors, p)[-1:]
+            assert row_error(got[i:i + 1], want).max() < tolerance, (rep, i)
+        if rep == 0:
+            first = got
+        if rep == len(batches):
+            assert np.array_equal(got, first)       # plain launches and the replayed graph: the same bits
+        # one more token each: the cache the step left is the right one
+        nxt = [int(np.argmax(got[i])) for i in range(len(prompts))]
+        dec = eng.step([StepEntry(s, [t], [0]) for s, t in zip(slots, nxt)]).cpu().numpy()
+        for i, p in enumerate(prompts):
+            want = P.forward(cfg, tensors, p + [nxt[i]])[-1:]
+            assert row_error(dec[i:i + 1], want).max() < tolerance, (rep, i, "decode")
+        for s in slots:
+            eng.release(s)
+    g = eng._prefill_graphs.get(bucket_of(sum(batches[0]), 3, max(batches[0]), 3))
+    assert g.steps == len(batches) + 1 and g._graph is not None
+    eng.verify()
