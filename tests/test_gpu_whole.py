@@ -78,3 +78,24 @@ def test_prompt_steps_of_one_bucket_plain_captured_and_replayed(tmp_path, name, 
     g = eng._prefill_graphs.get(bucket_of(sum(batches[0]), 3, max(batches[0]), 3))
     assert g.steps == len(batches) + 1 and g._graph is not None
     eng.verify()
+
+
+def test_prompt_step_buckets_are_dropped_and_come_back(tmp_path, monkeypatch):
+    """Only the most recently used buckets keep their graph; a bucket that was dropped starts over
+    (plain, then captured) and still gives the right logits."""
+    from burn_lm_b200 import StepEntry
+    from burn_lm_b200.engine import prefill_graph
+    monkeypatch.setattr(prefill_graph, "MAX_GRAPHS", 2)
+    folder = make_folder(tmp_path, "tiny_d", seed=6, dtype="bfloat16")
+    cfg, tensors = P.read_model_folder(folder)
+    eng = engine_for(folder, "bfloat16", max_tokens=4096)
+    lengths = [40, 100, 150, 300, 40, 100, 40, 40, 300, 300, 300]
+    for n, length in enumerate(lengths):
+        toks = random_tokens(50 + n, length, cfg["vocab_size"])
+        slot = eng.acquire()
+        got = eng.step([StepEntry(slot, toks, [length - 1])]).cpu().numpy()
+        eng.release(slot)
+        want = P.forward(cfg, tensors, toks)[-1:]
+        assert row_error(got, want).max() < BF16_TOL, (n, length)
+        assert len(eng._prefill_graphs) <= 2
+    eng.verify()
