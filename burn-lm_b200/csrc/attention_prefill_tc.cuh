@@ -37,7 +37,7 @@ struct AttnPrefillTcArgs {
     __nv_bfloat16* out;          // [N, n_heads * HD]
     int n_heads, n_kv, window;
     float scale_log2e;
-    int* status;                 // 0, or 31..35 when a bounded wait ran out
+    int* status;                 // 0, or 31..37 when a bounded wait ran out
 };
 
 namespace attn_tc {
