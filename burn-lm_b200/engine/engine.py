@@ -71,7 +71,8 @@ class Engine:
         # decode steps (one token each, its logits wanted) replay a CUDA graph when every part allows it
         self.use_graphs = all(getattr(p, "graph_safe", False) for p in model.parts())
         self._staging_free = None
-        self._decode_graphs: dict = {}
+        self._decode_graphs: dict = {}      # (batch, length bucket) -> DecodeGraph, least recently used first
+        self.max_decode_graphs = 48
         from .prefill_graph import PrefillGraphs
         self._prefill_graphs = PrefillGraphs(self)
 
@@ -103,9 +104,13 @@ class Engine:
         while pages * 64 < max_kv_len:
             pages *= 2
         bucket = min(pages * 64, -(-self.cache.max_seq_len // 64) * 64)
-        g = self._decode_graphs.get((batch, bucket))
+        graphs = self._decode_graphs
+        g = graphs.pop((batch, bucket), None)
         if g is None:
-            g = self._decode_graphs[(batch, bucket)] = DecodeGraph(self, batch, bucket)
+            g = DecodeGraph(self, batch, bucket)
+            while len(graphs) >= self.max_decode_graphs:      # the least recently used goes, with its buffers
+                del graphs[next(iter(graphs))]
+        graphs[(batch, bucket)] = g                             # most recently used last
         return g
 
     def decode_run(self, slots, tokens, n_steps: int) -> torch.Tensor:

@@ -226,3 +226,29 @@ def test_repeated_runs_and_captured_steps_give_the_same_tokens(tmp_path):
     sampled = [lm.generate(prompts, sample_len=40, ignore_stop=True, temperature=0.9, seed=8).tokens for _ in range(2)]
     assert sampled[0] == sampled[1]
     lm.engine.verify()
+
+
+def test_decode_graphs_are_dropped_and_made_again(tmp_path):
+    """The engine keeps a bounded number of captured decode steps; with room for two only, a batch whose
+    sequences leave one by one (a new batch size each time) generates the same tokens."""
+    import burn_lm_b200 as blm
+    folder = make_folder(tmp_path, "tiny_d", seed=23, dtype="bfloat16")
+    cfg = CONFIGS["tiny_d"]
+    prompts = [random_tokens(40 + n, length, cfg["vocab_size"]) for n, length in enumerate([5, 60, 31, 90, 12])]
+    lens = [10, 50, 20, 40, 30]
+
+    def run(limit):
+        lm = blm.load(folder, dtype="bfloat16", max_seq_len=256, max_batch=8)
+        if limit:
+            lm.engine.max_decode_graphs = limit
+        out = []
+        for _ in range(2):
+            # every request has its own length limit: requests leave at different steps
+            res = [lm.generate([p], sample_len=n, ignore_stop=True).tokens[0] for p, n in zip(prompts, lens)]
+            together = lm.generate(prompts, sample_len=max(lens), ignore_stop=True).tokens
+            out.append((res, together))
+        assert len(lm.engine._decode_graphs) <= (limit or lm.engine.max_decode_graphs)
+        lm.engine.verify()
+        return out
+
+    assert run(2) == run(None)
