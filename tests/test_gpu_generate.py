@@ -229,8 +229,8 @@ def test_repeated_runs_and_captured_steps_give_the_same_tokens(tmp_path):
 
 
 def test_decode_graphs_are_dropped_and_made_again(tmp_path):
-    """The engine keeps a bounded number of captured decode steps; with room for two only, a batch whose
-    sequences leave one by one (a new batch size each time) generates the same tokens."""
+    """The engine keeps a bounded number of captured decode steps; with room for two only, requests that
+    alternate between batch sizes and grow through several length buckets generate the same tokens."""
     import burn_lm_b200 as blm
     folder = make_folder(tmp_path, "tiny_d", seed=23, dtype="bfloat16")
     cfg = CONFIGS["tiny_d"]
@@ -243,7 +243,6 @@ def test_decode_graphs_are_dropped_and_made_again(tmp_path):
             lm.engine.max_decode_graphs = limit
         out = []
         for _ in range(2):
-            # every request has its own length limit: requests leave at different steps
             res = [lm.generate([p], sample_len=n, ignore_stop=True).tokens[0] for p, n in zip(prompts, lens)]
             together = lm.generate(prompts, sample_len=max(lens), ignore_stop=True).tokens
             out.append((res, together))
