@@ -2,7 +2,8 @@
 from the interpreter takes longer than the device needs to run them.
 
 A captured graph has fixed sizes, so a step is fitted into a bucket: its token count, its number of
-sequences, its longest run of new tokens and its number of wanted rows are rounded up (`bucket_of`),
+sequences, its longest run of new tokens and its number of wanted rows are rounded up (`bucket_of`: tokens
+to 16, then by 64, 128 or 256; sequences and wanted rows to a power of two),
 and what the rounding adds changes no result:
 
   * rows after the last token carry token 0 at position 0 and the sequence index -1.  They belong to no
@@ -28,6 +29,7 @@ from typing import Optional
 import torch
 
 from ..parts.base import StepContext
+from ..parts.linear import SKINNY_TOKENS
 from .decode_graph import _capturing
 from .engine import Workspace
 
@@ -52,7 +54,10 @@ def bucket_of(n_tokens: int, n_seqs: int, max_q_len: int, n_want: int) -> Option
     that runs plainly: a decode step (the decode graphs' business), a long one, one with many wanted rows."""
     if n_tokens == n_seqs or n_tokens > MAX_TOKENS or n_want > MAX_WANTED:
         return None
-    tokens = _round_up(n_tokens, 64 if n_tokens <= 512 else 128 if n_tokens <= 1024 else 256)
+    if n_tokens <= SKINNY_TOKENS:
+        tokens = SKINNY_TOKENS          # a few tokens keep the kernels made for a few tokens
+    else:
+        tokens = _round_up(n_tokens, 64 if n_tokens <= 512 else 128 if n_tokens <= 1024 else 256)
     longest = min(_round_up(max_q_len, 128), tokens)
     return tokens, _pow2(n_seqs), longest, _pow2(n_want) if n_want else 0
 

@@ -200,8 +200,8 @@ def test_prompt_step_buckets_hold_their_steps():
                     continue
                 for n_want in (0, 1, n_seqs):
                     t, s, q, w = bucket_of(n_tokens, n_seqs, longest, n_want)
-                    assert n_tokens <= t < n_tokens * 1.25 + 64 and t % 64 == 0
-                    assert n_seqs <= s < 2 * n_seqs and longest <= q <= t and q % 64 == 0
+                    assert n_tokens <= t < n_tokens * 1.25 + 64 and t % 16 == 0
+                    assert n_seqs <= s < 2 * n_seqs and longest <= q <= t and q % 16 == 0
                     assert (w == 0) == (n_want == 0) and n_want <= w < max(2 * n_want, 1)
                     seen.add((t, s, q, w))
     assert len(seen) < 400

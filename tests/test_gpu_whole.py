@@ -39,11 +39,13 @@ def test_whole_prompts(tmp_path, name, dtype, stored, tolerance):
 
 
 @pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("few", [None, [[5, 2, 7], [1, 9, 4], [6, 6, 3], [2, 1, 3, 8]]], ids=["dozens", "few"])
 @pytest.mark.parametrize("dtype,tolerance", [("float32", FP32_TOL), ("bfloat16", BF16_TOL)])
-def test_prompt_steps_of_one_bucket_plain_captured_and_replayed(tmp_path, name, dtype, tolerance):
+def test_prompt_steps_of_one_bucket_plain_captured_and_replayed(tmp_path, name, dtype, tolerance, few):
     """Prompt steps are fitted into buckets of sizes and replayed as CUDA graphs from a bucket's second use.
     Batches of different prompts that fall into one bucket: the first runs plainly, the second is captured,
-    the third replayed; each against the plain implementation, then the same batch again (replayed) to the
+    the third replayed (`few`: steps of at most 16 tokens, which keep the kernels made for a few tokens);
+    each against the plain implementation, then the same batch again (replayed) to the
     same bits; and the cache they leave gives the right next token's logits."""
     from burn_lm_b200 import StepEntry
     from burn_lm_b200.engine.prefill_graph import bucket_of
@@ -52,7 +54,7 @@ def test_prompt_steps_of_one_bucket_plain_captured_and_replayed(tmp_path, name, 
     eng = engine_for(folder, dtype)
     assert eng.use_graphs
     limit = cfg["max_position_embeddings"]
-    batches = [[33, 7, 20], [5, 40, 9], [17, 3, 38], [6, 36, 2, 11]]
+    batches = few or [[33, 7, 20], [5, 40, 9], [17, 3, 38], [6, 36, 2, 11]]
     batches = [[min(n, limit - 2) for n in b] for b in batches]
     assert len({bucket_of(sum(b), len(b), max(b), len(b)) for b in batches}) == 1
     first = None
