@@ -21,7 +21,11 @@ from .. import kernels as K
 
 SKINNY_TOKENS = 16        # the skinny kernel takes up to this many tokens
 FUSED_NORM_TOKENS = 16    # ... and normalises them in its prologue (every block redoes it)
-TENSOR_CORE_TOKENS = 128  # from this many tokens the gated product runs this package's tcgen05 kernel
+# From this many tokens the gated product runs this package's tcgen05 kernel.  Measured inside CUDA graphs on
+# the 1B shape (16,384 x 2,048 weight): with fewer tokens its 128 x 256 tiles fill the SMs unevenly and the
+# library's product followed by the activation kernel is faster (384 tokens: 28 against 36 us; 1,024: 61
+# against 60; 2,048: 119 against 103).
+TENSOR_CORE_TOKENS = 1024
 
 
 @dataclass

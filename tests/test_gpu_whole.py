@@ -101,3 +101,26 @@ def test_prompt_step_buckets_are_dropped_and_come_back(tmp_path, monkeypatch):
         assert row_error(got, want).max() < BF16_TOL, (n, length)
         assert len(eng._prefill_graphs) <= 2
     eng.verify()
+
+
+def test_a_step_of_more_than_a_thousand_tokens(tmp_path):
+    """From 1,024 tokens in a step the gated product runs the tcgen05 kernel with the activation in its
+    epilogue, and the prompts' attention the tcgen05 kernel: two prompts of 600 tokens in one step."""
+    from burn_lm_b200 import StepEntry
+    from burn_lm_b200.parts.linear import TENSOR_CORE_TOKENS
+    folder = make_folder(tmp_path, "tiny_d", seed=8, dtype="bfloat16")
+    cfg, tensors = P.read_model_folder(folder)
+    eng = engine_for(folder, "bfloat16", max_tokens=4096)
+    prompts = [random_tokens(70 + n, 600, cfg["vocab_size"]) for n in range(2)]
+    assert sum(len(p) for p in prompts) >= TENSOR_CORE_TOKENS
+    want_at = [0, 63, 64, 300, 599]
+    for rep in range(3):        # plain, captured, replayed
+        slots = [eng.acquire() for _ in prompts]
+        got = eng.step([StepEntry(s, p, want_at) for s, p in zip(slots, prompts)]).cpu().numpy()
+        for s in slots:
+            eng.release(s)
+        for i, p in enumerate(prompts):
+            want = P.forward(cfg, tensors, p)[want_at]
+            err = row_error(got[i * len(want_at):(i + 1) * len(want_at)], want)
+            assert err.max() < BF16_TOL, (rep, i, err)
+    eng.verify()
