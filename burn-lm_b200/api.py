@@ -21,8 +21,12 @@ class LanguageModel:
     """A loaded model with its cache, generation loop and sampler."""
 
     def __init__(self, folder: str, dtype: str = "bfloat16", max_seq_len: int = 8192, max_batch: int = 8,
-                 max_tokens: Optional[int] = None, device: str = "cuda:0"):
+                 max_tokens: Optional[int] = None, device: str = "cuda:0", decode_ahead: bool = False):
+        """`decode_ahead`: greedy generation enqueues the step after the one it waits for (fed on the device), so
+        the GPU does not idle while the host looks at a step's tokens; off, every step brings its tokens from
+        the host.  The tokens are the same either way."""
         self.folder, self.dtype, self.device = folder, dtype, device
+        self.decode_ahead = decode_ahead
         self.max_seq_len, self.max_batch, self.max_tokens = max_seq_len, max_batch, max_tokens
         self.engine: Optional[Engine] = None
         self.loop: Optional[GenerationLoop] = None
@@ -36,6 +40,7 @@ class LanguageModel:
             seq = min(self.max_seq_len, model.plan.max_positions)
             tokens = self.max_tokens or -(-seq // 64) * 64 * self.max_batch
             self.engine = Engine(model, max_tokens=tokens, max_seqs=max(self.max_batch, 1), max_seq_len=seq)
+            self.engine.decode_ahead = self.decode_ahead
             self.loop = GenerationLoop(self.engine, Sampler(model.runtime.device), model.plan.stop_ids)
             self.load_seconds = time.perf_counter() - t0
         return self
@@ -77,6 +82,6 @@ class LanguageModel:
 
 
 def load(folder: str, dtype: str = "bfloat16", max_seq_len: int = 8192, max_batch: int = 8,
-         max_tokens: Optional[int] = None, device: str = "cuda:0") -> LanguageModel:
+         max_tokens: Optional[int] = None, device: str = "cuda:0", decode_ahead: bool = False) -> LanguageModel:
     """Load the model a folder's config.json names; see LanguageModel."""
-    return LanguageModel(folder, dtype, max_seq_len, max_batch, max_tokens, device).load()
+    return LanguageModel(folder, dtype, max_seq_len, max_batch, max_tokens, device, decode_ahead).load()

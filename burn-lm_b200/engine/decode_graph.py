@@ -36,6 +36,20 @@ def _capturing(graph, pool=None):
             gc.enable()
 
 
+class StepInFlight:
+    """A greedy decode step that has been enqueued: the sequences' slots, their lengths before it, the tokens
+    it was fed (None until known: a chained step is fed on the device) and where its result will be."""
+
+    def __init__(self, graph, slots, starts, tokens_in, done, host):
+        self.graph, self.slots, self.starts, self.tokens_in = graph, slots, starts, tokens_in
+        self._done, self._host = done, host
+
+    def tokens(self) -> list:
+        """The sampled tokens, in the order of `slots` (waits for the step)."""
+        self._done.synchronize()
+        return self._host.numpy().tolist()
+
+
 class DecodeGraph:
     def __init__(self, engine, batch: int, max_kv_len: int):
         self._engine = weakref.ref(engine)      # the engine owns its graphs, not the other way round
@@ -65,6 +79,9 @@ class DecodeGraph:
         self._loop_graph = None     # forward + argmax + advance
         self._greedy_graph = None   # forward + argmax
         self._greedy_exec = None    # its cudaGraphExec_t (an integer) once known; False when torch does not give it out
+        self._chain_graph = None    # forward + argmax + advance: a step whose successor needs nothing from the host
+        self._chain_out = None      # two pinned buffers for its results, used in turn
+        self._chain_launches = 0
         self._sample_graph = None   # forward + temperature / nucleus draw
         self._sample_exec = None
         self._sample_key = None     # (sampling parameters, stream ids) now in the graph's buffers
@@ -142,6 +159,37 @@ class DecodeGraph:
             if self._greedy_exec is None:
                 self._greedy_exec = False      # asked once; stay on the interpreter's path
         return self._host_sampled_np.tolist()
+
+    def launch_greedy_chained(self, tokens, positions, slots) -> "StepInFlight":
+        """Enqueue one greedy step and the copy of its sampled tokens to pinned memory, and come back without
+        waiting.  The captured step ends by feeding itself: tokens = sampled, positions += 1 on the device, so
+        the step after it can be enqueued with `tokens=None` before this one's result has reached the host.
+        The result is in `StepInFlight.tokens()` once its event has passed."""
+        if tokens is not None:
+            self.load(tokens, positions, slots)
+        else:
+            self.ctx.host["slots"], self.ctx.host["start_pos"] = list(slots), list(positions)
+        if self._chain_out is None:
+            self._chain_out = [torch.zeros(self.batch, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        if self._chain_graph is None:
+            self._one_chained_step()                 # the first step runs plainly and warms everything up
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with _capturing(g):
+                self._one_chained_step()
+            self._chain_graph = g
+        else:
+            self._chain_graph.replay()
+        host = self._chain_out[self._chain_launches % 2]
+        self._chain_launches += 1
+        host.copy_(self.sampled, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return StepInFlight(self, list(slots), list(positions), None if tokens is None else list(tokens), done, host)
+
+    def _one_chained_step(self):
+        K.argmax(self._forward(), self.sampled)
+        K.decode_advance(self.tokens, self.pos, self.sampled, None, self.step_no)
 
     def step_sampled_host(self, tokens, positions, slots, params, stream_ids, counters) -> list:
         """A step that draws its tokens by temperature and nucleus inside the captured graph, from host

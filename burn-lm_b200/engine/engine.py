@@ -71,6 +71,8 @@ class Engine:
         # decode steps (one token each, its logits wanted) replay a CUDA graph when every part allows it
         self.use_graphs = all(getattr(p, "graph_safe", False) for p in model.parts())
         self._staging_free = None
+        self.decode_ahead = False           # decode_greedy(more=True) may enqueue the following step at once
+        self._ahead = None                  # decode_graph.StepInFlight: a greedy step enqueued before it was asked for
         self._decode_graphs: dict = {}      # (batch, length bucket) -> DecodeGraph, least recently used first
         self.max_decode_graphs = 48
         from .prefill_graph import PrefillGraphs
@@ -116,6 +118,7 @@ class Engine:
     def decode_run(self, slots, tokens, n_steps: int) -> torch.Tensor:
         """n_steps greedy decode steps for the sequences in `slots`, fed `tokens` first, without the
         host in between.  Returns the sampled tokens, int32 [n_steps, len(slots)], on the device."""
+        self._ahead = None
         starts = [self.cache.seq_len[s] for s in slots]
         self.cache.reserve([(s, st + n_steps) for s, st in zip(slots, starts)])
         g = self.decode_graph(len(slots), max(starts) + n_steps)
@@ -125,35 +128,85 @@ class Engine:
             self.cache.set_length(s, st + n_steps)
         return history
 
-    def decode_greedy(self, slots, tokens) -> Optional[list]:
+    def decode_greedy(self, slots, tokens, more: bool = False) -> Optional[list]:
         """One greedy decode step for the sequences in `slots`, each fed its token: the argmax runs in
         the captured graph and the sampled ids come back as a list.  The short way through a step for
-        the generation loop; None when this engine does not capture its decode steps."""
+        the generation loop; None when this engine does not capture its decode steps.
+
+        `more`: the caller expects to come back with the same sequences and these results as their next
+        tokens.  Then (with `decode_ahead` set) the step after this one is enqueued before this one's result is awaited (it is fed on
+        the device), so the GPU does not idle while the host looks at the tokens; the next call finds its
+        step in flight.  A call that asks for something else (other tokens, fewer sequences) is still served
+        from the step in flight where that computed it, and otherwise the step in flight is forgotten: what
+        it appended lies beyond its sequences' lengths."""
         if not self.use_graphs:
             return None
         cache = self.cache
-        starts = []
-        grow = None
-        for s, t in zip(slots, tokens):
-            if not 0 <= t < self.vocab_size:
-                raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
-            n = cache.seq_len[s]
-            starts.append(n)
-            if n % 64 == 0 or n >= cache.max_seq_len:       # a new page, or the limit: the careful path decides
-                grow = True
-        if grow or len(set(slots)) != len(slots):
-            cache.reserve([(s, n + 1) for s, n in zip(slots, starts)])
-        g = self.decode_graph(len(slots), max(starts) + 1)
-        out = g.step_greedy_host(tokens, starts, slots)
-        for s, n in zip(slots, starts):
+        slots, tokens = list(slots), list(tokens)
+        more = more and self.decode_ahead
+        ahead, self._ahead = self._ahead, None
+        cur = None
+        if ahead is not None and ahead.tokens_in is not None and len(set(slots)) == len(slots):
+            place = {s: i for i, s in enumerate(ahead.slots)}
+            if all(s in place and ahead.tokens_in[place[s]] == t and cache.seq_len[s] == ahead.starts[place[s]]
+                   for s, t in zip(slots, tokens)):
+                if slots == ahead.slots:
+                    cur = ahead
+                else:
+                    # some sequences have left: the others' results are what a step without them gives
+                    out = ahead.tokens()
+                    for s in slots:
+                        cache.seq_len[s] = ahead.starts[place[s]] + 1
+                    return [out[place[s]] for s in slots]
+        if cur is None:
+            starts = []
+            grow = None
+            for s, t in zip(slots, tokens):
+                if not 0 <= t < self.vocab_size:
+                    raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
+                n = cache.seq_len[s]
+                starts.append(n)
+                if n % 64 == 0 or n >= cache.max_seq_len:       # a new page, or the limit: the careful path decides
+                    grow = True
+            if grow or len(set(slots)) != len(slots):
+                cache.reserve([(s, n + 1) for s, n in zip(slots, starts)])
+            g = self.decode_graph(len(slots), max(starts) + 1)
+            if not more:
+                out = g.step_greedy_host(tokens, starts, slots)
+                for s, n in zip(slots, starts):
+                    cache.seq_len[s] = n + 1
+                return out
+            cur = g.launch_greedy_chained(tokens, starts, slots)
+        nxt = self._launch_ahead(cur) if more else None
+        out = cur.tokens()
+        for s, n in zip(cur.slots, cur.starts):
             cache.seq_len[s] = n + 1
+        if nxt is not None:
+            nxt.tokens_in = out
+            self._ahead = nxt
         return out
+
+    def _launch_ahead(self, cur):
+        """The step after `cur` for the same sequences, enqueued behind it; None where that step needs a
+        decision of the careful path (the context limit, no free page) or another graph (a longer bucket)."""
+        cache = self.cache
+        starts = [n + 1 for n in cur.starts]
+        if any(n + 1 > cache.max_seq_len for n in starts):
+            return None
+        if self.decode_graph(len(cur.slots), max(starts) + 1) is not cur.graph:
+            return None
+        try:
+            cache.reserve([(s, n + 1) for s, n in zip(cur.slots, starts)])
+        except CacheError:
+            return None
+        return cur.graph.launch_greedy_chained(None, starts, cur.slots)
 
     def decode_sampled(self, slots, tokens, params, stream_ids, counters) -> Optional[list]:
         """One decode step that draws every sequence's next token (temperature, nucleus) inside the captured
         graph; `stream_ids` and `counters` name the draws.  None when this engine does not capture its steps."""
         if not self.use_graphs:
             return None
+        self._ahead = None
         cache = self.cache
         starts = []
         grow = None
@@ -238,6 +291,7 @@ class Engine:
         when nothing is wanted.  Every sequence's cached length grows by its tokens.  The logits of a
         decode step (one token each) live in a buffer that the next such step overwrites: use or
         copy them before stepping again."""
+        self._ahead = None                  # a step enqueued ahead is forgotten: it wrote beyond its sequences' lengths
         (tokens, token_seq, token_pos, cu, slots, starts, want_rows, growth, max_q, max_kv) = self._pack(entries)
         self.cache.reserve(growth)          # raises before anything is launched, changing nothing
         if self.use_graphs and max_q == 1 and want_rows == list(range(len(entries))):

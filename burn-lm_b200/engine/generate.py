@@ -174,7 +174,10 @@ class GenerationLoop:
                     break
                 tokens = None
                 if params.greedy and fused is not None:      # the engine samples inside its captured step
-                    tokens = fused([slots[i] for i in live], [results[i].tokens[-1] for i in live])
+                    # will anyone need a step after this one (if no stop id turns up)?  Then the engine may enqueue it now.
+                    more = any(len(results[i].tokens) + 1 < sample_len and len(prompts[i]) + len(results[i].tokens) + 1 <= max_len
+                               for i in live)
+                    tokens = fused([slots[i] for i in live], [results[i].tokens[-1] for i in live], more=more)
                 elif not params.greedy and fused_draw is not None:
                     tokens = fused_draw([slots[i] for i in live], [results[i].tokens[-1] for i in live], params, live,
                                         [len(results[i].tokens) for i in live])

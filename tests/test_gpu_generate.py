@@ -251,3 +251,34 @@ def test_decode_graphs_are_dropped_and_made_again(tmp_path):
         return out
 
     assert run(2) == run(None)
+
+
+def test_decode_ahead_gives_the_same_tokens(tmp_path):
+    """With `decode_ahead` greedy generation enqueues a step before the one before it has been looked at.
+    Requests that end at different steps (length limits, stop ids that do turn up) leave a step in flight
+    that still holds the others' next tokens; batches follow one another on reused slots; a context limit
+    and page boundaries are crossed.  All of it must give the tokens of the plain loop."""
+    import burn_lm_b200 as blm
+    folder = make_folder(tmp_path, "tiny_d", seed=29, dtype="bfloat16")
+    cfg = CONFIGS["tiny_d"]
+    prompts = [random_tokens(300 + n, length, cfg["vocab_size"]) for n, length in enumerate([5, 60, 31, 90, 12, 64, 63, 1, 200, 17])]
+
+    def run(ahead):
+        lm = blm.load(folder, dtype="bfloat16", max_seq_len=256, max_batch=4, decode_ahead=ahead)
+        out = []
+        out.append(lm.generate(prompts, sample_len=70, ignore_stop=True).tokens)
+        # stop ids that occur in what the model says: requests end where nobody could foresee it
+        said = [t for seq in out[0] for t in seq]
+        stops = sorted(set(said[5::7]))[:12]
+        res = lm.generate(prompts, sample_len=70, stop_ids=stops)
+        out.append((res.tokens, [r.finish_reason for r in res.results]))
+        out.append(lm.generate(prompts[:3], sample_len=300, ignore_stop=True).tokens)     # runs into the context limit
+        one = [lm.generate([p], sample_len=n, ignore_stop=True).tokens[0] for p, n in zip(prompts[:4], [1, 2, 3, 40])]
+        out.append(one)
+        lm.engine.verify()
+        assert lm.engine.cache.slots.free_count == 4
+        return out
+
+    plain, ahead = run(False), run(True)
+    assert plain == ahead
+    assert any(reason == "stop" for reason in plain[1][1])
