@@ -83,7 +83,9 @@ class Part:
     family = ""
     # True when forward() only launches work on the current stream that depends on the step through
     # the device buffers of the StepContext (never through step.host or Python branches on its
-    # values): such a part can be captured in a CUDA graph and replayed for other sequences.
+    # values): such a part can be captured in a CUDA graph and replayed for other sequences.  It must also
+    # cope with the padding of captured prompt steps: rows whose token_seq is -1 belong to no sequence and
+    # must not reach a cache or a state; sequences of no tokens may follow the real ones.
     graph_safe = False
 
     def __init__(self, spec, tensors: dict, runtime: Runtime):
