@@ -314,8 +314,9 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     const float* __restrict__ logits, long long row_stride, int vocab, const float* __restrict__ temperature,
     const float* __restrict__ top_p, const unsigned long long* __restrict__ seeds,
     const unsigned long long* __restrict__ stream_ids, const unsigned long long* __restrict__ counters,
-    int* __restrict__ out, float* __restrict__ work) {
+    int* __restrict__ out, float* __restrict__ work, int n_pieces) {
     __shared__ float redf[33];
+    __shared__ float piece_z[8];                              // the normaliser's sums over this block's pieces
     __shared__ unsigned long long red[33];
     __shared__ unsigned int hist_lo[256], hist_hi[256];      // a bin's 64-bit sum in two words (see hist_add)
     __shared__ unsigned int s_prefix;
@@ -330,9 +331,13 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     const float inv_t = 1.0f / temperature[b];
     const int tid = threadIdx.x;
     if (tid == 0) words.turn = 0;
-    // this block's piece of the vocabulary (a multiple of 4 tokens, so that 16-byte loads stay aligned)
-    const int piece = ((vocab + (int)n_blocks - 1) / (int)n_blocks + 3) & ~3;
-    const int p_lo = min(vocab, (int)rank * piece), p_hi = min(vocab, p_lo + piece), p_len = p_hi - p_lo;
+    // The vocabulary is cut into n_pieces pieces (a multiple of 4 tokens each, so that 16-byte loads stay
+    // aligned) whatever the number of blocks: a block takes n_pieces / n_blocks of them, one after another.
+    // The only sum here that depends on its order, the normaliser, is taken piece by piece, so that a row's
+    // draw does not depend on how many blocks shared it (fewer when there are many rows).
+    const int piece = ((vocab + n_pieces - 1) / n_pieces + 3) & ~3;
+    const int per_block = n_pieces / (int)n_blocks;
+    const int p_lo = min(vocab, (int)rank * per_block * piece), p_hi = min(vocab, p_lo + per_block * piece), p_len = p_hi - p_lo;
     const float* ep = e + p_lo;
 
     // max and normaliser of softmax(logits / temperature)
@@ -348,14 +353,22 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     }
     __syncthreads();
     mx = cl_max_f32(redf[32], &words);
-    float z = 0.f;
-    for (int i = p_lo + tid; i < p_hi; i += blockDim.x) {
-        const float ei = expf(__fsub_rn(__fmul_rn(row[i], inv_t), mx));
-        e[i] = ei;
-        z += ei;
+    for (int k = 0; k < per_block; ++k) {
+        const int k_lo = min(p_hi, p_lo + k * piece), k_hi = min(p_hi, k_lo + piece);
+        float zk = 0.f;
+        for (int i = k_lo + tid; i < k_hi; i += blockDim.x) {
+            const float ei = expf(__fsub_rn(__fmul_rn(row[i], inv_t), mx));
+            e[i] = ei;
+            zk += ei;
+        }
+        zk = block_sum(zk, redf);    // (its barriers also make every thread's e visible to the others of the block)
+        if (tid == 0) piece_z[k] = zk;
     }
-    z = block_sum(z, redf);          // (its barriers also make every thread's e visible to the others of the block)
-    z = cl_sum_f32(z, &words);
+    // the pieces' sums in the order of the pieces: the blocks in the order of their ranks, each one's in turn
+    cl_sync();
+    float z = 0.f;
+    for (unsigned r = 0; r < n_blocks; ++r)
+        for (int k = 0; k < per_block; ++k) z += __uint_as_float(cl_ld_u32(reinterpret_cast<const unsigned*>(piece_z + k), r));
     const float inv_z = 1.0f / z;
 
     // contiguous chunk of the block's piece per thread (index order matters below)
@@ -555,8 +568,11 @@ BLM_API int blm_sample(const float* logits, long long row_stride, int n_rows, in
     if (n_rows == 0) return BLM_OK;
     BLM_REQUIRE(vocab > 0, "sample: empty vocabulary");
     BLM_REQUIRE(work != nullptr, "sample: no room for the rows' exponentials (n_rows x vocab floats)");
-    // a row is shared by the blocks of a cluster: eight for a large vocabulary, fewer for a small one
-    unsigned blocks = vocab >= 65536 ? 8u : (vocab >= 16384 ? 4u : (vocab >= 4096 ? 2u : 1u));
+    // a row is cut into pieces by the size of the vocabulary (eight for a large one) and shared by the blocks
+    // of a cluster: one per piece while all the rows' blocks fit the SMs at once, fewer when there are many rows
+    const unsigned pieces = vocab >= 65536 ? 8u : (vocab >= 16384 ? 4u : (vocab >= 4096 ? 2u : 1u));
+    unsigned blocks = pieces;
+    while (blocks > 1 && blocks * (unsigned)n_rows > 148u) blocks >>= 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(blocks * (unsigned)n_rows);
     cfg.blockDim = dim3(kSampleThreads);
@@ -568,7 +584,7 @@ BLM_API int blm_sample(const float* logits, long long row_stride, int n_rows, in
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t err = cudaLaunchKernelEx(&cfg, sample_kernel, logits, row_stride, vocab, temperature, top_p, seeds, stream_ids, counters, out, work);
+    cudaError_t err = cudaLaunchKernelEx(&cfg, sample_kernel, logits, row_stride, vocab, temperature, top_p, seeds, stream_ids, counters, out, work, (int)pieces);
     if (err != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "sample: %s", cudaGetErrorString(err));
     return blm_check_launch("sample");
 }

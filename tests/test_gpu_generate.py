@@ -82,6 +82,33 @@ def test_sampling_matches_plain_on_the_same_logits():
     assert smp.sample(logits, SamplingParams(0.0), [0] * B, [0] * B) == logits.argmax(-1).tolist()
 
 
+@pytest.mark.parametrize("vocab", [5000, 20000, 128256])
+def test_a_draw_does_not_depend_on_how_many_blocks_share_a_row(vocab):
+    """A row of a large vocabulary is shared by the blocks of a cluster, fewer of them when there are many
+    rows: a row sampled alone, among 20 and among 90 rows draws the same token, and the plain draw's."""
+    from burn_lm_b200 import kernels as K
+    from burn_lm_b200.sampling import Sampler, SamplingParams
+    g = torch.Generator(device="cuda").manual_seed(vocab)
+    B = 90
+    logits = 2.5 * torch.randn(B, vocab, device="cuda", generator=g)
+    smp = Sampler("cuda")
+    for temperature, top_p in [(0.8, 0.9), (1.2, 1.0), (0.7, 0.3)]:
+        params = SamplingParams(temperature, top_p, seed=99)
+        streams, counters = list(range(B)), [3 * b for b in range(B)]
+        many = smp.sample(logits, params, streams, counters)
+        some = smp.sample(logits[:20].contiguous(), params, streams[:20], counters[:20])
+        assert some == many[:20]
+        for b in (0, 7, 19, 55, 89):
+            alone = smp.sample(logits[b:b + 1].contiguous(), params, streams[b:b + 1], counters[b:b + 1])
+            assert alone == many[b:b + 1], (vocab, temperature, top_p, b)
+        same = 0
+        for b in range(0, B, 9):
+            probs = P.temperature_softmax(logits[b].cpu().numpy(), temperature)
+            u = K.uniform32(99, streams[b], counters[b]) / 2.0 ** 32
+            same += int(many[b] == P.top_p_draw(probs, top_p, u))
+        assert same >= 9, (vocab, temperature, top_p, same)
+
+
 def test_sampling_nucleus_far_below_the_largest_probability():
     """One token holds half of the mass and a large vocabulary shares the rest in crumbs 2^-17 of it and
     smaller: the nucleus reaches far below the sixteen exponents under the largest probability that the
