@@ -1,7 +1,8 @@
 """Each part of a layer alone against its plain twin, built directly from its spec with random
-tensors, and two toy architectures registered from here, without touching the package: one with a toy
+tensors, and three toy architectures registered from here, without touching the package: one with a toy
 mixer (state of its own), a layer that runs twice and a run that reads another run's cache; one with a
-feed-forward that routes tokens to experts and a position encoding that is added to the stream."""
+feed-forward that routes tokens to experts and a position encoding that is added to the stream; one whose
+layers take turns between attention over every key and over a window (two cache groups)."""
 import dataclasses
 import json
 import os
@@ -470,3 +471,80 @@ def test_toy_routed_feed_forward_and_stream_position(tmp_path):
         h = P.embedding(t["r.embed"], toks) + t["r.pos"][: len(toks)]
         used |= set(P.softmax(P.rms_norm(h, t["r.0.n1"], 1e-6) @ t["r.0.router"].T).argmax(-1).tolist())
     assert len(used) >= 3
+
+
+# --------------------------------------------------------------------------------------------------
+# a third toy: the package's own parts, arranged so that the layers differ: attention over every key in
+# the even layers, over a window of the latest keys in the odd ones (two cache groups)
+# --------------------------------------------------------------------------------------------------
+WINDOW = 24
+
+
+def register_windowed_toy():
+    from burn_lm_b200.architectures.llama import llama_plan
+    from burn_lm_b200.config.llama import LlamaConfig
+    from burn_lm_b200.registry import Architecture, architectures, register_architecture
+    if "ToyWindowedLM" in [a.name for a in architectures()]:
+        return
+
+    def plan(cfg):
+        base = llama_plan(cfg)
+        layers = []
+        for n, layer in enumerate(base.layers):
+            if n % 2 == 1:
+                spec = dataclasses.replace(layer.mixer.spec, window=WINDOW)
+                layer = dataclasses.replace(layer, mixer=dataclasses.replace(layer.mixer, spec=spec))
+            layers.append(layer)
+        return dataclasses.replace(base, architecture="ToyWindowedLM", layers=tuple(layers))
+
+    register_architecture(Architecture(name="ToyWindowedLM", config_class=LlamaConfig, plan=plan,
+                                       description="test only: full and windowed attention in turn"))
+
+
+def windowed_plain(cfg, tensors, tokens):
+    """The plain model with a window in the odd layers: one function per part, from tests/plain."""
+    cfg = P.complete_config(cfg)
+    inv_freq = P.model_inverse_frequencies(cfg)
+    h = P.embedding(tensors["model.embed_tokens.weight"], tokens)
+    for n in range(cfg["num_hidden_layers"]):
+        lw = P.layer_weights(tensors, n)
+        a = P.attention(P.rms_norm(h, lw["input_layernorm"], cfg["rms_norm_eps"]), lw["q_proj"], lw["k_proj"], lw["v_proj"],
+                        lw["o_proj"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], inv_freq, "half",
+                        window=WINDOW if n % 2 == 1 else None)
+        h = h + a
+        h = h + P.feed_forward(P.rms_norm(h, lw["post_attention_layernorm"], cfg["rms_norm_eps"]),
+                               lw["gate_proj"], lw["up_proj"], lw["down_proj"])
+    h = P.rms_norm(h, tensors["model.norm.weight"], cfg["rms_norm_eps"])
+    return h @ tensors["model.embed_tokens.weight"].T
+
+
+@pytest.mark.parametrize("dtype,tolerance", [("float32", 1e-4), ("bfloat16", 3e-2)])
+def test_layers_with_and_without_a_window_in_one_model(tmp_path, dtype, tolerance):
+    """Layers of one model that differ in their mixer's options: the windowed layers form a cache group of
+    their own, and prompts, single tokens and batches of unequal lengths agree with the plain model; the
+    window's edge is shown by comparing with the plain model without a window, which must differ."""
+    import traces
+    from burn_lm_b200 import Engine, write_random_model
+    from tiny import random_tokens, row_error
+    register_windowed_toy()
+    cfg = {"architectures": ["ToyWindowedLM"], "model_type": "toy", "num_hidden_layers": 4, "hidden_size": 128,
+           "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 192, "vocab_size": 300,
+           "rope_theta": 10000.0, "rope_scaling": None, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+           "max_position_embeddings": 512, "hidden_act": "silu"}
+    folder = write_random_model(str(tmp_path / "windowed"), cfg, seed=4, dtype="bfloat16")
+    _, tensors = P.read_model_folder(folder)
+    reqs = {"a": random_tokens(1, 150, 300), "b": random_tokens(2, 20, 300), "c": random_tokens(3, 70, 300), "d": random_tokens(4, WINDOW + 1, 300)}
+    want = {rid: windowed_plain(cfg, tensors, toks) for rid, toks in reqs.items()}
+    llama_like = dict(cfg, architectures=["LlamaForCausalLM"])
+    without = P.forward(llama_like, tensors, reqs["a"])
+    assert row_error(want["a"][WINDOW + 5:], without[WINDOW + 5:]).max() > 10 * tolerance      # the window matters
+    assert row_error(want["a"][:WINDOW], without[:WINDOW]).max() < 1e-9                        # ... from its edge on
+    for what, steps in (("whole", traces.whole(reqs)), ("tail", traces.tail(reqs, 32)), ("batched", traces.batched(reqs, 3, [5, 32]))):
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=traces.max_live_tokens(steps), max_seqs=3)
+        tables = {eng.cache.view(r).block_table.data_ptr() for r in range(4)}
+        assert len(tables) == 2 and eng.cache.view(1).window == WINDOW and not eng.cache.view(0).window
+        got = traces.run_in_process(eng, steps, str(tmp_path / what), 300)
+        for rid in reqs:
+            err = row_error(got[rid], want[rid])
+            assert err.max() < tolerance, (what, rid, float(err.max()), int(err.argmax()))
+        eng.verify()
