@@ -124,3 +124,25 @@ def test_a_step_of_more_than_a_thousand_tokens(tmp_path):
             err = row_error(got[i * len(want_at):(i + 1) * len(want_at)], want)
             assert err.max() < BF16_TOL, (rep, i, err)
     eng.verify()
+
+
+def test_every_prompt_product_on_the_tcgen05_kernel(tmp_path, monkeypatch):
+    """With the switch that sends the plain prompt products (qkv, output, down) to this package's tcgen05
+    kernel as well, a step of 300 tokens agrees with the plain implementation, and the kernel did run."""
+    from burn_lm_b200 import StepEntry, kernels
+    from burn_lm_b200.parts import linear
+    monkeypatch.setattr(linear, "OWN_PRODUCTS", True)
+    calls = []
+    real = kernels.gemm_tc
+    monkeypatch.setattr(kernels, "gemm_tc", lambda *a, **k: (calls.append(a[1].shape), real(*a, **k))[1])
+    folder = make_folder(tmp_path, "tiny_e", seed=9, dtype="bfloat16")
+    cfg, tensors = P.read_model_folder(folder)
+    eng = engine_for(folder, "bfloat16", max_tokens=1024)
+    toks = random_tokens(80, 300, cfg["vocab_size"])
+    slot = eng.acquire()
+    want_at = [0, 100, 299]
+    got = eng.step([StepEntry(slot, toks, want_at)]).cpu().numpy()
+    want = P.forward(cfg, tensors, toks)[want_at]
+    assert row_error(got, want).max() < BF16_TOL
+    assert len(calls) >= 3 * cfg["num_hidden_layers"]
+    eng.verify()
