@@ -470,16 +470,40 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
             });
             __syncthreads();
             merge_hist();
-            if (tid == 0) {
-                unsigned long long run = s_above;
-                int bin = 255;
-                for (; bin > 0; --bin) {
-                    const unsigned long long h = ((unsigned long long)hist_hi[bin] << 32) | hist_lo[bin];
-                    if (run + h >= target) break;
-                    run += h;
+            if (tid < 32) {
+                // The first bin from the top at which the mass reaches the target (bin 0 if none does).  Lane l
+                // takes the eight bins 255 - 8 l downwards; the lanes' sums are prefixed from lane 0 up; the
+                // lowest lane whose bins reach the target walks them.
+                const unsigned long long above0 = s_above;
+                unsigned long long h8[8], mine = 0;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int bin = 255 - 8 * tid - k;
+                    h8[k] = ((unsigned long long)hist_hi[bin] << 32) | hist_lo[bin];
+                    mine += h8[k];
                 }
-                s_above = run;
-                s_prefix = prefix | ((unsigned int)bin << shift);
+                unsigned long long incl = mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (tid >= o) incl += up;
+                }
+                const unsigned long long before_me = above0 + incl - mine;
+                const bool reaches = before_me + mine >= target;
+                const unsigned ballot = __ballot_sync(0xffffffffu, reaches);
+                const int owner = ballot ? __ffs(ballot) - 1 : 31;      // nobody: the last lane ends at bin 0
+                __syncwarp();                                           // every lane has read s_above
+                if (tid == owner) {
+                    unsigned long long run = before_me;
+                    int k = 0;
+                    for (; k < 8; ++k) {
+                        const int bin = 255 - 8 * tid - k;
+                        if (bin == 0 || run + h8[k] >= target) break;
+                        run += h8[k];
+                    }
+                    s_above = run;
+                    s_prefix = prefix | ((unsigned int)(255 - 8 * tid - k) << shift);
+                }
             }
             __syncthreads();
         }
