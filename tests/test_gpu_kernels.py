@@ -105,11 +105,13 @@ def paged_setup(lens_before, lens_new, n_kv, hd, dtype, seed, n_pages=None, shuf
 def write_history(setup, k_hist, v_hist):
     """Put per-sequence history [len, n_kv, hd] into the pool through the block table."""
     P = K().PAGE
+    pool = setup["pool"]
     for s, (kh, vh) in enumerate(zip(k_hist, v_hist)):
-        for pos in range(kh.shape[0]):
-            page = int(setup["host_table"][setup["host_slots"][s], pos // P])
-            setup["pool"][page, 0, :, pos % P] = kh[pos].to(setup["pool"].dtype)
-            setup["pool"][page, 1, :, pos % P] = vh[pos].to(setup["pool"].dtype)
+        pos = torch.arange(kh.shape[0])
+        pages = setup["host_table"][setup["host_slots"][s]][pos // P].long().to(pool.device)
+        offs = (pos % P).to(pool.device)
+        pool[pages, 0, :, offs] = kh.to(pool.dtype)        # [len, n_kv, hd] each
+        pool[pages, 1, :, offs] = vh.to(pool.dtype)
 
 
 def read_history(setup, s, length):
@@ -175,7 +177,7 @@ def attention_reference(q, k_all, v_all, start, scale, window):
     return out
 
 
-def run_attention_case(dtype, H, KV, hd, lens_before, lens_new, window, n_splits, seed):
+def run_attention_case(dtype, H, KV, hd, lens_before, lens_new, window, n_splits, seed, max_kv_len=0):
     k = K()
     st = paged_setup(lens_before, lens_new, KV, hd, dtype, seed=seed)
     g = torch.Generator(device="cuda").manual_seed(seed + 100)
@@ -191,7 +193,8 @@ def run_attention_case(dtype, H, KV, hd, lens_before, lens_new, window, n_splits
     if n_splits > 1:
         scratch = torch.empty(k.attention_scratch_floats(n, H, hd, n_splits), device="cuda")
     k.attention(qkv, q_stride, st["pool"], st["table"], st["cu"], st["slots"], st["starts"], out, n, len(lens_new),
-                max(lens_new), H, KV, hd, scale, window=window, n_splits=n_splits, scratch=scratch)
+                max(lens_new), H, KV, hd, scale, window=window, n_splits=n_splits, scratch=scratch, max_kv_len=max_kv_len)
+    k.check_status("cuda")
     if dtype == torch.bfloat16 and (max(lens_new) == 1 or max(lens_new) >= 16):
         # whichever kernel took the step, the general one must say the same (up to bf16 rounding of the output)
         out_general = torch.empty_like(out)
@@ -616,6 +619,59 @@ def test_prompt_attention_on_tensor_cores(H, KV, hd):
     run_attention_case(torch.bfloat16, H, KV, hd, [0, 0, 0, 0, 0], [16, 63, 64, 65, 333], 0, 1, seed=50)
     run_attention_case(torch.bfloat16, H, KV, hd, [10, 100, 64, 700], [17, 40, 128, 70], 0, 1, seed=51)
     run_attention_case(torch.bfloat16, H, KV, hd, [0, 130, 64], [200, 90, 31], 75, 1, seed=52)
+
+
+# (cached tokens, new tokens, window, positions of the planted key).  16 to 63 new tokens take the mma.sync prompt
+# kernel in bfloat16, 64 and more the tcgen05 one.  Planted: the first key, the ends of pages (63, 64, 127, 128),
+# the last cached key and the first new one, the last key of a partial page; with a window w, for a row at position
+# pos the key pos - w must be ignored and pos - w + 1 must win, for the rows at both ends of a 128-row tile of the
+# step (rows 0, 127, 128 and the last).
+PLANTED = [
+    (0, 40, 0, [0, 17, 39]),
+    (70, 50, 0, [0, 63, 64, 69, 70, 100, 119]),
+    (0, 200, 0, [0, 63, 64, 127, 128, 150, 199]),
+    (130, 300, 0, [0, 63, 64, 127, 128, 129, 130, 257, 258, 383, 384, 429]),
+    (200, 260, 75, [125, 126, 252, 253, 254, 384, 385, 459]),
+    (0, 300, 128, [0, 1, 63, 64, 127, 128, 171, 172, 299]),
+    (10, 50, 24, [0, 9, 10, 35, 36, 59]),
+    (100, 33, 37, [63, 64, 95, 96, 100, 132]),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KV,hd", [(4, 2, 64), (4, 1, 128)])
+@pytest.mark.parametrize("before,new,window,planted", PLANTED)
+def test_prompt_attention_finds_planted_keys(dtype, H, KV, hd, before, new, window, planted):
+    """Random keys and values hide a lost key or a window edge that is off by one (the output moves by 1/n).
+    Here all keys are tiny but one, which matches every query: a row that may see it must return that key's
+    value, a row that may not (the key lies after it, or before its window) the mean of what it does see."""
+    k = K()
+    S = before + new
+    scale = 1.0
+    for target in planted:
+        st = paged_setup([before], [new], KV, hd, dtype, seed=target)
+        g = torch.Generator(device="cuda").manual_seed(70 + target)
+        kh = (0.01 * torch.randn(S, KV, hd, device="cuda", generator=g)).to(dtype)
+        vh = torch.randn(S, KV, hd, device="cuda", generator=g).to(dtype)
+        kh[target] = 4.0
+        write_history(st, [kh], [vh])
+        q = torch.zeros(new, (H + 2 * KV) * hd, device="cuda", dtype=dtype)
+        q[:, : H * hd] = 1.0
+        out = torch.empty(new, H * hd, device="cuda", dtype=dtype)
+        k.attention(q, q.shape[1], st["pool"], st["table"], st["cu"], st["slots"], st["starts"], out, new, 1, new,
+                    H, KV, hd, scale, window=window, max_kv_len=S)
+        k.check_status("cuda")
+        want = attention_reference(q.double().view(new, -1, hd)[:, :H], kh.double(), vh.double(), before, scale, window)
+        got = out.double().view(new, H, hd)
+        assert not torch.isnan(got).any()
+        bad = ((got - want).abs() > 2e-2 + 2e-2 * want.abs()).flatten(1).any(1)
+        assert not bad.any(), (target, "first bad row", int(bad.nonzero()[0]), "of", new)
+        # the rows that may see the planted key return its value
+        pos = torch.arange(before, S, device="cuda")
+        sees = (pos >= target) & ((pos - target < window) if window else torch.ones_like(pos, dtype=torch.bool))
+        if sees.any():
+            won = vh[target].double().repeat_interleave(H // KV, dim=0)
+            assert (got[sees] - won).abs().max().item() < 2e-2
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (300, 520, 200), (77, 48, 1000), (2048, 3072, 2048), (513, 2048, 8192)])

@@ -146,3 +146,41 @@ def test_every_prompt_product_on_the_tcgen05_kernel(tmp_path, monkeypatch):
     assert row_error(got, want).max() < BF16_TOL
     assert len(calls) >= 3 * cfg["num_hidden_layers"]
     eng.verify()
+
+
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_d", "tiny_e"])
+@pytest.mark.parametrize("dtype,tolerance", [("float32", FP32_TOL), ("bfloat16", BF16_TOL)])
+def test_steps_that_hold_decoding_sequences_beside_fresh_prompts(tmp_path, name, dtype, tolerance):
+    """`Engine.step` takes any mix: a sequence that goes on by one token beside a prompt that starts, and a
+    prompt that goes on by several tokens.  The same mix three times with other tokens (the steps fall into
+    prompt buckets: launched plainly, captured, replayed), each against the plain implementation."""
+    from burn_lm_b200 import StepEntry
+    folder = make_folder(tmp_path, name, seed=11, dtype="bfloat16")
+    cfg, tensors = P.read_model_folder(folder)
+    eng = engine_for(folder, dtype)
+    vocab = cfg["vocab_size"]
+    for rep in range(3):
+        a = random_tokens(300 + rep, 70 + 3, vocab)
+        b = random_tokens(400 + rep, 40 + 2, vocab)
+        c = random_tokens(500 + rep, 33 + 5, vocab)
+        sa, sb, sc = eng.acquire(), eng.acquire(), eng.acquire()
+        got = {"a": [], "b": [], "c": []}
+
+        def run(entries):
+            """entries: (name, slot, tokens); logits are wanted everywhere."""
+            out = eng.step([StepEntry(slot, toks, list(range(len(toks)))) for _, slot, toks in entries]).cpu().numpy()
+            row = 0
+            for who, _, toks in entries:
+                got[who].extend(out[row: row + len(toks)])
+                row += len(toks)
+
+        run([("a", sa, a[:70])])
+        run([("a", sa, a[70:71]), ("b", sb, b[:40])])                            # decoding beside a fresh prompt
+        run([("c", sc, c[:33]), ("a", sa, a[71:72]), ("b", sb, b[40:41])])       # the fresh prompt first, two decoding
+        run([("b", sb, b[41:42]), ("c", sc, c[33:38]), ("a", sa, a[72:73])])     # a prompt that goes on by five tokens
+        for who, toks in (("a", a), ("b", b), ("c", c)):
+            err = row_error(np.stack(got[who]), P.forward(cfg, tensors, toks))
+            assert err.max() < tolerance, (rep, who, float(err.max()), "first bad place", int(np.argmax(err >= tolerance)))
+        for s in (sa, sb, sc):
+            eng.release(s)
+    eng.verify()

@@ -6,6 +6,7 @@ parameter with `arange(n) * 5 / n` in burn's `[d_in, d_out]` layout
 (crates/burn-lm-llama/src/lib.rs:142-148,199-205), so the plain functions, which take `[out, in]`
 matrices, get the transposes.
 """
+import ast
 import os
 import re
 
@@ -40,7 +41,9 @@ def rust_array(path, fn_name, which):
                     break
         lit = body[i: j + 1]
         lit = re.sub(r",\s*\]", "]", lit)
-        found.append(np.array(eval(lit), dtype=np.float64))  # digits, brackets and commas only
+        # the text comes from outside this repository: numbers, brackets and commas only, and never evaluated as code
+        assert re.fullmatch(r"[\s\d.,eE+\-\[\]]+", lit), f"not a plain array literal in {path}::{fn_name}: {lit[:60]!r}"
+        found.append(np.array(ast.literal_eval(lit), dtype=np.float64))
     return found[which]
 
 

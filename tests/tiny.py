@@ -51,7 +51,19 @@ TINY_E = {
     "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 1024, "hidden_act": "silu",
 }
 
+# eight kv heads of size 64 with two query heads each, as many kv heads as the 1B shape: with dozens of
+# sequences a decode step offers the attention kernel hundreds of (sequence, kv head) blocks
+TINY_F = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 192, "num_attention_heads": 16, "num_key_value_heads": 8,
+    "head_dim": 64, "intermediate_size": 448, "vocab_size": 300, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 128},
+    "rms_norm_eps": 2e-5, "tie_word_embeddings": False, "max_position_embeddings": 1024, "hidden_act": "silu",
+}
+
 CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D, "tiny_e": TINY_E}
+MORE_CONFIGS = dict(CONFIGS, tiny_f=TINY_F)
 
 
 def make_folder(tmp_path, name, seed=0, dtype="float32"):
@@ -59,7 +71,7 @@ def make_folder(tmp_path, name, seed=0, dtype="float32"):
 
     folder = os.path.join(str(tmp_path), f"{name}-{dtype}-{seed}")
     if not os.path.exists(os.path.join(folder, "model.safetensors")):
-        write_random_model(folder, CONFIGS[name], seed=seed, dtype=dtype)
+        write_random_model(folder, MORE_CONFIGS[name], seed=seed, dtype=dtype)
     return folder
 
 

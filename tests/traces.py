@@ -36,10 +36,12 @@ def tail(requests, n_tail=32, first_step=0):
     return steps
 
 
-def batched(requests, batch_size, decode_counts, first_step=0):
+def batched(requests, batch_size, decode_counts, first_step=0, prompt_steps=1):
     """Batches of `batch_size` requests of unequal lengths, one batch after another.  Request i of a
     batch brings all but its last decode_counts[i] tokens in the first step, then one token a step;
-    the requests with fewer tokens left end earlier."""
+    the requests with fewer tokens left end earlier.  With `prompt_steps` > 1 the first part is itself
+    cut into that many steps of several tokens per request (the engine takes that; the replay program's
+    callers do not ask for it)."""
     steps = []
     s = first_step
     items = list(requests.items())
@@ -49,10 +51,14 @@ def batched(requests, batch_size, decode_counts, first_step=0):
         for n, (rid, toks) in enumerate(batch):
             d = decode_counts[(b0 + n) % len(decode_counts)]
             heads[rid] = max(1, len(toks) - d)
-        entries = [{"id": rid, "tokens": list(toks[: heads[rid]]), "want": list(range(heads[rid]))} for rid, toks in batch]
-        done = [rid for rid, toks in batch if heads[rid] == len(toks)]
-        steps.append({"step": s, "entries": entries, "end": done})
-        s += 1
+        for part in range(prompt_steps):
+            cut = lambda rid, k: heads[rid] * k // prompt_steps
+            entries = [{"id": rid, "tokens": list(toks[cut(rid, part): cut(rid, part + 1)]),
+                        "want": list(range(cut(rid, part + 1) - cut(rid, part)))}
+                       for rid, toks in batch if cut(rid, part + 1) > cut(rid, part)]
+            done = [rid for rid, toks in batch if heads[rid] == len(toks)] if part == prompt_steps - 1 else []
+            steps.append({"step": s, "entries": entries, "end": done})
+            s += 1
         pos = dict(heads)
         live = [(rid, toks) for rid, toks in batch if heads[rid] < len(toks)]
         while live:
