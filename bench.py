@@ -1,6 +1,6 @@
 """Decode and prefill throughput of the Llama-3.2-1B shape with random weights on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 1b|3b|8b]
 
 A "step" is one decode step of the whole batch.  The default run has the layer sizes of the 1B
 configuration (16 layers, width 2048, 32 heads on 8 kv heads of 64, inner 8192, vocabulary 128256,
@@ -15,6 +15,11 @@ llama3 rotary scaling, tied head), bfloat16 random weights N(0, 0.02), a batch o
   roofline   the decode step against the HBM bandwidth: bytes it has to read / its time
   points     decode at batch 1 and 64
 
+--config 3b: the Llama-3.2-3B shape, 16 prompts of 64 to 4,096 tokens prefilled together, 128 greedy steps,
+context 8192.  --config 8b: the Llama-3.1-8B shape, 32 prompts of 128 to 2,048 tokens, 256 steps at temperature
+0.7 (the draw runs inside the captured step; the host launches every step), and a 2,048-token prefill.
+Models are built with random weights drawn on the device (`load_random`), no folder in between.
+
 Peaks come from MEASURED_PEAKS.json beside this file when it is there.  The weights (2.47 GB) are
 far larger than the L2, so nothing is flushed between steps.  For --gpus N > 1 it says that this
 library runs on one GPU and exits with 2.  The reference arm is unavailable: tracel-ai/burn-lm is a
@@ -23,30 +28,26 @@ Rust workspace and neither cargo nor its git dependency `burn` can be had offlin
 from __future__ import annotations
 
 import argparse
-import hashlib
 import json
 import os
 import statistics
 import sys
-import tempfile
 import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-LLAMA_1B = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
-    "num_hidden_layers": 16, "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 8,
-    "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256, "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
-                     "original_max_position_embeddings": 8192},
-    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 131072, "hidden_act": "silu",
+# The workloads, by the name --config takes.  "1b" is the headline and the default; "3b" and "8b" are the two
+# larger shapes with the batches their configurations state.  `prompts`: ("equal", n) or ("uniform", lo, hi).
+WORKLOADS = {
+    "1b": {"preset": "llama3_2_1b", "model": "llama-3.2-1b-shape-random", "context": 4096, "batch": 8,
+           "prompts": ("equal", 512), "steps": 256, "temperature": 0.0, "prefill": ("one", 2048), "points": (1, 64)},
+    "3b": {"preset": "llama3_2_3b", "model": "llama-3.2-3b-shape-random", "context": 8192, "batch": 16,
+           "prompts": ("uniform", 64, 4096), "steps": 128, "temperature": 0.0, "prefill": ("batch",), "points": ()},
+    "8b": {"preset": "llama3_1_8b", "model": "llama-3.1-8b-shape-random", "context": 8192, "batch": 32,
+           "prompts": ("uniform", 128, 2048), "steps": 256, "temperature": 0.7, "prefill": ("one", 2048), "points": ()},
 }
-FULL_LAYERS = 16
-CONTEXT = 4096
-PROMPT = 512
-PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -118,62 +119,95 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def model_folder(cfg, seed=0):
-    """A folder with the random 1B model, made once per box under the temporary folder."""
-    import burn_lm_b200 as blm
-    key = hashlib.sha256(json.dumps(cfg, sort_keys=True).encode()).hexdigest()[:12]
-    folder = os.path.join(tempfile.gettempdir(), f"burn-lm_b200-bench-{key}-{seed}")
-    done = os.path.join(folder, ".complete")
-    if not os.path.exists(done):
-        t0 = time.time()
-        blm.write_random_model(folder, cfg, seed=seed, dtype="bfloat16", device="cuda")
-        with open(done, "w") as f:
-            f.write("ok")
-        print(f"[bench] wrote random model to {folder} in {time.time() - t0:.1f} s", file=sys.stderr)
-    return folder
-
-
 def weight_bytes(cfg):
     d, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     h, kv, hd, layers = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["num_hidden_layers"]
     per_layer = d * (h + 2 * kv) * hd + h * hd * d + 3 * d * i + 2 * d
-    return 2 * (layers * per_layer + v * d + d)      # bf16; the tied table is read once, as the head
+    head = v * d if cfg.get("tie_word_embeddings") else 2 * v * d      # untied: the table is stored beside the head
+    return 2 * (layers * per_layer + head + d)      # bf16
+
+
+def decode_step_bytes(cfg, live_tokens):
+    """What a decode step has to read: every weight it uses once (the embedding table only as far as it is
+    the head: a step gathers a handful of its rows) and the cache of the live sequences."""
+    d, v = cfg["hidden_size"], cfg["vocab_size"]
+    used = weight_bytes(cfg) - (0 if cfg.get("tie_word_embeddings") else 2 * v * d)
+    return used + live_tokens * kv_bytes_per_token(cfg)
 
 
 def kv_bytes_per_token(cfg):
     return 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
 
 
-def prefill_flops(cfg, t):
+def prefill_flops(cfg, lengths):
+    """Flops of one prompt step over prompts of these lengths: the products over all tokens, attention within
+    each prompt (the causal half of QK^T and PV), the head on one row per prompt."""
     d, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     h, kv, hd, layers = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["num_hidden_layers"]
     per_layer = d * (h + 2 * kv) * hd + h * hd * d + 3 * d * i
-    gemm = 2.0 * t * layers * per_layer + 2.0 * v * d          # the head runs on one row
-    attn = layers * 2.0 * t * t * h * hd                        # causal half of QK^T and PV
+    total = sum(lengths)
+    gemm = 2.0 * total * layers * per_layer + 2.0 * v * d * len(lengths)
+    attn = layers * 2.0 * h * hd * sum(t * t for t in lengths)
     return gemm + attn
 
 
-def random_prompts(n, length, vocab, seed):
+def make_prompts(spec, n, vocab, seed):
+    """`spec`: ("equal", length) or ("uniform", lo, hi); ids uniform over the vocabulary, seeded."""
     import numpy as np
     rng = np.random.default_rng(seed)
-    return [[int(x) for x in rng.integers(0, vocab, size=length)] for _ in range(n)]
+    if spec[0] == "equal":
+        lengths = [spec[1]] * n
+    else:
+        lengths = [int(x) for x in rng.integers(spec[1], spec[2] + 1, size=n)]
+    return [[int(x) for x in rng.integers(0, vocab, size=length)] for length in lengths]
 
 
-def device_decode(engine, batch, steps, warmup, cfg, sample_clocks=False, prompt_len=None):
-    """Prefill `batch` prompts, then time `steps` decode steps that run back to back on the device."""
+def prefill_in_parts(engine, slots, prompts, most=8192):
+    """Prompts go in a few at a time to keep the prefill's activations small."""
+    from burn_lm_b200 import StepEntry
+    group, held = [], 0
+    for s, p in zip(slots, prompts):
+        if group and held + len(p) > most:
+            engine.step([StepEntry(a, b, []) for a, b in group])
+            group, held = [], 0
+        group.append((s, p))
+        held += len(p)
+    if group:
+        engine.step([StepEntry(a, b, []) for a, b in group])
+
+
+def device_decode(engine, prompts, steps, warmup, sample_clocks=False, temperature=0.0):
+    """Prefill the prompts, then time `steps` decode steps.  Greedy: the steps run back to back on the device
+    (captured graph, the argmax token fed back by a kernel).  With a temperature: every step is the captured
+    graph with the draw inside it, launched by the host with the step's tokens (the draw needs the host's counters)."""
     import torch
-    from burn_lm_b200 import StepEntry, kernels
-    plen = prompt_len or PROMPT
-    prompts = random_prompts(batch, plen, cfg["vocab_size"], seed=batch)
+    from burn_lm_b200 import kernels
+    from burn_lm_b200.sampling import SamplingParams
+    batch = len(prompts)
+    lengths = [len(p) for p in prompts]
     slots = [engine.acquire() for _ in range(batch)]
     try:
-        # prompts go in a few at a time to keep the prefill's activations small
-        for i in range(0, batch, 8):
-            engine.step([StepEntry(s, p, []) for s, p in zip(slots[i:i + 8], prompts[i:i + 8])])
+        prefill_in_parts(engine, slots, prompts)
         first = [p[-1] for p in prompts]
-        engine.decode_run(slots, first, max(warmup, 3))          # warm-up: captures the graph, W steps
-        for s in slots:                                          # rewind: the timed run decodes from the prompt's end
-            engine.cache.set_length(s, plen)
+        params = SamplingParams(temperature, 0.9, 1234) if temperature > 0 else None
+
+        def run(n):
+            if params is None:
+                return engine.decode_run(slots, first, n)
+            toks = list(first)
+            for k in range(n):
+                toks = engine.decode_sampled(slots, toks, params, list(range(batch)), [k] * batch)
+                assert toks is not None, "this engine does not capture its decode steps"
+            return toks
+
+        sampled_per_step = 0
+        if params is not None:                                   # the first drawn step runs plainly, then is captured
+            count0 = kernels.launch_count()
+            run(1)
+            sampled_per_step = (kernels.launch_count() - count0) // 2
+        run(max(warmup, 3))                                      # warm-up: captures the graph, W steps
+        for s, n in zip(slots, lengths):                         # rewind: the timed run decodes from the prompts' ends
+            engine.cache.set_length(s, n)
         torch.cuda.synchronize()
         before = kernels.launch_count()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -182,35 +216,34 @@ def device_decode(engine, batch, steps, warmup, cfg, sample_clocks=False, prompt
             sampler.__enter__()
         torch.cuda.synchronize()
         start.record()
-        history = engine.decode_run(slots, first, steps)
+        run(steps)
         stop.record()
         torch.cuda.synchronize()
         if sampler:
             sampler.__exit__()
         ms = start.elapsed_time(stop)
-        g = engine.decode_graph(batch, plen + steps)
-        launches = g.launches_per_step * steps + (kernels.launch_count() - before)
-        assert history.shape == (steps, batch)
+        g = engine.decode_graph(batch, max(lengths) + steps)
+        per_step = sampled_per_step or g.launches_per_step or 0
+        launches = per_step * steps + (kernels.launch_count() - before)
         engine.verify()        # no kernel gave up a bounded wait
         return {"ms_per_step": ms / steps, "tokens_per_s": batch * steps / (ms / 1e3), "launches": launches,
-                "clocks": sampler.summary() if sampler else None}
+                "clocks": sampler.summary() if sampler else None, "graph": g}
     finally:
         for s in slots:
             engine.release(s)
 
 
-def time_prefill(engine, cfg, reps=5, tokens=PREFILL_TOKENS, n_prompts=1):
-    """Median time of one prefill step: `n_prompts` prompts of `tokens` tokens each, the last logits wanted."""
+def time_prefill(engine, prompts, reps=5):
+    """Median time of one prefill step over `prompts`, the last logits of each wanted."""
     import torch
     from burn_lm_b200 import StepEntry
-    prompts = random_prompts(n_prompts, tokens, cfg["vocab_size"], seed=99)
     times = []
     for r in range(reps + 2):
         slots = [engine.acquire() for _ in prompts]
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         start.record()
-        engine.step([StepEntry(s, p, [tokens - 1]) for s, p in zip(slots, prompts)])
+        engine.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
         stop.record()
         torch.cuda.synchronize()
         for s in slots:
@@ -223,23 +256,21 @@ def time_prefill(engine, cfg, reps=5, tokens=PREFILL_TOKENS, n_prompts=1):
 def sweep(engine, cfg, pk):
     """Decode and prefill at further batch sizes and context lengths, one JSON line each, with the
     fraction of the measured peak (bytes a step has to read, or flops) beside the time."""
+    vocab = cfg["vocab_size"]
     for prompt_len in (512, 2048, 3840):
         for b in (1, 8, 64):
             steps = 128
-            r = device_decode(engine, b, steps, 3, cfg, prompt_len=prompt_len)
-            step_bytes = weight_bytes(cfg) + b * (prompt_len + steps / 2.0) * kv_bytes_per_token(cfg)
-            gbs = step_bytes / (r["ms_per_step"] / 1e3) / 1e9
+            r = device_decode(engine, make_prompts(("equal", prompt_len), b, vocab, seed=b), steps, 3)
+            gbs = decode_step_bytes(cfg, b * (prompt_len + steps / 2.0)) / (r["ms_per_step"] / 1e3) / 1e9
             print(json.dumps({"decode": {"batch": b, "context": prompt_len, "ms_per_step": round(r["ms_per_step"], 4),
                                          "tokens_per_s": round(r["tokens_per_s"], 1), "gb_per_s": round(gbs, 1),
                                          "frac_hbm": round(gbs / pk["hbm_gbs"], 3)}}), flush=True)
-    h, hd, layers = cfg["num_attention_heads"], cfg["head_dim"], cfg["num_hidden_layers"]
     for n_prompts, tokens in ((1, 128), (1, 512), (1, 2048), (1, 4096), (8, 512), (16, 1024)):
-        ms = time_prefill(engine, cfg, reps=3, tokens=tokens, n_prompts=n_prompts)
-        total = n_prompts * tokens
-        # products over all tokens, attention within each prompt
-        flops = prefill_flops(cfg, total) - layers * 2.0 * h * hd * (total * total - n_prompts * tokens * tokens)
+        prompts = make_prompts(("equal", tokens), n_prompts, vocab, seed=99)
+        ms = time_prefill(engine, prompts, reps=3)
+        flops = prefill_flops(cfg, [tokens] * n_prompts)
         print(json.dumps({"prefill": {"prompts": n_prompts, "tokens_each": tokens, "ms": round(ms, 3),
-                                      "tokens_per_s": round(total / (ms / 1e3), 1),
+                                      "tokens_per_s": round(n_prompts * tokens / (ms / 1e3), 1),
                                       "frac_bf16": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3)}}), flush=True)
 
 
@@ -252,66 +283,83 @@ def run_ours(args):
         print(json.dumps({"error": "no CUDA device: burn-lm_b200 has no CPU path"}))
         return 1
     pk = peaks()
-    cfg = dict(LLAMA_1B)
-    cfg["num_hidden_layers"] = args.layers
-    batch, steps, warmup = args.batch, args.steps, max(args.warmup, 3)
-    folder = model_folder(cfg)
-    lm = blm.LanguageModel(folder, dtype="bfloat16", max_seq_len=CONTEXT, max_batch=64,
-                           max_tokens=64 * CONTEXT).load()
+    w = WORKLOADS[args.config]
+    cfg = blm.preset(w["preset"])
+    full_layers = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = args.layers or full_layers
+    context = w["context"]
+    batch = args.batch or w["batch"]
+    steps, warmup = args.steps or w["steps"], max(args.warmup, 3)
+    vocab = cfg["vocab_size"]
+    most = max((batch,) + tuple(w["points"]))
+    lm = blm.load_random(cfg, seed=0, dtype="bfloat16", max_seq_len=context, max_batch=most, max_tokens=most * context)
     engine = lm.engine
+    prompts = make_prompts(w["prompts"], batch, vocab, seed=batch)
+    lengths = [len(p) for p in prompts]
+    if max(lengths) + steps + 1 > context:
+        print(f"--steps {steps} does not fit the context of {context} after a {max(lengths)}-token prompt")
+        return 2
+    one_prompt = make_prompts(("equal", w["prefill"][1]), 1, vocab, seed=99) if w["prefill"][0] == "one" else None
 
     if args.only == "decode":      # a short run of one workload, for profilers
-        r = device_decode(engine, batch, steps, warmup, cfg)
+        r = device_decode(engine, prompts, steps, warmup, temperature=w["temperature"])
         print(json.dumps({"only": "decode", "batch": batch, "ms_per_step": round(r["ms_per_step"], 4)}))
         return 0
     if args.only == "prefill":
-        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(time_prefill(engine, cfg, reps=1), 3)}))
+        ms = time_prefill(engine, one_prompt or prompts, reps=1)
+        print(json.dumps({"only": "prefill", "tokens": sum(len(p) for p in (one_prompt or prompts)), "ms": round(ms, 3)}))
         return 0
     if args.only == "sweep":
         sweep(engine, cfg, pk)
         return 0
-    main = device_decode(engine, batch, steps, warmup, cfg, sample_clocks=True)
+    main = device_decode(engine, prompts, steps, warmup, sample_clocks=True, temperature=w["temperature"])
     points = {}
-    for b in (1, 64):
-        r = device_decode(engine, b, min(steps, 128), warmup, cfg)
+    for b in w["points"]:
+        r = device_decode(engine, make_prompts(w["prompts"], b, vocab, seed=b), min(steps, 128), warmup)
         points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
 
     # end to end through the Python entry point: host tokens in and out every step
-    prompts = random_prompts(batch, PROMPT, cfg["vocab_size"], seed=batch)
-    lm.generate(prompts, sample_len=warmup + 2, ignore_stop=True)                  # warm-up (captures the graph)
-    out = lm.generate(prompts, sample_len=steps + 1, ignore_stop=True)             # steps decode steps after the prefill
+    options = dict(ignore_stop=True, temperature=w["temperature"], seed=1234)
+    lm.generate(prompts, sample_len=warmup + 2, **options)                  # warm-up (captures the graph)
+    out = lm.generate(prompts, sample_len=steps + 1, **options)             # steps decode steps after the prefill
     st = out.stats
     e2e_value = batch * st.decode_steps / st.decode_seconds
-    g = engine.decode_graph(batch, PROMPT + steps)
+    h2d = main["graph"].bytes_in_per_step() + (8 * batch if w["temperature"] > 0 else 0)      # + the draws' counters
 
-    prefill_ms = time_prefill(engine, cfg)
-    flops = prefill_flops(cfg, PREFILL_TOKENS)
+    pre_prompts = one_prompt or prompts
+    prefill_ms = time_prefill(engine, pre_prompts, reps=5 if one_prompt else 3)
+    pre_tokens = sum(len(p) for p in pre_prompts)
+    flops = prefill_flops(cfg, [len(p) for p in pre_prompts])
 
-    mean_len = PROMPT + steps / 2.0
-    step_bytes = weight_bytes(cfg) + batch * mean_len * kv_bytes_per_token(cfg)
-    achieved = step_bytes / (main["ms_per_step"] / 1e3) / 1e9
-
+    live = sum(lengths) + batch * steps / 2.0
+    achieved = decode_step_bytes(cfg, live) / (main["ms_per_step"] / 1e3) / 1e9
+    rs = cfg["rope_scaling"]
+    plen = w["prompts"]
     line = {
-        "metric": "decode tokens/s, Llama-3.2-1B shape, bf16, batch 8 (512-token prompts, context 4096)",
+        "metric": f"decode tokens/s, {w['model'].replace('-shape-random', '')} shape, bf16, batch {batch} "
+                  f"({'%d-token prompts' % plen[1] if plen[0] == 'equal' else 'prompts of %d to %d tokens' % plen[1:]}, context {context})",
         "value": round(main["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {
-            "model": "llama-3.2-1b-shape-random", "layers": cfg["num_hidden_layers"], "layers_full": FULL_LAYERS,
+            "model": w["model"], "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
             "hidden_size": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
-            "head_dim": cfg["head_dim"], "intermediate_size": cfg["intermediate_size"], "vocab_size": cfg["vocab_size"],
-            "tied_head": True, "rope": "theta 5e5, llama3 x32", "global_batch": batch, "seq_len": CONTEXT,
-            "prompt_len": PROMPT, "parallelism": "single-gpu", "weights": "random N(0,0.02) bf16",
-            "l2": "inputs (2.47 GB of weights) exceed the 126 MB L2; no flush", "sampling": "greedy",
+            "head_dim": cfg["head_dim"], "intermediate_size": cfg["intermediate_size"], "vocab_size": vocab,
+            "tied_head": bool(cfg["tie_word_embeddings"]), "rope": f"theta {cfg['rope_theta']:g}, llama3 x{rs['factor']:g}",
+            "global_batch": batch, "seq_len": context,
+            "prompt_len": plen[1] if plen[0] == "equal" else f"uniform {plen[1]}..{plen[2]} (mean {sum(lengths) // batch})",
+            "parallelism": "single-gpu", "weights": "random N(0,0.02) bf16",
+            "l2": f"inputs ({weight_bytes(cfg) / 1e9:.2f} GB of weights) exceed the 126 MB L2; no flush",
+            "sampling": "greedy" if w["temperature"] == 0 else f"temperature {w['temperature']}, top-p 0.9, host-launched steps",
             "peaks": pk["source"],
         },
         "clocks": main["clocks"],
-        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": g.bytes_in_per_step(),
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": 4 * batch, "ms_per_step": round(1e3 * st.decode_seconds / st.decode_steps, 4)},
         "gpu_launches": main["launches"],
-        "prefill": {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+        "prefill": {"value": round(pre_tokens / (prefill_ms / 1e3), 1), "tokens": pre_tokens,
                     "ms": round(prefill_ms, 3), "frac": round(flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
-                    "peak_tflops": pk["bf16_tflops"]},
+                    "peak_tflops": pk["bf16_tflops"], "prompts": len(pre_prompts)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
@@ -325,13 +373,15 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--steps", type=int, default=0, help="decode steps to time (default: the workload's: 256, 128, 256)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--config", default="1b", choices=sorted(WORKLOADS),
+                    help="the workload: 1b (the headline, default), 3b or 8b")
+    ap.add_argument("--batch", type=int, default=0, help="sequences decoded together (default: the workload's)")
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "sweep"],
                     help="run one workload briefly (for profilers), or a sweep over batch sizes and context lengths")
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration's 16 (named in config)")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (both numbers are named in config)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -340,9 +390,6 @@ def main():
         return 0
     if args.gpus != 1:
         print(f"burn-lm_b200 generates on ONE GPU; --gpus {args.gpus} is not built (no multi-GPU path)")
-        return 2
-    if args.steps + PROMPT > CONTEXT:
-        print(f"--steps {args.steps} does not fit the context of {CONTEXT} after a {PROMPT}-token prompt")
         return 2
     return run_ours(args)
 

@@ -15,7 +15,7 @@ from ..parts.embedding import EmbeddingSpec, HeadSpec
 from ..parts.feed_forward import SwiGLUSpec
 from ..parts.norm import RMSNormSpec
 from ..parts.position import Llama3Scaling, RotarySpec
-from ..plan import LayerPlan, ModelPlan, PartPlan, ScheduleEntry
+from ..plan import ModelPlan, PartPlan, ScheduleEntry, prenorm_layer
 from ..registry import Architecture, register_architecture
 
 
@@ -30,8 +30,7 @@ def llama_plan(cfg: LlamaConfig) -> ModelPlan:
     layers = []
     for n in range(cfg.num_hidden_layers):
         p = f"model.layers.{n}."
-        layers.append(LayerPlan(
-            block="prenorm",
+        layers.append(prenorm_layer(
             mixer_norm=PartPlan("rmsnorm", norm, {"weight": p + "input_layernorm.weight"}),
             mixer=PartPlan("attention",
                            AttentionSpec(cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads,
@@ -57,6 +56,8 @@ def llama_plan(cfg: LlamaConfig) -> ModelPlan:
         max_positions=cfg.max_position_embeddings,
         stop_ids=tuple(cfg.eos_token_ids),
         ignorable_tensors=(r"model\.layers\.\d+\.self_attn\.rotary_emb\.inv_freq",),
+        # some writers store the tied head as well: accepted when it is the table's copy, refused when it differs
+        duplicate_tensors=(("lm_head.weight", table),) if cfg.tie_word_embeddings else (),
     )
 
 

@@ -8,7 +8,7 @@ per-request options: --top-p, --temperature, --max-seq-len, --sample-len, --seed
 A model is a folder (config.json, model.safetensors).  There is no tokenizer here: a prompt is
 either a list of token ids ("12,7,99" or "12 7 99") or text, which is read as bytes, one token per
 byte, like the reference's ByteTokenizer (crates/burn-lm-llama/src/tokenizer/byte.rs:14-36; needs a
-vocabulary of at least 256).  `random` writes a model folder with random weights.
+vocabulary of at least 256).  `random` writes a model folder with random weights from a config.json or a named preset.
 """
 from __future__ import annotations
 
@@ -61,6 +61,7 @@ def add_request_flags(p):
     p.add_argument("--seed", type=int, default=0,
                    help="The seed to use when generating random samples. If it is 0 then a random seed is used.")
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="Compute dtype.")
+    p.add_argument("--include-stop", action="store_true", help="Print the stop token that ended the answer as well.")
 
 
 def build_parser(prog="burn-lm"):
@@ -76,8 +77,10 @@ def build_parser(prog="burn-lm"):
     chat.add_argument("model")
     add_request_flags(chat)
     rnd = sub.add_parser("random", help="Write a model folder with random weights")
-    rnd.add_argument("config", help="a config.json to take the sizes from")
     rnd.add_argument("folder", help="where to write config.json and model.safetensors")
+    src = rnd.add_mutually_exclusive_group(required=True)
+    src.add_argument("--config", help="a config.json to take the sizes from")
+    src.add_argument("--preset", help="a named configuration (see `models`)")
     rnd.add_argument("--seed", type=int, default=0)
     rnd.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     sub.add_parser("shell", help="Start a shell in which the commands run without the program's name (default)")
@@ -89,12 +92,18 @@ def cmd_models(_args):
     print("|--------------|------------")
     for a in architectures():
         print(f"| {a.name} | {a.description}")
+    from .config import preset_names
+    print("presets for `random --preset`: " + ", ".join(preset_names()))
 
 
 def cmd_random(args):
+    from .config import preset
     from .weights import write_random_model
-    with open(args.config) as f:
-        cfg = json.load(f)
+    if args.preset:
+        cfg = preset(args.preset)
+    else:
+        with open(args.config) as f:
+            cfg = json.load(f)
     write_random_model(args.folder, cfg, args.seed, args.dtype)
     print(f"wrote {args.folder}")
 
@@ -109,7 +118,7 @@ def _load(args):
 def _answer(lm, args, prompt_text, show_stats):
     tokens, as_text = parse_prompt(prompt_text, lm.engine.vocab_size)
     out = lm.generate([tokens], temperature=args.temperature, top_p=args.top_p, sample_len=args.sample_len,
-                      seed=args.seed)
+                      seed=args.seed, include_stop=args.include_stop)
     r = out.results[0]
     if r.error is not None:
         print(f"An error occurred: {r.error}", file=sys.stderr)

@@ -30,6 +30,7 @@ struct AttnDecodeArgs {
     float* part_acc;             // [N, n_heads, n_splits, HD]
     float* part_ml;              // [N, n_heads, n_splits, 2]: (max in natural-log units, sum)
     int n_heads, n_kv, window, n_splits;
+    int group;                   // query heads per kv head, 1 to 8: rows 0 .. group-1 of the 16-row tile
     int n_stages;                // pages the ring of a block holds (a multiple of n_groups)
     int n_groups;                // groups of four consumer warps; group g takes pages g, g + n_groups, ... of the block's
     float scale_log2e;           // softmax scale times log2(e): scores live in base-2 units
@@ -82,7 +83,8 @@ __device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned b
 // best, ahead of three or four pages).
 static inline int attn_decode_stages(int hd, int blocks, int pages_per_block) {
     const int page_kb = 2 * 64 * hd * 2 / 1024;                    // keys and values of a page of one kv head
-    const int room_kb = blocks <= 148 ? 192 : (blocks <= 296 ? 96 : 32);
+    const int sms = blm_sm_count();
+    const int room_kb = blocks <= sms ? 192 : (blocks <= 2 * sms ? 96 : 32);
     int s = room_kb / page_kb;
     if (s > pages_per_block) s = pages_per_block;
     return s < 2 ? 2 : s;
@@ -90,7 +92,8 @@ static inline int attn_decode_stages(int hd, int blocks, int pages_per_block) {
 // Groups of consumer warps.  One warp per scheduler waits out every latency of its chain of dependent
 // instructions; when a block is (almost) alone on its SM, several groups work on different pages at once.
 static inline int attn_decode_groups(int blocks, int pages_per_block, int stages) {
-    int ng = blocks <= 148 ? 4 : (blocks <= 296 ? 2 : 1);
+    const int sms = blm_sm_count();
+    int ng = blocks <= sms ? 4 : (blocks <= 2 * sms ? 2 : 1);
     while (ng > 1 && (ng > pages_per_block || ng > stages)) ng /= 2;
     return ng;
 }
@@ -115,9 +118,10 @@ __device__ __forceinline__ void dec_mma(float (&c)[4], const unsigned (&a)[4], u
 // instead of hundreds.  A page arrives as TMA boxes of 64 keys x 64 lanes with the 128-byte swizzle, which
 // ldmatrix reads without bank conflicts; the four consumer warps take 16 keys of every page each and keep
 // their own running (max, sum, output), merged at the end.
-template <int HD, int G, int NG>
+template <int HD, int NG>
 __global__ void __launch_bounds__((4 * NG + 1) * 32) attn_decode_kernel(const AttnDecodeArgs a, const __grid_constant__ CUtensorMap pool_map) {
     using namespace attn_decode;
+    const int G = a.group;
     constexpr int WARPS = 4 * NG;      // consumer warps (NG groups of four); the warp after them is the producer
     const int S = a.n_stages;
     constexpr int SUB = HD / 64;       // 64-lane boxes per row
@@ -431,8 +435,9 @@ static bool attn_decode_pool_map(const void* pool, int n_pages, int n_kv, int hd
     return true;
 }
 
-template <int HD, int G, int NG>
+template <int HD, int NG>
 static bool attn_decode_launch_ng(AttnDecodeArgs a, dim3 grid, int n_pages, cudaStream_t stream) {
+    const int G = a.group;
     auto bytes = [&](int stages) {
         return (size_t)stages * 2 * 64 * HD * 2 + (size_t)4 * a.n_groups * G * (HD + 2) * 4 + 2 * stages * 8 + 16 + 1024;
     };
@@ -443,29 +448,19 @@ static bool attn_decode_launch_ng(AttnDecodeArgs a, dim3 grid, int n_pages, cuda
     if (!attn_decode_pool_map(a.pool, n_pages, a.n_kv, HD, &map)) return false;
     static bool opted_in = false;
     if (!opted_in) {
-        if (cudaFuncSetAttribute(attn_decode_kernel<HD, G, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess) return false;
+        if (cudaFuncSetAttribute(attn_decode_kernel<HD, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess) return false;
         opted_in = true;
     }
-    return blm_launch_dependent(attn_decode_kernel<HD, G, NG>, grid, dim3((4 * NG + 1) * 32), smem, stream, a, map) == cudaSuccess;
-}
-
-template <int HD, int G>
-static bool attn_decode_launch(const AttnDecodeArgs& a, dim3 grid, int n_pages, cudaStream_t stream) {
-    switch (a.n_groups) {
-        case 1: return attn_decode_launch_ng<HD, G, 1>(a, grid, n_pages, stream);
-        case 2: return attn_decode_launch_ng<HD, G, 2>(a, grid, n_pages, stream);
-        case 4: return attn_decode_launch_ng<HD, G, 4>(a, grid, n_pages, stream);
-        default: return false;
-    }
+    return blm_launch_dependent(attn_decode_kernel<HD, NG>, grid, dim3((4 * NG + 1) * 32), smem, stream, a, map) == cudaSuccess;
 }
 
 template <int HD>
-static bool launch_attn_decode_g(const AttnDecodeArgs& a, int group, dim3 grid, int n_pages, cudaStream_t stream) {
-    switch (group) {
-        case 1: return attn_decode_launch<HD, 1>(a, grid, n_pages, stream);
-        case 2: return attn_decode_launch<HD, 2>(a, grid, n_pages, stream);
-        case 4: return attn_decode_launch<HD, 4>(a, grid, n_pages, stream);
-        case 8: return attn_decode_launch<HD, 8>(a, grid, n_pages, stream);
+static bool launch_attn_decode_g(const AttnDecodeArgs& a, dim3 grid, int n_pages, cudaStream_t stream) {
+    if (a.group < 1 || a.group > 8) return false;
+    switch (a.n_groups) {
+        case 1: return attn_decode_launch_ng<HD, 1>(a, grid, n_pages, stream);
+        case 2: return attn_decode_launch_ng<HD, 2>(a, grid, n_pages, stream);
+        case 4: return attn_decode_launch_ng<HD, 4>(a, grid, n_pages, stream);
         default: return false;
     }
 }
@@ -473,6 +468,7 @@ static bool launch_attn_decode_g(const AttnDecodeArgs& a, int group, dim3 grid, 
 // true when the specialised kernels were launched; false: the shape is left to the general kernel
 static bool launch_attn_decode(AttnDecodeArgs a, int hd, int group, int n_seqs, int n_pages, int max_kv_len, cudaStream_t stream) {
     const dim3 grid(a.n_splits, a.n_kv, n_seqs);
+    a.group = group;
     // the longest walk of a block: the pages of the longest sequence (all the cache could hold, when the
     // caller does not say), shared out over the splits
     const int most_pages = max_kv_len > 0 ? (max_kv_len + 63) / 64 : 4 * a.n_splits;
@@ -482,12 +478,12 @@ static bool launch_attn_decode(AttnDecodeArgs a, int hd, int group, int n_seqs, 
     a.n_stages -= a.n_stages % a.n_groups;
     const int n_rows = n_seqs * a.n_heads;
     if (hd == 64) {
-        if (!launch_attn_decode_g<64>(a, group, grid, n_pages, stream)) return false;
+        if (!launch_attn_decode_g<64>(a, grid, n_pages, stream)) return false;
         if (a.n_splits > 1) blm_launch_dependent(attn_decode_combine_kernel<64>, dim3((n_rows + 3) / 4), dim3(128), 0, stream, a, n_rows);
         return true;
     }
     if (hd == 128) {
-        if (!launch_attn_decode_g<128>(a, group, grid, n_pages, stream)) return false;
+        if (!launch_attn_decode_g<128>(a, grid, n_pages, stream)) return false;
         if (a.n_splits > 1) blm_launch_dependent(attn_decode_combine_kernel<128>, dim3((n_rows + 3) / 4), dim3(128), 0, stream, a, n_rows);
         return true;
     }

@@ -29,6 +29,19 @@ static inline int blm_check_launch(const char* what) {
     return BLM_OK;
 }
 
+// How many multiprocessors the current device has: asked once per device, never written down as a number.
+static inline int blm_sm_count() {
+    static int counts[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (counts[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 1;
+        counts[dev] = n;
+    }
+    return counts[dev];
+}
+
 #define BLM_REQUIRE(cond, ...)                                    \
     do {                                                          \
         if (!(cond)) return blm_fail(BLM_BAD_ARGUMENT, __VA_ARGS__); \

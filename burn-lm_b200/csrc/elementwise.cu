@@ -397,10 +397,10 @@ BLM_API int blm_swiglu(const void* gu, void* out, int dtype, int n_rows, int inn
     BLM_REQUIRE(tile >= 0 && (tile == 0 || inner % tile == 0), "swiglu: tiles of %d do not divide %d", tile, inner);
     const size_t total = (size_t)n_rows * inner;
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    const int blocks = (int)((total + threads - 1) / threads < blm_sm_count() * 16 ? (total + threads - 1) / threads : blm_sm_count() * 16);
     if (dtype == BLM_BF16 && inner % 8 == 0 && (tile == 0 || tile % 8 == 0) && ((size_t)gu & 15) == 0 && ((size_t)out & 15) == 0) {
         const size_t total8 = total / 8;
-        const int b8 = (int)((total8 + threads - 1) / threads < 148 * 16 ? (total8 + threads - 1) / threads : 148 * 16);
+        const int b8 = (int)((total8 + threads - 1) / threads < blm_sm_count() * 16 ? (total8 + threads - 1) / threads : blm_sm_count() * 16);
         swiglu_bf16x8_kernel<<<b8, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inner, total8, tile);
         return blm_check_launch("swiglu");
     }
@@ -426,7 +426,7 @@ __global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, 
 BLM_API int blm_convert(const void* in, int in_dtype, void* out, int out_dtype, size_t total, cudaStream_t stream) {
     if (total == 0) return BLM_OK;
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    const int blocks = (int)((total + threads - 1) / threads < blm_sm_count() * 16 ? (total + threads - 1) / threads : blm_sm_count() * 16);
     if (in_dtype == BLM_F32 && out_dtype == BLM_BF16)
         convert_kernel<float, __nv_bfloat16><<<blocks, threads, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, total);
     else if (in_dtype == BLM_BF16 && out_dtype == BLM_F32)

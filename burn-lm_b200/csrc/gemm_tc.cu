@@ -347,7 +347,7 @@ BLM_API int blm_gemm_tc(const void* x, long long ldx, const void* w, long long l
         opted_in = true;
     }
     const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
-    const int grid = (int)(tiles < 148 ? tiles : 148);        // persistent: one block per SM
+    const int grid = (int)(tiles < blm_sm_count() ? tiles : blm_sm_count());        // persistent: one block per SM
     gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(a, xmap, wmap);
     return blm_check_launch("gemm_tc");
 }

@@ -780,7 +780,8 @@ BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, 
     else a.rope = GemvRope{};
     const int out_per_tile = epi == EPI_SWIGLU ? 8 : 16;
     const int tiles = (M + out_per_tile - 1) / out_per_tile;
-    const int grid = tiles < 148 ? tiles : 148;
+    const int sms = blm_sm_count();
+    const int grid = tiles < sms ? tiles : sms;
     // Plain tokens: with one tile per block they travel with the weights; else they are fetched once by TMA;
     // and when they are too many for that (a very wide input) they travel with the weights after all, once
     // per tile.  A stream to normalise or gathered rows are staged by the consumers.
@@ -788,7 +789,7 @@ BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, 
     int nbt;
     size_t smem = 0;
     if (x != nullptr && rows == nullptr) {
-        a.x_mode = (tiles <= 148 && ssq_in == nullptr && K >= 2 * kStageK) ? X_IN_RING : X_BY_TMA;
+        a.x_mode = (tiles <= sms && ssq_in == nullptr && K >= 2 * kStageK) ? X_IN_RING : X_BY_TMA;
         smem = gemv_plan(N, K, a.x_mode, &a.n_stages, &nbt);
         if (smem == 0 && a.x_mode == X_BY_TMA) {
             a.x_mode = X_IN_RING;

@@ -596,7 +596,7 @@ BLM_API int blm_sample(const float* logits, long long row_stride, int n_rows, in
     // of a cluster: one per piece while all the rows' blocks fit the SMs at once, fewer when there are many rows
     const unsigned pieces = vocab >= 65536 ? 8u : (vocab >= 16384 ? 4u : (vocab >= 4096 ? 2u : 1u));
     unsigned blocks = pieces;
-    while (blocks > 1 && blocks * (unsigned)n_rows > 148u) blocks >>= 1;
+    while (blocks > 1 && blocks * (unsigned)n_rows > (unsigned)blm_sm_count()) blocks >>= 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(blocks * (unsigned)n_rows);
     cfg.blockDim = dim3(kSampleThreads);

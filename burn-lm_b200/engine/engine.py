@@ -49,12 +49,15 @@ class Engine:
     """A model with its cache.  `acquire()` starts a sequence, `step()` feeds tokens, `release()` ends it."""
 
     def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None,
-                 max_seq_len: Optional[int] = None):
+                 max_seq_len: Optional[int] = None, max_step_tokens: Optional[int] = None):
+        """`max_tokens`: token places of the cache (rounded up to pages); `max_seqs`: slots; `max_seq_len`: the most
+        one sequence may hold; `max_step_tokens`: the most tokens one step may bring (its activations are
+        sized by it); None: as many as the cache holds."""
         self.model = model
         rt = model.runtime
         if rt.device.type != "cuda":
             raise RuntimeError("burn-lm_b200 runs on a CUDA device only; there is no CPU path")
-        page = 64
+        page = K.PAGE
         pages = (max_tokens + page - 1) // page
         if max_seqs is None:
             max_seqs = max(1, min(pages, 1024))
@@ -65,11 +68,14 @@ class Engine:
                            rt.dtype, rt.device)
         self.workspace = Workspace(rt.device)
         K.prebuild(rt.dtype)
-        model.prepare(self.cache.max_seq_len)
+        # tables of positions reach to the end of the last page, as the length buckets of captured steps do
+        model.prepare(-(-self.cache.max_seq_len // page) * page)
         self.vocab_size = model.plan.vocab_size
+        self.max_step_tokens = max_step_tokens if max_step_tokens is not None else pages * page
         self._staging = None    # pinned int32 staging for the step's metadata
         # decode steps (one token each, its logits wanted) replay a CUDA graph when every part allows it
-        self.use_graphs = all(getattr(p, "graph_safe", False) for p in model.parts())
+        self.use_graphs = (all(getattr(p, "graph_safe", False) for p in model.parts())
+                           and all(getattr(layer.block, "graph_safe", False) for layer in model.layers))
         self._staging_free = None
         self.decode_ahead = False           # decode_greedy(more=True) may enqueue the following step at once
         self._ahead = None                  # decode_graph.StepInFlight: a greedy step enqueued before it was asked for
@@ -79,8 +85,9 @@ class Engine:
         self._prefill_graphs = PrefillGraphs(self)
 
     @classmethod
-    def from_folder(cls, folder, dtype="bfloat16", max_tokens=4096, max_seqs=None, max_seq_len=None, device="cuda"):
-        return cls(load_model(folder, dtype, device), max_tokens, max_seqs, max_seq_len)
+    def from_folder(cls, folder, dtype="bfloat16", max_tokens=4096, max_seqs=None, max_seq_len=None, device="cuda",
+                    max_step_tokens=None):
+        return cls(load_model(folder, dtype, device), max_tokens, max_seqs, max_seq_len, max_step_tokens)
 
     # -- sequences -----------------------------------------------------------------------------------
     def acquire(self) -> int:
@@ -103,9 +110,9 @@ class Engine:
         that split a sequence's keys is fixed in a captured graph."""
         from .decode_graph import DecodeGraph
         pages = 1
-        while pages * 64 < max_kv_len:
+        while pages * K.PAGE < max_kv_len:
             pages *= 2
-        bucket = min(pages * 64, -(-self.cache.max_seq_len // 64) * 64)
+        bucket = min(pages * K.PAGE, -(-self.cache.max_seq_len // K.PAGE) * K.PAGE)
         graphs = self._decode_graphs
         g = graphs.pop((batch, bucket), None)
         if g is None:
@@ -159,16 +166,8 @@ class Engine:
                         cache.seq_len[s] = ahead.starts[place[s]] + 1
                     return [out[place[s]] for s in slots]
         if cur is None:
-            starts = []
-            grow = None
-            for s, t in zip(slots, tokens):
-                if not 0 <= t < self.vocab_size:
-                    raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
-                n = cache.seq_len[s]
-                starts.append(n)
-                if n % 64 == 0 or n >= cache.max_seq_len:       # a new page, or the limit: the careful path decides
-                    grow = True
-            if grow or len(set(slots)) != len(slots):
+            starts, grow = self._decode_starts(slots, tokens)
+            if grow:
                 cache.reserve([(s, n + 1) for s, n in zip(slots, starts)])
             g = self.decode_graph(len(slots), max(starts) + 1)
             if not more:
@@ -185,6 +184,25 @@ class Engine:
             nxt.tokens_in = out
             self._ahead = nxt
         return out
+
+    def _decode_starts(self, slots, tokens):
+        """The checks of a step for the short ways through a decode step: every slot held and named once, every
+        token in the vocabulary.  Returns the sequences' lengths and whether the cache has to make room (a
+        new page, or the limit: the careful path decides)."""
+        cache = self.cache
+        if len(set(slots)) != len(slots):
+            raise ValueError(f"a slot appears twice in one step: {sorted(slots)}")
+        starts, grow = [], False
+        for s, t in zip(slots, tokens):
+            if not cache.slots.held(s):
+                raise CacheError(f"slot {s} is not held")
+            if not 0 <= t < self.vocab_size:
+                raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
+            n = cache.seq_len[s]
+            starts.append(n)
+            if n % K.PAGE == 0 or n >= cache.max_seq_len:
+                grow = True
+        return starts, grow
 
     def _launch_ahead(self, cur):
         """The step after `cur` for the same sequences, enqueued behind it; None where that step needs a
@@ -208,16 +226,9 @@ class Engine:
             return None
         self._ahead = None
         cache = self.cache
-        starts = []
-        grow = None
-        for s, t in zip(slots, tokens):
-            if not 0 <= t < self.vocab_size:
-                raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
-            n = cache.seq_len[s]
-            starts.append(n)
-            if n % 64 == 0 or n >= cache.max_seq_len:
-                grow = True
-        if grow or len(set(slots)) != len(slots):
+        slots, tokens = list(slots), list(tokens)
+        starts, grow = self._decode_starts(slots, tokens)
+        if grow:
             cache.reserve([(s, n + 1) for s, n in zip(slots, starts)])
         g = self.decode_graph(len(slots), max(starts) + 1)
         out = g.step_sampled_host(tokens, starts, slots, params, stream_ids, counters)
@@ -260,6 +271,8 @@ class Engine:
             growth.append((e.slot, start + len(toks)))
             max_q = max(max_q, len(toks))
             max_kv = max(max_kv, start + len(toks))
+        if len(tokens) > self.max_step_tokens:
+            raise ValueError(f"the step brings {len(tokens)} tokens; this engine takes at most {self.max_step_tokens} in one step")
         return tokens, token_seq, token_pos, cu, slots, starts, want_rows, growth, max_q, max_kv
 
     def _upload(self, arrays):

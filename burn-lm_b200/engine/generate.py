@@ -18,10 +18,9 @@ from dataclasses import dataclass, field
 from typing import Callable, Optional, Sequence
 
 from ..cache.allocators import ContextLengthExceeded
+from ..kernels import PAGE
 from ..sampling.sampler import SamplingParams
 from .engine import StepEntry
-
-PAGE = 64
 
 
 @dataclass(frozen=True)
@@ -35,6 +34,7 @@ class GenerateOptions:
     seed: int = 0
     stop_ids: Sequence[int] = ()
     ignore_stop: bool = False        # keep going over stop ids (benchmarks)
+    include_stop: bool = False       # the stop id that ends a sequence is part of its output (the reference drops it)
     batch_size: Optional[int] = None  # most sequences decoded together; None: as many as fit
 
 
@@ -126,11 +126,11 @@ class GenerationLoop:
         for i, err in rejected.items():
             results[i].finish_reason, results[i].error = "error", err
         for batch in batches:
-            self._run_batch(batch, prompts, results, params, stop, options.sample_len, stats, on_token)
+            self._run_batch(batch, prompts, results, params, stop, options.sample_len, stats, on_token, options.include_stop)
             stats.batches += 1
         return GenerationOutput(results, stats)
 
-    def _run_batch(self, batch, prompts, results, params, stop, sample_len, stats, on_token):
+    def _run_batch(self, batch, prompts, results, params, stop, sample_len, stats, on_token, include_stop=False):
         engine = self.engine
         max_len = engine.cache.max_seq_len
         slots = {i: engine.acquire() for i in batch}
@@ -157,6 +157,10 @@ class GenerationLoop:
                     stats.generated_tokens += 1           # a stop id is counted, not emitted
                     if tok in stop:
                         r.finish_reason = "stop"
+                        if include_stop:
+                            r.tokens.append(tok)
+                            if on_token is not None:
+                                on_token(i, tok)
                     else:
                         r.tokens.append(tok)
                         if on_token is not None:

@@ -23,6 +23,20 @@ class KernelError(RuntimeError):
     pass
 
 
+_sm_counts: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """How many multiprocessors the device has (asked once per device)."""
+    index = torch.device(device).index if device is not None else None
+    if index is None:
+        index = torch.cuda.current_device()
+    n = _sm_counts.get(index)
+    if n is None:
+        n = _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return n
+
+
 def _code(dtype: torch.dtype) -> int:
     if dtype == torch.float32:
         return F32
@@ -259,7 +273,7 @@ def decode_advance(tokens, pos, sampled, history, step_no, counters=None):
 def attention_decode_is_specialised(dtype, head_dim, group) -> bool:
     """Whether a step of one token per sequence runs the specialised decode kernel (whose blocks
     split the keys by pages and skip splits a sequence does not need)."""
-    return dtype == torch.bfloat16 and head_dim in (64, 128) and group in (1, 2, 4, 8)
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and 1 <= group <= 8
 
 
 def attention_scratch_floats(n_tokens, n_heads, head_dim, n_splits):
@@ -276,7 +290,7 @@ def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos
     `window` of them when window > 0).  n_splits > 1 cuts every sequence's keys over that many
     blocks and combines the partial results; it needs `scratch` (float32,
     attention_scratch_floats(...) elements).  bfloat16 steps of one token per sequence with a head
-    size of 64 or 128 and 1, 2, 4 or 8 query heads per kv head run a specialised kernel unless
+    size of 64 or 128 and up to 8 query heads per kv head run a specialised kernel unless
     `general_only`; `max_kv_len` (the longest sequence after the step, when known) lets it size its
     rings of pages."""
     _need_cuda(q, pool, block_table, cu_seqlens, slot_of_seq, start_pos, out, scratch)

@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from .config.reader import read_config_json
-from .parts.base import Runtime
+from .parts.base import CacheNeed, Runtime
 from .plan import ModelPlan
 from .registry import architecture_of, part_class
 from .weights.loader import load_tensors
@@ -39,15 +39,27 @@ def _build(plan_part, family, runtime):
 
 
 class Layer:
+    """The parts a layer plan names, built from their families' registries, and the block that arranges them."""
+
     def __init__(self, lp, runtime):
-        self.mixer = _build(lp.mixer, "mixer", runtime)
-        self.feed_forward = _build(lp.feed_forward, "feed_forward", runtime)
-        self.block = part_class("block", lp.block)(
-            _build(lp.mixer_norm, "norm", runtime), self.mixer,
-            _build(lp.feed_forward_norm, "norm", runtime), self.feed_forward)
+        self.named = {p.name: (p.family, _build(p.plan, p.family, runtime)) for p in lp.parts}
+        if len(self.named) != len(lp.parts):
+            raise ValueError(f"a layer names a part twice: {[p.name for p in lp.parts]}")
+        self.block = part_class("block", lp.block)({name: part for name, (_, part) in self.named.items()})
 
     def parts(self):
-        return self.block.parts()
+        return [part for _, part in self.named.values()]
+
+    def cache_need(self):
+        """What a run of this layer keeps per sequence: what its block says, else what its one mixer says."""
+        if hasattr(self.block, "cache_need"):
+            return self.block.cache_need()
+        mixers = [part for family, part in self.named.values() if family == "mixer"]
+        if not mixers:
+            return CacheNeed("none")
+        if len(mixers) > 1:
+            raise ValueError("a block with several mixers must say itself what a run keeps (cache_need())")
+        return mixers[0].cache_need()
 
 
 class Model:
@@ -83,11 +95,26 @@ class Model:
     def bind(self, loaded: dict):
         for p in self.parts():
             p.bind(loaded)
+        # a run that reads another run's cache line must agree with its writer on how the entries lie there
+        for run, e in enumerate(self.plan.schedule):
+            if e.cache_of is not None:
+                reader, writer = self._mixer_of(e.layer), self._mixer_of(self.plan.schedule[e.cache_of].layer)
+                a = reader.key_layout() if hasattr(reader, "key_layout") else None
+                b = writer.key_layout() if hasattr(writer, "key_layout") else None
+                if a != b or reader.cache_need() != writer.cache_need():
+                    raise ValueError(f"run {run} of the schedule reads the cache line of run {e.cache_of}, whose mixer "
+                                     f"keeps its entries in another layout ({b} against {a}) or another size")
         self.bound = True
+
+    def _mixer_of(self, layer: int):
+        mixers = [part for family, part in self.layers[layer].named.values() if family == "mixer"]
+        if len(mixers) != 1:
+            raise ValueError(f"layer {layer} shares a cache line and must have exactly one mixer; it has {len(mixers)}")
+        return mixers[0]
 
     def cache_needs(self):
         """The cache need of every run of the schedule (None for a run that reads another's line)."""
-        return [None if e.cache_of is not None else self.layers[e.layer].mixer.cache_need()
+        return [None if e.cache_of is not None else self.layers[e.layer].cache_need()
                 for e in self.plan.schedule]
 
     # -- forward ---------------------------------------------------------------------------------
@@ -138,6 +165,25 @@ def load_model(folder: str, dtype="bfloat16", device="cuda") -> Model:
     _, typed, plan = plan_of(config)
     runtime = Runtime(parse_dtype(dtype), torch.device(device))
     model = Model(plan, runtime, typed)
-    loaded = load_tensors(folder, model.tensor_specs(), runtime.dtype, runtime.device, plan.ignorable_tensors)
+    loaded = load_tensors(folder, model.tensor_specs(), runtime.dtype, runtime.device, plan.ignorable_tensors,
+                          plan.duplicate_tensors)
+    model.bind(loaded)
+    return model
+
+
+def random_model(config: dict, seed: int = 0, dtype="bfloat16", device="cuda", stored_dtype="bfloat16") -> Model:
+    """The model `config` names with random weights drawn on the device, without a folder in between: for
+    shapes whose files would take minutes to write and read back.  The numbers are the ones
+    `write_random_model(..., device=<the same device>)` stores (every tensor from its own generator, seeded
+    by the seed and the tensor's name), kept as a folder stored in `stored_dtype` would be loaded."""
+    from .weights.loader import _target_dtype
+    from .weights.random_init import _DTYPES, random_tensor
+    _, typed, plan = plan_of(config)
+    runtime = Runtime(parse_dtype(dtype), torch.device(device))
+    model = Model(plan, runtime, typed)
+    loaded = {}
+    for spec in model.tensor_specs():
+        t = random_tensor(spec, seed, _DTYPES[stored_dtype], runtime.device)
+        loaded[spec.name] = t.to(_target_dtype(t.dtype, spec.kind, runtime.dtype))
     model.bind(loaded)
     return model

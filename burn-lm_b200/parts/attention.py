@@ -22,7 +22,7 @@ from ..weights.loader import TensorSpec
 from .base import CacheNeed, Part
 from .linear import Linear
 
-_TARGET_BLOCKS = 2 * 148  # blocks a decode step should offer the 148 SMs
+BLOCKS_PER_SM = 2     # blocks a decode step should offer every multiprocessor
 
 
 @dataclass(frozen=True)
@@ -49,6 +49,11 @@ class Attention(Part):
         if spec.head_dim % 16 or not 16 <= spec.head_dim <= 256:
             raise ValueError(f"head_dim {spec.head_dim}: the attention kernels take multiples of 16 from 16 to 256")
         self.position = part_class("position", spec.position.kind)(spec.position.spec, spec.position.tensors, runtime)
+        if getattr(self.position, "score_bias", None) is not None and self.position.score_bias() is not None:
+            # an encoding that adds a per-head bias to the scores (by the distance of key and query, say): the
+            # attention kernels of this package compute q.k * scale and the mask only
+            raise ValueError(f"position encoding {spec.position.kind!r} asks for a bias on the attention scores, which "
+                             f"the attention kernels do not have; it needs a mixer of its own")
         self.scale = spec.softmax_scale if spec.softmax_scale is not None else 1.0 / math.sqrt(spec.head_dim)
 
     def tensor_specs(self):
@@ -85,6 +90,11 @@ class Attention(Part):
         if hasattr(self.position, "prepare"):
             self.position.prepare(max_positions)
 
+    def key_layout(self):
+        """How this mixer's keys lie in the cache (known once the weights are bound): the order of a head's lanes
+        and the rotation they carry.  A run that reads another run's cache line must have the same."""
+        return (self.pairs, self.spec.position)
+
     def cache_need(self) -> CacheNeed:
         s = self.spec
         return CacheNeed("kv", n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window)
@@ -101,10 +111,11 @@ class Attention(Part):
             # (measured best at batch 1, 8 and 64 with 9 pages).  Longer sequences are cut into a ring's
             # worth per block, as far as that still helps to fill the SMs about twice.
             by_length = (pages + 15) // 16
-            to_fill = (2 * 148 + step.n_seqs * s.n_kv_heads - 1) // (step.n_seqs * s.n_kv_heads)
+            want = BLOCKS_PER_SM * K.sm_count(self.runtime.device)
+            to_fill = (want + step.n_seqs * s.n_kv_heads - 1) // (step.n_seqs * s.n_kv_heads)
             return max(1, min(by_length, to_fill, pages, 64))
         blocks = step.n_seqs * s.n_kv_heads * ((group + 31) // 32)
-        return max(1, min(pages, (_TARGET_BLOCKS + blocks - 1) // blocks, 64))
+        return max(1, min(pages, (BLOCKS_PER_SM * K.sm_count(self.runtime.device) + blocks - 1) // blocks, 64))
 
     takes_pending_norm = True
     adds_to_stream = True

@@ -20,13 +20,15 @@ def _add_norm(norm, resid, delta, lazy, handoff):
 @register_part("block", "prenorm")
 class PreNormBlock:
     family = "block"
+    graph_safe = True     # it only calls its parts: a step of graph-safe parts can be captured
 
-    def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward):
-        self.mixer_norm, self.mixer = mixer_norm, mixer
-        self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
+    NAMES = ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
 
-    def parts(self):
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+    def __init__(self, parts: dict):
+        if set(parts) != set(self.NAMES):
+            raise ValueError(f"the prenorm block arranges parts named {self.NAMES}; the layer has {sorted(parts)}")
+        self.mixer_norm, self.mixer = parts["mixer_norm"], parts["mixer"]
+        self.feed_forward_norm, self.feed_forward = parts["feed_forward_norm"], parts["feed_forward"]
 
     def first_norm(self):
         """The norm that reads the stream first in this block: the block before may prepare its input."""

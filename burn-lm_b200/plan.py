@@ -20,13 +20,39 @@ class PartPlan:
 
 
 @dataclass(frozen=True)
+class NamedPart:
+    """A part of a layer under the name its block arrangement knows it by; `family` is the part
+    registry it is built from ("mixer", "feed_forward", "norm", ...)."""
+    name: str
+    family: str
+    plan: PartPlan
+
+
+@dataclass(frozen=True)
 class LayerPlan:
-    """One layer: a block arrangement around a mixer and a feed-forward with their norms."""
-    block: str            # key in the "block" registry, e.g. "prenorm"
-    mixer_norm: PartPlan
-    mixer: PartPlan
-    feed_forward_norm: PartPlan
-    feed_forward: PartPlan
+    """One layer: a block arrangement (its key in the "block" registry) and the parts it arranges.
+    Which parts a layer has is data: a block with one shared norm, with norms behind its parts as well, or
+    without a feed-forward lists other names than the pre-norm block of the Llama decoder does."""
+    block: str
+    parts: tuple          # of NamedPart, in the order their tensors are listed
+
+    def part(self, name: str) -> PartPlan:
+        for p in self.parts:
+            if p.name == name:
+                return p.plan
+        raise KeyError(f"the layer has no part named {name!r}; it has {[p.name for p in self.parts]}")
+
+    def with_part(self, name: str, plan: PartPlan) -> "LayerPlan":
+        """This layer with the part `name` replaced."""
+        self.part(name)
+        return LayerPlan(self.block, tuple(NamedPart(p.name, p.family, plan) if p.name == name else p for p in self.parts))
+
+
+def prenorm_layer(mixer_norm: PartPlan, mixer: PartPlan, feed_forward_norm: PartPlan, feed_forward: PartPlan) -> LayerPlan:
+    """The layer of the "prenorm" block: a norm and a mixer, a norm and a feed-forward."""
+    return LayerPlan("prenorm", (NamedPart("mixer_norm", "norm", mixer_norm), NamedPart("mixer", "mixer", mixer),
+                                 NamedPart("feed_forward_norm", "norm", feed_forward_norm),
+                                 NamedPart("feed_forward", "feed_forward", feed_forward)))
 
 
 @dataclass(frozen=True)
@@ -51,6 +77,8 @@ class ModelPlan:
     max_positions: int
     stop_ids: tuple = ()
     ignorable_tensors: tuple = ()   # regular expressions of stored names that may be left unread
+    duplicate_tensors: tuple = ()   # (stored name, wanted name) pairs: a stored tensor that may be there as a second copy
+                                    # of a wanted one (a tied head written out); it must hold the same values
     stream_position: Optional[PartPlan] = None   # family "position": an encoding added to the stream after the embedding
 
     def __post_init__(self):

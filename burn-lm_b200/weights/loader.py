@@ -22,13 +22,15 @@ from .safetensors_io import SafetensorsError, SafetensorsFile
 
 
 class WeightsError(ValueError):
-    """Weights that do not fit the model; `missing`, `unexpected`, `wrong_shape` hold the lists."""
+    """Weights that do not fit the model; `missing`, `unexpected`, `wrong_shape` and `differing` (stored
+    second copies that do not equal the tensor they should repeat) hold the lists."""
 
-    def __init__(self, message, missing=(), unexpected=(), wrong_shape=()):
+    def __init__(self, message, missing=(), unexpected=(), wrong_shape=(), differing=()):
         super().__init__(message)
         self.missing = list(missing)
         self.unexpected = list(unexpected)
         self.wrong_shape = list(wrong_shape)
+        self.differing = list(differing)
 
 
 @dataclass(frozen=True)
@@ -61,8 +63,10 @@ def _target_dtype(stored: torch.dtype, kind: str, compute: torch.dtype) -> torch
     return compute  # float16 and others
 
 
-def load_tensors(folder: str, specs: list, compute_dtype: torch.dtype, device, ignorable=()) -> dict:
-    """Read the tensors `specs` name from `folder` onto `device`; see the module text for dtypes."""
+def load_tensors(folder: str, specs: list, compute_dtype: torch.dtype, device, ignorable=(), duplicates=()) -> dict:
+    """Read the tensors `specs` name from `folder` onto `device`; see the module text for dtypes.
+    `ignorable`: regular expressions of stored names that may be left unread.  `duplicates`: (stored name,
+    wanted name) pairs; such a stored tensor is expected when it repeats the wanted one bit for bit."""
     try:
         files = _open_folder(folder)
     except SafetensorsError as e:
@@ -80,7 +84,13 @@ def load_tensors(folder: str, specs: list, compute_dtype: torch.dtype, device, i
             wanted[s.name] = s
         missing = [n for n in wanted if n not in where]
         patterns = [re.compile(p) for p in ignorable]
-        unexpected = [n for n in where if n not in wanted and not any(p.fullmatch(n) for p in patterns)]
+        copies = {a: b for a, b in duplicates if a in where and a not in wanted and b in where}
+        unexpected = [n for n in where if n not in wanted and n not in copies and not any(p.fullmatch(n) for p in patterns)]
+        differing = []
+        for a, b in copies.items():
+            ta, tb = where[a].get(a), where[b].get(b)
+            if ta.shape != tb.shape or ta.dtype != tb.dtype or not torch.equal(ta, tb):
+                differing.append((a, b))
         wrong = []
         for n, s in wanted.items():
             if n in where:
@@ -89,7 +99,7 @@ def load_tensors(folder: str, specs: list, compute_dtype: torch.dtype, device, i
                     wrong.append((n, tuple(s.shape), tuple(f.shape(n))))
                 elif (s.kind == "int") == f.dtype(n).is_floating_point:
                     wrong.append((n, f"{s.kind} table", str(f.dtype(n))))
-        if missing or unexpected or wrong:
+        if missing or unexpected or wrong or differing:
             lines = [f"{folder}: the stored tensors do not fit the model"]
             if missing:
                 lines.append(f"  missing ({len(missing)}): " + ", ".join(sorted(missing)))
@@ -98,7 +108,10 @@ def load_tensors(folder: str, specs: list, compute_dtype: torch.dtype, device, i
             if wrong:
                 lines.append(f"  wrong shape ({len(wrong)}): " + "; ".join(
                     f"{n} expected {e} found {g}" for n, e, g in sorted(wrong, key=lambda w: w[0])))
-            raise WeightsError("\n".join(lines), missing, unexpected, wrong)
+            if differing:
+                lines.append(f"  differing ({len(differing)}): " + "; ".join(
+                    f"{a} is stored beside {b}, which the model uses for both, and does not equal it" for a, b in sorted(differing)))
+            raise WeightsError("\n".join(lines), missing, unexpected, wrong, differing)
         out = {}
         for n, s in wanted.items():
             f = where[n]

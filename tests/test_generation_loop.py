@@ -205,3 +205,25 @@ def test_prompt_step_buckets_hold_their_steps():
                     assert (w == 0) == (n_want == 0) and n_want <= w < max(2 * n_want, 1)
                     seen.add((t, s, q, w))
     assert len(seen) < 400
+
+
+def test_include_stop_emits_the_stop_id_and_still_ends_there():
+    """The reference counts the stop id and leaves it out of the answer (generation/context.rs:142-170); with
+    include_stop it is the answer's last token, streamed like the others."""
+    prompts = [[1, 2, 3], [4], [2, 2]]
+    streamed = []
+    eng = ScriptedEngine()
+    out = GenerationLoop(eng, ArgmaxSampler(), default_stop_ids=(13,)).generate(
+        prompts, GenerateOptions(sample_len=12, stop_ids=(29,), include_stop=True), on_token=lambda i, t: streamed.append((i, t)))
+    seen_stop = False
+    for i, (p, r) in enumerate(zip(prompts, out.results)):
+        toks, why = expected(p, 12, stop=(13, 29))
+        if why == "stop":
+            seen_stop = True
+            assert r.finish_reason == "stop" and r.tokens[:-1] == toks and r.tokens[-1] in (13, 29)
+        else:
+            assert r.tokens == toks
+        assert [t for j, t in streamed if j == i] == r.tokens
+    assert seen_stop
+    assert out.stats.generated_tokens == sum(len(r.tokens) for r in out.results)
+    assert eng.cache.slots.held_count == 0

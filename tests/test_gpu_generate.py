@@ -318,3 +318,61 @@ def test_decode_ahead_gives_the_same_tokens(tmp_path):
     plain, ahead = run(False), run(True)
     assert plain == ahead
     assert any(reason == "stop" for reason in plain[1][1])
+
+
+def test_the_short_ways_through_a_decode_step_check_their_slots(tmp_path):
+    """decode_greedy and decode_sampled refuse what step() refuses: a slot named twice, a slot that is not held
+    (its block-table row is stale and its pages may be someone else's by now), a token outside the vocabulary,
+    and a step of more tokens than the engine was built for; nothing is launched and nothing changes."""
+    from burn_lm_b200 import Engine, StepEntry
+    from burn_lm_b200.cache import CacheError
+    from burn_lm_b200.sampling import SamplingParams
+    folder = make_folder(tmp_path, "tiny_d", seed=31, dtype="bfloat16")
+    eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=1024, max_seqs=4)
+    a, b = eng.acquire(), eng.acquire()
+    eng.step([StepEntry(a, [1, 2, 3], [2]), StepEntry(b, [4, 5], [1])])
+    lengths = (eng.length(a), eng.length(b))
+    with pytest.raises(ValueError, match="twice"):
+        eng.decode_greedy([a, a], [1, 2])
+    with pytest.raises(CacheError, match="not held"):
+        eng.decode_greedy([a, 3], [1, 2])
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.decode_greedy([a, b], [1, 515])
+    params = SamplingParams(0.7, 0.9, 5)
+    with pytest.raises(ValueError, match="twice"):
+        eng.decode_sampled([b, b], [1, 2], params, [0, 1], [0, 0])
+    eng.release(b)
+    with pytest.raises(CacheError, match="not held"):
+        eng.decode_sampled([a, b], [1, 2], params, [0, 1], [0, 0])
+    assert (eng.length(a), eng.length(b)) == (lengths[0], 0)
+    assert len(eng.decode_greedy([a], [7])) == 1 and eng.length(a) == lengths[0] + 1
+    small = Engine.from_folder(folder, dtype="bfloat16", max_tokens=1024, max_seqs=2, max_step_tokens=100)
+    s = small.acquire()
+    with pytest.raises(ValueError, match="at most 100"):
+        small.step([StepEntry(s, [1] * 101, [])])
+    assert small.length(s) == 0
+    small.step([StepEntry(s, [1] * 100, [])])
+    assert small.length(s) == 100
+
+
+@pytest.mark.parametrize("max_seq_len", [1000, 200])
+def test_a_context_limit_that_is_no_multiple_of_a_page(tmp_path, max_seq_len):
+    """With a limit of 1,000 (or 200) tokens the longest length bucket of the captured decode steps ends beyond
+    the limit, at the end of the last page; generation runs up to the limit on the kernels it always uses
+    (the rotary table reaches as far as the bucket) and gives the plain implementation's tokens."""
+    import burn_lm_b200 as blm
+    folder = make_folder(tmp_path, "tiny_d", seed=33, dtype="float32")
+    cfg, tensors = P.read_model_folder(folder)
+    lm = blm.load(folder, dtype="float32", max_seq_len=max_seq_len, max_batch=2)
+    prompt = random_tokens(3, max_seq_len - 40, cfg["vocab_size"])
+    out = lm.generate([prompt], sample_len=100, ignore_stop=True)
+    r = out.results[0]
+    assert r.finish_reason == "context" and len(prompt) + len(r.tokens) == max_seq_len + 1
+    assert r.tokens[:12] == P.greedy_generate(cfg, tensors, prompt, 12)
+    lm16 = blm.load(folder, dtype="bfloat16", max_seq_len=max_seq_len, max_batch=2)
+    from burn_lm_b200.parts.attention import Attention
+    mixer = [p for p in lm16.engine.model.parts() if isinstance(p, Attention)][0]
+    assert mixer.position.table().shape[0] >= -(-max_seq_len // 64) * 64
+    r16 = lm16.generate([prompt], sample_len=100, ignore_stop=True).results[0]
+    assert r16.finish_reason == "context" and len(r16.tokens) == len(r.tokens)
+    lm16.engine.verify()

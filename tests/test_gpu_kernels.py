@@ -566,7 +566,7 @@ def test_gemv_refuses_what_it_cannot_do():
         k.gemv(w, 1, x=torch.zeros(1, 96, device="cuda", dtype=torch.bfloat16), out=torch.zeros(1, 16, device="cuda"))
 
 
-@pytest.mark.parametrize("H,KV,hd", [(32, 8, 64), (8, 8, 64), (16, 2, 128), (4, 2, 128)])
+@pytest.mark.parametrize("H,KV,hd", [(32, 8, 64), (8, 8, 64), (16, 2, 128), (4, 2, 128), (24, 8, 128), (12, 2, 64), (5, 1, 64), (7, 1, 128)])
 @pytest.mark.parametrize("n_splits", [1, 4, 11])
 def test_decode_attention_specialised_equals_general(H, KV, hd, n_splits):
     """The specialised decode kernel and the general kernel on the same cache, and both against the

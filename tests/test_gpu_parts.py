@@ -158,7 +158,7 @@ def register_toy():
     from burn_lm_b200 import register_architecture, register_part, Architecture, TensorSpec
     from burn_lm_b200.config import KeyReader
     from burn_lm_b200.parts import CacheNeed, Part, RMSNormSpec, SwiGLUSpec, AttentionSpec, NoPositionSpec, EmbeddingSpec, HeadSpec
-    from burn_lm_b200.plan import LayerPlan, ModelPlan, PartPlan, ScheduleEntry
+    from burn_lm_b200.plan import ModelPlan, PartPlan, ScheduleEntry, prenorm_layer
     from burn_lm_b200 import registry
 
     if "ToyDecayLM" in [a.name for a in registry.architectures()]:
@@ -218,7 +218,7 @@ def register_toy():
                 mixer = PartPlan("attention", AttentionSpec(cfg.width, cfg.heads, 1, cfg.width // cfg.heads,
                                                             PartPlan("none", NoPositionSpec())),
                                  {"q": p + "q", "k": p + "k", "v": p + "v", "o": p + "o"})
-            layers.append(LayerPlan("prenorm", PartPlan("rmsnorm", norm, {"weight": p + "n1"}), mixer,
+            layers.append(prenorm_layer(PartPlan("rmsnorm", norm, {"weight": p + "n1"}), mixer,
                                     PartPlan("rmsnorm", norm, {"weight": p + "n2"}),
                                     PartPlan("swiglu", SwiGLUSpec(cfg.width, cfg.inner),
                                              {"gate": p + "g", "up": p + "u", "down": p + "d"})))
@@ -324,7 +324,7 @@ def register_routed_toy():
     from burn_lm_b200 import register_architecture, register_part, Architecture, TensorSpec
     from burn_lm_b200.config import KeyReader
     from burn_lm_b200.parts import CacheNeed, Part, RMSNormSpec, AttentionSpec, NoPositionSpec, EmbeddingSpec, HeadSpec
-    from burn_lm_b200.plan import LayerPlan, ModelPlan, PartPlan, ScheduleEntry
+    from burn_lm_b200.plan import ModelPlan, PartPlan, ScheduleEntry, prenorm_layer
     from burn_lm_b200 import registry
 
     if "ToyRoutedLM" in [a.name for a in registry.architectures()]:
@@ -398,8 +398,8 @@ def register_routed_toy():
         layers = []
         for n in range(cfg.depth):
             p = f"r.{n}."
-            layers.append(LayerPlan(
-                "prenorm", PartPlan("rmsnorm", norm, {"weight": p + "n1"}),
+            layers.append(prenorm_layer(
+                PartPlan("rmsnorm", norm, {"weight": p + "n1"}),
                 PartPlan("attention", AttentionSpec(cfg.width, cfg.heads, cfg.heads, cfg.width // cfg.heads, PartPlan("none", NoPositionSpec())),
                          {"q": p + "q", "k": p + "k", "v": p + "v", "o": p + "o"}),
                 PartPlan("rmsnorm", norm, {"weight": p + "n2"}),
@@ -492,8 +492,8 @@ def register_windowed_toy():
         layers = []
         for n, layer in enumerate(base.layers):
             if n % 2 == 1:
-                spec = dataclasses.replace(layer.mixer.spec, window=WINDOW)
-                layer = dataclasses.replace(layer, mixer=dataclasses.replace(layer.mixer, spec=spec))
+                mixer = layer.part("mixer")
+                layer = layer.with_part("mixer", dataclasses.replace(mixer, spec=dataclasses.replace(mixer.spec, window=WINDOW)))
             layers.append(layer)
         return dataclasses.replace(base, architecture="ToyWindowedLM", layers=tuple(layers))
 
@@ -543,6 +543,107 @@ def test_layers_with_and_without_a_window_in_one_model(tmp_path, dtype, toleranc
         eng = Engine.from_folder(folder, dtype=dtype, max_tokens=traces.max_live_tokens(steps), max_seqs=3)
         tables = {eng.cache.view(r).block_table.data_ptr() for r in range(4)}
         assert len(tables) == 2 and eng.cache.view(1).window == WINDOW and not eng.cache.view(0).window
+        got = traces.run_in_process(eng, steps, str(tmp_path / what), 300)
+        for rid in reqs:
+            err = row_error(got[rid], want[rid])
+            assert err.max() < tolerance, (what, rid, float(err.max()), int(err.argmax()))
+        eng.verify()
+
+
+# --------------------------------------------------------------------------------------------------
+# a fourth toy: another arrangement of a layer's parts.  One norm feeds the mixer and the feed-forward
+# side by side, h = x + mixer(norm(x)) + feed_forward(norm(x)); every third layer has no feed-forward at
+# all.  The block is written and registered here; the layer plans name other parts than the Llama
+# decoder's pre-norm block does.
+# --------------------------------------------------------------------------------------------------
+def register_parallel_toy():
+    from burn_lm_b200 import register_architecture, register_part, Architecture
+    from burn_lm_b200.config.llama import LlamaConfig
+    from burn_lm_b200.architectures.llama import llama_plan
+    from burn_lm_b200.plan import LayerPlan, NamedPart
+    from burn_lm_b200 import registry, kernels as K
+
+    if "ToyParallelLM" in [a.name for a in registry.architectures()]:
+        return
+
+    @register_part("block", "toy_parallel")
+    class ParallelBlock:
+        family = "block"
+        graph_safe = True
+
+        def __init__(self, parts):
+            assert set(parts) <= {"norm", "mixer", "feed_forward"} and {"norm", "mixer"} <= set(parts)
+            self.norm, self.mixer, self.feed_forward = parts["norm"], parts["mixer"], parts.get("feed_forward")
+
+        def forward(self, resid, delta, step, cache_view):
+            x = self.norm.add_norm(resid, delta)              # adds the block before into the stream, then normalises
+            a = self.mixer.forward(x, step, cache_view)
+            if self.feed_forward is None:
+                return a
+            f = self.feed_forward.forward(x, step)
+            if a.dtype == torch.float32:
+                return a + f
+            both = torch.empty_like(a, dtype=torch.float32)   # the two branches are summed in 32-bit
+            K.convert(a, both)
+            f32 = torch.empty_like(both)
+            K.convert(f, f32)
+            out = torch.empty_like(a)
+            K.convert(both + f32, out)
+            return out
+
+    def plan(cfg):
+        base = llama_plan(cfg)
+        layers = []
+        for n, layer in enumerate(base.layers):
+            parts = [NamedPart("norm", "norm", layer.part("mixer_norm")), NamedPart("mixer", "mixer", layer.part("mixer"))]
+            if n % 3 != 2:
+                parts.append(NamedPart("feed_forward", "feed_forward", layer.part("feed_forward")))
+            layers.append(LayerPlan("toy_parallel", tuple(parts)))
+        return dataclasses.replace(base, architecture="ToyParallelLM", layers=tuple(layers),
+                                   ignorable_tensors=base.ignorable_tensors)
+
+    register_architecture(Architecture(name="ToyParallelLM", config_class=LlamaConfig, plan=plan,
+                                       description="test only: one norm, mixer and feed-forward side by side"))
+
+
+def parallel_plain(cfg, tensors, tokens):
+    cfg = P.complete_config(cfg)
+    inv_freq = P.model_inverse_frequencies(cfg)
+    h = P.embedding(tensors["model.embed_tokens.weight"], tokens)
+    for n in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{n}."
+        x = P.rms_norm(h, tensors[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        a = P.attention(x, tensors[p + "self_attn.q_proj.weight"], tensors[p + "self_attn.k_proj.weight"],
+                        tensors[p + "self_attn.v_proj.weight"], tensors[p + "self_attn.o_proj.weight"],
+                        cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], inv_freq, "half")
+        h = h + a
+        if n % 3 != 2:
+            h = h + P.feed_forward(x, tensors[p + "mlp.gate_proj.weight"], tensors[p + "mlp.up_proj.weight"], tensors[p + "mlp.down_proj.weight"])
+    return P.rms_norm(h, tensors["model.norm.weight"], cfg["rms_norm_eps"]) @ tensors["model.embed_tokens.weight"].T
+
+
+@pytest.mark.parametrize("dtype,tolerance", [("float32", 1e-4), ("bfloat16", 3e-2)])
+def test_a_block_of_another_shape_is_a_plan_entry(tmp_path, dtype, tolerance):
+    """A block with one shared norm, and layers without a feed-forward, registered from here: the model
+    lists only the tensors those parts need, builds, and replays like any other."""
+    import traces
+    from burn_lm_b200 import Engine, write_random_model
+    from burn_lm_b200.model import tensor_specs_of
+    from tiny import random_tokens, row_error
+    register_parallel_toy()
+    cfg = {"architectures": ["ToyParallelLM"], "model_type": "toy", "num_hidden_layers": 3, "hidden_size": 128,
+           "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 192, "vocab_size": 300,
+           "rope_theta": 10000.0, "rope_scaling": None, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+           "max_position_embeddings": 512, "hidden_act": "silu"}
+    names = {s.name for s in tensor_specs_of(cfg)}
+    assert "model.layers.0.post_attention_layernorm.weight" not in names and "model.layers.2.mlp.down_proj.weight" not in names
+    assert "model.layers.1.mlp.down_proj.weight" in names
+    folder = write_random_model(str(tmp_path / "parallel"), cfg, seed=5, dtype="bfloat16")
+    _, tensors = P.read_model_folder(folder)
+    reqs = {"a": random_tokens(1, 150, 300), "b": random_tokens(2, 20, 300), "c": random_tokens(3, 70, 300)}
+    want = {rid: parallel_plain(cfg, tensors, toks) for rid, toks in reqs.items()}
+    for what, steps in (("whole", traces.whole(reqs)), ("tail", traces.tail(reqs, 32)), ("batched", traces.batched(reqs, 3, [5, 32, 9]))):
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=traces.max_live_tokens(steps), max_seqs=3)
         got = traces.run_in_process(eng, steps, str(tmp_path / what), 300)
         for rid in reqs:
             err = row_error(got[rid], want[rid])

@@ -119,3 +119,54 @@ def test_random_mode_is_seeded_and_order_free(tmp_path):
     assert "lm_head.weight" not in ft.names() and ft.dtype("model.norm.weight") == torch.float32
     for f in (fa, fb, fc, ft):
         f.close()
+
+
+def _stored(folder):
+    f = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    tensors = {n: f.get(n).clone() for n in f.names()}
+    f.close()
+    return tensors
+
+
+def test_a_tied_model_may_store_its_head_when_it_equals_the_table(tmp_path):
+    from burn_lm_b200.model import plan_of
+    folder = write_random_model(str(tmp_path / "m"), TINY_A, seed=2, dtype="float32")
+    _, _, plan = plan_of(TINY_A)
+    assert plan.duplicate_tensors == (("lm_head.weight", "model.embed_tokens.weight"),)
+    tensors = _stored(folder)
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+    got = load_tensors(folder, tensor_specs_of(TINY_A), torch.float32, "cpu", plan.ignorable_tensors, plan.duplicate_tensors)
+    assert "lm_head.weight" not in got and "model.embed_tokens.weight" in got
+    tensors["lm_head.weight"][3, 5] += 1.0
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+    with pytest.raises(WeightsError, match="differing") as e:
+        load_tensors(folder, tensor_specs_of(TINY_A), torch.float32, "cpu", plan.ignorable_tensors, plan.duplicate_tensors)
+    assert e.value.differing == [("lm_head.weight", "model.embed_tokens.weight")] and not e.value.unexpected
+    # an untied model names no such pair: there the head is simply a wanted tensor
+    assert plan_of(TINY_B)[2].duplicate_tensors == ()
+
+
+def test_a_folder_of_shards_with_an_index(tmp_path):
+    """model.safetensors.index.json with two files loads as the single file does; a tensor the index's files
+    do not hold is reported as missing."""
+    folder = write_random_model(str(tmp_path / "m"), TINY_B, seed=3, dtype="bfloat16")
+    specs = tensor_specs_of(TINY_B)
+    whole = load_tensors(folder, specs, torch.bfloat16, "cpu")
+    tensors = _stored(folder)
+    names = sorted(tensors)
+    parts = {"model-00001-of-00002.safetensors": names[: len(names) // 2], "model-00002-of-00002.safetensors": names[len(names) // 2:]}
+    sharded = str(tmp_path / "s")
+    os.makedirs(sharded)
+    for fname, ns in parts.items():
+        write_safetensors(os.path.join(sharded, fname), {n: tensors[n] for n in ns})
+    index = {"metadata": {}, "weight_map": {n: fname for fname, ns in parts.items() for n in ns}}
+    json.dump(index, open(os.path.join(sharded, "model.safetensors.index.json"), "w"))
+    json.dump(TINY_B, open(os.path.join(sharded, "config.json"), "w"))
+    got = load_tensors(sharded, specs, torch.bfloat16, "cpu")
+    assert sorted(got) == sorted(whole) and all(torch.equal(got[n], whole[n]) for n in whole)
+    first = parts["model-00001-of-00002.safetensors"]
+    write_safetensors(os.path.join(sharded, "model-00001-of-00002.safetensors"), {n: tensors[n] for n in first[1:]})
+    with pytest.raises(WeightsError) as e:
+        load_tensors(sharded, specs, torch.bfloat16, "cpu")
+    assert e.value.missing == [first[0]]

@@ -4,23 +4,11 @@ import os
 
 import numpy as np
 
-TINY_A = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
-    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
-    "head_dim": 16, "intermediate_size": 160, "vocab_size": 256, "rope_theta": 10000.0,
-    "rope_scaling": None, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
-    "max_position_embeddings": 128, "hidden_act": "silu",
-}
+from burn_lm_b200.config import preset
 
-TINY_B = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
-    "num_hidden_layers": 3, "hidden_size": 192, "num_attention_heads": 6, "num_key_value_heads": 1,
-    "head_dim": 32, "intermediate_size": 512, "vocab_size": 384, "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
-                     "original_max_position_embeddings": 64},
-    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 256,
-    "hidden_act": "silu", "eos_token_id": [7, 11],
-}
+# the two that differ in every size and option; they are the package's presets of the same names
+TINY_A = preset("tiny_a")
+TINY_B = preset("tiny_b")
 
 # head_dim 48 (not a power of two), 5 query heads on 5 kv heads, a width that is no multiple of 64,
 # room for long decoding
