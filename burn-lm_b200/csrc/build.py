@@ -35,6 +35,7 @@ MODULES = {
     "gemm": ["gemm_f32.cu"],
     "gemv": ["gemv.cu"],
     "gemm_tc": ["gemm_tc.cu"],
+    "gemm_sk": ["gemm_sk.cu"],
     "sampling": ["sampling.cu"],
     "runtime": ["runtime.cu"],
 }

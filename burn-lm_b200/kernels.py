@@ -105,6 +105,12 @@ _protos = {
                         c_void_p, c_void_p],
         "blm_gemm_tc_supported": [c_int, c_int, c_int],
     },
+    "gemm_sk": {
+        "blm_gemm_sk": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int,
+                        c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "blm_gemm_sk_supported": [c_int, c_int, c_int],
+        "blm_gemm_sk_squares_row": [],
+    },
     "sampling": {
         "blm_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "blm_argmax_scratch_floats": [c_int, c_int],
@@ -358,6 +364,72 @@ def gemm_tc(x, w, out, swiglu=False):
           1 if swiglu else 0, _ptr(status_word(x.device)), _stream())
 
 
+SK_SQUARES_ROWS = 64     # row length of the sums of squares that go with a norm handed over between gemm_sk products
+SK_TOKENS = 128          # gemm_sk takes up to this many tokens
+
+
+def gemm_sk_supported(n_tokens, m, k) -> bool:
+    return bool(_lib("gemm_sk").blm_gemm_sk_supported(n_tokens, m, k))
+
+
+def gemm_sk(w, x, out=None, add_into=None, swiglu=False, squares=None, eps=0.0, hand_over=None, rope=None):
+    """x [N, K] times w [M, K] transposed for up to 128 tokens on the tcgen05 tensor cores, the weight rows as the
+    wide operand, K cut over the blocks of a cluster where the weight has few rows; bfloat16 operands, fp32 sums.
+
+    Ends, one at a time: `out` [N, M] bfloat16 or float32; `swiglu`: w is [2 I, K] in tiles of GATE_TILE gate rows
+    followed by their up rows and out [N, I] = silu(gate) * up; `add_into` (fp32 [N, M]) += the product, with
+    `hand_over` = (gamma, scaled bfloat16 [N, M], squares float32 [ceil(M / 16), SK_SQUARES_ROWS]) also the next
+    norm's input; `rope` (as for gemv): w is a step's [q; k; v] with q and k rows in tiled_pair_order(), q goes
+    to `out`, the rotated k and the v to the cache.  `squares` (+ `eps`): x is a handed-over norm,
+    bfloat16(stream * gamma), and the results' rows are divided by the stream rows' root mean square."""
+    _need_cuda(w, x, out, add_into, squares)
+    if w.dtype != torch.bfloat16 or x.dtype != torch.bfloat16 or x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise KernelError("gemm_sk: bfloat16 x [N, K] and w [M, K]")
+    n, k = x.shape
+    m_rows = w.shape[0]
+    m = m_rows // 2 if swiglu else m_rows
+    epi = EPI_SWIGLU if swiglu else (EPI_RESID_ADD if add_into is not None else (EPI_ROPE if rope is not None else EPI_STORE))
+    if sum(v is not None and v is not False for v in (add_into, rope, swiglu or None)) > 1:
+        raise KernelError("gemm_sk: one epilogue at a time")
+    rope_arg = None
+    if rope is not None:
+        r = rope
+        hd, table, pool = r["head_dim"], r["table"], r["pool"]
+        _need_cuda(r["token_pos"], r["token_seq"], r["slot_of_seq"], r["block_table"], table, pool)
+        if table is None or table.dtype != torch.float32 or tuple(table.shape[1:]) != (hd // 2, 2) \
+                or r.get("max_position") is None or r["max_position"] >= table.shape[0]:
+            raise KernelError("gemm_sk: the rotary epilogue needs a table [positions, head_dim / 2, 2] that covers the step")
+        if r["write_cache"] and (pool.dtype != torch.bfloat16 or tuple(pool.shape[1:]) != (2, r["n_kv"], PAGE, hd)):
+            raise KernelError(f"gemm_sk: pool must be bfloat16 [pages, 2, {r['n_kv']}, {PAGE}, {hd}]")
+        if out is None or out.dtype != torch.bfloat16 or tuple(out.shape) != (n, r["n_heads"] * hd):
+            raise KernelError("gemm_sk: the rotary epilogue writes q to a bfloat16 out [N, n_heads * head_dim]")
+        rope_arg = _GemvRope(r["token_pos"].data_ptr(), r["token_seq"].data_ptr(), r["slot_of_seq"].data_ptr(),
+                             r["block_table"].data_ptr(), table.data_ptr(), pool.data_ptr() if pool is not None else 0,
+                             r["block_table"].shape[1], r["n_heads"], r["n_kv"], hd, PAGE, 1 if r["write_cache"] else 0)
+    if squares is not None and (squares.dtype != torch.float32 or squares.dim() != 2 or squares.shape[1] != SK_SQUARES_ROWS
+                                or n > SK_SQUARES_ROWS):
+        raise KernelError(f"gemm_sk: squares are float32 [parts, {SK_SQUARES_ROWS}] for up to {SK_SQUARES_ROWS} tokens")
+    next_gamma = scaled = squares_out = None
+    if hand_over is not None:
+        next_gamma, scaled, squares_out = hand_over
+        _need_cuda(next_gamma, scaled, squares_out)
+        if (epi != EPI_RESID_ADD or scaled.dtype != torch.bfloat16 or tuple(scaled.shape) != (n, m) or squares_out.dtype != torch.float32
+                or tuple(squares_out.shape) != ((m + 15) // 16, SK_SQUARES_ROWS) or next_gamma.numel() != m or n > SK_SQUARES_ROWS):
+            raise KernelError(f"gemm_sk: hand_over = (gamma [M], scaled bfloat16 [N, M], squares float32 [ceil(M / 16), {SK_SQUARES_ROWS}]) "
+                              "with add_into")
+    if epi == EPI_RESID_ADD:
+        if add_into.dtype != torch.float32 or tuple(add_into.shape) != (n, m):
+            raise KernelError("gemm_sk: add_into must be float32 [N, M]")
+    elif epi != EPI_ROPE and (out is None or tuple(out.shape) != (n, m) or out.dtype not in (torch.bfloat16, torch.float32)
+                              or (swiglu and out.dtype != torch.bfloat16)):
+        raise KernelError("gemm_sk: out must be [N, M] bfloat16 (or float32 for a plain store)")
+    _call("gemm_sk", "blm_gemm_sk", _ptr(w), w.stride(0), m_rows, k, _ptr(x), x.stride(0), n, _ptr(out),
+          out.stride(0) if out is not None else 0, 1 if (out is not None and out.dtype == torch.float32) else 0, _ptr(add_into), epi,
+          _ptr(squares), squares.shape[0] if squares is not None else 0, c_float(eps), _ptr(next_gamma),
+          1 if (next_gamma is not None and next_gamma.dtype == torch.float32) else 0, _ptr(scaled), _ptr(squares_out),
+          ctypes.byref(rope_arg) if rope_arg is not None else None, _ptr(status_word(w.device)), _stream())
+
+
 def graph_step(graph_exec: int, dev_in, host_in, host_out, dev_out, dev_in2=None, host_in2=None) -> None:
     """One captured step driven from native code: host_in (pinned) -> dev_in (and host_in2 -> dev_in2), the
     instantiated graph `graph_exec` (a cudaGraphExec_t as an integer), dev_out -> host_out (pinned), and the
@@ -394,7 +466,9 @@ def check_status(device) -> None:
                 35: "prompt attention: the probabilities were not written", 36: "prompt attention: the product with the values did not arrive",
                 37: "prompt attention: the producer waited in vain for a free stage",
                 11: "gemm_tc: the tensor-core thread waited in vain for a stage", 12: "gemm_tc: the producer waited in vain for a free stage",
-                13: "gemm_tc: the epilogue waited in vain for the accumulator"}
+                13: "gemm_tc: the epilogue waited in vain for the accumulator",
+                41: "gemm_sk: the tensor-core thread waited in vain for a stage", 42: "gemm_sk: the producer waited in vain for a free stage",
+                43: "gemm_sk: the epilogue waited in vain for the accumulator"}
         raise KernelError(f"{what.get(code, 'status ' + str(code))}; the step's results are not valid")
 
 
