@@ -70,6 +70,7 @@ struct SkArgs {
     __nv_bfloat16* xg_out;
     float* ssq_out;
     SkRope rope;
+    int vec;                     // 1: rows of the outputs are 16-byte aligned, eight results leave as one store
     int* status;
 };
 
@@ -144,11 +145,19 @@ __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 // a float of block `rank`'s shared memory, at the place `local` has in this block's
-__device__ __forceinline__ float ld_peer(const float* local, unsigned rank) {
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    const __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
+    return make_uint4(*reinterpret_cast<const unsigned*>(&a), *reinterpret_cast<const unsigned*>(&b),
+                      *reinterpret_cast<const unsigned*>(&c), *reinterpret_cast<const unsigned*>(&d));
+}
+// four floats of block `rank`'s shared memory, at the place `local` has in this block's (read after the cluster's
+// barrier, which orders it; no memory clobber, so that several of these loads are in flight together)
+__device__ __forceinline__ float4 ld_peer4(const float* local, unsigned rank) {
     unsigned remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote));
     return v;
 }
 
@@ -162,8 +171,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_sk_kernel(const SkArgs a, co
     constexpr int kTmemCols = NP < 32 ? 32 : NP;
     constexpr unsigned kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(NP >> 3) << 17) | ((unsigned)(TM >> 4) << 24);
     unsigned char* ring = smem;                                                  // [n_stages][W tile | x tile]
-    float* part = reinterpret_cast<float*>(ring + (size_t)n_stages * kStage);    // [NP][TM]: this block's sums over its slice of K
-    float* row_scale = part + NP * TM;                                           // [NP] 1 / rms of a handed-over norm's rows
+    // [NP][TM]: this block's sums over its slice of K, token by token.  It lies over the ring: it is written when the
+    // accumulator is complete, and by then the tensor core has read every stage and no copy is in flight.
+    float* part = reinterpret_cast<float*>(ring);
+    const size_t ring_bytes = max((size_t)n_stages * kStage, (size_t)NP * TM * 4);
+    float* row_scale = reinterpret_cast<float*>(ring + ring_bytes);                                         // [NP] 1 / rms of a handed-over norm's rows
     long long* rope_where = reinterpret_cast<long long*>(row_scale + NP);        // [NP] where a token's k row of kv head 0 starts in the pool
     int* rope_pos = reinterpret_cast<int*>(rope_where + NP);                     // [NP]
     unsigned long long* full = reinterpret_cast<unsigned long long*>(rope_pos + NP);
@@ -178,8 +190,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_sk_kernel(const SkArgs a, co
     const int k_iters = (a.K + BK - 1) / BK, k_per = (k_iters + S - 1) / S;
     const int k_lo = rank * k_per;
     const int my_iters = max(0, min(k_iters, k_lo + k_per) - k_lo);
+    // The blocks that run together start at different places of their K range: requests that go out at the same
+    // moment then differ in the address bits that pick the memory channel (rows of W lie a multiple of K apart).
+    // A tile's order of summation depends on the tile only, never on the tokens.
+    const int skew = my_iters > 0 ? (tile * 5 + rank * 3) % my_iters : 0;
+    auto k_of = [&](int it) { const int j = it + skew; return k_lo + (j >= my_iters ? j - my_iters : j); };
 
     if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&wmap) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&xmap) : "memory");
         for (int s = 0; s < n_stages; ++s) {
             mbar_init(full + s, 1);
             mbar_init(empty + s, 1);
@@ -196,6 +215,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_sk_kernel(const SkArgs a, co
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = *tmem_slot;
     pdl_launch_dependents();
+    blm_trace(0x500);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -203,10 +223,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_sk_kernel(const SkArgs a, co
             const int pre = min(n_stages, my_iters);
             for (int i = 0; i < pre; ++i) {           // weights are nobody's output: they go out at once
                 mbar_expect_tx(full + i, kStage);
-                tma_load_2d(ring + (size_t)i * kStage, &wmap, (k_lo + i) * BK, m0, full + i);
+                tma_load_2d(ring + (size_t)i * kStage, &wmap, k_of(i) * BK, m0, full + i);
             }
             pdl_wait();                               // the tokens are the work of the kernel before
-            for (int i = 0; i < pre; ++i) tma_load_2d(ring + (size_t)i * kStage + kWBytes, &xmap, (k_lo + i) * BK, 0, full + i);
+            blm_trace_here(0x510);
+            for (int i = 0; i < pre; ++i) tma_load_2d(ring + (size_t)i * kStage + kWBytes, &xmap, k_of(i) * BK, 0, full + i);
             for (int it = pre; it < my_iters; ++it) {
                 const int s = it % n_stages;
                 if (!mbar_wait(empty + s, ((it / n_stages) - 1) & 1)) {
@@ -214,8 +235,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_sk_kernel(const SkArgs a, co
                     break;
                 }
                 mbar_expect_tx(full + s, kStage);
-                tma_load_2d(ring + (size_t)s * kStage, &wmap, (k_lo + it) * BK, m0, full + s);
-                tma_load_2d(ring + (size_t)s * kStage + kWBytes, &xmap, (k_lo + it) * BK, 0, full + s);
+                tma_load_2d(ring + (size_t)s * kStage, &wmap, k_of(it) * BK, m0, full + s);
+                tma_load_2d(ring + (size_t)s * kStage + kWBytes, &xmap, k_of(it) * BK, 0, full + s);
             }
         }
     } else if (warp == 1) {
@@ -230,26 +251,60 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_sk_kernel(const SkArgs a, co
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                if (it == 0) blm_trace_here(0x520);
                 const unsigned long long ad = umma_desc(ring + (size_t)s * kStage), bd = umma_desc(ring + (size_t)s * kStage + kWBytes);
 #pragma unroll
                 for (int kk = 0; kk < BK / 16; ++kk) umma(tmem_base, ad + 2 * kk, bd + 2 * kk, kIdesc, (it > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(empty + s);
             }
             if (ok && my_iters > 0) umma_commit(acc_full);
+            blm_trace_here(0x530);
         }
     } else {
         // ---------------- epilogue, first half: this block's sums to its shared memory ----------------
         const int e = (int)threadIdx.x - 64;          // 0 .. 127
         const int quarter = warp & 3;                 // the 32 lanes of tensor memory this warp may read
         pdl_wait();
-        if (e < NP) {
-            float sc = 1.0f;
-            if (a.ssq_in != nullptr && e < a.N) {
-                float ssq = 0.f;
-                for (int p = 0; p < a.ssq_parts; ++p) ssq += a.ssq_in[(size_t)p * kSquaresRow + e];      // one fixed order
-                sc = 1.0f / sqrtf(ssq / (float)a.K + a.eps);
+        if (NP <= kSquaresRow && a.ssq_in != nullptr) {
+            // A handed-over norm: warp w sums the parts for its quarter of the tokens.  The lanes go over the parts
+            // (lane, lane + 32, ...), each reading its tokens 16 bytes at a time, four parts in flight together (one
+            // round trip for up to 128 parts); then the butterfly over the lanes: one fixed order.
+            constexpr int TQ = NP / 4;                // tokens of a warp
+            constexpr int V4 = TQ / 4;                // 16-byte loads per part
+            const int t0 = (warp - 2) * TQ;
+            float ssq[TQ];
+#pragma unroll
+            for (int u = 0; u < TQ; ++u) ssq[u] = 0.f;
+            if (t0 < kSquaresRow) {
+                for (int p0 = lane; p0 < a.ssq_parts; p0 += 128) {
+                    float4 got[4][V4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int x = 0; x < V4; ++x)
+                            got[q][x] = (p0 + 32 * q < a.ssq_parts && t0 + 4 * x < kSquaresRow)
+                                            ? *reinterpret_cast<const float4*>(a.ssq_in + (size_t)(p0 + 32 * q) * kSquaresRow + t0 + 4 * x)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int x = 0; x < V4; ++x) {      // what lies beyond the step's tokens was never written: it is not added
+                            if (t0 + 4 * x + 0 < a.N) ssq[4 * x + 0] += got[q][x].x;
+                            if (t0 + 4 * x + 1 < a.N) ssq[4 * x + 1] += got[q][x].y;
+                            if (t0 + 4 * x + 2 < a.N) ssq[4 * x + 2] += got[q][x].z;
+                            if (t0 + 4 * x + 3 < a.N) ssq[4 * x + 3] += got[q][x].w;
+                        }
+                }
             }
-            row_scale[e] = sc;
+#pragma unroll
+            for (int u = 0; u < TQ; ++u) {
+                const float total = warp_sum(ssq[u]);
+                if (lane == 0) row_scale[t0 + u] = (t0 + u < a.N) ? 1.0f / sqrtf(total / (float)a.K + a.eps) : 1.0f;
+            }
+        } else if (e < NP) {
+            row_scale[e] = 1.0f;
+        }
+        if (e < NP) {
             if (a.epi == EPI_ROPE && e < a.N) {
                 const SkRope& r = a.rope;
                 const int pos = r.token_pos[e];
@@ -272,6 +327,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_sk_kernel(const SkArgs a, co
             have = false;
         }
         have = __all_sync(0xffffffffu, have);         // tcgen05.ld is a warp's instruction: all lanes or none
+        if (e == 0) blm_trace_here(0x540);
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16);
 #pragma unroll 1
@@ -289,74 +345,141 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_sk_kernel(const SkArgs a, co
         asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     }
     __syncthreads();
+    blm_trace(0x550);
     cluster_sync();          // every block's sums are in its shared memory
+    blm_trace(0x560);
 
     if (warp >= 2) {
         // ---------------- epilogue, second half: this block's share of the tile's rows, summed over the cluster ----------------
+        // A unit of work is (eight consecutive rows, one token): the sums of the S blocks are read 16 bytes at a time
+        // and added in the order of the ranks; the eight results leave as one 16-byte store.  Neighbouring lanes
+        // hold the two halves of a tile of 16 rows (gates | ups, or the two halves of eight rotary pairs).
         const int e = (int)threadIdx.x - 64;
-        const int R = TM / S;                         // rows per block: 128, 64, 32 or 16 (16 lanes are always 16 rows of one tile of 16)
-        const int mr = rank * R + e % R;              // row of the tile
-        const int m = m0 + mr;
-        const bool m_ok = m < a.M;
-        const int half16 = lane & 8;                  // 0: rows 0..7 of a tile of 16; 8: rows 8..15
-        for (int t = e / R; t < NP; t += S) {
-            float v = 0.f;
-            for (int c = 0; c < S; ++c) v += ld_peer(part + t * TM + mr, (unsigned)c);      // in the order of the ranks
-            v *= row_scale[t];
-            const bool ok = m_ok && t < a.N;
+        const int R = TM / S, G8 = R / 8;             // rows per block, groups of eight rows per block
+        const int items = G8 * NP;
+        const bool vec = a.vec != 0;
+        for (int it = e; it < items; it += 128) {     // a warp's lanes are all inside or all outside
+            const int t = it / G8, mr0 = rank * R + 8 * (it % G8);
+            const int m = m0 + mr0;
+            const bool odd = (it & 1) != 0;           // rows 8..15 of a tile of 16
+            const float* mine = part + t * TM + mr0;
+            float v[8];
+            {
+                float4 lo[8], hi[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    if (c < S) {
+                        if (S == 1) { lo[c] = *reinterpret_cast<const float4*>(mine); hi[c] = *reinterpret_cast<const float4*>(mine + 4); }
+                        else { lo[c] = ld_peer4(mine, (unsigned)c); hi[c] = ld_peer4(mine + 4, (unsigned)c); }
+                    }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = 0.f;
+#pragma unroll
+                for (int c = 0; c < 8; ++c)           // in the order of the ranks
+                    if (c < S) {
+                        v[0] += lo[c].x; v[1] += lo[c].y; v[2] += lo[c].z; v[3] += lo[c].w;
+                        v[4] += hi[c].x; v[5] += hi[c].y; v[6] += hi[c].z; v[7] += hi[c].w;
+                    }
+            }
+            const float sc = row_scale[t];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] *= sc;
+            const bool t_ok = t < a.N;
+            const bool whole = vec && m + 8 <= a.M;   // all eight rows exist and 16-byte stores are aligned
             if (a.epi == EPI_STORE) {
-                if (ok) {
-                    if (a.y_f32) reinterpret_cast<float*>(a.y)[(size_t)t * a.ldy + m] = v;
-                    else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)t * a.ldy + m] = __float2bfloat16_rn(v);
+                if (!t_ok || m >= a.M) continue;
+                if (a.y_f32) {
+                    float* dst = reinterpret_cast<float*>(a.y) + (size_t)t * a.ldy + m;
+                    if (whole) {
+                        reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+                        reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+                    } else {
+                        for (int i = 0; i < 8 && m + i < a.M; ++i) dst[i] = v[i];
+                    }
+                } else {
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.y) + (size_t)t * a.ldy + m;
+                    if (whole) *reinterpret_cast<uint4*>(dst) = pack8(v);
+                    else for (int i = 0; i < 8 && m + i < a.M; ++i) dst[i] = __float2bfloat16_rn(v[i]);
                 }
             } else if (a.epi == EPI_RESID_ADD) {
-                float nv = 0.f;
-                if (ok) {
-                    nv = a.acc[(size_t)t * a.M + m] + v;
-                    a.acc[(size_t)t * a.M + m] = nv;
+                float nv[8], sq = 0.f;
+                float* dst = a.acc + (size_t)t * a.M + m;
+                const bool live = t_ok && m < a.M;
+                if (live && whole) {
+                    const float4 o0 = reinterpret_cast<const float4*>(dst)[0], o1 = reinterpret_cast<const float4*>(dst)[1];
+                    nv[0] = o0.x + v[0]; nv[1] = o0.y + v[1]; nv[2] = o0.z + v[2]; nv[3] = o0.w + v[3];
+                    nv[4] = o1.x + v[4]; nv[5] = o1.y + v[5]; nv[6] = o1.z + v[6]; nv[7] = o1.w + v[7];
+                    reinterpret_cast<float4*>(dst)[0] = make_float4(nv[0], nv[1], nv[2], nv[3]);
+                    reinterpret_cast<float4*>(dst)[1] = make_float4(nv[4], nv[5], nv[6], nv[7]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        nv[i] = 0.f;
+                        if (live && m + i < a.M) { nv[i] = dst[i] + v[i]; dst[i] = nv[i]; }
+                    }
                 }
                 if (a.xg_out != nullptr) {
-                    if (ok) {
-                        const float gm = a.next_gamma_f32 ? reinterpret_cast<const float*>(a.next_gamma)[m]
-                                                          : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.next_gamma)[m]);
-                        a.xg_out[(size_t)t * a.M + m] = __float2bfloat16_rn(nv * gm);
+                    float gm[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        gm[i] = (live && m + i < a.M) ? (a.next_gamma_f32 ? reinterpret_cast<const float*>(a.next_gamma)[m + i]
+                                                                          : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.next_gamma)[m + i]))
+                                                      : 0.f;
+                    float xg[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) { xg[i] = nv[i] * gm[i]; sq += nv[i] * nv[i]; }       // the eight rows in order
+                    if (live) {
+                        __nv_bfloat16* xd = a.xg_out + (size_t)t * a.M + m;
+                        if (whole) *reinterpret_cast<uint4*>(xd) = pack8(xg);
+                        else for (int i = 0; i < 8 && m + i < a.M; ++i) xd[i] = __float2bfloat16_rn(xg[i]);
                     }
-                    float sq = nv * nv;               // over the tile of 16 rows: the lanes of a group of 16, in a fixed order
-                    sq += __shfl_xor_sync(0xffffffffu, sq, 1);
-                    sq += __shfl_xor_sync(0xffffffffu, sq, 2);
-                    sq += __shfl_xor_sync(0xffffffffu, sq, 4);
-                    sq += __shfl_xor_sync(0xffffffffu, sq, 8);
-                    if ((lane & 15) == 0 && ok) a.ssq_out[(size_t)(m >> 4) * kSquaresRow + t] = sq;
+                    const float other = __shfl_xor_sync(0xffffffffu, sq, 1);
+                    if (!odd && live) a.ssq_out[(size_t)(m >> 4) * kSquaresRow + t] = sq + other;        // rows 0..7, then rows 8..15
                 }
             } else if (a.epi == EPI_SWIGLU) {
-                const float other = __shfl_xor_sync(0xffffffffu, v, 8);      // rows 0..7 of a tile are gates, rows 8..15 their ups
-                const int i = (m >> 4) * 8 + (m & 7);
-                if (half16 == 0 && t < a.N && i < (a.M >> 1))
-                    reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)t * a.ldy + i] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * other);
+                float up[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) up[i] = __shfl_xor_sync(0xffffffffu, v[i], 1);       // the odd lane holds the ups of these gates
+                const int i0 = (m >> 4) * 8, inner = a.M >> 1;
+                if (odd || !t_ok || i0 >= inner) continue;
+                float r8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) r8[i] = v[i] / (1.0f + expf(-v[i])) * up[i];
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.y) + (size_t)t * a.ldy + i0;
+                if (vec && i0 + 8 <= inner) *reinterpret_cast<uint4*>(dst) = pack8(r8);
+                else for (int i = 0; i < 8 && i0 + i < inner; ++i) dst[i] = __float2bfloat16_rn(r8[i]);
             } else {
-                // EPI_ROPE: rows 0..7 of a tile of 16 are lanes 8j..8j+7 of a head (in its dealt order), rows 8..15 their partners
+                // EPI_ROPE: the even lane holds lanes 8j..8j+7 of a head (in its dealt order), the odd lane their partners
                 const SkRope& r = a.rope;
-                const float other = __shfl_xor_sync(0xffffffffu, v, 8);
-                if (ok) {
-                    const int head = m / r.hd, lane_of_head = m % r.hd;
-                    float res = v;
-                    if (head < r.n_heads + r.n_kv) {
-                        const float2 cs = r.table[(size_t)rope_pos[t] * (r.hd >> 1) + 8 * (lane_of_head >> 4) + (m & 7)];
-                        res = half16 == 0 ? v * cs.x - other * cs.y : other * cs.y + v * cs.x;
-                    }
-                    if (head < r.n_heads) {
-                        reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)t * a.ldy + m] = __float2bfloat16_rn(res);
-                    } else if (rope_where[t] >= 0) {
-                        const int kvh = head - r.n_heads;          // k heads, then v heads
-                        const size_t head_stride = (size_t)r.page_size * r.hd, page_elems = (size_t)r.n_kv * head_stride;
-                        __nv_bfloat16* dst = r.pool + rope_where[t] +
-                                             (kvh < r.n_kv ? (size_t)kvh * head_stride : page_elems + (size_t)(kvh - r.n_kv) * head_stride);
-                        dst[lane_of_head] = __float2bfloat16_rn(res);
+                float other[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) other[i] = __shfl_xor_sync(0xffffffffu, v[i], 1);
+                if (!t_ok || m >= a.M) continue;
+                const int head = m / r.hd, lane_of_head = m % r.hd;
+                if (head < r.n_heads + r.n_kv) {
+                    const float2* cs = r.table + (size_t)rope_pos[t] * (r.hd >> 1) + 8 * (lane_of_head >> 4);
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2) {
+                        const float4 c2 = *reinterpret_cast<const float4*>(cs + i);      // (cos, sin) of pairs i and i + 1
+                        if (!odd) { v[i] = v[i] * c2.x - other[i] * c2.y; v[i + 1] = v[i + 1] * c2.z - other[i + 1] * c2.w; }
+                        else { v[i] = other[i] * c2.y + v[i] * c2.x; v[i + 1] = other[i + 1] * c2.w + v[i + 1] * c2.z; }
                     }
                 }
+                __nv_bfloat16* dst;
+                if (head < r.n_heads) {
+                    dst = reinterpret_cast<__nv_bfloat16*>(a.y) + (size_t)t * a.ldy + m;
+                } else {
+                    if (rope_where[t] < 0) continue;
+                    const int kvh = head - r.n_heads;          // k heads, then v heads
+                    const size_t head_stride = (size_t)r.page_size * r.hd, page_elems = (size_t)r.n_kv * head_stride;
+                    dst = r.pool + rope_where[t] + (kvh < r.n_kv ? (size_t)kvh * head_stride : page_elems + (size_t)(kvh - r.n_kv) * head_stride) + lane_of_head;
+                }
+                if (vec) *reinterpret_cast<uint4*>(dst) = pack8(v);
+                else for (int i = 0; i < 8; ++i) dst[i] = __float2bfloat16_rn(v[i]);
             }
         }
     }
+    if (threadIdx.x == 64) blm_trace_here(0x570);
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     cluster_sync();          // nobody leaves while a peer may still read its shared memory
     if (warp == 1) {
@@ -403,11 +526,18 @@ int make_map(const void* base, long long ld, int rows, int K, int box_rows, CUte
 
 int padded_tokens(int N) { return N <= 16 ? 16 : (N <= 32 ? 32 : (N <= 64 ? 64 : 128)); }
 
-// bytes of shared memory beside the ring, and the ring's depth that fits with it
-size_t fixed_bytes(int NP) { return (size_t)NP * TM * 4 + (size_t)NP * 16 + 1024 + 512; }
-int ring_depth(int NP, int k_per) {
+// bytes of shared memory beside the ring (which also holds the block's sums once it is drained), and the ring's
+// depth that fits with it
+size_t fixed_bytes(int NP) { return (size_t)NP * 16 + 1024 + 512; }
+size_t ring_bytes_of(int NP, int n_stages) {
+    const size_t ring = (size_t)n_stages * (kWBytes + (size_t)NP * BK * 2), sums = (size_t)NP * TM * 4;
+    return ring > sums ? ring : sums;
+}
+// `room`: what a block may take: all of an SM's shared memory, or half of it when the blocks come in more than
+// one wave, so that a second block streams while the first one is in its epilogue
+int ring_depth(int NP, int k_per, size_t room) {
     const size_t stage = kWBytes + (size_t)NP * BK * 2;
-    int n = (int)((220 * 1024 - fixed_bytes(NP)) / (stage + 16));
+    int n = room > fixed_bytes(NP) ? (int)((room - fixed_bytes(NP)) / (stage + 16)) : 0;
     if (n > k_per) n = k_per;
     if (n > 32) n = 32;
     return n < 2 ? 2 : n;
@@ -416,8 +546,11 @@ int ring_depth(int NP, int k_per) {
 template <int NP>
 int launch(const SkArgs& a, const CUtensorMap& wmap, const CUtensorMap& xmap, int tiles, cudaStream_t stream) {
     const int k_iters = (a.K + BK - 1) / BK, k_per = (k_iters + a.S - 1) / a.S;
-    const int n_stages = ring_depth(NP, k_per);
-    const size_t smem = (size_t)n_stages * (kWBytes + (size_t)NP * BK * 2 + 16) + fixed_bytes(NP);
+    // A block that allocates tensor memory has its SM to itself (cudaOccupancyMaxActiveBlocksPerMultiprocessor
+    // answers 1 for such a kernel whatever its size), so the ring takes what shared memory there is; measured, a ring
+    // of four stages streams as fast as one of seven.
+    int n_stages = ring_depth(NP, k_per, 220 * 1024);
+    const size_t smem = ring_bytes_of(NP, n_stages) + (size_t)n_stages * 16 + fixed_bytes(NP);
     static bool opted_in = false;
     if (!opted_in) {
         cudaError_t e = cudaFuncSetAttribute(gemm_sk_kernel<NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
@@ -438,6 +571,19 @@ int launch(const SkArgs& a, const CUtensorMap& wmap, const CUtensorMap& xmap, in
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
+    if (a.S > 1) {
+        // all clusters at once, or smaller ones: a cluster that has to wait for SMs of one GPC to come free starts a
+        // second wave (how many fit is asked once per cluster size and shared-memory size)
+        static std::map<std::pair<int, size_t>, int> fits;
+        const auto key = std::make_pair(a.S, smem);
+        auto it = fits.find(key);
+        if (it == fits.end()) {
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_sk_kernel<NP>, &cfg) != cudaSuccess) n = 0;
+            it = fits.emplace(key, n).first;
+        }
+        if (it->second > 0 && it->second < tiles) return -1;       // the caller halves the clusters
+    }
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_sk_kernel<NP>, a, wmap, xmap, n_stages);
     if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "gemm_sk: %s", cudaGetErrorString(e));
     return blm_check_launch("gemm_sk");
@@ -481,20 +627,29 @@ BLM_API int blm_gemm_sk(const void* w, long long ldw, int M, int K, const void* 
                     "gemm_sk: the rotary epilogue writes the cache and needs its pool and tables");
         a.rope = *rope;
     }
+    auto aligned = [](const void* p) { return ((size_t)p & 15) == 0; };
+    if (epi == EPI_STORE) a.vec = aligned(y) && ldy % (y_f32 ? 4 : 8) == 0;
+    else if (epi == EPI_SWIGLU) a.vec = aligned(y) && ldy % 8 == 0;
+    else if (epi == EPI_RESID_ADD) a.vec = M % 8 == 0 && aligned(acc) && (xg_out == nullptr || aligned(xg_out));
+    else a.vec = aligned(y) && ldy % 8 == 0 && (!rope->write_cache || aligned(rope->pool)) && aligned(rope->table);
     const int tiles = (M + TM - 1) / TM, k_iters = (K + BK - 1) / BK, sms = blm_sm_count();
+    const int NP = padded_tokens(N);
     int S = 8;
     while (S > 1 && (tiles * S > sms || k_iters < 2 * S)) S >>= 1;
     a.S = S;
-    const int NP = padded_tokens(N);
     CUtensorMap wmap, xmap;
     int rc = make_map(w, ldw, M, K, TM, &wmap);
     if (rc != BLM_OK) return rc;
     rc = make_map(x, ldx, N, K, NP, &xmap);
     if (rc != BLM_OK) return rc;
-    switch (NP) {
-        case 16: return launch<16>(a, wmap, xmap, tiles, stream);
-        case 32: return launch<32>(a, wmap, xmap, tiles, stream);
-        case 64: return launch<64>(a, wmap, xmap, tiles, stream);
-        default: return launch<128>(a, wmap, xmap, tiles, stream);
+    for (;;) {
+        switch (NP) {
+            case 16: rc = launch<16>(a, wmap, xmap, tiles, stream); break;
+            case 32: rc = launch<32>(a, wmap, xmap, tiles, stream); break;
+            case 64: rc = launch<64>(a, wmap, xmap, tiles, stream); break;
+            default: rc = launch<128>(a, wmap, xmap, tiles, stream); break;
+        }
+        if (rc != -1 || a.S == 1) return rc == -1 ? blm_fail(BLM_CUDA_ERROR, "gemm_sk: no room for a block") : rc;
+        a.S >>= 1;       // the clusters did not all fit at once
     }
 }

@@ -22,6 +22,13 @@ from .. import kernels as K
 
 SKINNY_TOKENS = 16        # the skinny kernel takes up to this many tokens
 FUSED_NORM_TOKENS = 16    # ... and normalises them in its prologue (every block redoes it)
+# BURN_LM_B200_SK_TOKENS=n: steps of more tokens than that, up to n (at most 128), run the tcgen05 product whose
+# wide operand is the weight (kernels.gemm_sk: K cut over a cluster, sums met in distributed shared memory, the
+# same fused ends as the skinny kernel).  Off by default (16): measured on the 1B shape at 64 tokens its products
+# take 13 / 10 / 25 / 20 us (qkv / output / gate-up / down, with their fused ends) against 5.7 / 5.9 / 13.6 / 13.7 us
+# for the library's, which more than eats what the four launches it saves a layer are worth (a batch-64 decode
+# step: 1.52 ms against 1.14 ms).
+SK_TOKENS = int(os.environ.get("BURN_LM_B200_SK_TOKENS", "16"))
 # From this many tokens the gated product runs this package's tcgen05 kernel.  Measured inside CUDA graphs on
 # the 1B shape (16,384 x 2,048 weight): with fewer tokens its 128 x 256 tiles fill the SMs unevenly and the
 # library's product followed by the activation kernel is faster (384 tokens: 28 against 36 us; 1,024: 61
@@ -106,6 +113,27 @@ class Linear:
         return (w.dtype == torch.bfloat16 and w.is_cuda and n_tokens <= SKINNY_TOKENS
                 and K.gemv_supported(n_tokens, m, self.in_features, plain_tokens=plain))
 
+    def _sk(self, n_tokens: int) -> bool:
+        """Whether the step runs kernels.gemm_sk (asked after _skinny has said no)."""
+        w = self.weight
+        return (w.dtype == torch.bfloat16 and w.is_cuda and w.is_contiguous() and n_tokens <= min(SK_TOKENS, K.SK_TOKENS)
+                and K.gemm_sk_supported(n_tokens, self.out_features, self.in_features))
+
+    @staticmethod
+    def _sk_source(x):
+        """Keyword arguments that hand x (a tensor or a pending norm) to gemm_sk: dense bfloat16 rows, or a norm
+        that the writer of the stream handed over in gemm_sk's layout."""
+        if isinstance(x, NormedStream):
+            h = x.handed
+            if h is not None and x.rows is None and h.squares.shape[1] == K.SK_SQUARES_ROWS:
+                return dict(x=h.scaled, squares=h.squares, eps=x.eps)
+            x = x.materialize()
+        if x.dtype != torch.bfloat16:
+            xc = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+            K.convert(x, xc)
+            x = xc
+        return dict(x=x if x.is_contiguous() else x.contiguous())
+
     @staticmethod
     def _tokens(x) -> int:
         return x.n_tokens if isinstance(x, NormedStream) else x.shape[0]
@@ -113,7 +141,7 @@ class Linear:
     def _source(self, x):
         """Keyword arguments that hand x (a tensor or a pending norm) to the skinny kernel."""
         if isinstance(x, NormedStream):
-            if x.handed is not None and x.n_tokens <= SKINNY_TOKENS:
+            if x.handed is not None and x.n_tokens <= SKINNY_TOKENS and x.handed.squares.shape[1] == K.SQUARES_ROWS:
                 return dict(x=x.handed.scaled, squares=x.handed.squares, eps=x.eps, rows=x.rows)
             if x.n_tokens <= FUSED_NORM_TOKENS:
                 return dict(stream_rows=x.resid, gamma=x.gamma, eps=x.eps, rows=x.rows)
@@ -132,6 +160,10 @@ class Linear:
                 out = torch.empty((n, self.out_features), dtype=out_dtype, device=self.weight.device)
                 K.gemv(self.weight, n, out=out, **self._source(x))
                 return out
+        elif self._sk(n) and (out_dtype or torch.bfloat16) in (torch.bfloat16, torch.float32):
+            out = torch.empty((n, self.out_features), dtype=out_dtype or torch.bfloat16, device=self.weight.device)
+            K.gemm_sk(self.weight, out=out, **self._sk_source(x))
+            return out
         if isinstance(x, NormedStream):
             x = x.materialize()
         return self._library(x, out_dtype or x.dtype)
@@ -153,6 +185,18 @@ class Linear:
             if hand_over is not None:
                 handoff.leave(stream, norm.gamma, handed)
             return None
+        if stream is not None and self._sk(n):
+            hand_over = None
+            norm = handoff.wanted if handoff is not None else None
+            if norm is not None and n <= K.SK_SQUARES_ROWS and norm.gamma.numel() == self.out_features:
+                handed = HandedNorm(torch.empty((n, self.out_features), dtype=torch.bfloat16, device=stream.device),
+                                    torch.empty(((self.out_features + 15) // 16, K.SK_SQUARES_ROWS), dtype=torch.float32,
+                                                device=stream.device))
+                hand_over = (norm.gamma, handed.scaled, handed.squares)
+            K.gemm_sk(self.weight, add_into=stream, hand_over=hand_over, **self._sk_source(x))
+            if hand_over is not None:
+                handoff.leave(stream, norm.gamma, handed)
+            return None
         return self(x, out_dtype)
 
     def with_rotary(self, x, q_out: torch.Tensor, rope: dict) -> bool:
@@ -160,10 +204,15 @@ class Linear:
         takes the step, it rotates q and k and appends k and v to the cache in its epilogue, writes q to
         `q_out` and this returns True; else nothing is done."""
         n = self._tokens(x)
-        if q_out.dtype != torch.bfloat16 or not self._skinny(n, self.out_features, x):
+        if q_out.dtype != torch.bfloat16:
             return False
-        K.gemv(self.weight, n, out=q_out, rope=rope, **self._source(x))
-        return True
+        if self._skinny(n, self.out_features, x):
+            K.gemv(self.weight, n, out=q_out, rope=rope, **self._source(x))
+            return True
+        if self._sk(n):
+            K.gemm_sk(self.weight, out=q_out, rope=rope, **self._sk_source(x))
+            return True
+        return False
 
     def gated(self, x, out_dtype: torch.dtype) -> torch.Tensor:
         """silu(x Wgate^T) * (x Wup^T) for a fused [gate; up] weight."""
@@ -172,6 +221,9 @@ class Linear:
         act = torch.empty((n, inner), dtype=out_dtype, device=self.weight.device)
         if out_dtype == torch.bfloat16 and self.gate_tile == K.GATE_TILE and self._skinny(n, inner, x):
             K.gemv(self.weight, n, out=act, swiglu=True, **self._source(x))
+            return act
+        if out_dtype == torch.bfloat16 and self.gate_tile == K.GATE_TILE and self._sk(n):
+            K.gemm_sk(self.weight, out=act, swiglu=True, **self._sk_source(x))
             return act
         if (out_dtype == torch.bfloat16 and self.gate_tile == K.GATE_TILE and self.weight.dtype == torch.bfloat16
                 and n >= TENSOR_CORE_TOKENS and K.gemm_tc_supported(n, self.out_features, self.in_features)):

@@ -48,6 +48,30 @@ def test_forty_eight_sequences_prompts_then_token_by_token(tmp_path, dtype, tole
         assert err.max() < tolerance, (rid, len(toks), float(err.max()), "first bad place", int(np.argmax(err >= tolerance)))
 
 
+def test_forty_eight_sequences_on_the_cluster_product(tmp_path, monkeypatch):
+    """The same with the switch that sends steps of 17 to 64 tokens to kernels.gemm_sk (the tcgen05 product with K
+    cut over a cluster, with the rotary, gated and stream-adding ends and the handed-over norms): the kernel did
+    run, and the logits are the plain implementation's."""
+    from burn_lm_b200 import Engine, kernels
+    from burn_lm_b200.parts import linear
+    monkeypatch.setattr(linear, "SK_TOKENS", 64)
+    calls = []
+    real = kernels.gemm_sk
+    monkeypatch.setattr(kernels, "gemm_sk", lambda *a, **k: (calls.append(sorted(k)), real(*a, **k))[1])
+    folder = make_folder(tmp_path, "tiny_f", seed=9, dtype="bfloat16")
+    cfg, tensors = P.read_model_folder(folder)
+    reqs = many_requests(48, 4)
+    steps = traces.batched(reqs, 48, DECODE_COUNTS, prompt_steps=3)
+    eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=traces.max_live_tokens(steps), max_seqs=48)
+    got = traces.run_in_process(eng, steps, str(tmp_path / "sk"), cfg["vocab_size"])
+    eng.verify()
+    kinds = {tuple(c) for c in calls}
+    assert any("rope" in c for c in kinds) and any("swiglu" in c for c in kinds) and any("hand_over" in c for c in kinds) and any("squares" in c for c in kinds)
+    for rid, toks in reqs.items():
+        err = row_error(got[rid], P.forward(cfg, tensors, toks))
+        assert err.max() < 3e-2, (rid, len(toks), float(err.max()), int(err.argmax()))
+
+
 def test_two_batches_of_forty_through_the_same_slots(tmp_path):
     """A second batch of 40 takes the slots and pages the first one gave back (bfloat16, captured steps)."""
     from burn_lm_b200 import Engine
