@@ -334,7 +334,7 @@ BLM_API int blm_attention(const void* q, long long q_stride, const void* pool, i
                           const int* slot_of_seq, const int* start_pos, void* out, float* scratch,
                           int n_tokens, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd,
                           int page_size, int window, int n_splits, float scale, int general_only, int* status,
-                          int n_pages, int max_kv_len, cudaStream_t stream) {
+                          int n_pages, int max_kv_len, const int* seq_table, cudaStream_t stream) {
     if (n_tokens == 0 || n_seqs == 0) return BLM_OK;
     BLM_REQUIRE(page_size == kPage, "attention: the cache page holds %d positions, the kernel wants %d", page_size, kPage);
     BLM_REQUIRE(hd >= 16 && hd <= 8 * kColGroups * kChunksMax && hd % 16 == 0,
@@ -347,7 +347,7 @@ BLM_API int blm_attention(const void* q, long long q_stride, const void* pool, i
         // one new token per sequence: the specialised kernel, where it has the shape
         AttnDecodeArgs d;
         d.q = (const __nv_bfloat16*)q; d.q_stride = q_stride; d.pool = (const __nv_bfloat16*)pool;
-        d.block_table = block_table; d.table_stride = table_stride; d.cu_seqlens = cu_seqlens;
+        d.block_table = block_table; d.table_stride = table_stride; d.seq_table = seq_table; d.cu_seqlens = cu_seqlens;
         d.slot_of_seq = slot_of_seq; d.start_pos = start_pos; d.out = (__nv_bfloat16*)out;
         d.part_acc = scratch;
         d.part_ml = scratch ? scratch + (size_t)n_tokens * n_heads * n_splits * hd : nullptr;

@@ -23,6 +23,7 @@ struct AttnDecodeArgs {
     const __nv_bfloat16* pool;   // [pages][2][n_kv][64][HD]
     const int* block_table;
     int table_stride;
+    const int* seq_table;        // optional: the block table's rows in the order of the step's sequences
     const int* cu_seqlens;
     const int* slot_of_seq;
     const int* start_pos;
@@ -159,7 +160,8 @@ __global__ void __launch_bounds__((4 * NG + 1) * 32) attn_decode_kernel(const At
     const int per = (n_pg + active - 1) / active;
     const int pg_lo = pg_first + split * per;
     const int pg_hi = min(pg_first + n_pg, pg_lo + per);          // exclusive
-    const int* pages = a.block_table + (size_t)a.slot_of_seq[seq] * a.table_stride;
+    const int* pages = a.seq_table != nullptr ? a.seq_table + (size_t)seq * a.table_stride
+                                              : a.block_table + (size_t)a.slot_of_seq[seq] * a.table_stride;
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {

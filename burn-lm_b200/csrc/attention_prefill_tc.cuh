@@ -323,90 +323,129 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
             if (r == 0) blm_trace_here(0x510);
             // A block whose every key every row sees (all but the diagonal and the window's edge) needs no masks.
             const bool open_block = key0 + BKV - 1 <= start + q0 && (a.window <= 0 || key0 >= start + q0 + BQ - a.window);
-            // the row's maximum (of the raw scores: the scale is positive)
-            float mx = -INFINITY;
             unsigned buf[2][32];           // two loads of 32 columns: one in flight, one being worked on
-            tmem_ld32_issue(taddr, buf[0]);
-#pragma unroll
-            for (int c = 0; c < BKV / 32; ++c) {
-                tmem_ld32_wait(buf[c & 1]);
-                // the next columns of this pass, or the first of the next pass
-                tmem_ld32_issue(taddr + ((c + 1) & 3) * 32, buf[(c + 1) & 1]);
-                float v[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(buf[c & 1][i]);
-                if (open_block) {
-                    float m4[4] = {v[0], v[1], v[2], v[3]};
-#pragma unroll
-                    for (int i = 4; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], v[i]);
-                    mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int key = key0 + c * 32 + i;
-                        if (live && key >= lo && key <= pos) mx = fmaxf(mx, v[i]);
-                    }
-                }
-            }
-            if (r == 0) blm_trace_here(0x520);
-            const float m_blk = mx * a.scale_log2e;
-            const bool move = m_blk > m_run + kLazy;                     // also the first block that shows the row a key
-            if (__any_sync(0xffffffffu, move)) {
-                const float alpha = move ? (m_run == -INFINITY ? 0.f : ex2(m_run - m_blk)) : 1.0f;
-                if (j > 0) {
-                    // the last product into O must have landed before its rows are touched
-                    if (!mbar_wait(pv_full, (j - 1) & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_PV); ok = false; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll 1
-                    for (int c = 0; c < HD / 32; ++c) {
-                        float v[32];
-                        tmem_ld32(taddr + 128 + c * 32, v);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] *= alpha;
-                        tmem_st32(taddr + 128 + c * 32, v);
-                    }
-                }
-                if (move) {
-                    l_run *= alpha;
-                    m_run = m_blk;
-                }
-            }
-            const float neg_m = m_run == -INFINITY ? 0.f : -m_run;      // a row without a visible key: every probability is masked anyway
-            // probabilities, as bf16 into the P tile: 16-byte chunk c of the row's half h at h * kTile + r * 128 + ((c ^ (r & 7)) << 4)
             float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+            // An open block of a row that has its reference maximum already: ONE pass over the scores.  The
+            // exponentials are taken against the reference as it stands while the same pass finds the block's
+            // maximum; only if some row of the warp has outgrown its reference by more than 2^kLazy (rare after
+            // the first blocks) is the step done again the long way, maximum first.  The numbers are the same
+            // either way: the same reference, the same operations.
+            bool done = false;
+            if (open_block && __all_sync(0xffffffffu, m_run != -INFINITY)) {
+                const float neg_ref = -m_run;
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                tmem_ld32_issue(taddr, buf[0]);
 #pragma unroll
-            for (int c = 0; c < BKV / 32; ++c) {
-                tmem_ld32_wait(buf[c & 1]);
-                if (c + 1 < BKV / 32) tmem_ld32_issue(taddr + (c + 1) * 32, buf[(c + 1) & 1]);
-                float v[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(buf[c & 1][i]);
-                unsigned packed[16];
-                if (open_block) {
+                for (int c = 0; c < BKV / 32; ++c) {
+                    tmem_ld32_wait(buf[c & 1]);
+                    if (c + 1 < BKV / 32) tmem_ld32_issue(taddr + (c + 1) * 32, buf[(c + 1) & 1]);
+                    unsigned packed[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const float p0 = ex2(fmaf(v[i], a.scale_log2e, neg_m)), p1 = ex2(fmaf(v[i + 1], a.scale_log2e, neg_m));
+                        const float s0 = __uint_as_float(buf[c & 1][i]), s1 = __uint_as_float(buf[c & 1][i + 1]);
+                        m4[(i >> 1) & 3] = fmaxf(m4[(i >> 1) & 3], fmaxf(s0, s1));
+                        const float p0 = ex2(fmaf(s0, a.scale_log2e, neg_ref)), p1 = ex2(fmaf(s1, a.scale_log2e, neg_ref));
                         rs4[(i >> 1) & 3] += p0 + p1;
                         const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                         packed[i >> 1] = *reinterpret_cast<const unsigned*>(&pk);
                     }
-                } else {
+                    unsigned char* prow = Ps + (c >> 1) * kTile + r * 128;
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const int key = key0 + c * 32 + i;
-                        const float p0 = (live && key >= lo && key <= pos) ? ex2(fmaf(v[i], a.scale_log2e, neg_m)) : 0.f;
-                        const float p1 = (live && key + 1 >= lo && key + 1 <= pos) ? ex2(fmaf(v[i + 1], a.scale_log2e, neg_m)) : 0.f;
-                        rs4[(i >> 1) & 3] += p0 + p1;
-                        const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-                        packed[i >> 1] = *reinterpret_cast<const unsigned*>(&pk);
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const int chunk = (c & 1) * 4 + q4;
+                        *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
+                            make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
                     }
                 }
-                unsigned char* prow = Ps + (c >> 1) * kTile + r * 128;
+                const float m_one = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * a.scale_log2e;
+                done = !__any_sync(0xffffffffu, m_one > m_run + kLazy);
+                if (!done) { rs4[0] = 0.f; rs4[1] = 0.f; rs4[2] = 0.f; rs4[3] = 0.f; }
+                if (r == 0) blm_trace_here(0x520);
+            }
+            if (!done) {
+                // the row's maximum (of the raw scores: the scale is positive)
+                float mx = -INFINITY;
+                tmem_ld32_issue(taddr, buf[0]);
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = (c & 1) * 4 + q4;
-                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
-                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                for (int c = 0; c < BKV / 32; ++c) {
+                    tmem_ld32_wait(buf[c & 1]);
+                    // the next columns of this pass, or the first of the next pass
+                    tmem_ld32_issue(taddr + ((c + 1) & 3) * 32, buf[(c + 1) & 1]);
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(buf[c & 1][i]);
+                    if (open_block) {
+                        float m4[4] = {v[0], v[1], v[2], v[3]};
+#pragma unroll
+                        for (int i = 4; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], v[i]);
+                        mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int key = key0 + c * 32 + i;
+                            if (live && key >= lo && key <= pos) mx = fmaxf(mx, v[i]);
+                        }
+                    }
+                }
+                if (r == 0) blm_trace_here(0x520);
+                const float m_blk = mx * a.scale_log2e;
+                const bool move = m_blk > m_run + kLazy;                     // also the first block that shows the row a key
+                if (__any_sync(0xffffffffu, move)) {
+                    const float alpha = move ? (m_run == -INFINITY ? 0.f : ex2(m_run - m_blk)) : 1.0f;
+                    if (j > 0) {
+                        // the last product into O must have landed before its rows are touched
+                        if (!mbar_wait(pv_full, (j - 1) & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_PV); ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+                        for (int c = 0; c < HD / 32; ++c) {
+                            float v[32];
+                            tmem_ld32(taddr + 128 + c * 32, v);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] *= alpha;
+                            tmem_st32(taddr + 128 + c * 32, v);
+                        }
+                    }
+                    if (move) {
+                        l_run *= alpha;
+                        m_run = m_blk;
+                    }
+                }
+                const float neg_m = m_run == -INFINITY ? 0.f : -m_run;      // a row without a visible key: every probability is masked anyway
+                // probabilities, as bf16 into the P tile: 16-byte chunk c of the row's half h at h * kTile + r * 128 + ((c ^ (r & 7)) << 4)
+#pragma unroll
+                for (int c = 0; c < BKV / 32; ++c) {
+                    tmem_ld32_wait(buf[c & 1]);
+                    if (c + 1 < BKV / 32) tmem_ld32_issue(taddr + (c + 1) * 32, buf[(c + 1) & 1]);
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(buf[c & 1][i]);
+                    unsigned packed[16];
+                    if (open_block) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float p0 = ex2(fmaf(v[i], a.scale_log2e, neg_m)), p1 = ex2(fmaf(v[i + 1], a.scale_log2e, neg_m));
+                            rs4[(i >> 1) & 3] += p0 + p1;
+                            const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                            packed[i >> 1] = *reinterpret_cast<const unsigned*>(&pk);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const int key = key0 + c * 32 + i;
+                            const float p0 = (live && key >= lo && key <= pos) ? ex2(fmaf(v[i], a.scale_log2e, neg_m)) : 0.f;
+                            const float p1 = (live && key + 1 >= lo && key + 1 <= pos) ? ex2(fmaf(v[i + 1], a.scale_log2e, neg_m)) : 0.f;
+                            rs4[(i >> 1) & 3] += p0 + p1;
+                            const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                            packed[i >> 1] = *reinterpret_cast<const unsigned*>(&pk);
+                        }
+                    }
+                    unsigned char* prow = Ps + (c >> 1) * kTile + r * 128;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const int chunk = (c & 1) * 4 + q4;
+                        *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
+                            make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                    }
                 }
             }
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);

@@ -463,6 +463,34 @@ __global__ void bump_kernel(int* step_no) {
     *step_no += 1;
 }
 
+// Once per step and group of cache lines, for every layer of the group: the page each new token goes to, and the
+// block table's rows put in the order of the step's sequences.  The kernels that append to the cache and that walk
+// a sequence's pages then read one array each instead of following token -> sequence -> slot -> table.
+__global__ void step_tables_kernel(const int* __restrict__ token_seq, const int* __restrict__ token_pos, const int* __restrict__ slot_of_seq,
+                                   const int* __restrict__ block_table, int table_stride, int page_size, int n_tokens, int n_seqs,
+                                   int* __restrict__ token_page, int* __restrict__ seq_table) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < n_tokens) {
+        const int seq = token_seq[idx];
+        token_page[idx] = seq >= 0 ? block_table[(size_t)slot_of_seq[seq] * table_stride + token_pos[idx] / page_size] : -1;   // -1: a row of no sequence
+    }
+    const int cell = idx - n_tokens;
+    if (cell >= 0 && cell < n_seqs * table_stride)
+        seq_table[cell] = block_table[(size_t)slot_of_seq[cell / table_stride] * table_stride + cell % table_stride];
+}
+
+BLM_API int blm_step_tables(const int* token_seq, const int* token_pos, const int* slot_of_seq, const int* block_table, int table_stride,
+                            int page_size, int n_tokens, int n_seqs, int* token_page, int* seq_table, cudaStream_t stream) {
+    const long long total = (long long)n_tokens + (long long)n_seqs * table_stride;
+    if (total == 0) return BLM_OK;
+    BLM_REQUIRE(page_size > 0 && table_stride > 0, "step_tables: page size %d, table stride %d", page_size, table_stride);
+    blm_launch_dependent(step_tables_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, token_seq, token_pos, slot_of_seq,
+                         block_table, table_stride, page_size, n_tokens, n_seqs, token_page, seq_table);
+    return blm_check_launch("step_tables");
+}
+
 BLM_API int blm_decode_advance(int* tokens, int* pos, const int* sampled, int* history, int* step_no,
                                long long* counters, int batch, int history_steps, cudaStream_t stream) {
     if (batch == 0) return BLM_OK;

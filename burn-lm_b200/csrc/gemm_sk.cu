@@ -52,6 +52,7 @@ struct SkRope {
     const float2* table;         // (cos, sin) [positions][hd / 2]
     __nv_bfloat16* pool;         // [pages][2][n_kv][page_size][hd]
     int table_stride, n_heads, n_kv, hd, page_size, write_cache;
+    const int* token_page;       // optional [N]: the page every token goes to (-1: a row of no sequence)
 };
 
 struct SkArgs {
@@ -311,11 +312,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_sk_kernel(const SkArgs a, co
                 rope_pos[e] = pos;
                 long long where = -1;                  // a row of no sequence: nothing of it reaches the cache
                 if (r.write_cache) {
-                    const int seq = r.token_seq[e];
-                    if (seq >= 0) {
-                        const int page = r.block_table[(size_t)r.slot_of_seq[seq] * r.table_stride + pos / r.page_size];
-                        where = ((long long)page * 2 * r.n_kv * r.page_size + pos % r.page_size) * r.hd;
+                    int page = -1;
+                    if (r.token_page != nullptr) {
+                        page = r.token_page[e];
+                    } else {
+                        const int seq = r.token_seq[e];
+                        if (seq >= 0) page = r.block_table[(size_t)r.slot_of_seq[seq] * r.table_stride + pos / r.page_size];
                     }
+                    if (page >= 0) where = ((long long)page * 2 * r.n_kv * r.page_size + pos % r.page_size) * r.hd;
                 }
                 rope_where[e] = where;
             }

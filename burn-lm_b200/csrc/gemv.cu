@@ -61,6 +61,7 @@ struct GemvRope {
     const float2* table;         // (cos, sin) [positions][hd / 2]; covers every position of the step
     __nv_bfloat16* pool;         // [pages][2][n_kv][page_size][hd] of this cache line
     int table_stride, n_heads, n_kv, hd, page_size, write_cache;
+    const int* token_page;       // optional [N]: the page every token goes to (-1: a row of no sequence), looked up once per step
 };
 enum { GEMV_OK = 0, GEMV_TIMEOUT_FULL = 1, GEMV_TIMEOUT_EMPTY = 2 };
 enum { X_STAGED = 0, X_IN_RING = 1, X_BY_TMA = 2 };
@@ -408,12 +409,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
         const int pos = r.token_pos[tid];
         rope_pos[tid] = pos;
         if (r.write_cache) {
-            const int seq = r.token_seq[tid];
             long long where = -1;       // a row of no sequence (padding): nothing of it reaches the cache
-            if (seq >= 0) {
-                const int slot = r.slot_of_seq[seq];
-                const int page = r.block_table[(size_t)slot * r.table_stride + pos / r.page_size];
-                where = ((long long)page * 2 * r.n_kv * r.page_size + pos % r.page_size) * r.hd;
+            if (r.token_page != nullptr) {
+                const int page = r.token_page[tid];          // read beside the position: one round trip, not three
+                if (page >= 0) where = ((long long)page * 2 * r.n_kv * r.page_size + pos % r.page_size) * r.hd;
+            } else {
+                const int seq = r.token_seq[tid];
+                if (seq >= 0) {
+                    const int slot = r.slot_of_seq[seq];
+                    const int page = r.block_table[(size_t)slot * r.table_stride + pos / r.page_size];
+                    where = ((long long)page * 2 * r.n_kv * r.page_size + pos % r.page_size) * r.hd;
+                }
             }
             rope_cache[tid] = where;
         }

@@ -80,11 +80,12 @@ _protos = {
         "blm_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "blm_convert": [c_void_p, c_int, c_void_p, c_int, c_size_t, c_void_p],
         "blm_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "blm_step_tables": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     },
     "attention": {
         "blm_attention": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                          c_int, c_int, c_float, c_int, c_void_p, c_int, c_int, c_void_p],
+                          c_int, c_int, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
     },
     "gemm": {
         "blm_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
@@ -276,6 +277,19 @@ def decode_advance(tokens, pos, sampled, history, step_no, counters=None):
           _ptr(counters), b, steps, _stream(), kernels=2)
 
 
+def step_tables(token_seq, token_pos, slot_of_seq, block_table, n_seqs):
+    """Looked up once per step for all layers that share a block table: (token_page int32 [N], the page every new
+    token goes to, -1 for a row of no sequence; seq_table int32 [n_seqs, pages per sequence], the block table's
+    rows in the order of the step's sequences)."""
+    _need_cuda(token_seq, token_pos, slot_of_seq, block_table)
+    n = token_seq.numel()
+    token_page = torch.empty(n, dtype=torch.int32, device=block_table.device)
+    seq_table = torch.empty((n_seqs, block_table.shape[1]), dtype=torch.int32, device=block_table.device)
+    _call("elementwise", "blm_step_tables", _ptr(token_seq), _ptr(token_pos), _ptr(slot_of_seq), _ptr(block_table),
+          block_table.shape[1], PAGE, n, n_seqs, _ptr(token_page), _ptr(seq_table), _stream())
+    return token_page, seq_table
+
+
 def attention_decode_is_specialised(dtype, head_dim, group) -> bool:
     """Whether a step of one token per sequence runs the specialised decode kernel (whose blocks
     split the keys by pages and skip splits a sequence does not need)."""
@@ -288,7 +302,7 @@ def attention_scratch_floats(n_tokens, n_heads, head_dim, n_splits):
 
 def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos, out, n_tokens, n_seqs,
               max_q_len, n_heads, n_kv, head_dim, scale, window=0, n_splits=1, scratch=None, general_only=False,
-              max_kv_len=0):
+              max_kv_len=0, seq_table=None):
     """Causal grouped-query attention of the step's tokens over the paged cache (after the append).
 
     q: tensor whose token n, head h starts at element n * q_stride + h * head_dim (the qkv buffer).
@@ -298,8 +312,10 @@ def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos
     attention_scratch_floats(...) elements).  bfloat16 steps of one token per sequence with a head
     size of 64 or 128 and up to 8 query heads per kv head run a specialised kernel unless
     `general_only`; `max_kv_len` (the longest sequence after the step, when known) lets it size its
-    rings of pages."""
-    _need_cuda(q, pool, block_table, cu_seqlens, slot_of_seq, start_pos, out, scratch)
+    rings of pages; `seq_table` (from step_tables) spares it the way through the slots."""
+    _need_cuda(q, pool, block_table, cu_seqlens, slot_of_seq, start_pos, out, scratch, seq_table)
+    if seq_table is not None and (seq_table.dtype != torch.int32 or tuple(seq_table.shape) != (n_seqs, block_table.shape[1])):
+        raise KernelError("attention: seq_table must be int32 [n_seqs, pages per sequence]")
     if tuple(out.shape) != (n_tokens, n_heads * head_dim) or out.dtype != q.dtype or pool.dtype != q.dtype:
         raise KernelError("attention: out must be [N, heads * head_dim] in q's dtype, as the pool")
     if tuple(pool.shape[1:]) != (2, n_kv, PAGE, head_dim):
@@ -311,7 +327,7 @@ def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos
     _call("attention", "blm_attention", _ptr(q), q_stride, _ptr(pool), _code(q.dtype), _ptr(block_table),
           block_table.shape[1], _ptr(cu_seqlens), _ptr(slot_of_seq), _ptr(start_pos), _ptr(out), _ptr(scratch),
           n_tokens, n_seqs, max_q_len, n_heads, n_kv, head_dim, PAGE, int(window or 0), n_splits,
-          c_float(scale), 1 if general_only else 0, _ptr(status_word(q.device)), pool.shape[0], int(max_kv_len), _stream(),
+          c_float(scale), 1 if general_only else 0, _ptr(status_word(q.device)), pool.shape[0], int(max_kv_len), _ptr(seq_table), _stream(),
           kernels=2 if n_splits > 1 else 1)
 
 
@@ -336,7 +352,7 @@ EPI_STORE, EPI_SWIGLU, EPI_RESID_ADD, EPI_ROPE = 0, 1, 2, 3
 class _GemvRope(ctypes.Structure):
     _fields_ = [("token_pos", c_void_p), ("token_seq", c_void_p), ("slot_of_seq", c_void_p), ("block_table", c_void_p),
                 ("table", c_void_p), ("pool", c_void_p), ("table_stride", c_int), ("n_heads", c_int), ("n_kv", c_int),
-                ("hd", c_int), ("page_size", c_int), ("write_cache", c_int)]
+                ("hd", c_int), ("page_size", c_int), ("write_cache", c_int), ("token_page", c_void_p)]
 
 
 def gemv_supported(n_tokens, m, k, plain_tokens=False) -> bool:
@@ -405,7 +421,8 @@ def gemm_sk(w, x, out=None, add_into=None, swiglu=False, squares=None, eps=0.0, 
             raise KernelError("gemm_sk: the rotary epilogue writes q to a bfloat16 out [N, n_heads * head_dim]")
         rope_arg = _GemvRope(r["token_pos"].data_ptr(), r["token_seq"].data_ptr(), r["slot_of_seq"].data_ptr(),
                              r["block_table"].data_ptr(), table.data_ptr(), pool.data_ptr() if pool is not None else 0,
-                             r["block_table"].shape[1], r["n_heads"], r["n_kv"], hd, PAGE, 1 if r["write_cache"] else 0)
+                             r["block_table"].shape[1], r["n_heads"], r["n_kv"], hd, PAGE, 1 if r["write_cache"] else 0,
+                             r["token_page"].data_ptr() if r.get("token_page") is not None else 0)
     if squares is not None and (squares.dtype != torch.float32 or squares.dim() != 2 or squares.shape[1] != SK_SQUARES_ROWS
                                 or n > SK_SQUARES_ROWS):
         raise KernelError(f"gemm_sk: squares are float32 [parts, {SK_SQUARES_ROWS}] for up to {SK_SQUARES_ROWS} tokens")
@@ -517,7 +534,8 @@ def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, 
             raise KernelError("gemv: the rotary epilogue writes q to a bfloat16 out [N, n_heads * head_dim]")
         rope_arg = _GemvRope(r["token_pos"].data_ptr(), r["token_seq"].data_ptr(), r["slot_of_seq"].data_ptr(),
                              r["block_table"].data_ptr(), table.data_ptr(), pool.data_ptr() if pool is not None else 0,
-                             r["block_table"].shape[1], r["n_heads"], r["n_kv"], hd, PAGE, 1 if r["write_cache"] else 0)
+                             r["block_table"].shape[1], r["n_heads"], r["n_kv"], hd, PAGE, 1 if r["write_cache"] else 0,
+                             r["token_page"].data_ptr() if r.get("token_page") is not None else 0)
     if x is not None and (x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != k
                           or (rows is None and x.shape[0] != n_tokens)):
         raise KernelError("gemv: x must be bfloat16 [N, K]")

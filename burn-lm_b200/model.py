@@ -122,6 +122,7 @@ class Model:
         """Logits (fp32 [n_want, vocab]) at the wanted rows of the step, or None when none is wanted."""
         if not self.bound:
             raise RuntimeError("the model has no weights yet")
+        step.memo.clear()
         resid = torch.empty((step.n_tokens, self.plan.hidden_size), dtype=torch.float32, device=self.runtime.device)
         self.embedding.forward(step.tokens, resid)
         if self.stream_position is not None:

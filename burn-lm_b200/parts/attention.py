@@ -127,12 +127,21 @@ class Attention(Part):
         n = step.n_tokens
         product = self.qkv if cache.writes else self.q_only     # a run that reads another run's cache line needs q only
         qkv = None
+        # the page of every new token and the sequences' rows of the block table: looked up once per step for all
+        # the layers that share this block table
+        tables = None
+        if rt.dtype == torch.bfloat16:
+            key = ("step_tables", cache.block_table.data_ptr())
+            tables = step.memo.get(key)
+            if tables is None:
+                tables = step.memo[key] = K.step_tables(step.token_seq, step.token_pos, step.slot_of_seq, cache.block_table, step.n_seqs)
         if self.pairs == K.PAIRS_TILED and table is not None and step.max_kv_len <= table.shape[0]:
             # few tokens: the skinny product rotates and appends in its epilogue and leaves q
             q = torch.empty((n, s.n_heads * s.head_dim), dtype=rt.dtype, device=cache.pool.device)
             rope = dict(token_pos=step.token_pos, token_seq=step.token_seq, slot_of_seq=step.slot_of_seq,
                         block_table=cache.block_table, table=table, pool=cache.pool, n_heads=s.n_heads,
-                        n_kv=s.n_kv_heads, head_dim=s.head_dim, write_cache=cache.writes, max_position=step.max_kv_len - 1)
+                        n_kv=s.n_kv_heads, head_dim=s.head_dim, write_cache=cache.writes, max_position=step.max_kv_len - 1,
+                        token_page=tables[0] if tables is not None else None)
             if product.with_rotary(x, q, rope):
                 qkv = q
         if qkv is None:
@@ -147,5 +156,6 @@ class Attention(Part):
             scratch = step.workspace.scratch("attention", K.attention_scratch_floats(n, s.n_heads, s.head_dim, n_splits))
         K.attention(qkv, qkv.shape[1], cache.pool, cache.block_table, step.cu_seqlens, step.slot_of_seq,
                     step.start_pos, out, n, step.n_seqs, step.max_q_len, s.n_heads, s.n_kv_heads, s.head_dim,
-                    self.scale, window=s.window or 0, n_splits=n_splits, scratch=scratch, max_kv_len=step.max_kv_len)
+                    self.scale, window=s.window or 0, n_splits=n_splits, scratch=scratch, max_kv_len=step.max_kv_len,
+                    seq_table=tables[1] if tables is not None else None)
         return self.o.into_stream(out, stream, rt.dtype, handoff=getattr(step, "handoff", None))

@@ -77,6 +77,7 @@ class StepContext:
     workspace: "object" = None   # the engine's scratch provider: scratch(name, n_floats) -> fp32 tensor
     host: dict = field(default_factory=dict)   # host copies for parts that plan on the CPU
     handoff: "object" = None     # parts.linear.NormHandoff of the step, when the block uses one
+    memo: dict = field(default_factory=dict)   # what parts look up once per step and share (emptied when a forward begins)
 
 
 class Part:

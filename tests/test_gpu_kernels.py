@@ -701,3 +701,52 @@ def test_gemm_tc_gated(m, inner, k):
     want = gu[:, :inner] / (1 + torch.exp(-gu[:, :inner])) * gu[:, inner:]
     assert not torch.isnan(out.float()).any()
     assert (out.double() - want).abs().max().item() < 1e-2 * want.abs().max().item()
+
+
+def test_step_tables_and_their_users():
+    """The page of every new token and the block table's rows by sequence, looked up once per step: the tables
+    themselves, and the kernels that take them (the rotary epilogue of the skinny product, decode attention) give
+    what they give without them."""
+    k = K()
+    H, KV, hd, width = 4, 2, 64, 256
+    lens_before = [5, 63, 64, 300, 129, 700]
+    n = len(lens_before)
+    st = paged_setup(lens_before, [1] * n, KV, hd, torch.bfloat16, seed=41)
+    seq = st["token_seq"].clone()
+    seq[2] = -1                                     # a row of no sequence
+    token_page, seq_table = k.step_tables(seq, st["token_pos"], st["slots"], st["table"], n)
+    for i in range(n):
+        slot = st["host_slots"][i]
+        want = -1 if i == 2 else int(st["host_table"][slot, lens_before[i] // k.PAGE])
+        assert int(token_page[i]) == want
+        assert torch.equal(seq_table[i].cpu(), st["host_table"][slot])
+    g = torch.Generator(device="cuda").manual_seed(42)
+    w = (torch.randn((H + 2 * KV) * hd, width, device="cuda", generator=g) * 0.08).to(torch.bfloat16)
+    x = torch.randn(n, width, device="cuda", generator=g).to(torch.bfloat16)
+    inv_freq = torch.tensor([5e5 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64, device="cuda")
+    table = k.rope_table(inv_freq, max(lens_before) + 2)
+    pools, qs = [], []
+    for tp in (None, token_page):
+        s2 = paged_setup(lens_before, [1] * n, KV, hd, torch.bfloat16, seed=41)
+        q = torch.empty((n, H * hd), device="cuda", dtype=torch.bfloat16)
+        rope = dict(token_pos=s2["token_pos"], token_seq=seq, slot_of_seq=s2["slots"], block_table=s2["table"], table=table,
+                    pool=s2["pool"], n_heads=H, n_kv=KV, head_dim=hd, write_cache=True, max_position=max(lens_before), token_page=tp)
+        k.gemv(w, n, x=x, out=q, rope=rope)
+        pools.append(s2["pool"].float())
+        qs.append(q)
+    assert torch.equal(qs[0], qs[1])
+    assert torch.equal(torch.isnan(pools[0]), torch.isnan(pools[1])) and torch.equal(torch.nan_to_num(pools[0]), torch.nan_to_num(pools[1]))
+    # decode attention over a cache with history, with and without the rows by sequence
+    hist_k = [torch.randn(t, KV, hd, device="cuda", generator=g).to(torch.bfloat16) for t in st["total"]]
+    hist_v = [torch.randn(t, KV, hd, device="cuda", generator=g).to(torch.bfloat16) for t in st["total"]]
+    write_history(st, hist_k, hist_v)
+    qkv = torch.randn(n, (H + 2 * KV) * hd, device="cuda", generator=g).to(torch.bfloat16)
+    outs = []
+    _, seq_table = k.step_tables(st["token_seq"], st["token_pos"], st["slots"], st["table"], n)
+    for tab in (None, seq_table):
+        out = torch.empty(n, H * hd, device="cuda", dtype=torch.bfloat16)
+        k.attention(qkv, qkv.shape[1], st["pool"], st["table"], st["cu"], st["slots"], st["starts"], out, n, n, 1, H, KV, hd, 0.125,
+                    max_kv_len=max(st["total"]), seq_table=tab)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    k.check_status("cuda")
