@@ -42,8 +42,9 @@ BLM_API const char* blm_gemv_last_error() { return g_blm_error; }
 
 constexpr int kConsumerWarps = 8;
 constexpr int kGemvThreads = (kConsumerWarps + 1) * 32;   // + the producer warp
-constexpr int kStageK = 256;                              // k elements per stage: 8 units of 32
-constexpr int kStageBytes = 16 * kStageK * 2;             // [4 chunks][16 rows][128 bytes], swizzled
+// k elements per stage, a parameter of the kernel: 256 (8 KB of weights a stage), or 128 (4 KB) where many wide
+// tokens leave the ring too little room for two stages of 256 per warp; a stage is [SK / 64 chunks][16 rows][128
+// bytes], swizzled
 constexpr unsigned kSpinLimit = 1u << 20;   // polls of a wait before it gives up (seconds; a real wait is microseconds)
 
 enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESID_ADD = 2, EPI_ROPE = 3 };
@@ -240,10 +241,12 @@ __device__ __forceinline__ void gemv_stage_tokens(const GemvArgs& a, __nv_bfloat
     }
 }
 
-template <int NBT>
+template <int NBT, int SK>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap) {
     extern __shared__ __align__(1024) unsigned char smem[];
     constexpr int nrows = NBT * 8;
+    constexpr int kStageK = SK;
+    constexpr int kStageBytes = 16 * SK * 2;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int kpad = (a.K + kStageK - 1) / kStageK * kStageK;
     const int xstride = kpad + 8;                                   // bf16 elements; 16 bytes of padding
@@ -271,9 +274,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
     // in turn, in rounds of eight.
     const int my_tiles = n_tiles > (int)blockIdx.x ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     // few tiles in this block: several warps share a tile, each on a slice of K (1, 2, 4 or 8 of them)
+    // The slices are cut in units of 256 k whatever the stage size: where a sum is cut, and so its rounding, then
+    // does not depend on the stage size, which follows the number of tokens.
+    const int units_per_tile = (a.K + 255) / 256;
     int ks = 1;
-    while (ks * 2 * my_tiles <= kConsumerWarps && ks * 2 <= stages_per_tile) ks *= 2;
-    const int stages_per_slice = (stages_per_tile + ks - 1) / ks;
+    while (ks * 2 * my_tiles <= kConsumerWarps && ks * 2 <= units_per_tile) ks *= 2;
+    const int stages_per_slice = (units_per_tile + ks - 1) / ks * (256 / kStageK);
     const int my_units = my_tiles * ks;
     const int n_rounds = (my_units + kConsumerWarps - 1) / kConsumerWarps;
     // the ring is dealt out to the warps that work (fewer units than warps: fewer, deeper parts); a warp
@@ -651,25 +657,47 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
     blm_trace(0x130 | a.epi);
 }
 
-// Shared memory for a shape and the ring depth it leaves room for; 0 when the tokens do not fit.
-static size_t gemv_plan(int N, int K, int x_mode, int* n_stages_out, int* nbt_out) {
+// Shared memory for a shape and the ring depth it leaves room for; 0 when the tokens do not fit.  `stage_k`: k per
+// stage.  The ring has a whole number of stages for each of the eight warps where that is possible.
+static size_t gemv_plan(int N, int K, int x_mode, int stage_k, int* n_stages_out, int* nbt_out) {
     int nbt = 1;
     while (nbt * 8 < N) nbt *= 2;
     if (nbt > 2) return 0;
     const int nrows = nbt * 8;
-    const int kpad = (K + kStageK - 1) / kStageK * kStageK;
+    const int kpad = (K + stage_k - 1) / stage_k * stage_k;
     const size_t tokens = x_mode == X_IN_RING ? 0 : (x_mode == X_BY_TMA ? (size_t)nrows * kpad * 2 : (size_t)nrows * (kpad + 8) * 2);
-    const size_t stage = kStageBytes + (x_mode == X_IN_RING ? (size_t)nrows * kStageK * 2 : 0);
-    const size_t fixed = 128 + 1024 + (size_t)(kpad / kStageK) * 8 + 256;      // the other barriers, the row scales, the rotary epilogue's tables, alignment
+    const size_t stage = (size_t)16 * stage_k * 2 + (x_mode == X_IN_RING ? (size_t)nrows * stage_k * 2 : 0);
+    const size_t fixed = 128 + 1024 + (size_t)(kpad / stage_k) * 8 + 256;      // the other barriers, the row scales, the rotary epilogue's tables, alignment
     const size_t red = (size_t)kConsumerWarps * 16 * nrows * 4;
     const size_t limit = 220 * 1024;
-    int stages = 16;
+    int stages = stage_k == 256 ? 16 : 32;
     while (stages > 8 && (size_t)stages * stage + tokens + red + (size_t)stages * 16 + fixed > limit) --stages;
+    if (stages > 8) stages -= stages % 8;
     const size_t total = (size_t)stages * stage + tokens + red + (size_t)stages * 16 + fixed;
     if (total > limit) return 0;
     *n_stages_out = stages;
     *nbt_out = nbt;
     return total;
+}
+// The plan with stages of 256 k, or, where that leaves a warp a single stage (it could then not fetch one stage
+// while it works on another), the plan with stages of 128 k when that gives it at least two.
+static size_t gemv_plan_best(int N, int K, int x_mode, int* stage_k_out, int* n_stages_out, int* nbt_out) {
+    int st = 0, nbt = 0;
+    size_t smem = gemv_plan(N, K, x_mode, 256, &st, &nbt);
+    *stage_k_out = 256;
+    if (smem > 0 && st < 2 * kConsumerWarps) {
+        int st2 = 0, nbt2 = 0;
+        const size_t smem2 = gemv_plan(N, K, x_mode, 128, &st2, &nbt2);
+        if (smem2 > 0 && st2 >= 2 * kConsumerWarps) {
+            *stage_k_out = 128;
+            st = st2;
+            nbt = nbt2;
+            smem = smem2;
+        }
+    }
+    *n_stages_out = st;
+    *nbt_out = nbt;
+    return smem;
 }
 
 // 1 when blm_gemv takes the shape, else 0 (the caller then uses the library product).  `plain_tokens`: the
@@ -678,8 +706,8 @@ static size_t gemv_plan(int N, int K, int x_mode, int* n_stages_out, int* nbt_ou
 BLM_API int blm_gemv_supported(int N, int M, int K, int plain_tokens) {
     int st, nbt;
     if (!(N >= 1 && N <= 16 && K % 64 == 0 && M >= 1)) return 0;
-    if (gemv_plan(N, K, X_STAGED, &st, &nbt) > 0) return 1;
-    return plain_tokens && gemv_plan(N, K, X_IN_RING, &st, &nbt) > 0;
+    if (gemv_plan(N, K, X_STAGED, 256, &st, &nbt) > 0) return 1;
+    return plain_tokens && gemv_plan(N, K, X_IN_RING, 256, &st, &nbt) > 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -687,7 +715,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // The TMA's view of a weight [rows, K] (row stride ldw): dims (64 k, rows, K / 64); box (64, 16, 4).
-static int weight_map(const void* w, long long ldw, int rows, int K, CUtensorMap* out) {
+static int weight_map(const void* w, long long ldw, int rows, int K, int stage_k, CUtensorMap* out) {
     static EncodeTiledFn encode = nullptr;
     if (!encode) {
         void* fn = nullptr;
@@ -697,14 +725,14 @@ static int weight_map(const void* w, long long ldw, int rows, int K, CUtensorMap
             return blm_fail(BLM_CUDA_ERROR, "gemv: the driver has no cuTensorMapEncodeTiled");
         encode = (EncodeTiledFn)fn;
     }
-    static std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> cache;
-    const auto key = std::make_tuple(w, ldw, rows, K);
+    static std::map<std::tuple<const void*, long long, int, int, int>, CUtensorMap> cache;
+    const auto key = std::make_tuple(w, ldw, rows, K, stage_k);
     auto it = cache.find(key);
     if (it == cache.end()) {
         CUtensorMap m;
         const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(K / 64)};
         const cuuint64_t strides[2] = {(cuuint64_t)ldw * 2, 128};     // bytes: between rows, between chunks
-        const cuuint32_t box[3] = {64, 16, kStageK / 64};
+        const cuuint32_t box[3] = {64, 16, (cuuint32_t)(stage_k / 64)};
         const cuuint32_t estr[3] = {1, 1, 1};
         CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w), dims, strides, box, estr,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -718,7 +746,7 @@ static int weight_map(const void* w, long long ldw, int rows, int K, CUtensorMap
 }
 
 // The TMA's view of the tokens [N, K] (row stride ldx): dims (64 k, N, K / 64); box (64, token rows, 4).
-static int token_map(const void* x, long long ldx, int N, int K, int nrows, CUtensorMap* out) {
+static int token_map(const void* x, long long ldx, int N, int K, int nrows, int stage_k, CUtensorMap* out) {
     static EncodeTiledFn encode = nullptr;
     if (!encode) {
         void* fn = nullptr;
@@ -728,14 +756,14 @@ static int token_map(const void* x, long long ldx, int N, int K, int nrows, CUte
             return blm_fail(BLM_CUDA_ERROR, "gemv: the driver has no cuTensorMapEncodeTiled");
         encode = (EncodeTiledFn)fn;
     }
-    static std::map<std::tuple<const void*, long long, int, int, int>, CUtensorMap> cache;
-    const auto key = std::make_tuple(x, ldx, N, K, nrows);
+    static std::map<std::tuple<const void*, long long, int, int, int, int>, CUtensorMap> cache;
+    const auto key = std::make_tuple(x, ldx, N, K, nrows, stage_k);
     auto it = cache.find(key);
     if (it == cache.end()) {
         CUtensorMap m;
         const cuuint64_t dims[3] = {64, (cuuint64_t)N, (cuuint64_t)(K / 64)};
         const cuuint64_t strides[2] = {(cuuint64_t)ldx * 2, 128};
-        const cuuint32_t box[3] = {64, (cuuint32_t)nrows, kStageK / 64};
+        const cuuint32_t box[3] = {64, (cuuint32_t)nrows, (cuuint32_t)(stage_k / 64)};
         const cuuint32_t estr[3] = {1, 1, 1};
         CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(x), dims, strides, box, estr,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -792,40 +820,42 @@ BLM_API int blm_gemv(const void* w, long long ldw, int M, int K, const void* x, 
     // and when they are too many for that (a very wide input) they travel with the weights after all, once
     // per tile.  A stream to normalise or gathered rows are staged by the consumers.
     a.x_mode = X_STAGED;
-    int nbt;
+    int nbt, stage_k = 256;
     size_t smem = 0;
     if (x != nullptr && rows == nullptr) {
-        a.x_mode = (tiles <= sms && ssq_in == nullptr && K >= 2 * kStageK) ? X_IN_RING : X_BY_TMA;
-        smem = gemv_plan(N, K, a.x_mode, &a.n_stages, &nbt);
+        a.x_mode = (tiles <= sms && ssq_in == nullptr && K >= 2 * 256) ? X_IN_RING : X_BY_TMA;
+        smem = gemv_plan_best(N, K, a.x_mode, &stage_k, &a.n_stages, &nbt);
         if (smem == 0 && a.x_mode == X_BY_TMA) {
             a.x_mode = X_IN_RING;
-            smem = gemv_plan(N, K, X_IN_RING, &a.n_stages, &nbt);
+            smem = gemv_plan_best(N, K, X_IN_RING, &stage_k, &a.n_stages, &nbt);
         }
     }
     if (smem == 0) {
         a.x_mode = X_STAGED;
-        smem = gemv_plan(N, K, X_STAGED, &a.n_stages, &nbt);
+        smem = gemv_plan_best(N, K, X_STAGED, &stage_k, &a.n_stages, &nbt);
     }
     BLM_REQUIRE(smem > 0, "gemv: the shape N=%d K=%d does not fit shared memory", N, K);
     CUtensorMap wmap, xmap;
-    int rc = weight_map(w, ldw, epi == EPI_SWIGLU ? 2 * M : M, K, &wmap);
+    int rc = weight_map(w, ldw, epi == EPI_SWIGLU ? 2 * M : M, K, stage_k, &wmap);
     if (rc != BLM_OK) return rc;
     if (a.x_mode != X_STAGED) {
-        rc = token_map(x, ldx, N, K, nbt * 8, &xmap);
+        rc = token_map(x, ldx, N, K, nbt * 8, stage_k, &xmap);
         if (rc != BLM_OK) return rc;
     } else {
         xmap = wmap;      // not used
     }
-    static bool opted_in[3] = {false, false, false};     // per token-tile variant of the kernel
+    static bool opted_in[3][2] = {};     // per variant of the kernel
     auto launch = [&](auto kernel) -> int {
-        if (!opted_in[nbt]) {
+        bool& done = opted_in[nbt][stage_k == 128];
+        if (!done) {
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
             if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "gemv: %s", cudaGetErrorString(e));
-            opted_in[nbt] = true;
+            done = true;
         }
         cudaError_t e = blm_launch_dependent(kernel, dim3(grid), dim3(kGemvThreads), smem, stream, a, wmap, xmap);
         if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "gemv: %s", cudaGetErrorString(e));
         return blm_check_launch("gemv");
     };
-    return nbt == 1 ? launch(gemv_kernel<1>) : launch(gemv_kernel<2>);
+    if (stage_k == 128) return nbt == 1 ? launch(gemv_kernel<1, 128>) : launch(gemv_kernel<2, 128>);
+    return nbt == 1 ? launch(gemv_kernel<1, 256>) : launch(gemv_kernel<2, 256>);
 }

@@ -140,7 +140,7 @@ def _lib(module: str) -> ctypes.CDLL:
 def prebuild(dtype) -> None:
     """Compile, side by side, the modules that every step of a model of this dtype uses, so that a first
     call waits for the slowest of them instead of for their sum.  The others are still built when first used."""
-    _build.build_many(["elementwise", "attention"] + (["gemv", "gemm_sk"] if dtype == torch.bfloat16 else ["gemm"]))
+    _build.build_many(["elementwise", "attention", "gemv" if dtype == torch.bfloat16 else "gemm"])
 
 
 _launches = 0
