@@ -2,24 +2,31 @@
 // attention of a step's new tokens over the paged cache, the products on tcgen05 with their accumulators
 // in tensor memory.
 //
-// A block owns 128 query rows of one head of one sequence and walks the keys in blocks of 128 (two cache
-// pages).  Warp 0 (one thread) is the producer: TMA tile loads with the 128-byte swizzle of the query
-// tile (once, from the step's q rows), of the keys (a ring of two stages) and of the values (one stage),
-// completion on mbarriers.  Warp 1 (one thread) issues the products: S = Q K^T (M 128, N 128, both
-// operands K-major in shared memory) into tensor memory, and, once the softmax warps have written the
-// probabilities, PV = P V (A = P from shared memory, B = V as it lies in the cache, keys by lanes, read
-// MN-major) into other columns; tcgen05.commit frees the stages and tells the softmax warps.  Warps 2..5
-// are the softmax: a thread owns one query row (its lane of tensor memory), reads the row of S with
-// tcgen05.ld twice (maximum, then exponentials), writes the probabilities as bf16 into the swizzled P
-// tile, and keeps the row's reference maximum and sum in registers.  O accumulates in tensor memory over
-// the blocks; a row of it is rescaled there (tcgen05.ld, multiply, tcgen05.st) only when a block's
-// maximum exceeds the row's reference by more than 2^8, which after the first blocks is rare.  Two
-// blocks share an SM (256 columns of tensor memory each), one's softmax under the other's products.
+// A block owns 128 query rows of one head of one sequence and walks the keys a cache page (64 keys) a
+// step.  Seven warps:
+//   warp 0 (one thread), the producer: TMA tile loads with the 128-byte swizzle of the query tile (once,
+//     from the step's q rows), of the pages' keys (a ring of four) and values (a ring of two), completion
+//     on mbarriers;
+//   warp 1 (one thread), the scores: S(j) = Q K(j)^T (M 128, N 64, both operands K-major in shared memory)
+//     into a ring of three 64-column tiles of tensor memory, so that a step's scores are formed two steps
+//     before the softmax warps come for them;
+//   warp 2 (one thread), the values: O += P(j) V(j), with A = P read from tensor memory and B = V as it
+//     lies in the cache (keys by lanes, read MN-major);
+//   warps 3..6, the softmax: a thread owns one query row (its lane of tensor memory), reads the row of S
+//     with tcgen05.ld, keeps the row's reference maximum and sum in registers, and writes the
+//     probabilities as bf16 pairs over the first 32 columns of the same S tile (tcgen05.st), from where
+//     the values warp's product takes them: they never pass through shared memory.
+// tcgen05.commit frees stages and tells the next warp.  Two issuing warps, because one thread that issues
+// both products is the longest chain of a step (each instruction it issues costs it some fifty cycles).
+// O accumulates in tensor memory over the steps; a row of it is rescaled there (tcgen05.ld, multiply,
+// tcgen05.st) only when a step's maximum exceeds the row's reference by more than 2^8, which after the
+// first steps is rare.  Head size 64: 256 columns of tensor memory and 66 KB of shared memory a block,
+// two blocks to an SM, one's softmax under the other's; head size 128: 512 columns, one block.
 //
-// Rows of a value tile that no key of the sequence has written (a page's tail) are cleared by the softmax
-// threads before the product: a probability of zero does not silence a NaN.  Every mbarrier wait is
-// bounded; one that runs out records a code in the status word and the block goes to its end, where the
-// tensor memory is given back.
+// Rows of a value page that no key of the sequence has written (the page's tail) are cleared by the
+// softmax threads before the product: a probability of zero does not silence a NaN.  Every mbarrier wait
+// is bounded; one that runs out records a code in the status word and the block goes to its end, where
+// the tensor memory is given back.
 #pragma once
 #include <cuda.h>
 
@@ -42,8 +49,12 @@ struct AttnPrefillTcArgs {
 
 namespace attn_tc {
 constexpr unsigned kSpinLimit = 1u << 22;
-constexpr int kThreads = 192;        // producer warp, tensor-core warp, four softmax warps
-constexpr int BQ = 128, BKV = 128;   // query rows of a block, keys of a step
+constexpr int kThreads = 224;        // producer warp, two tensor-core warps (scores; values), four softmax warps
+constexpr int BQ = 128, BKV = 64;    // query rows of a block, keys of a step (one cache page)
+constexpr int kVStages = 2;          // pages of values in shared memory
+// pages of keys in shared memory and score tiles in tensor memory: what lets two blocks share an SM
+__host__ __device__ constexpr int key_stages(int hd) { return hd == 64 ? 4 : 2; }
+__host__ __device__ constexpr int score_ring(int hd) { return hd == 64 ? 3 : 2; }
 enum { TC_ATTN_Q = 31, TC_ATTN_K = 32, TC_ATTN_V = 33, TC_ATTN_S = 34, TC_ATTN_P = 35, TC_ATTN_PV = 36, TC_ATTN_FREE = 37 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -58,6 +69,17 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned
 }
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
     const unsigned addr = smem_u32(bar);
+    {   // a phase that is over already answers at once
+        unsigned done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
     for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
         unsigned done;
         asm volatile(
@@ -110,6 +132,15 @@ __device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a_desc,
         "setp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
         "l"(a_desc), "l"(b_desc), "r"(id), "r"(accumulate)
+        : "memory");
+}
+// the same with the A operand read from tensor memory (row m in lane m, two bf16 of k a column)
+__device__ __forceinline__ void umma_a_tmem(unsigned tmem_d, unsigned tmem_a, unsigned long long b_desc, unsigned id, unsigned accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(b_desc), "r"(id), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
@@ -171,32 +202,44 @@ __device__ __forceinline__ void tmem_st32(unsigned taddr, const float (&v)[32]) 
         : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
+__device__ __forceinline__ void tmem_st32_bits(unsigned taddr, const unsigned (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+        "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
+        "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]),
+        "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
 constexpr float kLazy = 8.0f;     // the reference maximum of a row moves only when a block exceeds it by more than 2^kLazy
 }  // namespace attn_tc
 
 template <int HD>
-__global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(const AttnPrefillTcArgs a, const __grid_constant__ CUtensorMap qmap,
+__global__ void __launch_bounds__(attn_tc::kThreads, 2) attn_prefill_tc_kernel(const AttnPrefillTcArgs a, const __grid_constant__ CUtensorMap qmap,
                                                                             const __grid_constant__ CUtensorMap pool_map) {
     using namespace attn_tc;
     constexpr int SUB = HD / 64;                         // 64-lane sub-tiles of a row
+    constexpr int kKStages = key_stages(HD), kSRing = score_ring(HD);
     constexpr unsigned kTile = 128 * 128;                // bytes of a sub-tile: 128 rows of 128 bytes
-    constexpr unsigned kQBytes = SUB * kTile, kKBytes = SUB * kTile, kVBytes = SUB * kTile, kPBytes = 2 * kTile;
-    constexpr int kTmemCols = 256;                       // S: columns 0..127; PV: columns 128..128 + HD
+    constexpr unsigned kPage = 64 * 128;                 // bytes of a page's sub-tile: 64 keys of 128 bytes
+    constexpr unsigned kQBytes = SUB * kTile, kKBytes = SUB * kPage, kVBytes = SUB * kPage;
+    constexpr int kOCol = kSRing * BKV;                  // S of step j: columns 64 (j % kSRing) ..; O: the columns behind the ring
+    constexpr int kTmemCols = kOCol + HD <= 256 ? 256 : 512;
     extern __shared__ __align__(1024) unsigned char smem_tc_raw[];
     unsigned char* smem = smem_tc_raw + ((1024u - (smem_u32(smem_tc_raw) & 1023u)) & 1023u);
     unsigned char* Qs = smem;                            // [SUB][128 rows][128 bytes]
-    unsigned char* Ks = Qs + kQBytes;                    // [2 stages][SUB][128 keys][128 bytes]
-    unsigned char* Vs = Ks + 2 * kKBytes;                // [SUB][128 keys][128 bytes]
-    unsigned char* Ps = Vs + kVBytes;                    // [2 halves of 64 keys][128 rows][128 bytes]
-    unsigned long long* q_full = reinterpret_cast<unsigned long long*>(Ps + kPBytes);
-    unsigned long long* k_full = q_full + 1;             // [2]
-    unsigned long long* k_empty = k_full + 2;            // [2]
-    unsigned long long* v_full = k_empty + 2;
-    unsigned long long* v_empty = v_full + 1;
-    unsigned long long* s_full = v_empty + 1;
-    unsigned long long* p_full = s_full + 1;
-    unsigned long long* pv_full = p_full + 1;
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(pv_full + 1);
+    unsigned char* Ks = Qs + kQBytes;                    // [kKStages][SUB][64 keys][128 bytes]
+    unsigned char* Vs = Ks + kKStages * kKBytes;         // [kVStages][SUB][64 keys][128 bytes]
+    unsigned long long* q_full = reinterpret_cast<unsigned long long*>(Vs + kVStages * kVBytes);
+    unsigned long long* k_full = q_full + 1;             // [kKStages] a page's keys have landed
+    unsigned long long* k_empty = k_full + kKStages;     // [kKStages] the scores that read them are formed
+    unsigned long long* v_full = k_empty + kKStages;     // [kVStages] a page's values have landed
+    unsigned long long* s_full = v_full + kVStages;      // [kSRing] the scores of a step are in tensor memory
+    unsigned long long* p_full = s_full + kSRing;        // [kSRing] its probabilities are written and its scores read
+    unsigned long long* pv_done = p_full + kSRing;       // [kSRing] its product into O is over: its columns of tensor memory and the value stage are free
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(pv_done + kSRing);
 
     pdl_wait();          // q and the keys are the work of the kernels before
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -218,12 +261,13 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
-        mbar_init(v_full, 1);
-        mbar_init(v_empty, 1);
-        mbar_init(s_full, 1);
-        mbar_init(p_full, 4);            // one arrival per softmax warp
-        mbar_init(pv_full, 1);
+        for (int s = 0; s < kKStages; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); }
+        for (int s = 0; s < kVStages; ++s) mbar_init(v_full + s, 1);
+        for (int s = 0; s < kSRing; ++s) {
+            mbar_init(s_full + s, 1);
+            mbar_init(p_full + s, 4);    // one arrival per softmax warp
+            mbar_init(pv_done + s, 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
@@ -235,81 +279,93 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = *tmem_slot;
 
+    // Who waits for whom, step j (a page of 64 keys; t = j % 3, b = j & 1):
+    //   scores warp:  pv_done[t] of step j - 3 (its columns were read), k_full  ->  S(j)  ->  s_full[t], k_empty
+    //   softmax:      s_full[t]                                                  ->  P(j) over S(j)'s first columns  ->  p_full[t]
+    //   values warp:  p_full[t], v_full[b]                                        ->  O += P V  ->  pv_done[t]
+    //   producer:     pv_done of step j - 2  ->  the values of step j;  k_empty of step j - 1  ->  the keys of step j + 3
+    // so the scores of a step are formed two steps before the softmax warps come for them.
     if (warp == 0) {
         if (lane == 0) {
             // ---------------- producer ----------------
             const int* pages = a.block_table + (size_t)a.slot_of_seq[seq] * a.table_stride;
-            const int last_page = (kv_total - 1) / 64;
             mbar_expect_tx(q_full, kQBytes);
 #pragma unroll
             for (int h = 0; h < SUB; ++h) tma_load_2d(Qs + h * kTile, &qmap, head * HD + h * 64, tok0 + q0, q_full);
-            bool ok = true;
-            for (int j = 0; j < n_blocks && ok; ++j) {
-                const int kb = kb_lo + j;
-                // the block's two pages; a second page the sequence does not have is read from the first (its
-                // keys are masked and its value rows cleared)
-                const int pa = pages[2 * kb], pb = 2 * kb + 1 <= last_page ? pages[2 * kb + 1] : pa;
-                const int ka = ((pa * 2) * a.n_kv + kvh) * 64, kbr = ((pb * 2) * a.n_kv + kvh) * 64;
-                const int s = j & 1;
-                if (j >= 2 && !mbar_wait(k_empty + s, ((j >> 1) - 1) & 1)) { atomicCAS(a.status, 0, TC_ATTN_FREE); ok = false; break; }
-                mbar_expect_tx(k_full + s, kKBytes);
+            auto row_of = [&](int step) { return ((pages[kb_lo + step] * 2) * a.n_kv + kvh) * 64; };      // the page's keys of this kv head
+            auto load_keys = [&](int step) -> bool {
+                const int ks = step % kKStages;
+                if (step >= kKStages && !mbar_wait(k_empty + ks, ((step / kKStages) - 1) & 1)) { atomicCAS(a.status, 0, TC_ATTN_FREE); return false; }
+                mbar_expect_tx(k_full + ks, kKBytes);
+                const int krow = row_of(step);
 #pragma unroll
-                for (int h = 0; h < SUB; ++h) {
-                    tma_load_2d(Ks + s * kKBytes + h * kTile, &pool_map, h * 64, ka, k_full + s);
-                    tma_load_2d(Ks + s * kKBytes + h * kTile + 64 * 128, &pool_map, h * 64, kbr, k_full + s);
-                }
-                if (j >= 1 && !mbar_wait(v_empty, (j - 1) & 1)) { atomicCAS(a.status, 0, TC_ATTN_FREE); ok = false; break; }
-                mbar_expect_tx(v_full, kVBytes);
+                for (int h = 0; h < SUB; ++h) tma_load_2d(Ks + ks * kKBytes + h * kPage, &pool_map, h * 64, krow, k_full + ks);
+                return true;
+            };
+            for (int j = 0; j < kKStages - 1 && j < n_blocks; ++j) load_keys(j);
+            for (int j = 0; j < n_blocks; ++j) {
+                const int b = j & 1;
+                if (j >= 2 && !mbar_wait(pv_done + (j - 2) % kSRing, ((j - 2) / kSRing) & 1)) { atomicCAS(a.status, 0, TC_ATTN_FREE); break; }
+                mbar_expect_tx(v_full + b, kVBytes);
+                const int vrow = row_of(j) + a.n_kv * 64;                    // the values lie n_kv * 64 rows after the keys
 #pragma unroll
-                for (int h = 0; h < SUB; ++h) {
-                    tma_load_2d(Vs + h * kTile, &pool_map, h * 64, ka + a.n_kv * 64, v_full);
-                    tma_load_2d(Vs + h * kTile + 64 * 128, &pool_map, h * 64, kbr + a.n_kv * 64, v_full);
-                }
+                for (int h = 0; h < SUB; ++h) tma_load_2d(Vs + b * kVBytes + h * kPage, &pool_map, h * 64, vrow, v_full + b);
+                if (j + kKStages - 1 < n_blocks && !load_keys(j + kKStages - 1)) break;
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // ---------------- tensor core ----------------
-            constexpr unsigned kIdescS = idesc(BKV, false), kIdescPV = idesc(HD, true);
+            // ---------------- tensor core, scores: S(j) = Q K(j)^T into columns 64 (j % 3) .. ----------------
+            constexpr unsigned kIdescS = idesc(BKV, false);
+            // operand descriptors: the address field counts 16 bytes, so a stage or a sub-tile further is an addition
+            const unsigned long long q_desc = desc_k_major(Qs), k_desc = desc_k_major(Ks);
             bool ok = mbar_wait(q_full, 0);
             if (!ok) atomicCAS(a.status, 0, TC_ATTN_Q);
             for (int j = 0; j < n_blocks && ok; ++j) {
-                const int s = j & 1;
-                if (!mbar_wait(k_full + s, (j >> 1) & 1)) { atomicCAS(a.status, 0, TC_ATTN_K); break; }
+                const int t = j % kSRing, ks = j % kKStages;
+                if (j >= kSRing && !mbar_wait(pv_done + t, ((j / kSRing) - 1) & 1)) { atomicCAS(a.status, 0, TC_ATTN_PV); break; }
+                if (!mbar_wait(k_full + ks, (j / kKStages) & 1)) { atomicCAS(a.status, 0, TC_ATTN_K); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                // S = Q K^T: HD / 16 steps of k; a step is 32 bytes along the swizzled row (+2 in the address
-                // field), the second half of a 128-lane head lies in the next sub-tile
+                // HD / 16 steps of k; a step is 32 bytes along the swizzled row (+2 in the address field), the
+                // second half of a 128-lane head lies in the next sub-tile
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
-                    const unsigned long long ad = desc_k_major(Qs + (kk >> 2) * kTile) + 2 * (kk & 3);
-                    const unsigned long long bd = desc_k_major(Ks + s * kKBytes + (kk >> 2) * kTile) + 2 * (kk & 3);
-                    umma(tmem_base, ad, bd, kIdescS, kk > 0 ? 1u : 0u);
+                    const unsigned long long ad = q_desc + (unsigned)((kk >> 2) * (kTile >> 4) + 2 * (kk & 3));
+                    const unsigned long long bd = k_desc + (unsigned)(ks * (kKBytes >> 4) + (kk >> 2) * (kPage >> 4) + 2 * (kk & 3));
+                    umma(tmem_base + (unsigned)(t * BKV), ad, bd, kIdescS, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(k_empty + s);
-                umma_commit(s_full);
-                // PV = P V once the probabilities are written (which also says that S and the last PV were read)
-                if (!mbar_wait(p_full, j & 1)) { atomicCAS(a.status, 0, TC_ATTN_P); break; }
-                if (!mbar_wait(v_full, j & 1)) { atomicCAS(a.status, 0, TC_ATTN_V); break; }
+                umma_commit(k_empty + ks);
+                umma_commit(s_full + t);
+            }
+        }
+    } else if (warp == 2) {
+        if (lane == 0) {
+            // ---------------- tensor core, values: O += P(j) V(j) ----------------
+            constexpr unsigned kIdescPV = idesc(HD, true);
+            const unsigned long long v_desc = desc_mn_major(Vs, kPage);
+            for (int j = 0; j < n_blocks; ++j) {
+                const int b = j & 1, t = j % kSRing;
+                if (!mbar_wait(p_full + t, (j / kSRing) & 1)) { atomicCAS(a.status, 0, TC_ATTN_P); break; }
+                if (!mbar_wait(v_full + b, (j >> 1) & 1)) { atomicCAS(a.status, 0, TC_ATTN_V); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
                 for (int kk = 0; kk < BKV / 16; ++kk) {
-                    const unsigned long long ad = desc_k_major(Ps + (kk >> 2) * kTile) + 2 * (kk & 3);
-                    // 16 keys further: two groups of eight rows, 2048 bytes
-                    const unsigned long long bd = desc_mn_major(Vs, kTile) + (unsigned long long)(kk * (2048 >> 4));
-                    umma(tmem_base + 128, ad, bd, kIdescPV, (j > 0 || kk > 0) ? 1u : 0u);      // O accumulates over the blocks
+                    // A: the probabilities in tensor memory, 16 keys = 8 columns of two bf16 a step; B: 16 keys further
+                    // are two groups of eight rows, 2048 bytes
+                    const unsigned long long bd = v_desc + (unsigned)(b * (kVBytes >> 4) + kk * (2048 >> 4));
+                    umma_a_tmem(tmem_base + kOCol, tmem_base + (unsigned)(t * BKV + 8 * kk), bd, kIdescPV, (j > 0 || kk > 0) ? 1u : 0u);      // O accumulates over the steps
                 }
-                umma_commit(v_empty);
-                umma_commit(pv_full);
+                umma_commit(pv_done + t);
             }
         }
     } else {
         // ---------------- softmax: thread <-> query row ----------------
-        const int quarter = warp & 3;
+        const int quarter = warp & 3;                            // the lanes of tensor memory this warp may read
         const int r = quarter * 32 + lane;                       // row of the tile, lane of tensor memory
         const bool live = r < rows;
         const int pos = start + q0 + r;                          // this row's position: it sees keys lo .. pos
         const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-        const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16);
+        const unsigned trow = tmem_base + ((unsigned)(quarter * 32) << 16);
         // O accumulates in tensor memory over the blocks, against a reference maximum m_run per row that only
         // moves when a block's maximum exceeds it by more than 2^kLazy: then the row of O is rescaled in tensor
         // memory (read, multiply, write back).  Otherwise probabilities may exceed one, by at most that factor.
@@ -317,12 +373,16 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
         bool ok = true;
         for (int j = 0; j < n_blocks && ok; ++j) {
             const int key0 = (kb_lo + j) * BKV;
-            if (r == 0) blm_trace_here(0x500);
-            if (!mbar_wait(s_full, j & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_S); ok = false; break; }
+            const int b = j & 1, t = j % kSRing;                 // which P tile and V stage, which S columns this step has
+            if (!mbar_wait(s_full + t, (j / kSRing) & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_S); ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            if (r == 0) blm_trace_here(0x510);
-            // A block whose every key every row sees (all but the diagonal and the window's edge) needs no masks.
-            const bool open_block = key0 + BKV - 1 <= start + q0 && (a.window <= 0 || key0 >= start + q0 + BQ - a.window);
+            // Decided by warp (32 rows): a page whose every key every row of the warp sees needs no masks (all but
+            // the diagonal and the window's edge); one of which no row of the warp sees a key gives probabilities
+            // of zero without a look at the scores.
+            const unsigned taddr = trow + (unsigned)(t * BKV);
+            const int wpos_lo = start + q0 + quarter * 32, wpos_hi = wpos_lo + 31;
+            const bool open_block = key0 + BKV - 1 <= wpos_lo && (a.window <= 0 || key0 >= wpos_hi - a.window + 1);
+            const bool dead = key0 > wpos_hi || (a.window > 0 && key0 + BKV - 1 < wpos_lo - a.window + 1);
             unsigned buf[2][32];           // two loads of 32 columns: one in flight, one being worked on
             float rs4[4] = {0.f, 0.f, 0.f, 0.f};
             // An open block of a row that has its reference maximum already: ONE pass over the scores.  The
@@ -330,8 +390,14 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
             // maximum; only if some row of the warp has outgrown its reference by more than 2^kLazy (rare after
             // the first blocks) is the step done again the long way, maximum first.  The numbers are the same
             // either way: the same reference, the same operations.
-            bool done = false;
-            if (open_block && __all_sync(0xffffffffu, m_run != -INFINITY)) {
+            // the row's probabilities as bf16 pairs: kept in registers until the scores need not be read again, then
+            // written over the first 32 of their columns
+            unsigned packed[BKV / 2];
+            bool done = dead;
+            if (dead) {
+#pragma unroll
+                for (int i = 0; i < BKV / 2; ++i) packed[i] = 0u;
+            } else if (open_block && __all_sync(0xffffffffu, m_run != -INFINITY)) {
                 const float neg_ref = -m_run;
                 float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                 tmem_ld32_issue(taddr, buf[0]);
@@ -339,7 +405,6 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
                 for (int c = 0; c < BKV / 32; ++c) {
                     tmem_ld32_wait(buf[c & 1]);
                     if (c + 1 < BKV / 32) tmem_ld32_issue(taddr + (c + 1) * 32, buf[(c + 1) & 1]);
-                    unsigned packed[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
                         const float s0 = __uint_as_float(buf[c & 1][i]), s1 = __uint_as_float(buf[c & 1][i + 1]);
@@ -347,20 +412,12 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
                         const float p0 = ex2(fmaf(s0, a.scale_log2e, neg_ref)), p1 = ex2(fmaf(s1, a.scale_log2e, neg_ref));
                         rs4[(i >> 1) & 3] += p0 + p1;
                         const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-                        packed[i >> 1] = *reinterpret_cast<const unsigned*>(&pk);
-                    }
-                    unsigned char* prow = Ps + (c >> 1) * kTile + r * 128;
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const int chunk = (c & 1) * 4 + q4;
-                        *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
-                            make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                        packed[c * 16 + (i >> 1)] = *reinterpret_cast<const unsigned*>(&pk);
                     }
                 }
                 const float m_one = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * a.scale_log2e;
                 done = !__any_sync(0xffffffffu, m_one > m_run + kLazy);
                 if (!done) { rs4[0] = 0.f; rs4[1] = 0.f; rs4[2] = 0.f; rs4[3] = 0.f; }
-                if (r == 0) blm_trace_here(0x520);
             }
             if (!done) {
                 // the row's maximum (of the raw scores: the scale is positive)
@@ -370,7 +427,7 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
                 for (int c = 0; c < BKV / 32; ++c) {
                     tmem_ld32_wait(buf[c & 1]);
                     // the next columns of this pass, or the first of the next pass
-                    tmem_ld32_issue(taddr + ((c + 1) & 3) * 32, buf[(c + 1) & 1]);
+                    tmem_ld32_issue(taddr + ((c + 1) % (BKV / 32)) * 32, buf[(c + 1) & 1]);
                     float v[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(buf[c & 1][i]);
@@ -387,22 +444,21 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
                         }
                     }
                 }
-                if (r == 0) blm_trace_here(0x520);
                 const float m_blk = mx * a.scale_log2e;
                 const bool move = m_blk > m_run + kLazy;                     // also the first block that shows the row a key
                 if (__any_sync(0xffffffffu, move)) {
                     const float alpha = move ? (m_run == -INFINITY ? 0.f : ex2(m_run - m_blk)) : 1.0f;
                     if (j > 0) {
                         // the last product into O must have landed before its rows are touched
-                        if (!mbar_wait(pv_full, (j - 1) & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_PV); ok = false; break; }
+                        if (!mbar_wait(pv_done + (j - 1) % kSRing, ((j - 1) / kSRing) & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_PV); ok = false; break; }
                         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll 1
                         for (int c = 0; c < HD / 32; ++c) {
                             float v[32];
-                            tmem_ld32(taddr + 128 + c * 32, v);
+                            tmem_ld32(trow + kOCol + c * 32, v);
 #pragma unroll
                             for (int i = 0; i < 32; ++i) v[i] *= alpha;
-                            tmem_st32(taddr + 128 + c * 32, v);
+                            tmem_st32(trow + kOCol + c * 32, v);
                         }
                     }
                     if (move) {
@@ -419,14 +475,13 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
                     float v[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(buf[c & 1][i]);
-                    unsigned packed[16];
                     if (open_block) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
                             const float p0 = ex2(fmaf(v[i], a.scale_log2e, neg_m)), p1 = ex2(fmaf(v[i + 1], a.scale_log2e, neg_m));
                             rs4[(i >> 1) & 3] += p0 + p1;
                             const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-                            packed[i >> 1] = *reinterpret_cast<const unsigned*>(&pk);
+                            packed[c * 16 + (i >> 1)] = *reinterpret_cast<const unsigned*>(&pk);
                         }
                     } else {
 #pragma unroll
@@ -436,49 +491,41 @@ __global__ void __launch_bounds__(attn_tc::kThreads) attn_prefill_tc_kernel(cons
                             const float p1 = (live && key + 1 >= lo && key + 1 <= pos) ? ex2(fmaf(v[i + 1], a.scale_log2e, neg_m)) : 0.f;
                             rs4[(i >> 1) & 3] += p0 + p1;
                             const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-                            packed[i >> 1] = *reinterpret_cast<const unsigned*>(&pk);
+                            packed[c * 16 + (i >> 1)] = *reinterpret_cast<const unsigned*>(&pk);
                         }
-                    }
-                    unsigned char* prow = Ps + (c >> 1) * kTile + r * 128;
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const int chunk = (c & 1) * 4 + q4;
-                        *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
-                            make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
                     }
                 }
             }
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-            if (r == 0) blm_trace_here(0x530);
             l_run += rs;
             // value rows no key of the sequence has written (beyond its last key) may hold anything: cleared
             if (key0 + BKV > kv_total) {
-                if (!mbar_wait(v_full, j & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_V); ok = false; break; }
-                if (key0 + r >= kv_total) {
+                if (!mbar_wait(v_full + b, (j >> 1) & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_V); ok = false; break; }
+                if (r < BKV && key0 + r >= kv_total) {
 #pragma unroll
                     for (int h = 0; h < SUB; ++h)
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(Vs + h * kTile + r * 128 + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                        for (int c = 0; c < 8; ++c)
+                            *reinterpret_cast<uint4*>(Vs + b * kVBytes + h * kPage + r * 128 + c * 16) = make_uint4(0u, 0u, 0u, 0u);
                 }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // these writes become visible to the tensor core
             }
-            // the writes to shared memory become visible to the tensor core; S has been read
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            tmem_st32_bits(taddr, packed);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
-            if (r == 0) blm_trace_here(0x540);
+            if (lane == 0) mbar_arrive(p_full + t);
         }
         // the last product into O, then the row: O / l
         float o[HD];
         if (ok) {
-            if (!mbar_wait(pv_full, (n_blocks - 1) & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_PV); ok = false; }
+            if (!mbar_wait(pv_done + (n_blocks - 1) % kSRing, ((n_blocks - 1) / kSRing) & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_PV); ok = false; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         }
         if (ok) {
 #pragma unroll
             for (int c = 0; c < HD / 32; ++c) {
                 float v[32];
-                tmem_ld32(taddr + 128 + c * 32, v);
+                tmem_ld32(trow + kOCol + c * 32, v);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) o[c * 32 + i] = v[i];
             }
@@ -546,7 +593,7 @@ static bool attn_tc_map(const void* base, long long ld, long long rows, int widt
 template <int HD>
 static int attn_prefill_tc_launch(const AttnPrefillTcArgs& a, const CUtensorMap& qmap, const CUtensorMap& pmap, dim3 grid, cudaStream_t stream) {
     constexpr int SUB = HD / 64;
-    const size_t smem = (size_t)(SUB + 2 * SUB + SUB + 2) * 128 * 128 + 16 * 8 + 16 + 1024;
+    const size_t smem = (size_t)SUB * 128 * 128 + (size_t)(attn_tc::key_stages(HD) + attn_tc::kVStages) * SUB * 64 * 128 + 24 * 8 + 16 + 1024;
     static bool opted_in = false;
     if (!opted_in) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
