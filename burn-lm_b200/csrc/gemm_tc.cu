@@ -57,6 +57,17 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned
 }
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
     const unsigned addr = smem_u32(bar);
+    {   // a phase that is over already answers at once (the blocking form takes some hundred cycles even then)
+        unsigned done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
     for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
         unsigned done;
         asm volatile(
@@ -218,6 +229,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs a, co
             unsigned it = 0;
             int n_tile = 0;
             bool ok = true;
+            // operand descriptors: the address field counts 16 bytes, so a stage further is an addition
+            const unsigned long long a_desc = umma_desc(As), b_desc = umma_desc(Bs);
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++n_tile) {
                 const int b = n_tile & 1;
                 if (n_tile >= 2 && !mbar_wait(acc_empty + b, ((n_tile >> 1) - 1) & 1)) {      // the epilogue has read this accumulator
@@ -235,7 +248,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs a, co
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    const unsigned long long ad = umma_desc(As + s * kABytes), bd = umma_desc(Bs + s * kBBytes);
+                    const unsigned long long ad = a_desc + (unsigned)(s * (kABytes >> 4)), bd = b_desc + (unsigned)(s * (kBBytes >> 4));
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk)      // 16 bf16 = 32 bytes further along the swizzled row: +2 in the address field
                         umma(tmem_d, ad + 2 * kk, bd + 2 * kk, (k > 0 || kk > 0) ? 1u : 0u);

@@ -635,6 +635,10 @@ PLANTED = [
     (0, 300, 128, [0, 1, 63, 64, 127, 128, 171, 172, 299]),
     (10, 50, 24, [0, 9, 10, 35, 36, 59]),
     (100, 33, 37, [63, 64, 95, 96, 100, 132]),
+    # two dozen pages: the rings of key pages, value pages and score tiles go round several times before the planted
+    # key makes a row move its reference maximum and rescale what it has summed
+    (1000, 600, 0, [0, 640, 999, 1000, 1343, 1599]),
+    (900, 700, 512, [388, 389, 900, 1087, 1088, 1599]),
 ]
 
 
