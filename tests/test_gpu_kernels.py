@@ -621,6 +621,17 @@ def test_prompt_attention_on_tensor_cores(H, KV, hd):
     run_attention_case(torch.bfloat16, H, KV, hd, [0, 130, 64], [200, 90, 31], 75, 1, seed=52)
 
 
+@pytest.mark.parametrize("H,KV,hd", [(8, 2, 64), (6, 2, 128)])
+def test_prompt_attention_over_thousands_of_keys(H, KV, hd):
+    """Prompts of the lengths that are served: 4,096 tokens at once (64 pages: every ring of the kernel goes round
+    many times, and the long blocks run beside short ones), long prompts that continue a long cached prefix, a
+    batch of unequal prompts, and a window of a thousand keys; against the general kernel and the plain
+    restatement."""
+    run_attention_case(torch.bfloat16, H, KV, hd, [0], [4096], 0, 1, seed=80)
+    run_attention_case(torch.bfloat16, H, KV, hd, [2000, 130, 0], [1500, 700, 333], 0, 1, seed=81)
+    run_attention_case(torch.bfloat16, H, KV, hd, [1000, 0], [1100, 2100], 1000, 1, seed=82)
+
+
 # (cached tokens, new tokens, window, positions of the planted key).  16 to 63 new tokens take the mma.sync prompt
 # kernel in bfloat16, 64 and more the tcgen05 one.  Planted: the first key, the ends of pages (63, 64, 127, 128),
 # the last cached key and the first new one, the last key of a partial page; with a window w, for a row at position
