@@ -334,7 +334,7 @@ BLM_API int blm_attention(const void* q, long long q_stride, const void* pool, i
                           const int* slot_of_seq, const int* start_pos, void* out, float* scratch,
                           int n_tokens, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd,
                           int page_size, int window, int n_splits, float scale, int general_only, int* status,
-                          int n_pages, int max_kv_len, const int* seq_table, cudaStream_t stream) {
+                          int n_pages, int max_kv_len, const int* seq_table, int ahead, cudaStream_t stream) {
     if (n_tokens == 0 || n_seqs == 0) return BLM_OK;
     BLM_REQUIRE(page_size == kPage, "attention: the cache page holds %d positions, the kernel wants %d", page_size, kPage);
     BLM_REQUIRE(hd >= 16 && hd <= 8 * kColGroups * kChunksMax && hd % 16 == 0,
@@ -354,6 +354,7 @@ BLM_API int blm_attention(const void* q, long long q_stride, const void* pool, i
         d.n_heads = n_heads; d.n_kv = n_kv; d.window = window; d.n_splits = n_splits;
         d.scale_log2e = scale * 1.4426950408889634f;
         d.status = status;
+        d.ahead = ahead ? 1 : 0;
         BLM_REQUIRE(status != nullptr, "attention: no status word");
         BLM_REQUIRE(n_splits <= 64, "attention: at most 64 splits, got %d", n_splits);
         BLM_REQUIRE(n_pages > 0 && ((size_t)pool & 15) == 0, "attention: the pool's page count is needed");

@@ -36,6 +36,10 @@ struct AttnDecodeArgs {
     int n_groups;                // groups of four consumer warps; group g takes pages g, g + n_groups, ... of the block's
     float scale_log2e;           // softmax scale times log2(e): scores live in base-2 units
     int* status;                 // 0, or 21 / 22 when a bounded wait ran out
+    // 1: the kernel before this one let it start only after its own wait, so all but that kernel's work (the step's
+    // positions and page tables, the cache pages of earlier tokens) is written and may be read before this kernel's
+    // wait; only q and the page that holds the new token wait for it
+    int ahead;
 };
 
 // How many of the n_splits blocks of a (sequence, kv head) work: at most one per page the keys touch.
@@ -145,7 +149,7 @@ __global__ void __launch_bounds__((4 * NG + 1) * 32) attn_decode_kernel(const At
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     pdl_launch_dependents();
     blm_trace(0x400);
-    pdl_wait();          // the queries and this step's keys are the work of the kernels before
+    if (!a.ahead) pdl_wait();          // the queries and this step's keys are the work of the kernels before
     blm_trace(0x410);
     const int tok = seq;                         // one token per sequence: the packed row is the sequence
     const int pos = a.start_pos[seq];            // the new token's position; keys 0..pos are visible
@@ -184,6 +188,7 @@ __global__ void __launch_bounds__((4 * NG + 1) * 32) attn_decode_kernel(const At
             const int n = min(32, pg_hi - base);
             for (int j = 0; j < n; ++j, ++i) {
                 const int page = __shfl_sync(0xffffffffu, mine, j);
+                if (a.ahead && base + j == (kv_len - 1) / 64) pdl_wait();      // the page the new token was just written to
                 if (++s == S) { s = 0; phase ^= 1; }
                 if (lane != 0 || failed) continue;
                 if (i >= S && !mbar_wait(empty + s, phase ^ 1)) {
@@ -211,6 +216,7 @@ __global__ void __launch_bounds__((4 * NG + 1) * 32) attn_decode_kernel(const At
     } else {
         // ---------------- consumers: the warps of a group take 16 keys each of the group's pages ----------------
         // Q as the A operand: row g is head g of the group (rows G.. and 8.. are zero)
+        if (a.ahead) pdl_wait();
         unsigned qf[KS][4];
         {
             const __nv_bfloat16* qrow = a.q + (size_t)tok * a.q_stride + (size_t)(kvh * G + (g < G ? g : 0)) * HD;

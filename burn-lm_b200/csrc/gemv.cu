@@ -298,8 +298,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
     }
     __syncthreads();
     // The weights are nobody's output: the producer streams them at once, also while the kernel before this
-    // one still runs; the consumers wait for it before they touch the tokens.
-    pdl_launch_dependents();
+    // one still runs; the consumers wait for it before they touch the tokens.  The rotary product lets its
+    // dependent start only after its own wait: that kernel (the attention) may then take everything but this
+    // product's output as written, the cache pages of earlier tokens among it, and fetch them before its own wait.
+    if (a.epi != EPI_ROPE) pdl_launch_dependents();
 
     if (warp == kConsumerWarps) {
         // ---------------- producer: lane w of this warp feeds consumer warp w's part of the ring ----------------
@@ -395,6 +397,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a,
     // ---------------- consumers ----------------
     blm_trace(0x100 | a.epi);
     pdl_wait();
+    if (a.epi == EPI_ROPE) pdl_launch_dependents();
     blm_trace(0x110 | a.epi);
     if (a.x_mode == X_STAGED) gemv_stage_tokens<NBT>(a, xs, xstride, kpad, tid, lane, warp);
     if (a.ssq_in != nullptr) {

@@ -85,7 +85,7 @@ _protos = {
     "attention": {
         "blm_attention": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                          c_int, c_int, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
+                          c_int, c_int, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
     },
     "gemm": {
         "blm_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
@@ -302,7 +302,7 @@ def attention_scratch_floats(n_tokens, n_heads, head_dim, n_splits):
 
 def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos, out, n_tokens, n_seqs,
               max_q_len, n_heads, n_kv, head_dim, scale, window=0, n_splits=1, scratch=None, general_only=False,
-              max_kv_len=0, seq_table=None):
+              max_kv_len=0, seq_table=None, ahead=False):
     """Causal grouped-query attention of the step's tokens over the paged cache (after the append).
 
     q: tensor whose token n, head h starts at element n * q_stride + h * head_dim (the qkv buffer).
@@ -312,7 +312,10 @@ def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos
     attention_scratch_floats(...) elements).  bfloat16 steps of one token per sequence with a head
     size of 64 or 128 and up to 8 query heads per kv head run a specialised kernel unless
     `general_only`; `max_kv_len` (the longest sequence after the step, when known) lets it size its
-    rings of pages; `seq_table` (from step_tables) spares it the way through the slots."""
+    rings of pages; `seq_table` (from step_tables) spares it the way through the slots.  `ahead`: the kernel
+    launched just before this one was gemv() with `rope`, which lets its successor start only after its own wait;
+    the specialised kernel then reads the step's tables and fetches the pages of earlier tokens before it waits
+    for that kernel itself (for q and the page of the new token).  Say so only when it is so."""
     _need_cuda(q, pool, block_table, cu_seqlens, slot_of_seq, start_pos, out, scratch, seq_table)
     if seq_table is not None and (seq_table.dtype != torch.int32 or tuple(seq_table.shape) != (n_seqs, block_table.shape[1])):
         raise KernelError("attention: seq_table must be int32 [n_seqs, pages per sequence]")
@@ -327,8 +330,8 @@ def attention(q, q_stride, pool, block_table, cu_seqlens, slot_of_seq, start_pos
     _call("attention", "blm_attention", _ptr(q), q_stride, _ptr(pool), _code(q.dtype), _ptr(block_table),
           block_table.shape[1], _ptr(cu_seqlens), _ptr(slot_of_seq), _ptr(start_pos), _ptr(out), _ptr(scratch),
           n_tokens, n_seqs, max_q_len, n_heads, n_kv, head_dim, PAGE, int(window or 0), n_splits,
-          c_float(scale), 1 if general_only else 0, _ptr(status_word(q.device)), pool.shape[0], int(max_kv_len), _ptr(seq_table), _stream(),
-          kernels=2 if n_splits > 1 else 1)
+          c_float(scale), 1 if general_only else 0, _ptr(status_word(q.device)), pool.shape[0], int(max_kv_len), _ptr(seq_table),
+          1 if ahead else 0, _stream(), kernels=2 if n_splits > 1 else 1)
 
 
 def gemm_f32(x, w, out=None):

@@ -127,6 +127,7 @@ class Attention(Part):
         n = step.n_tokens
         product = self.qkv if cache.writes else self.q_only     # a run that reads another run's cache line needs q only
         qkv = None
+        ahead = False
         # the page of every new token and the sequences' rows of the block table: looked up once per step for all
         # the layers that share this block table
         tables = None
@@ -142,8 +143,10 @@ class Attention(Part):
                         block_table=cache.block_table, table=table, pool=cache.pool, n_heads=s.n_heads,
                         n_kv=s.n_kv_heads, head_dim=s.head_dim, write_cache=cache.writes, max_position=step.max_kv_len - 1,
                         token_page=tables[0] if tables is not None else None)
-            if product.with_rotary(x, q, rope):
+            took = product.with_rotary(x, q, rope)
+            if took:
                 qkv = q
+                ahead = took == "skinny"      # that kernel lets the attention start only after its own wait
         if qkv is None:
             qkv = product(x, out_dtype=rt.dtype)
             K.rope_append(qkv, step.token_seq, step.token_pos, step.slot_of_seq, cache.block_table, inv_freq, rot,
@@ -157,5 +160,5 @@ class Attention(Part):
         K.attention(qkv, qkv.shape[1], cache.pool, cache.block_table, step.cu_seqlens, step.slot_of_seq,
                     step.start_pos, out, n, step.n_seqs, step.max_q_len, s.n_heads, s.n_kv_heads, s.head_dim,
                     self.scale, window=s.window or 0, n_splits=n_splits, scratch=scratch, max_kv_len=step.max_kv_len,
-                    seq_table=tables[1] if tables is not None else None)
+                    seq_table=tables[1] if tables is not None else None, ahead=ahead)
         return self.o.into_stream(out, stream, rt.dtype, handoff=getattr(step, "handoff", None))

@@ -199,20 +199,21 @@ class Linear:
             return None
         return self(x, out_dtype)
 
-    def with_rotary(self, x, q_out: torch.Tensor, rope: dict) -> bool:
-        """For a [q; k; v] weight whose q and k rows are in kernels.tiled_pair_order(): when the skinny kernel
-        takes the step, it rotates q and k and appends k and v to the cache in its epilogue, writes q to
-        `q_out` and this returns True; else nothing is done."""
+    def with_rotary(self, x, q_out: torch.Tensor, rope: dict) -> str:
+        """For a [q; k; v] weight whose q and k rows are in kernels.tiled_pair_order(): when one of this package's
+        skinny products takes the step, it rotates q and k and appends k and v to the cache in its epilogue, writes q
+        to `q_out`, and this returns which one did ("skinny": kernels.gemv, "cluster": kernels.gemm_sk); else nothing
+        is done and "" comes back."""
         n = self._tokens(x)
         if q_out.dtype != torch.bfloat16:
-            return False
+            return ""
         if self._skinny(n, self.out_features, x):
             K.gemv(self.weight, n, out=q_out, rope=rope, **self._source(x))
-            return True
+            return "skinny"
         if self._sk(n):
             K.gemm_sk(self.weight, out=q_out, rope=rope, **self._sk_source(x))
-            return True
-        return False
+            return "cluster"
+        return ""
 
     def gated(self, x, out_dtype: torch.dtype) -> torch.Tensor:
         """silu(x Wgate^T) * (x Wup^T) for a fused [gate; up] weight."""
