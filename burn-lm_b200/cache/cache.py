@@ -5,9 +5,12 @@ Storage is sized in tokens.  Keys and values live in pages of 64 positions; a se
 many pages as its length needs, listed in its row of the block table, so `max_tokens` bounds the sum
 over live sequences of their lengths rounded up to 64, whatever their number.  Runs of the schedule
 whose mixers need the same thing (all keys of n heads of size d; a window; a state of some shape)
-form a group with storage, page allocator and block table of its own.  Pages and slots are given
-back when a sequence ends and are used again without being cleared: a kernel never reads a
-position at or beyond a sequence's length.  State blocks are zeroed when a slot is acquired.
+form a group with storage, page allocator and block table of its own.  A group whose mixers look
+back over a window only gives a sequence's pages back as soon as every key in them lies before the
+window of every token still to come, so a long sequence holds about window / 64 + 2 of its pages.
+Pages and slots are given back when a sequence ends and are used again without being cleared: a
+kernel never reads a position at or beyond a sequence's length, nor one before the window.  State
+blocks are zeroed when a slot is acquired.
 
 The reference preallocates [max_batch, kv heads, max_seq_len, head_dim] per layer with one length
 for the whole batch (crates/burn-lm-llama/src/nn/attention/kv_cache.rs:14-34, nn/transformer.rs:
@@ -41,7 +44,28 @@ class _KVGroup:
         self.pool = torch.empty((len(runs), n_pages, 2, need.n_kv_heads, PAGE, need.head_dim), dtype=dtype, device=device)
         self.pages = IdAllocator(n_pages, "cache page")
         self.block_table = torch.zeros((max_seqs, max_pages_per_seq), dtype=torch.int32, device=device)
-        self.pages_of: list[list[int]] = [[] for _ in range(max_seqs)]
+        # pages_of[slot][i]: the page that holds positions 64 i .. 64 i + 63 of the slot's sequence, or None once a
+        # windowed group has given it back; dropped[slot]: how many leading pages that is
+        self.pages_of: list[list] = [[] for _ in range(max_seqs)]
+        self.dropped = [0] * max_seqs
+
+    def live_pages(self, slot: int) -> list:
+        return self.pages_of[slot][self.dropped[slot]:]
+
+    def drop_before_window(self, slot: int, length: int) -> None:
+        """`length`: how long the slot's sequence is now; the tokens still to come sit at positions >= length and see
+        the keys from length - window + 1 on.  Pages that lie wholly before that are given back."""
+        if not self.need.window:
+            return
+        first_needed = max(0, length - self.need.window + 1) // PAGE
+        last = min(first_needed, len(self.pages_of[slot]))
+        if last > self.dropped[slot]:
+            for i in range(self.dropped[slot], last):
+                self.pages.release(self.pages_of[slot][i])
+                self.pages_of[slot][i] = None
+            # the table's entries stay valid page numbers: no kernel reads them, but none may point outside the pool
+            self.block_table[slot, self.dropped[slot]:last] = 0
+            self.dropped[slot] = last
 
     def bytes(self):
         return self.pool.numel() * self.pool.element_size()
@@ -74,8 +98,8 @@ class Cache:
                 by_need.setdefault(need, []).append(run)
         for need, runs in by_need.items():
             if need.kind == "kv":
-                # (a windowed group has storage of its own; the window is applied in the kernels and
-                # the group still keeps every page of a sequence)
+                # (a windowed group has storage of its own; the window is applied in the kernels, and the
+                # group gives the pages before it back as the sequence grows)
                 g = _KVGroup(need, runs, self.n_pages, max_seqs, self.max_pages_per_seq, dtype, device)
                 self._kv_groups.append(g)
                 for i, r in enumerate(runs):
@@ -127,9 +151,10 @@ class Cache:
         if not self.slots.held(slot):
             raise CacheError(f"sequence slot {slot} is released but not held")
         for g in self._kv_groups:
-            for p in g.pages_of[slot]:
+            for p in g.live_pages(slot):
                 g.pages.release(p)
             g.pages_of[slot] = []
+            g.dropped[slot] = 0
         self.seq_len[slot] = 0
         self.slots.release(slot)
 
@@ -139,7 +164,7 @@ class Cache:
                 self.release(slot)
 
     def reserve(self, growth: list) -> None:
-        """Make room for every (slot, new_length) pair, or change nothing and raise."""
+        """Make room for every (slot, new_length) pair, or acquire nothing and raise."""
         plan = []
         for slot, new_len in growth:
             if not self.slots.held(slot):
@@ -147,6 +172,11 @@ class Cache:
             if new_len > self.max_seq_len:
                 raise ContextLengthExceeded(new_len, self.max_seq_len)
             plan.append((slot, (new_len + PAGE - 1) // PAGE))
+        # what lies before the window of every token still to come goes back first (the sequence's length is that of
+        # the steps already run: this step's tokens start there)
+        for g in self._kv_groups:
+            for slot, _ in plan:
+                g.drop_before_window(slot, self.seq_len[slot])
         for g in self._kv_groups:
             extra = sum(max(0, pages - len(g.pages_of[slot])) for slot, pages in plan)
             if extra > g.pages.free_count:

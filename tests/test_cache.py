@@ -58,6 +58,39 @@ def test_windowed_runs_get_storage_of_their_own():
     assert c.view(0).block_table is not c.view(1).block_table and c.view(1).window == 32
 
 
+def test_a_windowed_group_gives_back_what_lies_before_the_window():
+    """Two groups, one with a window of 100 keys: as a sequence grows, the windowed group holds only the pages that
+    a token still to come can see (about window / 64 + 2), the other one all of them; nothing is lost or held
+    twice, and what a second sequence is given are the pages the first one gave back."""
+    full = CacheNeed("kv", n_kv_heads=2, head_dim=16)
+    win = CacheNeed("kv", n_kv_heads=2, head_dim=16, window=100)
+    c = Cache([full, win], [ScheduleEntry(0), ScheduleEntry(1)], 64 * 12, 2, 64 * 10, torch.float32, torch.device("cpu"))
+    gf, gw = c._kv_groups
+    assert not gf.need.window and gw.need.window == 100
+    a = c.acquire()
+    length = 0
+    for grow in (70, 30, 1, 1, 200, 64, 1, 150):
+        c.reserve([(a, length + grow)])
+        length += grow
+        c.set_length(a, length)
+        live = gw.live_pages(a)
+        assert None not in live and len(set(live)) == len(live)
+        assert len(gf.live_pages(a)) == -(-length // 64) == len(gw.pages_of[a])
+        assert len(live) + gw.pages.free_count == c.n_pages
+        # the step that made the sequence this long still saw its keys from (length - grow) - 99 on
+        assert gw.dropped[a] == max(0, (length - grow) - 99) // 64
+    assert length == 517 and gw.dropped[a] == 4 and len(gw.live_pages(a)) == 5
+    assert c.view(1).block_table[a, :4].tolist() == [0, 0, 0, 0]
+    held = set(gw.live_pages(a))
+    b = c.acquire()
+    c.reserve([(a, 518), (b, 64 * 3)])  # a's next dead pages go back first; b is given pages (lowest first)
+    assert not (set(gw.live_pages(b)) & set(gw.live_pages(a))) and gw.dropped[a] == (517 - 99) // 64
+    assert set(gw.live_pages(b)) & held                       # among them pages that a held a moment ago
+    c.release(a)
+    c.release(b)
+    assert gw.pages.free_count == gf.pages.free_count == c.n_pages and gw.dropped == [0, 0]
+
+
 def test_reserve_release_and_reuse():
     c = make_cache()
     a, b = c.acquire(), c.acquire()

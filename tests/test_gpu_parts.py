@@ -550,6 +550,44 @@ def test_layers_with_and_without_a_window_in_one_model(tmp_path, dtype, toleranc
         eng.verify()
 
 
+def test_windowed_layers_give_pages_back_while_sequences_grow(tmp_path):
+    """Sequences of some hundred tokens on the model with a window of 24 keys in every other layer: the windowed
+    group holds two or three pages a sequence however long it gets, the pages it gives back go to the other
+    sequences of the batch and to the next batch, and every logit is still the plain model's (bfloat16, captured
+    decode steps; prompts in two steps, then up to 200 single tokens, the shorter requests leaving earlier)."""
+    import traces
+    from burn_lm_b200 import Engine, write_random_model
+    from tiny import random_tokens, row_error
+    register_windowed_toy()
+    cfg = {"architectures": ["ToyWindowedLM"], "model_type": "toy", "num_hidden_layers": 4, "hidden_size": 128,
+           "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 192, "vocab_size": 300,
+           "rope_theta": 10000.0, "rope_scaling": None, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+           "max_position_embeddings": 512, "hidden_act": "silu"}
+    folder = write_random_model(str(tmp_path / "windowed_long"), cfg, seed=6, dtype="bfloat16")
+    _, tensors = P.read_model_folder(folder)
+    lengths = [500, 333, 260, 410, 129, 480]
+    reqs = {f"r{n}": random_tokens(20 + n, length, 300) for n, length in enumerate(lengths)}
+    steps = traces.batched(reqs, 3, [200, 60, 130], prompt_steps=2)
+    eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=traces.max_live_tokens(steps), max_seqs=3)
+    windowed = [g for g in eng.cache._kv_groups if g.need.window][0]
+    most_held = 0
+    real_reserve = eng.cache.reserve
+
+    def watching(growth):
+        nonlocal most_held
+        real_reserve(growth)
+        most_held = max(most_held, max(len(windowed.live_pages(s)) for s, _ in growth))
+    eng.cache.reserve = watching
+    got = traces.run_in_process(eng, steps, str(tmp_path / "o"), 300)
+    eng.verify()
+    assert max(windowed.dropped) == 0 and windowed.pages.free_count == eng.cache.n_pages      # all given back at the end
+    # a prompt part of up to 150 tokens needs its own pages and those of the window before it; a decoding sequence two
+    assert most_held <= 4
+    for rid, toks in reqs.items():
+        err = row_error(got[rid], windowed_plain(cfg, tensors, toks))
+        assert err.max() < 3e-2, (rid, len(toks), float(err.max()), int(err.argmax()))
+
+
 # --------------------------------------------------------------------------------------------------
 # a fourth toy: another arrangement of a layer's parts.  One norm feeds the mixer and the feed-forward
 # side by side, h = x + mixer(norm(x)) + feed_forward(norm(x)); every third layer has no feed-forward at
