@@ -1,5 +1,6 @@
 // Matrix product for prompts on the 5th-generation tensor cores: y[M, N] = x[M, K] . W[N, K]^T, bf16
-// operands, fp32 accumulation in tensor memory, with the gated activation fused into the epilogue.
+// operands, fp32 accumulation in tensor memory, with the gated activation or the addition into the fp32
+// residual stream fused into the epilogue.
 //
 // Persistent blocks, one per SM, walk 128 x 256 tiles of y.  Warp 0 (one thread) is the producer: TMA
 // tile loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of 128 x 64 of x and 256 x 64 of W per stage
@@ -11,7 +12,8 @@
 // store bf16, while the tensor core already fills the other accumulator with the next tile; for a fused
 // [gate; up] weight laid out in tiles of 8 gate rows followed by their 8 up rows, 16 columns are
 // exactly 8 gates and their 8 ups, so silu(gate) * up is formed in registers and the [M, 2 I]
-// intermediate never exists.  Edges: the TMA fills what lies outside x or W with zeros, the epilogue
+// intermediate never exists; with the stream epilogue the product is added into an fp32 [M, N] matrix in place
+// (one writer per element), so a prompt step's output and down products need no bf16 round trip.  Edges: the TMA fills what lies outside x or W with zeros, the epilogue
 // stores only what lies inside y.
 //
 // Every mbarrier wait is bounded; a wait that runs out records a code in the caller's status word and
@@ -34,12 +36,13 @@ constexpr int kTmemCols = 512;                  // two fp32 accumulators of 256 
 constexpr unsigned kABytes = BM * BK * 2, kBBytes = BN * BK * 2;
 constexpr unsigned kSpinLimit = 1u << 22;
 
-enum { EPI_STORE = 0, EPI_SWIGLU = 1 };
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESID_ADD = 2 };
 enum { TC_OK = 0, TC_TIMEOUT_FULL = 11, TC_TIMEOUT_EMPTY = 12, TC_TIMEOUT_ACCUM = 13, TC_TIMEOUT_DRAIN = 14 };
 
 struct TcArgs {
     __nv_bfloat16* y;
     long long ldy;
+    float* acc;         // EPI_RESID_ADD: fp32 [M, N] (row stride ldy), the product is added into it
     int M, N, K;        // N: rows of W
     int epi;
     int* status;
@@ -127,6 +130,22 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
 // Stores 16 accumulator columns of one row: plain (16 outputs) or gated (8 gates and their 8 ups -> 8 outputs).
 __device__ __forceinline__ void store_columns(const TcArgs& a, const float (&v)[16], int row, int n0, int j) {
     if (row >= a.M) return;
+    if (a.epi == EPI_RESID_ADD) {
+        const int c0 = n0 + j * 16;
+        if (c0 >= a.N) return;
+        float* dst = a.acc + (size_t)row * a.ldy + c0;
+        if (c0 + 16 <= a.N && ((a.ldy & 3) == 0)) {
+            float4 o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) o[q] = reinterpret_cast<const float4*>(dst)[q];       // all loads first
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                reinterpret_cast<float4*>(dst)[q] = make_float4(o[q].x + v[4 * q], o[q].y + v[4 * q + 1], o[q].z + v[4 * q + 2], o[q].w + v[4 * q + 3]);
+        } else {
+            for (int e = 0; e < 16 && c0 + e < a.N; ++e) dst[e] += v[e];
+        }
+        return;
+    }
     if (a.epi == EPI_SWIGLU) {
         const int inner = a.N >> 1, o0 = (n0 >> 1) + j * 8;
         if (o0 >= inner) return;
@@ -336,14 +355,16 @@ int make_map(const void* base, long long ld, int rows, int K, int box_rows, bool
 BLM_API int blm_gemm_tc_supported(int M, int N, int K) { return M >= 1 && N >= 16 && K >= 64 && K % 8 == 0; }
 
 // y[M, N] = x[M, K] . w[N, K]^T (epi 0), or y[M, N / 2] = silu(gate) * up for a weight in tiles of 8 gate rows
-// followed by their 8 up rows (epi 1).  x, w, y bfloat16; ldx, ldw, ldy in elements.
+// followed by their 8 up rows (epi 1), or y[M, N] += x . w^T with y fp32 (epi 2: the residual stream).  x, w
+// bfloat16, y bfloat16 but for epi 2; ldx, ldw, ldy in elements.
 BLM_API int blm_gemm_tc(const void* x, long long ldx, const void* w, long long ldw, void* y, long long ldy, int M, int N, int K,
                         int epi, int* status, cudaStream_t stream) {
     if (M == 0 || N == 0) return BLM_OK;
     BLM_REQUIRE(blm_gemm_tc_supported(M, N, K), "gemm_tc: shape %d x %d x %d (K a multiple of 8, at least 64)", M, N, K);
     BLM_REQUIRE(ldx % 8 == 0 && ldw % 8 == 0 && ((size_t)x & 15) == 0 && ((size_t)w & 15) == 0,
                 "gemm_tc: operand rows must be 16-byte aligned");
-    BLM_REQUIRE(epi == EPI_STORE || (epi == EPI_SWIGLU && N % 16 == 0), "gemm_tc: epilogue %d with %d weight rows", epi, N);
+    BLM_REQUIRE(epi == EPI_STORE || epi == EPI_RESID_ADD || (epi == EPI_SWIGLU && N % 16 == 0), "gemm_tc: epilogue %d with %d weight rows", epi, N);
+    BLM_REQUIRE(epi != EPI_RESID_ADD || ((size_t)y & 15) == 0, "gemm_tc: the stream must be 16-byte aligned");
     BLM_REQUIRE(status != nullptr, "gemm_tc: no status word");
     CUtensorMap xmap, wmap;
     int rc = make_map(x, ldx, M, K, BM, false, &xmap);
@@ -351,7 +372,7 @@ BLM_API int blm_gemm_tc(const void* x, long long ldx, const void* w, long long l
     rc = make_map(w, ldw, N, K, BN, true, &wmap);
     if (rc != BLM_OK) return rc;
     TcArgs a;
-    a.y = (__nv_bfloat16*)y; a.ldy = ldy; a.M = M; a.N = N; a.K = K; a.epi = epi; a.status = status;
+    a.y = (__nv_bfloat16*)y; a.acc = (float*)y; a.ldy = ldy; a.M = M; a.N = N; a.K = K; a.epi = epi; a.status = status;
     const size_t smem = (size_t)kStages * (kABytes + kBBytes) + (2 * kStages + 4) * 8 + 16 + 1024;
     static bool opted_in = false;
     if (!opted_in) {

@@ -368,17 +368,25 @@ def gemm_tc_supported(m, n, k) -> bool:
     return bool(_lib("gemm_tc").blm_gemm_tc_supported(m, n, k))
 
 
-def gemm_tc(x, w, out, swiglu=False):
+def gemm_tc(x, w, out=None, swiglu=False, add_into=None):
     """x [M, K] times w [N, K] transposed on the tcgen05 tensor cores (bfloat16, fp32 accumulation in
     tensor memory).  out [M, N]; with `swiglu`, w is a fused gate/up weight in tiles of GATE_TILE gate
-    rows followed by their up rows and out [M, N / 2] = silu(gate) * up, formed in the epilogue."""
-    _need_cuda(x, w, out)
+    rows followed by their up rows and out [M, N / 2] = silu(gate) * up, formed in the epilogue; with
+    `add_into` (float32 [M, N], the residual stream) the product is added into it in the epilogue and
+    nothing else is written."""
+    _need_cuda(x, w, out, add_into)
     m, k = x.shape
     n = w.shape[0]
-    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or w.shape[1] != k:
-        raise KernelError("gemm_tc: bfloat16 x [M, K], w [N, K], out")
-    if tuple(out.shape) != (m, n // 2 if swiglu else n):
-        raise KernelError("gemm_tc: out must be [M, N] (or [M, N / 2] with the gated epilogue)")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != k:
+        raise KernelError("gemm_tc: bfloat16 x [M, K] and w [N, K]")
+    if add_into is not None:
+        if swiglu or out is not None or add_into.dtype != torch.float32 or tuple(add_into.shape) != (m, n) or add_into.stride(1) != 1:
+            raise KernelError("gemm_tc: add_into must be float32 [M, N], alone")
+        _call("gemm_tc", "blm_gemm_tc", _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(add_into), add_into.stride(0), m, n, k,
+              2, _ptr(status_word(x.device)), _stream())
+        return
+    if out is None or out.dtype != torch.bfloat16 or tuple(out.shape) != (m, n // 2 if swiglu else n):
+        raise KernelError("gemm_tc: out must be bfloat16 [M, N] (or [M, N / 2] with the gated epilogue)")
     _call("gemm_tc", "blm_gemm_tc", _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), m, n, k,
           1 if swiglu else 0, _ptr(status_word(x.device)), _stream())
 

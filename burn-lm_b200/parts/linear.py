@@ -35,9 +35,12 @@ SK_TOKENS = int(os.environ.get("BURN_LM_B200_SK_TOKENS", "16"))
 # against 60; 2,048: 119 against 103).
 TENSOR_CORE_TOKENS = 1024
 # BURN_LM_B200_OWN_PRODUCTS=1: the plain products of a prompt (qkv, output, down, head) run this package's
-# tcgen05 kernel too, from 128 tokens, instead of the library.  Off by default: measured at 2,048 tokens they
-# reach 0.70 (qkv), 0.88 (output) and 0.92 (down) of the library's speed, and the whole prompt step takes
-# 4.93 ms against 4.56 ms.
+# tcgen05 kernel too, from 128 tokens, instead of the library, and the two that feed the residual stream add
+# into it in their epilogue (fp32, in place).  Off by default: measured at 2,048 tokens they reach 0.70 (qkv),
+# 0.88 (output) and 0.92 (down) of the library's speed, the whole prompt step took 4.93 ms against 4.56 ms, and
+# the adding epilogue does not win that back: output product + norm 37 us against 27 us for the library's product
+# and the norm kernel that also adds, down 78 against 58 us (a thread of the epilogue owns a row of the tile, so
+# its 64-byte reads and writes of the stream lie a row apart).
 OWN_PRODUCTS = os.environ.get("BURN_LM_B200_OWN_PRODUCTS", "") == "1"
 OWN_PRODUCTS_TOKENS = 128
 
@@ -197,6 +200,13 @@ class Linear:
             if hand_over is not None:
                 handoff.leave(stream, norm.gamma, handed)
             return None
+        if (OWN_PRODUCTS and stream is not None and self.weight.dtype == torch.bfloat16 and n >= OWN_PRODUCTS_TOKENS
+                and K.gemm_tc_supported(n, self.out_features, self.in_features)):
+            if isinstance(x, NormedStream):
+                x = x.materialize()
+            if x.dtype == torch.bfloat16 and x.is_contiguous() and tuple(stream.shape) == (n, self.out_features) and stream.is_contiguous():
+                K.gemm_tc(x, self.weight, add_into=stream)        # prompts: the tcgen05 product adds into the stream itself
+                return None
         return self(x, out_dtype)
 
     def with_rotary(self, x, q_out: torch.Tensor, rope: dict) -> str:

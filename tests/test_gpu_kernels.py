@@ -718,6 +718,23 @@ def test_gemm_tc_gated(m, inner, k):
     assert (out.double() - want).abs().max().item() < 1e-2 * want.abs().max().item()
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 520, 200), (77, 48, 1000), (2048, 2048, 2048), (513, 2052, 512)])
+def test_gemm_tc_adds_into_the_stream(m, n, k):
+    """The tcgen05 product with the stream epilogue: an fp32 [M, N] matrix gets the product added in place, at
+    sizes that are no multiples of the tiles (and a row length that is no multiple of four floats)."""
+    k_ = K()
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    stream = torch.randn(m, n, device="cuda", generator=g)
+    want = stream.double() + x.double() @ w.double().t()
+    k_.gemm_tc(x, w, add_into=stream)
+    k_.check_status("cuda")
+    torch.testing.assert_close(stream.double(), want, rtol=1e-4, atol=1e-4 * (k ** 0.5))
+    with pytest.raises(k_.KernelError):
+        k_.gemm_tc(x, w, add_into=stream.to(torch.bfloat16))
+
+
 def test_step_tables_and_their_users():
     """The page of every new token and the block table's rows by sequence, looked up once per step: the tables
     themselves, and the kernels that take them (the rotary epilogue of the skinny product, decode attention) give

@@ -128,13 +128,14 @@ def test_a_step_of_more_than_a_thousand_tokens(tmp_path):
 
 def test_every_prompt_product_on_the_tcgen05_kernel(tmp_path, monkeypatch):
     """With the switch that sends the plain prompt products (qkv, output, down) to this package's tcgen05
-    kernel as well, a step of 300 tokens agrees with the plain implementation, and the kernel did run."""
+    kernel as well (output and down with the epilogue that adds into the fp32 stream), a step of 300 tokens
+    agrees with the plain implementation, and the kernel did run."""
     from burn_lm_b200 import StepEntry, kernels
     from burn_lm_b200.parts import linear
     monkeypatch.setattr(linear, "OWN_PRODUCTS", True)
     calls = []
     real = kernels.gemm_tc
-    monkeypatch.setattr(kernels, "gemm_tc", lambda *a, **k: (calls.append(a[1].shape), real(*a, **k))[1])
+    monkeypatch.setattr(kernels, "gemm_tc", lambda *a, **k: (calls.append((a[1].shape, "add_into" in k)), real(*a, **k))[1])
     folder = make_folder(tmp_path, "tiny_e", seed=9, dtype="bfloat16")
     cfg, tensors = P.read_model_folder(folder)
     eng = engine_for(folder, "bfloat16", max_tokens=1024)
@@ -145,6 +146,7 @@ def test_every_prompt_product_on_the_tcgen05_kernel(tmp_path, monkeypatch):
     want = P.forward(cfg, tensors, toks)[want_at]
     assert row_error(got, want).max() < BF16_TOL
     assert len(calls) >= 3 * cfg["num_hidden_layers"]
+    assert sum(1 for _, adds in calls if adds) == 2 * cfg["num_hidden_layers"]      # output and down add into the stream themselves
     eng.verify()
 
 
