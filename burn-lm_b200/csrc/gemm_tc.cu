@@ -127,26 +127,29 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// Stores 16 accumulator columns of one row: plain (16 outputs) or gated (8 gates and their 8 ups -> 8 outputs).
+// Stores 16 accumulator columns of one row: plain (16 outputs), gated (8 gates and their 8 ups -> 8 outputs), or
+// added into the fp32 stream.  The end is a parameter of the kernel: each variant carries only its own code.
+template <int EPI>
 __device__ __forceinline__ void store_columns(const TcArgs& a, const float (&v)[16], int row, int n0, int j) {
     if (row >= a.M) return;
-    if (a.epi == EPI_RESID_ADD) {
+    if (EPI == EPI_RESID_ADD) {
         const int c0 = n0 + j * 16;
         if (c0 >= a.N) return;
         float* dst = a.acc + (size_t)row * a.ldy + c0;
         if (c0 + 16 <= a.N && ((a.ldy & 3) == 0)) {
-            float4 o[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) o[q] = reinterpret_cast<const float4*>(dst)[q];       // all loads first
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-                reinterpret_cast<float4*>(dst)[q] = make_float4(o[q].x + v[4 * q], o[q].y + v[4 * q + 1], o[q].z + v[4 * q + 2], o[q].w + v[4 * q + 3]);
+            // all loads first
+            const float4 o0 = reinterpret_cast<const float4*>(dst)[0], o1 = reinterpret_cast<const float4*>(dst)[1];
+            const float4 o2 = reinterpret_cast<const float4*>(dst)[2], o3 = reinterpret_cast<const float4*>(dst)[3];
+            reinterpret_cast<float4*>(dst)[0] = make_float4(o0.x + v[0], o0.y + v[1], o0.z + v[2], o0.w + v[3]);
+            reinterpret_cast<float4*>(dst)[1] = make_float4(o1.x + v[4], o1.y + v[5], o1.z + v[6], o1.w + v[7]);
+            reinterpret_cast<float4*>(dst)[2] = make_float4(o2.x + v[8], o2.y + v[9], o2.z + v[10], o2.w + v[11]);
+            reinterpret_cast<float4*>(dst)[3] = make_float4(o3.x + v[12], o3.y + v[13], o3.z + v[14], o3.w + v[15]);
         } else {
             for (int e = 0; e < 16 && c0 + e < a.N; ++e) dst[e] += v[e];
         }
         return;
     }
-    if (a.epi == EPI_SWIGLU) {
+    if (EPI == EPI_SWIGLU) {
         const int inner = a.N >> 1, o0 = (n0 >> 1) + j * 8;
         if (o0 >= inner) return;
         unsigned packed[4];
@@ -183,6 +186,7 @@ __device__ __forceinline__ void store_columns(const TcArgs& a, const float (&v)[
     }
 }
 
+template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap xmap,
                                                               const __grid_constant__ CUtensorMap wmap) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -294,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs a, co
             for (int j = 0; j < BN / 16; ++j) {
                 float v[16];
                 tmem_ld16(taddr + j * 16, v);
-                store_columns(a, v, row, n0, j);
+                store_columns<EPI>(a, v, row, n0, j);
             }
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
@@ -376,12 +380,16 @@ BLM_API int blm_gemm_tc(const void* x, long long ldx, const void* w, long long l
     const size_t smem = (size_t)kStages * (kABytes + kBBytes) + (2 * kStages + 4) * 8 + 16 + 1024;
     static bool opted_in = false;
     if (!opted_in) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<EPI_RESID_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "gemm_tc: %s", cudaGetErrorString(e));
         opted_in = true;
     }
     const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     const int grid = (int)(tiles < blm_sm_count() ? tiles : blm_sm_count());        // persistent: one block per SM
-    gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(a, xmap, wmap);
+    if (epi == EPI_SWIGLU) gemm_tc_kernel<EPI_SWIGLU><<<grid, kThreads, smem, stream>>>(a, xmap, wmap);
+    else if (epi == EPI_RESID_ADD) gemm_tc_kernel<EPI_RESID_ADD><<<grid, kThreads, smem, stream>>>(a, xmap, wmap);
+    else gemm_tc_kernel<EPI_STORE><<<grid, kThreads, smem, stream>>>(a, xmap, wmap);
     return blm_check_launch("gemm_tc");
 }

@@ -36,8 +36,8 @@ SK_TOKENS = int(os.environ.get("BURN_LM_B200_SK_TOKENS", "16"))
 TENSOR_CORE_TOKENS = 1024
 # BURN_LM_B200_OWN_PRODUCTS=1: the plain products of a prompt (qkv, output, down, head) run this package's
 # tcgen05 kernel too, from 128 tokens, instead of the library, and the two that feed the residual stream add
-# into it in their epilogue (fp32, in place).  Off by default: measured at 2,048 tokens they reach 0.70 (qkv),
-# 0.88 (output) and 0.92 (down) of the library's speed, the whole prompt step took 4.93 ms against 4.56 ms, and
+# into it in their epilogue (fp32, in place).  Off by default: measured at 2,048 tokens they reach 0.88 (qkv),
+# 0.83 (output) and 0.94 (down) of the library's speed, the whole prompt step takes 5.1 ms against 4.3 ms, and
 # the adding epilogue does not win that back: output product + norm 37 us against 27 us for the library's product
 # and the norm kernel that also adds, down 78 against 58 us (a thread of the epilogue owns a row of the tile, so
 # its 64-byte reads and writes of the stream lie a row apart).
