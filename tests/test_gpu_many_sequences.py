@@ -98,3 +98,17 @@ def test_decode_attention_with_hundreds_of_blocks(H, KV, hd, window):
     run_attention_case(torch.bfloat16, H, KV, hd, before, [1] * 64, window, 1, seed=60, max_kv_len=max(before) + 1)
     # fewer, longer walks: 40 sequences, two splits
     run_attention_case(torch.bfloat16, H, KV, hd, before[:40], [1] * 40, window, 2, seed=61, max_kv_len=max(before[:40]) + 1)
+
+
+@pytest.mark.parametrize("H,KV,hd,n_splits", [(24, 8, 128, 3), (32, 8, 64, 5), (8, 8, 128, 4)])
+def test_decode_attention_of_very_unequal_lengths_in_many_blocks(H, KV, hd, n_splits):
+    """16 to 24 sequences of 1 to 4,200 tokens, cut into several splits: more blocks than fill the SMs twice, so a
+    sequence takes blocks in proportion to its length (a short one a single block that writes the output itself, the
+    longest all the splits, merged by the combine kernel); with and without a window that leaves a sequence fewer
+    pages than its length has."""
+    rng = np.random.default_rng(H + hd + n_splits)
+    before = [int(x) for x in rng.integers(0, 4200, size=24 if hd == 64 else 16)]
+    before[:6] = [0, 63, 64, 4199, 2100, 1400]
+    for window in (0, 900):
+        run_attention_case(torch.bfloat16, H, KV, hd, before, [1] * len(before), window, n_splits, seed=90 + window,
+                           max_kv_len=4224)
