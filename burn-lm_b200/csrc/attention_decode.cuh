@@ -105,7 +105,7 @@ static inline int attn_decode_stages(int hd, int blocks, int pages_per_block) {
 // 128-lane head spill (measured, 8 sequences of 2,000 tokens: 35.7 us with four groups, 24.6 us with two).
 static inline int attn_decode_groups(int blocks, int pages_per_block, int stages, int hd = 64) {
     const int sms = blm_sm_count();
-    int ng = blocks <= sms ? (hd > 64 ? 2 : 4) : (blocks <= 2 * sms ? 2 : 1);
+    int ng = blocks <= sms ? (hd > 64 ? 2 : 4) : (blocks <= 2 * sms && hd <= 64 ? 2 : 1);
     while (ng > 1 && (ng > pages_per_block || ng > stages)) ng /= 2;
     return ng;
 }
