@@ -5,11 +5,11 @@
 // A block owns 128 query rows of one head of one sequence and walks the keys a cache page (64 keys) a
 // step.  Seven warps:
 //   warp 0 (one thread), the producer: TMA tile loads with the 128-byte swizzle of the query tile (once,
-//     from the step's q rows), of the pages' keys (a ring of four) and values (a ring of two), completion
-//     on mbarriers;
+//     from the step's q rows), of the pages' keys (a ring of four; two at head size 128) and values (a ring
+//     of two), completion on mbarriers;
 //   warp 1 (one thread), the scores: S(j) = Q K(j)^T (M 128, N 64, both operands K-major in shared memory)
-//     into a ring of three 64-column tiles of tensor memory, so that a step's scores are formed two steps
-//     before the softmax warps come for them;
+//     into a ring of three 64-column tiles of tensor memory (two at head size 128), so that a step's scores
+//     are formed two steps (one) before the softmax warps come for them;
 //   warp 2 (one thread), the values: O += P(j) V(j), with A = P read from tensor memory and B = V as it
 //     lies in the cache (keys by lanes, read MN-major);
 //   warps 3..6, the softmax: a thread owns one query row (its lane of tensor memory), reads the row of S
@@ -20,8 +20,8 @@
 // both products is the longest chain of a step (each instruction it issues costs it some fifty cycles).
 // O accumulates in tensor memory over the steps; a row of it is rescaled there (tcgen05.ld, multiply,
 // tcgen05.st) only when a step's maximum exceeds the row's reference by more than 2^8, which after the
-// first steps is rare.  Head size 64: 256 columns of tensor memory and 66 KB of shared memory a block,
-// two blocks to an SM, one's softmax under the other's; head size 128: 512 columns, one block.
+// first steps is rare.  Either head size: 256 columns of tensor memory a block (3 x 64 for the scores and 64
+// for O; 2 x 64 and 128) and 66 or 99 KB of shared memory, two blocks to an SM, one's softmax under the other's.
 //
 // Rows of a value page that no key of the sequence has written (the page's tail) are cleared by the
 // softmax threads before the product: a probability of zero does not silence a NaN.  Every mbarrier wait
@@ -279,12 +279,12 @@ __global__ void __launch_bounds__(attn_tc::kThreads, 2) attn_prefill_tc_kernel(c
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = *tmem_slot;
 
-    // Who waits for whom, step j (a page of 64 keys; t = j % 3, b = j & 1):
-    //   scores warp:  pv_done[t] of step j - 3 (its columns were read), k_full  ->  S(j)  ->  s_full[t], k_empty
-    //   softmax:      s_full[t]                                                  ->  P(j) over S(j)'s first columns  ->  p_full[t]
-    //   values warp:  p_full[t], v_full[b]                                        ->  O += P V  ->  pv_done[t]
-    //   producer:     pv_done of step j - 2  ->  the values of step j;  k_empty of step j - 1  ->  the keys of step j + 3
-    // so the scores of a step are formed two steps before the softmax warps come for them.
+    // Who waits for whom, step j (a page of 64 keys; t = j % kSRing, b = j & 1):
+    //   scores warp:  pv_done[t] of step j - kSRing (its columns were read), k_full  ->  S(j)  ->  s_full[t], k_empty
+    //   softmax:      s_full[t]                                            ->  P(j) over S(j)'s first columns  ->  p_full[t]
+    //   values warp:  p_full[t], v_full[b]                                  ->  O += P V  ->  pv_done[t]
+    //   producer:     pv_done of step j - 2  ->  the values of step j;  k_empty  ->  the keys of step j + kKStages - 1
+    // so the scores of a step are formed kSRing - 1 steps before the softmax warps come for them.
     if (warp == 0) {
         if (lane == 0) {
             // ---------------- producer ----------------
@@ -373,7 +373,7 @@ __global__ void __launch_bounds__(attn_tc::kThreads, 2) attn_prefill_tc_kernel(c
         bool ok = true;
         for (int j = 0; j < n_blocks && ok; ++j) {
             const int key0 = (kb_lo + j) * BKV;
-            const int b = j & 1, t = j % kSRing;                 // which P tile and V stage, which S columns this step has
+            const int b = j & 1, t = j % kSRing;                 // which V stage, which score tile this step has
             if (!mbar_wait(s_full + t, (j / kSRing) & 1)) { if (lane == 0) atomicCAS(a.status, 0, TC_ATTN_S); ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             // Decided by warp (32 rows): a page whose every key every row of the warp sees needs no masks (all but
@@ -467,7 +467,7 @@ __global__ void __launch_bounds__(attn_tc::kThreads, 2) attn_prefill_tc_kernel(c
                     }
                 }
                 const float neg_m = m_run == -INFINITY ? 0.f : -m_run;      // a row without a visible key: every probability is masked anyway
-                // probabilities, as bf16 into the P tile: 16-byte chunk c of the row's half h at h * kTile + r * 128 + ((c ^ (r & 7)) << 4)
+                // the probabilities, as bf16 pairs
 #pragma unroll
                 for (int c = 0; c < BKV / 32; ++c) {
                     tmem_ld32_wait(buf[c & 1]);
