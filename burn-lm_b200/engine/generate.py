@@ -136,6 +136,7 @@ class GenerationLoop:
         slots = {i: engine.acquire() for i in batch}
         fused = getattr(engine, "decode_greedy", None)
         fused_draw = getattr(engine, "decode_sampled", None)
+        looks_ahead = bool(getattr(engine, "decode_ahead", False))
         # a request's draws are numbered from 0 in a stream of its own: (seed, request index)
         live = list(batch)
         try:
@@ -150,6 +151,7 @@ class GenerationLoop:
             stats.prompt_tokens += sum(len(prompts[i]) for i in live)
             stats.prefill_seconds += time.perf_counter() - t0
             t0 = time.perf_counter()
+            live_slots = None
             while True:
                 nxt = []
                 for i, tok in zip(live, tokens):
@@ -173,17 +175,19 @@ class GenerationLoop:
                             nxt.append(i)
                     if r.finish_reason:
                         engine.release(slots.pop(i))      # its slot and pages are free for others
+                if len(nxt) != len(live) or live_slots is None:       # someone left: the others' slots, in their order
+                    live_slots = [slots[i] for i in nxt]
                 live = nxt
                 if not live:
                     break
                 tokens = None
                 if params.greedy and fused is not None:      # the engine samples inside its captured step
                     # will anyone need a step after this one (if no stop id turns up)?  Then the engine may enqueue it now.
-                    more = any(len(results[i].tokens) + 1 < sample_len and len(prompts[i]) + len(results[i].tokens) + 1 <= max_len
-                               for i in live)
-                    tokens = fused([slots[i] for i in live], [results[i].tokens[-1] for i in live], more=more)
+                    more = looks_ahead and any(len(results[i].tokens) + 1 < sample_len and len(prompts[i]) + len(results[i].tokens) + 1 <= max_len
+                                               for i in live)
+                    tokens = fused(live_slots, [results[i].tokens[-1] for i in live], more=more)
                 elif not params.greedy and fused_draw is not None:
-                    tokens = fused_draw([slots[i] for i in live], [results[i].tokens[-1] for i in live], params, live,
+                    tokens = fused_draw(live_slots, [results[i].tokens[-1] for i in live], params, live,
                                         [len(results[i].tokens) for i in live])
                 if tokens is None:
                     entries = [StepEntry(slots[i], [results[i].tokens[-1]], [0]) for i in live]
