@@ -7,10 +7,15 @@ BLM_API const char* blm_elementwise_last_error() { return g_blm_error; }
 
 // ---------------------------------------------------------------------------------------------
 // embedding: out[n, :] = table[tokens[n], :]  (fp32 residual stream from a bf16 or fp32 table)
+// With `xg` the kernel also leaves the input of the norm that reads the stream first, as the products that write
+// the stream do: xg[n, :] = bf16(out[n, :] * gamma) and ssq[n] = the row's sum of squares (one part: a row of up to
+// `ssq_row` tokens), so that the first product of a decode step need not normalise the stream in every block.
 // ---------------------------------------------------------------------------------------------
 template <typename TT>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TT* __restrict__ table,
-                             float* __restrict__ out, int width, int vocab) {
+                             float* __restrict__ out, int width, int vocab, const void* __restrict__ gamma, int gamma_f32,
+                             __nv_bfloat16* __restrict__ xg, float* __restrict__ ssq) {
+    __shared__ float red[33];
     pdl_launch_dependents();
     pdl_wait();
     blm_trace(0x220);
@@ -19,18 +24,34 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TT* __restric
     if ((unsigned)tok >= (unsigned)vocab) tok = 0;  // ids are validated on the host; never read wild
     const TT* row = table + (size_t)tok * width;
     float* o = out + (size_t)n * width;
-    for (int d = threadIdx.x; d < width; d += blockDim.x) o[d] = to_f32(row[d]);
+    if (xg == nullptr) {
+        for (int d = threadIdx.x; d < width; d += blockDim.x) o[d] = to_f32(row[d]);
+        return;
+    }
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        const float v = to_f32(row[d]);
+        const float g = gamma_f32 ? reinterpret_cast<const float*>(gamma)[d] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(gamma)[d]);
+        o[d] = v;
+        xg[(size_t)n * width + d] = __float2bfloat16_rn(v * g);
+        ss += v * v;
+    }
+    const float total = block_sum(ss, red);
+    if (threadIdx.x == 0) ssq[n] = total;
 }
 
 BLM_API int blm_embed(const int* tokens, const void* table, int table_dtype, float* out,
-                      int n_tokens, int width, int vocab, cudaStream_t stream) {
+                      int n_tokens, int width, int vocab, const void* gamma, int gamma_f32, void* xg, float* ssq, int ssq_row,
+                      cudaStream_t stream) {
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0, "embed: bad sizes");
+    BLM_REQUIRE(xg == nullptr || (gamma != nullptr && ssq != nullptr && n_tokens <= ssq_row), "embed: a norm is handed over with gamma and room for %d sums", n_tokens);
     const int threads = width >= 1024 ? 256 : 128;
+    __nv_bfloat16* x = (__nv_bfloat16*)xg;
     if (table_dtype == BLM_F32)
-        blm_launch_dependent(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, width, vocab);
+        blm_launch_dependent(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, width, vocab, gamma, gamma_f32, x, ssq);
     else if (table_dtype == BLM_BF16)
-        blm_launch_dependent(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, width, vocab);
+        blm_launch_dependent(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, width, vocab, gamma, gamma_f32, x, ssq);
     else
         return blm_fail(BLM_BAD_ARGUMENT, "embed: table dtype %d", table_dtype);
     return blm_check_launch("embed");

@@ -60,9 +60,24 @@ __global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* __restri
     const int lo = blockIdx.x * kArgmaxChunk, hi = min(vocab, lo + kArgmaxChunk);
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    if (hi - lo == kArgmaxChunk && ((size_t)(row + lo) & 15) == 0) {
+        // a whole chunk, 16-byte aligned: a thread's four loads of four values are all asked for before any is looked at
+        float4 v[kArgmaxChunk / (4 * 256)];
+#pragma unroll
+        for (int q = 0; q < kArgmaxChunk / (4 * 256); ++q) v[q] = reinterpret_cast<const float4*>(row + lo)[q * 256 + threadIdx.x];
+#pragma unroll
+        for (int q = 0; q < kArgmaxChunk / (4 * 256); ++q) {
+            const int i = lo + 4 * (q * 256 + (int)threadIdx.x);      // ascending in q, so a tie keeps the lower index
+            if (v[q].x > best) { best = v[q].x; idx = i; }
+            if (v[q].y > best) { best = v[q].y; idx = i + 1; }
+            if (v[q].z > best) { best = v[q].z; idx = i + 2; }
+            if (v[q].w > best) { best = v[q].w; idx = i + 3; }
+        }
+    } else {
+        for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            const float v = row[i];
+            if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {

@@ -71,7 +71,7 @@ def _need_cuda(*tensors):
 
 _protos = {
     "elementwise": {
-        "blm_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "blm_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p],
         "blm_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                             c_float, c_void_p],
         "blm_rope_append": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
@@ -166,13 +166,25 @@ def loaded_modules():
 
 
 # ------------------------------------------------------------------------------------------------
-def embed(tokens, table, out):
-    """out[n, :] = table[tokens[n], :] as fp32.  tokens int32 [N]; table [V, D]; out fp32 [N, D]."""
+def embed(tokens, table, out, hand_over=None):
+    """out[n, :] = table[tokens[n], :] as fp32.  tokens int32 [N]; table [V, D]; out fp32 [N, D].
+    `hand_over` = (gamma [D], scaled bfloat16 [N, D], squares float32 [1, SQUARES_ROWS]) for up to SQUARES_ROWS
+    tokens: the kernel also leaves the input of the norm that reads the stream first, scaled = out * gamma and the
+    rows' sums of squares in one part, as gemv's `hand_over` does."""
     _need_cuda(tokens, table, out)
     n, (v, d) = tokens.numel(), table.shape
     if tokens.dtype != torch.int32 or out.dtype != torch.float32 or tuple(out.shape) != (n, d):
         raise KernelError("embed: tokens int32 [N], out float32 [N, D]")
-    _call("elementwise", "blm_embed", _ptr(tokens), _ptr(table), _code(table.dtype), _ptr(out), n, d, v, _stream())
+    gamma = scaled = squares = None
+    if hand_over is not None:
+        gamma, scaled, squares = hand_over
+        _need_cuda(gamma, scaled, squares)
+        if (n > SQUARES_ROWS or gamma.numel() != d or scaled.dtype != torch.bfloat16 or tuple(scaled.shape) != (n, d)
+                or not scaled.is_contiguous() or squares.dtype != torch.float32 or tuple(squares.shape) != (1, SQUARES_ROWS)):
+            raise KernelError("embed: hand_over = (gamma [D], scaled bfloat16 [N, D], squares float32 [1, 16]) for up to 16 tokens")
+    _call("elementwise", "blm_embed", _ptr(tokens), _ptr(table), _code(table.dtype), _ptr(out), n, d, v,
+          _ptr(gamma), 1 if (gamma is not None and gamma.dtype == torch.float32) else 0, _ptr(scaled), _ptr(squares),
+          SQUARES_ROWS, _stream())
 
 
 def add_rmsnorm(resid, delta, gamma, eps, out, rows=None):

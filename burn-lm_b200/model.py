@@ -8,6 +8,7 @@ import torch
 
 from .config.reader import read_config_json
 from .parts.base import CacheNeed, Runtime
+from .parts.linear import NormHandoff
 from .plan import ModelPlan
 from .registry import architecture_of, part_class
 from .weights.loader import load_tensors
@@ -124,11 +125,20 @@ class Model:
             raise RuntimeError("the model has no weights yet")
         step.memo.clear()
         resid = torch.empty((step.n_tokens, self.plan.hidden_size), dtype=torch.float32, device=self.runtime.device)
-        self.embedding.forward(step.tokens, resid)
+        schedule = self.plan.schedule
+        first = self.layers[schedule[0].layer].block if schedule else None
+        if (getattr(self.embedding, "hands_norm_over", False) and self.stream_position is None
+                and first is not None and hasattr(first, "first_norm")):
+            # the embedding writes the stream: it may leave the input of the norm that reads it first
+            if step.handoff is None:
+                step.handoff = NormHandoff()
+            step.handoff.expect(first.first_norm())
+            self.embedding.forward(step.tokens, resid, handoff=step.handoff)
+        else:
+            self.embedding.forward(step.tokens, resid)
         if self.stream_position is not None:
             self.stream_position.on_embedding(resid, step)      # an encoding that is added to the stream
         delta = None
-        schedule = self.plan.schedule
         for run, entry in enumerate(schedule):
             block = self.layers[entry.layer].block
             if hasattr(block, "first_norm"):

@@ -12,7 +12,7 @@ from .. import kernels as K
 from ..registry import register_part
 from ..weights.loader import TensorSpec
 from .base import Part
-from .linear import Linear
+from .linear import HandedNorm, Linear
 
 
 @dataclass(frozen=True)
@@ -33,7 +33,20 @@ class Embedding(Part):
     def bind(self, loaded):
         self.table = loaded[self.tensor_names["table"]]
 
-    def forward(self, tokens, out):
+    hands_norm_over = True      # forward() takes the step's handoff and may leave the first norm's input there
+
+    def forward(self, tokens, out, handoff=None):
+        """`handoff` (parts.linear.NormHandoff) with a norm expected: for a few tokens the kernel also leaves that
+        norm's input (the stream times gamma, the rows' sums of squares), as the products that write the stream do."""
+        norm = handoff.wanted if handoff is not None else None
+        n = tokens.numel()
+        if (norm is not None and n <= K.SQUARES_ROWS and self.runtime.dtype == torch.bfloat16 and out.is_cuda
+                and getattr(norm, "gamma", None) is not None and norm.gamma.numel() == out.shape[1]):
+            handed = HandedNorm(torch.empty((n, out.shape[1]), dtype=torch.bfloat16, device=out.device),
+                                torch.empty((1, K.SQUARES_ROWS), dtype=torch.float32, device=out.device))
+            K.embed(tokens, self.table, out, hand_over=(norm.gamma, handed.scaled, handed.squares))
+            handoff.leave(out, norm.gamma, handed)
+            return
         K.embed(tokens, self.table, out)
 
 

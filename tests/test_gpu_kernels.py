@@ -29,6 +29,32 @@ def test_embed(table_dtype):
     torch.testing.assert_close(out, table[tokens.long()].float(), rtol=0, atol=0)
 
 
+@pytest.mark.parametrize("gdt", DTYPES)
+@pytest.mark.parametrize("n,width", [(1, 64), (7, 2048), (16, 1000)])
+def test_embed_hands_the_first_norm_over(gdt, n, width):
+    """With `hand_over` the embedding leaves what the products that write the stream leave: the stream times gamma in
+    bfloat16 and the rows' sums of squares (one part), beside the same fp32 rows as without it."""
+    k = K()
+    g = torch.Generator(device="cuda").manual_seed(n + width)
+    table = torch.randn(300, width, device="cuda", generator=g).to(torch.bfloat16)
+    tokens = torch.randint(0, 300, (n,), device="cuda", generator=g, dtype=torch.int32)
+    gamma = (1 + 0.1 * torch.randn(width, device="cuda", generator=g)).to(gdt)
+    plain = torch.empty(n, width, device="cuda")
+    k.embed(tokens, table, plain)
+    out = torch.empty(n, width, device="cuda")
+    scaled = torch.full((n, width), float("nan"), device="cuda", dtype=torch.bfloat16)
+    squares = torch.full((1, 16), float("nan"), device="cuda")
+    k.embed(tokens, table, out, hand_over=(gamma, scaled, squares))
+    assert torch.equal(out, plain) and torch.equal(out, table[tokens.long()].float())
+    want = out.double() * gamma.double()
+    assert (scaled.double() - want).abs().max().item() <= 2 ** -8 * want.abs().max().item()
+    ssq = (out.double() ** 2).sum(-1)
+    assert (squares[0, :n].double() - ssq).abs().max().item() < 1e-5 * ssq.max().item()
+    with pytest.raises(k.KernelError):
+        k.embed(torch.zeros(17, dtype=torch.int32, device="cuda"), table, torch.empty(17, width, device="cuda"),
+                hand_over=(gamma, torch.empty(17, width, device="cuda", dtype=torch.bfloat16), squares))
+
+
 @pytest.mark.parametrize("act", DTYPES)
 @pytest.mark.parametrize("gdt", DTYPES)
 @pytest.mark.parametrize("width", [72, 1000, 4100])
