@@ -12,8 +12,18 @@ constexpr int kSampleThreads = 1024;
 // ---------------------------------------------------------------------------------------------
 // greedy: the largest logit; the lowest index wins a tie
 // ---------------------------------------------------------------------------------------------
+// A row's result; `mirror`, where given, is pinned host memory as the device sees it: the host may be polling it
+// (blm_graph_step), so the value is pushed out at once.
+__device__ __forceinline__ void blm_store_result(int* out, int* mirror, int row, int value) {
+    out[row] = value;
+    if (mirror != nullptr) {
+        *reinterpret_cast<volatile int*>(mirror + row) = value;
+        __threadfence_system();
+    }
+}
+
 __global__ void __launch_bounds__(kSampleThreads) argmax_kernel(const float* __restrict__ logits, long long row_stride,
-                                                                int vocab, int* __restrict__ out) {
+                                                                int vocab, int* __restrict__ out, int* __restrict__ mirror) {
     __shared__ float bv[32];
     __shared__ int bi[32];
     const float* row = logits + (size_t)blockIdx.x * row_stride;
@@ -42,7 +52,7 @@ __global__ void __launch_bounds__(kSampleThreads) argmax_kernel(const float* __r
             const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
             if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
         }
-        if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+        if (lane == 0) blm_store_result(out, mirror, blockIdx.x, idx == 0x7fffffff ? 0 : idx);
     }
 }
 
@@ -96,7 +106,7 @@ __global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* __restri
 }
 
 __global__ void argmax_merge_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int chunks,
-                                    int* __restrict__ out) {
+                                    int* __restrict__ out, int* __restrict__ mirror) {
     pdl_launch_dependents();
     pdl_wait();
     blm_trace(0x320);
@@ -113,7 +123,7 @@ __global__ void argmax_merge_kernel(const float* __restrict__ part_val, const in
         const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
         if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
     }
-    if (threadIdx.x == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+    if (threadIdx.x == 0) blm_store_result(out, mirror, blockIdx.x, idx == 0x7fffffff ? 0 : idx);
 }
 
 // How many floats of scratch blm_argmax wants for a vocabulary (0: none).
@@ -122,19 +132,20 @@ BLM_API int blm_argmax_scratch_floats(int n_rows, int vocab) {
     return 2 * n_rows * ((vocab + kArgmaxChunk - 1) / kArgmaxChunk);
 }
 
-BLM_API int blm_argmax(const float* logits, long long row_stride, int n_rows, int vocab, int* out, float* scratch,
+// `mirror`: null, or pinned host memory (its device address) that gets the results as well.
+BLM_API int blm_argmax(const float* logits, long long row_stride, int n_rows, int vocab, int* out, int* mirror, float* scratch,
                        cudaStream_t stream) {
     if (n_rows == 0) return BLM_OK;
     BLM_REQUIRE(vocab > 0, "argmax: empty vocabulary");
     if (vocab <= 2 * kArgmaxChunk || scratch == nullptr) {
-        argmax_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, row_stride, vocab, out);
+        argmax_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, row_stride, vocab, out, mirror);
         return blm_check_launch("argmax");
     }
     const int chunks = (vocab + kArgmaxChunk - 1) / kArgmaxChunk;
     float* part_val = scratch;
     int* part_idx = reinterpret_cast<int*>(scratch + (size_t)n_rows * chunks);
     blm_launch_dependent(argmax_chunk_kernel, dim3(chunks, n_rows), dim3(256), 0, stream, logits, row_stride, vocab, part_val, part_idx);
-    blm_launch_dependent(argmax_merge_kernel, dim3(n_rows), dim3(32), 0, stream, (const float*)part_val, (const int*)part_idx, chunks, out);
+    blm_launch_dependent(argmax_merge_kernel, dim3(n_rows), dim3(32), 0, stream, (const float*)part_val, (const int*)part_idx, chunks, out, mirror);
     return blm_check_launch("argmax");
 }
 
@@ -329,7 +340,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     const float* __restrict__ logits, long long row_stride, int vocab, const float* __restrict__ temperature,
     const float* __restrict__ top_p, const unsigned long long* __restrict__ seeds,
     const unsigned long long* __restrict__ stream_ids, const unsigned long long* __restrict__ counters,
-    int* __restrict__ out, float* __restrict__ work, int n_pieces) {
+    int* __restrict__ out, int* __restrict__ mirror, float* __restrict__ work, int n_pieces) {
     __shared__ float redf[33];
     __shared__ float piece_z[8];                              // the normaliser's sums over this block's pieces
     __shared__ unsigned long long red[33];
@@ -596,14 +607,14 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
             float best = -INFINITY; r = 0;
             for (int i = 0; i < vocab; ++i) if (row[i] > best) { best = row[i]; r = i; }
         }
-        out[b] = r;
+        blm_store_result(out, mirror, b, r);
     }
     cl_sync();       // nobody leaves while its shared memory may still be read
 }
 
 BLM_API int blm_sample(const float* logits, long long row_stride, int n_rows, int vocab, const float* temperature,
                        const float* top_p, const unsigned long long* seeds, const unsigned long long* stream_ids,
-                       const unsigned long long* counters, int* out, float* work, cudaStream_t stream) {
+                       const unsigned long long* counters, int* out, int* mirror, float* work, cudaStream_t stream) {
     if (n_rows == 0) return BLM_OK;
     BLM_REQUIRE(vocab > 0, "sample: empty vocabulary");
     BLM_REQUIRE(work != nullptr, "sample: no room for the rows' exponentials (n_rows x vocab floats)");
@@ -623,7 +634,7 @@ BLM_API int blm_sample(const float* logits, long long row_stride, int n_rows, in
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t err = cudaLaunchKernelEx(&cfg, sample_kernel, logits, row_stride, vocab, temperature, top_p, seeds, stream_ids, counters, out, work, (int)pieces);
+    cudaError_t err = cudaLaunchKernelEx(&cfg, sample_kernel, logits, row_stride, vocab, temperature, top_p, seeds, stream_ids, counters, out, mirror, work, (int)pieces);
     if (err != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "sample: %s", cudaGetErrorString(err));
     return blm_check_launch("sample");
 }
@@ -661,6 +672,6 @@ BLM_API int blm_argmax_no_alloc(const float* logits, long long row_stride, int n
     float* part_val = g_argmax_no_alloc_ptr[device];
     int* part_idx = reinterpret_cast<int*>(part_val + BLM_ARGMAX_NO_ALLOC_MAX_PARTIALS);
     argmax_chunk_kernel<<<dim3(chunks, n_rows), 256, 0, stream>>>(logits, row_stride, vocab, part_val, part_idx);
-    argmax_merge_kernel<<<n_rows, 32, 0, stream>>>(part_val, part_idx, chunks, out);
+    argmax_merge_kernel<<<n_rows, 32, 0, stream>>>(part_val, part_idx, chunks, out, (int*)nullptr);
     return blm_check_launch("argmax_no_alloc");
 }

@@ -19,6 +19,11 @@ from .. import kernels as K
 from ..parts.base import StepContext
 from .engine import Workspace
 
+# A captured step that samples hands its tokens to the host through pinned memory that its last kernel writes and the
+# native step driver polls (no copy out, no wait for the stream: 14 us of a 0.79 ms step at batch 8).  False: the
+# tokens are copied out and the stream is waited for.
+RESULTS_BY_POLLING = True
+
 
 @contextlib.contextmanager
 def _capturing(graph, pool=None):
@@ -79,6 +84,8 @@ class DecodeGraph:
         self._loop_graph = None     # forward + argmax + advance
         self._greedy_graph = None   # forward + argmax
         self._greedy_exec = None    # its cudaGraphExec_t (an integer) once known; False when torch does not give it out
+        self._greedy_again = None   # (stream, the native call for one more step on it)
+        self._sample_again = None
         self._chain_graph = None    # forward + argmax + advance: a step whose successor needs nothing from the host
         self._chain_out = None      # two pinned buffers for its results, used in turn
         self._chain_launches = 0
@@ -132,7 +139,7 @@ class DecodeGraph:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with _capturing(g):
-                K.argmax(self._forward(), self.sampled)
+                K.argmax(self._forward(), self.sampled, mirror=self.host_sampled)
             self._greedy_graph = g
             return self.sampled
         self._greedy_graph.replay()
@@ -145,7 +152,13 @@ class DecodeGraph:
         if self._greedy_exec:
             self._host_meta_np[:] = [*tokens, *positions, *slots]
             self.ctx.host["slots"], self.ctx.host["start_pos"] = list(slots), list(positions)
-            K.graph_step(self._greedy_exec, self.meta, self.host_meta, self.host_sampled, self.sampled)
+            stream = K.stream_handle()
+            if self._greedy_again is None or self._greedy_again[0] != stream:
+                # the captured argmax writes the pinned buffer itself (its `mirror`): nothing to copy out
+                self._greedy_again = (stream, K.graph_step(self._greedy_exec, self.meta, self.host_meta, self.host_sampled,
+                                                           self.sampled, written_by_graph=RESULTS_BY_POLLING))
+            else:
+                self._greedy_again[1]()
             return self._host_sampled_np.tolist()
         self.load(tokens, positions, slots)
         sampled = self.step_greedy()
@@ -215,12 +228,17 @@ class DecodeGraph:
 
         def draw():
             K.sample(self._forward(), self._sample_f[0], self._sample_f[1], self._sample_ids[0], self._sample_ids[1],
-                     self._sample_counters, self.sampled)
+                     self._sample_counters, self.sampled, mirror=self.host_sampled)
 
         if self._sample_exec:
             self._host_meta_np[:] = [*tokens, *positions, *slots]
-            K.graph_step(self._sample_exec, self.meta, self.host_meta, self.host_sampled, self.sampled,
-                         dev_in2=self._sample_counters, host_in2=self._host_counters)
+            stream = K.stream_handle()
+            if self._sample_again is None or self._sample_again[0] != stream:
+                self._sample_again = (stream, K.graph_step(self._sample_exec, self.meta, self.host_meta, self.host_sampled, self.sampled,
+                                                           dev_in2=self._sample_counters, host_in2=self._host_counters,
+                                                           written_by_graph=RESULTS_BY_POLLING))
+            else:
+                self._sample_again[1]()
             return self._host_sampled_np.tolist()
         self.load(tokens, positions, slots)
         self._sample_counters.copy_(self._host_counters, non_blocking=True)

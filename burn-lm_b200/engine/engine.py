@@ -81,6 +81,7 @@ class Engine:
         self._ahead = None                  # decode_graph.StepInFlight: a greedy step enqueued before it was asked for
         self._decode_graphs: dict = {}      # (batch, length bucket) -> DecodeGraph, least recently used first
         self.max_decode_graphs = 48
+        self._last_decode_graph = None      # (batch, lengths above, lengths up to, graph) of the last step
         from .prefill_graph import PrefillGraphs
         self._prefill_graphs = PrefillGraphs(self)
 
@@ -108,11 +109,15 @@ class Engine:
         """The captured decode step for `batch` sequences of at most `max_kv_len` tokens (made at first
         use).  Lengths come in buckets (64 tokens times a power of two), because the number of blocks
         that split a sequence's keys is fixed in a captured graph."""
+        last = self._last_decode_graph
+        if last is not None and last[0] == batch and last[1] < max_kv_len <= last[2]:
+            return last[3]                                      # the one of the step before: already the most recently used
         from .decode_graph import DecodeGraph
         pages = 1
         while pages * K.PAGE < max_kv_len:
             pages *= 2
-        bucket = min(pages * K.PAGE, -(-self.cache.max_seq_len // K.PAGE) * K.PAGE)
+        longest = -(-self.cache.max_seq_len // K.PAGE) * K.PAGE
+        bucket = min(pages * K.PAGE, longest)
         graphs = self._decode_graphs
         g = graphs.pop((batch, bucket), None)
         if g is None:
@@ -120,6 +125,9 @@ class Engine:
             while len(graphs) >= self.max_decode_graphs:      # the least recently used goes, with its buffers
                 del graphs[next(iter(graphs))]
         graphs[(batch, bucket)] = g                             # most recently used last
+        # the lengths this graph serves: more than the bucket below it (half of it, unless the bucket was cut to the cache's limit)
+        below = pages * K.PAGE // 2 if pages > 1 else 0
+        self._last_decode_graph = (batch, below, bucket, g)
         return g
 
     def decode_run(self, slots, tokens, n_steps: int) -> torch.Tensor:
@@ -192,15 +200,16 @@ class Engine:
         cache = self.cache
         if len(set(slots)) != len(slots):
             raise ValueError(f"a slot appears twice in one step: {sorted(slots)}")
+        held, seq_len, vocab, longest = cache.slots.held, cache.seq_len, self.vocab_size, cache.max_seq_len
         starts, grow = [], False
         for s, t in zip(slots, tokens):
-            if not cache.slots.held(s):
+            if not held(s):
                 raise CacheError(f"slot {s} is not held")
-            if not 0 <= t < self.vocab_size:
-                raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
-            n = cache.seq_len[s]
+            if not 0 <= t < vocab:
+                raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
+            n = seq_len[s]
             starts.append(n)
-            if n % K.PAGE == 0 or n >= cache.max_seq_len:
+            if n % K.PAGE == 0 or n >= longest:
                 grow = True
         return starts, grow
 

@@ -99,7 +99,8 @@ _protos = {
     },
     "runtime": {
         "blm_graph_step": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
-                           c_void_p],
+                           c_int, c_void_p],
+        "blm_host_device_pointer": [c_void_p, c_void_p],
     },
     "gemm_tc": {
         "blm_gemm_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
@@ -113,10 +114,10 @@ _protos = {
         "blm_gemm_sk_squares_row": [],
     },
     "sampling": {
-        "blm_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "blm_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
         "blm_argmax_scratch_floats": [c_int, c_int],
         "blm_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                       c_void_p, c_void_p, c_void_p],
+                       c_void_p, c_void_p, c_void_p, c_void_p],
     },
 }
 _bound: dict[str, ctypes.CDLL] = {}
@@ -149,6 +150,11 @@ _launches = 0
 def launch_count() -> int:
     """How many kernels of this package have been launched (or captured) by this process."""
     return _launches
+
+
+def stream_handle() -> int:
+    """torch's current stream as an integer."""
+    return _stream().value or 0
 
 
 def _call(module: str, name: str, *args, kernels: int = 1):
@@ -470,14 +476,34 @@ def gemm_sk(w, x, out=None, add_into=None, swiglu=False, squares=None, eps=0.0, 
           ctypes.byref(rope_arg) if rope_arg is not None else None, _ptr(status_word(w.device)), _stream())
 
 
-def graph_step(graph_exec: int, dev_in, host_in, host_out, dev_out, dev_in2=None, host_in2=None) -> None:
+def graph_step(graph_exec: int, dev_in, host_in, host_out, dev_out, dev_in2=None, host_in2=None, written_by_graph=False):
     """One captured step driven from native code: host_in (pinned) -> dev_in (and host_in2 -> dev_in2), the
     instantiated graph `graph_exec` (a cudaGraphExec_t as an integer), dev_out -> host_out (pinned), and the
-    wait, on the current stream."""
+    wait, on the current stream.  `written_by_graph`: the graph's last kernel writes host_out itself (int32 >= 0,
+    see `argmax`'s `mirror`); then nothing is copied out and the call returns as soon as every entry is there.
+
+    Returns a function of no arguments that does the same again (same buffers, same stream) at the cost of one
+    foreign call: every argument is converted once, here."""
     nbytes = lambda t: t.numel() * t.element_size() if t is not None else 0
-    _call("runtime", "blm_graph_step", c_void_p(graph_exec), _ptr(dev_in), c_void_p(host_in.data_ptr()), nbytes(host_in),
-          _ptr(dev_in2), c_void_p(host_in2.data_ptr()) if host_in2 is not None else c_void_p(0), nbytes(host_in2),
-          c_void_p(host_out.data_ptr()), _ptr(dev_out), nbytes(host_out), _stream(), kernels=0)
+    fn = getattr(_lib("runtime"), "blm_graph_step")
+    args = (c_void_p(graph_exec), _ptr(dev_in), c_void_p(host_in.data_ptr()), nbytes(host_in),
+            _ptr(dev_in2), c_void_p(host_in2.data_ptr()) if host_in2 is not None else c_void_p(0), nbytes(host_in2),
+            c_void_p(host_out.data_ptr()), _ptr(dev_out), nbytes(host_out), 1 if written_by_graph else 0, _stream())
+
+    def again():
+        if fn(*args) != 0:
+            raise KernelError("graph_step: " + _lib("runtime").blm_runtime_last_error().decode(errors="replace"))
+    again()
+    return again
+
+
+def host_device_pointer(pinned) -> int:
+    """The address under which kernels see a pinned host tensor."""
+    if not pinned.is_pinned():
+        raise KernelError("host_device_pointer: the tensor is not in pinned host memory")
+    dev = c_void_p(0)
+    _call("runtime", "blm_host_device_pointer", c_void_p(pinned.data_ptr()), ctypes.byref(dev), kernels=0)
+    return int(dev.value or 0)
 
 
 _status: dict = {}
@@ -597,34 +623,43 @@ def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, 
           _ptr(status_word(w.device)), _stream())
 
 
-def argmax(logits, out):
-    """out[b] = index of the largest logit of row b (the lowest index on a tie)."""
+def argmax(logits, out, mirror=None):
+    """out[b] = index of the largest logit of row b (the lowest index on a tie).  `mirror`: a pinned host int32
+    tensor that the kernel fills as well, through the address the device sees it under, so that a host which
+    polls it has the result without a copy (`graph_step`)."""
     _need_cuda(logits, out)
     if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() < logits.shape[0]:
         raise KernelError("argmax: float32 logits [B, V], int32 out [B]")
     b, v = logits.shape
+    if mirror is not None and (mirror.dtype != torch.int32 or mirror.numel() < b or not mirror.is_contiguous()):
+        raise KernelError("argmax: the mirror is a pinned int32 tensor of at least B entries")
     need = _lib("sampling").blm_argmax_scratch_floats(b, v)
     scratch = torch.empty(need, dtype=torch.float32, device=logits.device) if need else None
-    _call("sampling", "blm_argmax", _ptr(logits), logits.stride(0), b, v, _ptr(out), _ptr(scratch), _stream(),
+    _call("sampling", "blm_argmax", _ptr(logits), logits.stride(0), b, v, _ptr(out),
+          c_void_p(host_device_pointer(mirror) if mirror is not None else 0), _ptr(scratch), _stream(),
           kernels=2 if need else 1)
 
 
-def sample(logits, temperature, top_p, seeds, stream_ids, counters, out):
+def sample(logits, temperature, top_p, seeds, stream_ids, counters, out, mirror=None):
     """Draw out[b] from softmax(logits[b] / temperature[b]) restricted to its top-p nucleus.
 
     temperature, top_p float32 [B]; seeds, stream_ids, counters int64 [B] (read as unsigned): the
-    uniform number of a draw is a hash of the three, so it does not depend on the batch."""
+    uniform number of a draw is a hash of the three, so it does not depend on the batch.
+    `mirror`: as `argmax`'s."""
     _need_cuda(logits, temperature, top_p, seeds, stream_ids, counters, out)
     b = logits.shape[0]
     if logits.dtype != torch.float32 or out.dtype != torch.int32:
         raise KernelError("sample: float32 logits, int32 out")
+    if mirror is not None and (mirror.dtype != torch.int32 or mirror.numel() < b or not mirror.is_contiguous()):
+        raise KernelError("sample: the mirror is a pinned int32 tensor of at least B entries")
     for t, dt in ((temperature, torch.float32), (top_p, torch.float32), (seeds, torch.int64),
                   (stream_ids, torch.int64), (counters, torch.int64)):
         if t.dtype != dt or t.numel() < b:
             raise KernelError("sample: per-row arguments must be float32/int64 of length B")
     work = torch.empty((b, logits.shape[1]), dtype=torch.float32, device=logits.device)     # the rows' exponentials
     _call("sampling", "blm_sample", _ptr(logits), logits.stride(0), b, logits.shape[1], _ptr(temperature),
-          _ptr(top_p), _ptr(seeds), _ptr(stream_ids), _ptr(counters), _ptr(out), _ptr(work), _stream())
+          _ptr(top_p), _ptr(seeds), _ptr(stream_ids), _ptr(counters), _ptr(out),
+          c_void_p(host_device_pointer(mirror) if mirror is not None else 0), _ptr(work), _stream())
 
 
 def uniform32(seed, stream_id, counter) -> int:

@@ -264,6 +264,31 @@ def test_repeated_runs_and_captured_steps_give_the_same_tokens(tmp_path):
     lm.engine.verify()
 
 
+def test_tokens_reach_the_host_by_polling_or_by_copy(tmp_path, monkeypatch):
+    """A captured step that samples writes its tokens into pinned memory itself and the native step driver polls for
+    them; with that switched off they are copied out and the stream is waited for.  Greedy and drawn tokens are the
+    same both ways, over batches that shrink and slots used again; the greedy ones also equal the steps launched
+    plainly (a draw may fall on the other side of a boundary when another split of the keys rounds a logit differently)."""
+    import burn_lm_b200 as blm
+    from burn_lm_b200.engine import decode_graph
+    folder = make_folder(tmp_path, "tiny_d", seed=27, dtype="bfloat16")
+    cfg = CONFIGS["tiny_d"]
+    prompts = [random_tokens(500 + n, length, cfg["vocab_size"]) for n, length in enumerate([9, 70, 33, 128, 1, 64])]
+
+    def run(polling, graphs=True):
+        monkeypatch.setattr(decode_graph, "RESULTS_BY_POLLING", polling)
+        lm = blm.load(folder, dtype="bfloat16", max_seq_len=256, max_batch=4)
+        lm.engine.use_graphs = graphs
+        greedy = lm.generate(prompts, sample_len=60, ignore_stop=True).tokens
+        drawn = lm.generate(prompts, sample_len=60, ignore_stop=True, temperature=0.8, top_p=0.9, seed=3).tokens
+        lm.engine.verify()
+        return greedy, drawn
+
+    polled = run(True)
+    assert polled == run(False)
+    assert polled[0] == run(True, graphs=False)[0]
+
+
 def test_decode_graphs_are_dropped_and_made_again(tmp_path):
     """The engine keeps a bounded number of captured decode steps; with room for two only, requests that
     alternate between batch sizes and grow through several length buckets generate the same tokens."""

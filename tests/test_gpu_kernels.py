@@ -637,6 +637,35 @@ def test_argmax_large_vocabulary():
     assert out.tolist() == want.tolist()
 
 
+@pytest.mark.parametrize("vocab", [1000, 128256])
+def test_argmax_and_sample_fill_a_pinned_mirror(vocab):
+    """The sampling kernels write their results to pinned host memory as well when given a `mirror` (the captured
+    decode step's way of handing tokens to a polling host): after the stream is done it holds what `out` holds,
+    for the one-kernel argmax, the two-stage one and the draw; rows beyond the batch are left alone."""
+    g = torch.Generator(device="cuda").manual_seed(41)
+    logits = torch.randn(5, vocab, device="cuda", generator=g) * 3
+    out = torch.empty(5, device="cuda", dtype=torch.int32)
+    mirror = torch.full((7,), -1, dtype=torch.int32).pin_memory()
+    K().argmax(logits, out, mirror=mirror)
+    torch.cuda.synchronize()
+    assert out.tolist() == logits.argmax(-1).tolist()
+    assert mirror.tolist() == out.tolist() + [-1, -1]
+    mirror.fill_(-1)
+    f = torch.tensor([[0.8] * 5, [0.9] * 5], dtype=torch.float32, device="cuda")
+    ids = torch.tensor([[7] * 5, [1, 2, 3, 4, 5]], dtype=torch.int64, device="cuda")
+    counters = torch.arange(5, dtype=torch.int64, device="cuda")
+    K().sample(logits, f[0], f[1], ids[0], ids[1], counters, out, mirror=mirror)
+    torch.cuda.synchronize()
+    plain = torch.empty(5, device="cuda", dtype=torch.int32)
+    K().sample(logits, f[0], f[1], ids[0], ids[1], counters, plain)
+    assert out.tolist() == plain.tolist()
+    assert mirror.tolist() == out.tolist() + [-1, -1]
+    with pytest.raises(K().KernelError):
+        K().argmax(logits, out, mirror=torch.zeros(7, dtype=torch.int32))          # not pinned
+    with pytest.raises(K().KernelError):
+        K().argmax(logits, out, mirror=torch.zeros(3, dtype=torch.int32).pin_memory())   # too short
+
+
 @pytest.mark.parametrize("H,KV,hd", [(8, 2, 64), (4, 4, 128), (6, 1, 64)])
 def test_prompt_attention_on_tensor_cores(H, KV, hd):
     """Prompts of head size 64 / 128 in bfloat16 take the tensor-core kernel: whole prompts of unequal
