@@ -184,12 +184,19 @@ class Cache:
                 raise CacheFull(f"the step needs {extra} more cache pages of {PAGE} tokens; {g.pages.free_count} of "
                                 f"{self.n_pages} are free ({held * PAGE} of {self.n_pages * PAGE} token places held)")
         for g in self._kv_groups:
+            cells, values = [], []              # all the step's new entries of the block table go over in one piece
             for slot, pages in plan:
                 have = len(g.pages_of[slot])
                 if pages > have:
                     new = g.pages.acquire_many(pages - have)
                     g.pages_of[slot].extend(new)
-                    g.block_table[slot, have:pages] = torch.tensor(new, dtype=torch.int32)
+                    first = slot * self.max_pages_per_seq + have
+                    cells.extend(range(first, first + len(new)))
+                    values.extend(new)
+            if cells:
+                dev = g.block_table.device
+                g.block_table.view(-1).index_put_((torch.tensor(cells, dtype=torch.int64).to(dev),),
+                                                  torch.tensor(values, dtype=torch.int32).to(dev))
 
     def set_length(self, slot: int, length: int) -> None:
         self.seq_len[slot] = length

@@ -59,13 +59,30 @@ __global__ void __launch_bounds__(kSampleThreads) argmax_kernel(const float* __r
 // Large vocabularies: many blocks per row find the best of their chunk, one block per row merges.
 constexpr int kArgmaxChunk = 4096;
 
+// What a step that feeds itself does with a row's token (see decode_advance_kernel in elementwise.cu, which does the
+// same as a launch of its own): the token becomes the row's next input, its position moves on, the token joins the
+// history of the run; when every row has done so, the run's step counter moves on.
+struct ArgmaxAdvance {
+    int* tokens;            // null: nothing of this
+    int* pos;
+    int* history;           // [history_steps, rows] or null
+    int* step_no;
+    long long* counters;    // per row, or null
+    int history_steps;
+};
+
+// `tickets` (rows + 1 ints, zero before and after): null, and the chunks' results wait for argmax_merge_kernel; else
+// the block that finishes a row's last chunk merges the row itself, so the row's result needs no second launch.
 __global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
-                                                           float* __restrict__ part_val, int* __restrict__ part_idx) {
+                                                           float* __restrict__ part_val, int* __restrict__ part_idx,
+                                                           int* __restrict__ tickets, int* __restrict__ out, int* __restrict__ mirror,
+                                                           ArgmaxAdvance adv) {
     pdl_launch_dependents();
     pdl_wait();
     blm_trace(0x310);
     __shared__ float bv[8];
     __shared__ int bi[8];
+    __shared__ int s_last;
     const float* row = logits + (size_t)blockIdx.y * row_stride;
     const int lo = blockIdx.x * kArgmaxChunk, hi = min(vocab, lo + kArgmaxChunk);
     float best = -INFINITY;
@@ -102,6 +119,47 @@ __global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* __restri
             if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
         part_val[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = best;
         part_idx[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = idx;
+        if (tickets != nullptr) {
+            __threadfence();
+            s_last = atomicAdd(&tickets[blockIdx.y], 1) == (int)gridDim.x - 1;
+        }
+    }
+    if (tickets == nullptr) return;
+    __syncthreads();
+    if (!s_last || threadIdx.x >= 32) return;
+    // the row's last block: every chunk's result is written (the fences around the ticket); the lowest index among the
+    // largest values does not depend on which block this is
+    __threadfence();
+    const int chunks = gridDim.x, r = blockIdx.y, rows = gridDim.y;
+    best = -INFINITY;
+    idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < chunks; i += 32) {
+        const float v = __ldcg(part_val + (size_t)r * chunks + i);
+        const int vi = __ldcg(part_idx + (size_t)r * chunks + i);
+        if (v > best || (v == best && vi < idx)) { best = v; idx = vi; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    if (threadIdx.x != 0) return;
+    blm_trace(0x320);
+    const int token = idx == 0x7fffffff ? 0 : idx;
+    tickets[r] = 0;
+    blm_store_result(out, mirror, r, token);
+    if (adv.tokens != nullptr) {
+        const int s = *reinterpret_cast<volatile int*>(adv.step_no);     // read before this row's ticket below
+        adv.tokens[r] = token;
+        adv.pos[r] += 1;
+        if (adv.counters != nullptr) adv.counters[r] += 1;
+        if (adv.history != nullptr && s < adv.history_steps) adv.history[(size_t)s * rows + r] = token;
+        __threadfence();
+        if (atomicAdd(&tickets[rows], 1) == rows - 1) {      // every row has read the counter: it may move on
+            tickets[rows] = 0;
+            *adv.step_no = s + 1;
+        }
     }
 }
 
@@ -133,19 +191,30 @@ BLM_API int blm_argmax_scratch_floats(int n_rows, int vocab) {
 }
 
 // `mirror`: null, or pinned host memory (its device address) that gets the results as well.
+// `tickets`: null, or rows + 1 ints that are zero (and are zero again afterwards), used by no other launch in flight:
+// then a large vocabulary takes one launch instead of two.  tokens .. history_steps: null / 0, or the step feeds itself
+// (ArgmaxAdvance; needs the tickets and a large vocabulary: ask blm_argmax_advances).
+BLM_API int blm_argmax_advances(int vocab) { return vocab > 2 * kArgmaxChunk ? 1 : 0; }
+
 BLM_API int blm_argmax(const float* logits, long long row_stride, int n_rows, int vocab, int* out, int* mirror, float* scratch,
+                       int* tickets, int* tokens, int* pos, int* history, int* step_no, long long* counters, int history_steps,
                        cudaStream_t stream) {
     if (n_rows == 0) return BLM_OK;
     BLM_REQUIRE(vocab > 0, "argmax: empty vocabulary");
+    ArgmaxAdvance adv = {tokens, pos, history, step_no, counters, history_steps};
     if (vocab <= 2 * kArgmaxChunk || scratch == nullptr) {
+        BLM_REQUIRE(tokens == nullptr, "argmax: a step feeds itself only from the chunked kernel (a vocabulary above %d, scratch and tickets)", 2 * kArgmaxChunk);
         argmax_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, row_stride, vocab, out, mirror);
         return blm_check_launch("argmax");
     }
+    BLM_REQUIRE(tokens == nullptr || (tickets != nullptr && pos != nullptr && step_no != nullptr), "argmax: a step that feeds itself needs tickets, positions and a step counter");
     const int chunks = (vocab + kArgmaxChunk - 1) / kArgmaxChunk;
     float* part_val = scratch;
     int* part_idx = reinterpret_cast<int*>(scratch + (size_t)n_rows * chunks);
-    blm_launch_dependent(argmax_chunk_kernel, dim3(chunks, n_rows), dim3(256), 0, stream, logits, row_stride, vocab, part_val, part_idx);
-    blm_launch_dependent(argmax_merge_kernel, dim3(n_rows), dim3(32), 0, stream, (const float*)part_val, (const int*)part_idx, chunks, out, mirror);
+    blm_launch_dependent(argmax_chunk_kernel, dim3(chunks, n_rows), dim3(256), 0, stream, logits, row_stride, vocab, part_val, part_idx,
+                         tickets, out, mirror, adv);
+    if (tickets == nullptr)
+        blm_launch_dependent(argmax_merge_kernel, dim3(n_rows), dim3(32), 0, stream, (const float*)part_val, (const int*)part_idx, chunks, out, mirror);
     return blm_check_launch("argmax");
 }
 
@@ -671,7 +740,7 @@ BLM_API int blm_argmax_no_alloc(const float* logits, long long row_stride, int n
     }
     float* part_val = g_argmax_no_alloc_ptr[device];
     int* part_idx = reinterpret_cast<int*>(part_val + BLM_ARGMAX_NO_ALLOC_MAX_PARTIALS);
-    argmax_chunk_kernel<<<dim3(chunks, n_rows), 256, 0, stream>>>(logits, row_stride, vocab, part_val, part_idx);
+    argmax_chunk_kernel<<<dim3(chunks, n_rows), 256, 0, stream>>>(logits, row_stride, vocab, part_val, part_idx, (int*)nullptr, (int*)nullptr, (int*)nullptr, ArgmaxAdvance{});
     argmax_merge_kernel<<<n_rows, 32, 0, stream>>>(part_val, part_idx, chunks, out, (int*)nullptr);
     return blm_check_launch("argmax_no_alloc");
 }

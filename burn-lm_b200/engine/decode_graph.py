@@ -78,6 +78,7 @@ class DecodeGraph:
             host={"cu_seqlens": list(range(b + 1)), "slots": None, "start_pos": None})
         self.sampled = torch.zeros(b, dtype=torch.int32, device=dev)
         self.step_no = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.tickets = torch.zeros(b + 1, dtype=torch.int32, device=dev)     # the argmax kernel's, zero between launches
         self.history = None
         self.logits = None
         self._graph = None          # forward only
@@ -135,11 +136,11 @@ class DecodeGraph:
         """One decode step on the loaded inputs with the argmax inside the captured graph; the
         sampled tokens, int32 [B], in a buffer that the next step overwrites."""
         if self._greedy_graph is None:
-            K.argmax(self._forward(), self.sampled)  # the first step runs plainly and warms everything up
+            K.argmax(self._forward(), self.sampled, tickets=self.tickets)  # the first step runs plainly and warms everything up
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with _capturing(g):
-                K.argmax(self._forward(), self.sampled, mirror=self.host_sampled)
+                K.argmax(self._forward(), self.sampled, mirror=self.host_sampled, tickets=self.tickets)
             self._greedy_graph = g
             return self.sampled
         self._greedy_graph.replay()
@@ -201,8 +202,7 @@ class DecodeGraph:
         return StepInFlight(self, list(slots), list(positions), None if tokens is None else list(tokens), done, host)
 
     def _one_chained_step(self):
-        K.argmax(self._forward(), self.sampled)
-        K.decode_advance(self.tokens, self.pos, self.sampled, None, self.step_no)
+        K.argmax(self._forward(), self.sampled, tickets=self.tickets, advance=(self.tokens, self.pos, None, self.step_no))
 
     def step_sampled_host(self, tokens, positions, slots, params, stream_ids, counters) -> list:
         """A step that draws its tokens by temperature and nucleus inside the captured graph, from host
@@ -284,5 +284,4 @@ class DecodeGraph:
 
     def _one_loop_step(self):
         logits = self._forward()
-        K.argmax(logits, self.sampled)
-        K.decode_advance(self.tokens, self.pos, self.sampled, self.history, self.step_no)
+        K.argmax(logits, self.sampled, tickets=self.tickets, advance=(self.tokens, self.pos, self.history, self.step_no))

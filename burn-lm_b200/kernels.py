@@ -114,7 +114,9 @@ _protos = {
         "blm_gemm_sk_squares_row": [],
     },
     "sampling": {
-        "blm_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        "blm_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_int, c_void_p],
+        "blm_argmax_advances": [c_int],
         "blm_argmax_scratch_floats": [c_int, c_int],
         "blm_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_void_p, c_void_p],
@@ -623,21 +625,44 @@ def gemv(w, n_tokens, x=None, stream_rows=None, gamma=None, eps=0.0, rows=None, 
           _ptr(status_word(w.device)), _stream())
 
 
-def argmax(logits, out, mirror=None):
+def argmax(logits, out, mirror=None, tickets=None, advance=None):
     """out[b] = index of the largest logit of row b (the lowest index on a tie).  `mirror`: a pinned host int32
     tensor that the kernel fills as well, through the address the device sees it under, so that a host which
-    polls it has the result without a copy (`graph_step`)."""
+    polls it has the result without a copy (`graph_step`).  `tickets`: B + 1 zeroed int32 on the device that belong
+    to the caller and to no other launch in flight (the kernel leaves them zero): a large vocabulary then takes one
+    launch instead of two.  `advance` = (tokens, positions, history or None, step counter): the step feeds itself
+    as `decode_advance` says, in that same launch where there is one."""
     _need_cuda(logits, out)
     if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() < logits.shape[0]:
         raise KernelError("argmax: float32 logits [B, V], int32 out [B]")
     b, v = logits.shape
     if mirror is not None and (mirror.dtype != torch.int32 or mirror.numel() < b or not mirror.is_contiguous()):
         raise KernelError("argmax: the mirror is a pinned int32 tensor of at least B entries")
-    need = _lib("sampling").blm_argmax_scratch_floats(b, v)
+    lib = _lib("sampling")
+    need = lib.blm_argmax_scratch_floats(b, v)
     scratch = torch.empty(need, dtype=torch.float32, device=logits.device) if need else None
+    if tickets is not None:
+        _need_cuda(tickets)
+        if tickets.dtype != torch.int32 or tickets.numel() < b + 1 or not tickets.is_contiguous():
+            raise KernelError("argmax: the tickets are B + 1 int32")
+        if not need:
+            tickets = None
+    fed = None
+    if advance is not None and tickets is not None and lib.blm_argmax_advances(v):
+        fed = advance
+        tokens, pos, history, step_no = fed
+        _need_cuda(tokens, pos, step_no)
+        if tokens.dtype != torch.int32 or pos.dtype != torch.int32 or tokens.numel() != b or pos.numel() != b:
+            raise KernelError("argmax: a step that feeds itself has int32 tokens and positions [B]")
+        if history is not None and (history.dtype != torch.int32 or history.shape[1] != b or not history.is_contiguous()):
+            raise KernelError("argmax: the history is int32 [steps, B]")
+    tokens, pos, history, step_no = fed if fed is not None else (None, None, None, None)
     _call("sampling", "blm_argmax", _ptr(logits), logits.stride(0), b, v, _ptr(out),
-          c_void_p(host_device_pointer(mirror) if mirror is not None else 0), _ptr(scratch), _stream(),
-          kernels=2 if need else 1)
+          c_void_p(host_device_pointer(mirror) if mirror is not None else 0), _ptr(scratch), _ptr(tickets),
+          _ptr(tokens), _ptr(pos), _ptr(history), _ptr(step_no), c_void_p(0), history.shape[0] if history is not None else 0,
+          _stream(), kernels=(1 if tickets is not None else 2) if need else 1)
+    if advance is not None and fed is None:
+        decode_advance(advance[0], advance[1], out, advance[2], advance[3])
 
 
 def sample(logits, temperature, top_p, seeds, stream_ids, counters, out, mirror=None):

@@ -637,6 +637,42 @@ def test_argmax_large_vocabulary():
     assert out.tolist() == want.tolist()
 
 
+@pytest.mark.parametrize("vocab,rows", [(128256, 9), (20000, 70), (1000, 5)])
+def test_argmax_in_one_launch_feeds_the_next_step(vocab, rows):
+    """With tickets a large vocabulary's argmax is one launch (the block that finishes a row's last chunk merges the
+    row) and gives what the two launches give, planted ties across chunks included, the tickets zero again; with
+    `advance` the same launch makes the step feed itself: tokens, positions, the run's history and its step counter
+    over several steps, as the separate kernel does (which a small vocabulary still takes)."""
+    g = torch.Generator(device="cuda").manual_seed(42)
+    tickets = torch.zeros(rows + 1, device="cuda", dtype=torch.int32)
+    tokens = torch.zeros(rows, device="cuda", dtype=torch.int32)
+    pos = torch.arange(rows, device="cuda", dtype=torch.int32) * 7
+    history = torch.full((3, rows), -1, device="cuda", dtype=torch.int32)
+    step_no = torch.zeros(1, device="cuda", dtype=torch.int32)
+    want_history = []
+    for step in range(4):            # one more than the history holds: the last is not recorded
+        logits = torch.randn(rows, vocab, device="cuda", generator=g)
+        logits[1, vocab - 1] = logits[1, 17] = 40.0                   # a tie across chunks: the lower index
+        logits[2, vocab - 1] = 41.0
+        want = logits.argmax(-1)
+        want[1] = 17
+        two = torch.empty(rows, device="cuda", dtype=torch.int32)
+        K().argmax(logits, two)
+        one = torch.empty(rows, device="cuda", dtype=torch.int32)
+        K().argmax(logits, one, tickets=tickets)
+        assert two.tolist() == want.tolist() and one.tolist() == want.tolist()
+        fed = torch.empty(rows, device="cuda", dtype=torch.int32)
+        K().argmax(logits, fed, tickets=tickets, advance=(tokens, pos, history, step_no))
+        want_history.append(want.tolist())
+        assert fed.tolist() == want.tolist() and tokens.tolist() == want.tolist()
+        assert pos.tolist() == [7 * r + step + 1 for r in range(rows)]
+        assert step_no.item() == step + 1
+        assert tickets.tolist() == [0] * (rows + 1)
+    assert history.tolist() == want_history[:3]
+    with pytest.raises(K().KernelError):
+        K().argmax(logits, fed, tickets=tickets[:rows])
+
+
 @pytest.mark.parametrize("vocab", [1000, 128256])
 def test_argmax_and_sample_fill_a_pinned_mirror(vocab):
     """The sampling kernels write their results to pinned host memory as well when given a `mirror` (the captured
