@@ -306,6 +306,8 @@ def run_ours(args):
         print(json.dumps({"only": "decode", "batch": batch, "ms_per_step": round(r["ms_per_step"], 4)}))
         return 0
     if args.only == "prefill":
+        if args.prompt_tokens:
+            one_prompt = make_prompts(("equal", args.prompt_tokens), 1, vocab, seed=99)
         ms = time_prefill(engine, one_prompt or prompts, reps=1)
         print(json.dumps({"only": "prefill", "tokens": sum(len(p) for p in (one_prompt or prompts)), "ms": round(ms, 3)}))
         return 0
@@ -381,6 +383,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="sequences decoded together (default: the workload's)")
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "sweep"],
                     help="run one workload briefly (for profilers), or a sweep over batch sizes and context lengths")
+    ap.add_argument("--prompt-tokens", type=int, default=0, help="with --only prefill: one prompt of this many tokens instead of the workload's")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (both numbers are named in config)")
     args = ap.parse_args()
     if args.impl == "reference":

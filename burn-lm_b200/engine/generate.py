@@ -181,6 +181,41 @@ class GenerationLoop:
                 if not live:
                     break
                 tokens = None
+                step_fn = fused if params.greedy else fused_draw
+                # How many more tokens every live request takes for certain, unless a stop id turns up: until the
+                # first of them reaches its length or the context's end.  Steps within that stretch need no look
+                # at single requests: the step's tokens are fed back as they came, and they join the requests'
+                # lists in one go when the stretch ends (or an error ends it).
+                quiet = 0
+                if step_fn is not None and on_token is None:
+                    quiet = min(min(sample_len - 1 - len(results[i].tokens), max_len - len(prompts[i]) - len(results[i].tokens)) for i in live)
+                if quiet > 0:
+                    last = [results[i].tokens[-1] for i in live]
+                    counts = None if params.greedy else [len(results[i].tokens) for i in live]
+                    columns = []
+                    try:
+                        while quiet > 0:
+                            if params.greedy:
+                                got = step_fn(live_slots, last, more=looks_ahead)
+                            else:
+                                got = step_fn(live_slots, last, params, live, counts)
+                            if got is None:                    # this engine has no short way: the careful one below
+                                break
+                            stats.decode_steps += 1
+                            if stop and not stop.isdisjoint(got):
+                                tokens = got                   # someone stops here: looked at one by one above
+                                break
+                            stats.generated_tokens += len(got)
+                            columns.append(got)
+                            last = got
+                            if counts is not None:
+                                counts = [c + 1 for c in counts]
+                            quiet -= 1
+                    finally:
+                        for j, i in enumerate(live):
+                            results[i].tokens.extend([column[j] for column in columns])
+                    if tokens is not None:
+                        continue
                 if params.greedy and fused is not None:      # the engine samples inside its captured step
                     # will anyone need a step after this one (if no stop id turns up)?  Then the engine may enqueue it now.
                     more = looks_ahead and any(len(results[i].tokens) + 1 < sample_len and len(prompts[i]) + len(results[i].tokens) + 1 <= max_len

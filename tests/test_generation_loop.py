@@ -227,3 +227,73 @@ def test_include_stop_emits_the_stop_id_and_still_ends_there():
     assert seen_stop
     assert out.stats.generated_tokens == sum(len(r.tokens) for r in out.results)
     assert eng.cache.slots.held_count == 0
+
+
+class QuickEngine(ScriptedEngine):
+    """The scripted engine with the short ways through a decode step that the real engine has: the loop then takes
+    stretches of steps in which nobody can end without looking at single requests."""
+
+    def __init__(self, fail_at=None, **kw):
+        super().__init__(**kw)
+        self.quick_calls, self.draws, self.fail_at = 0, [], fail_at
+
+    def _quick(self, slots, tokens):
+        from burn_lm_b200.engine.engine import StepEntry
+        self.quick_calls += 1
+        if self.fail_at is not None and self.quick_calls == self.fail_at:
+            raise RuntimeError("the device fell over")
+        return self.step([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)]).argmax(-1).tolist()
+
+    def decode_greedy(self, slots, tokens, more=False):
+        return self._quick(slots, tokens)
+
+    def decode_sampled(self, slots, tokens, params, stream_ids, counters):
+        self.draws.append((params, list(stream_ids), list(counters)))
+        return self._quick(slots, tokens)
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.7])
+def test_stretches_of_quiet_steps_decide_what_single_steps_decide(temperature):
+    """With an engine that samples inside its step, the loop runs the steps in which no request can reach its
+    length or the context's end without looking at single requests, and hands the tokens out when the stretch
+    ends.  Requests, finish reasons, counts and the numbering of the draws are those of the loop that looks at every
+    token: over stop ids inside a stretch, unequal lengths, the context's end, batches after one another."""
+    prompts = [[1, 2, 3], [4], [5, 6, 7, 8, 9, 10, 11], [2, 2], [9] * 30, [3, 1]]
+    reasons = set()
+    for kw in (dict(sample_len=12, stop_ids=(29,)), dict(sample_len=40, ignore_stop=True), dict(sample_len=1),
+               dict(sample_len=2), dict(sample_len=25, stop_ids=(7, 31), include_stop=True), dict(sample_len=100, ignore_stop=True)):
+        opts = GenerateOptions(temperature=temperature, seed=5, **kw)
+        slow_eng, slow_smp = ScriptedEngine(max_seqs=3, max_seq_len=48), ArgmaxSampler()
+        slow = GenerationLoop(slow_eng, slow_smp, default_stop_ids=(13,)).generate(prompts, opts)
+        quick_eng = QuickEngine(max_seqs=3, max_seq_len=48)
+        quick = GenerationLoop(quick_eng, ArgmaxSampler(), default_stop_ids=(13,)).generate(prompts, opts)
+        assert [r.tokens for r in quick.results] == [r.tokens for r in slow.results], kw
+        assert [r.finish_reason for r in quick.results] == [r.finish_reason for r in slow.results], kw
+        reasons |= {r.finish_reason for r in slow.results}
+        assert quick.stats.generated_tokens == slow.stats.generated_tokens and quick.stats.decode_steps == slow.stats.decode_steps
+        assert quick_eng.steps == slow_eng.steps                 # the same steps with the same sequences
+        assert quick_eng.cache.slots.held_count == 0
+        if kw["sample_len"] > 2:
+            assert quick_eng.quick_calls > 0
+        if temperature > 0:
+            # every draw carries its request's number and how many tokens the request has: as the sampler saw them
+            assert quick_eng.draws == [c for c in slow_smp.calls if c[2] != [0] * len(c[2])], kw
+    assert reasons == {"stop", "length", "context"}                # the script makes all three happen
+
+
+def test_an_error_inside_a_stretch_keeps_the_tokens_so_far():
+    eng = QuickEngine(fail_at=5)
+    loop = GenerationLoop(eng, ArgmaxSampler())
+    with pytest.raises(RuntimeError):
+        loop.generate([[1, 2, 3], [4]], GenerateOptions(sample_len=30, ignore_stop=True))
+    assert eng.cache.slots.held_count == 0
+
+
+def test_streaming_looks_at_every_token():
+    prompts = [[1, 2, 3], [4]]
+    seen = []
+    eng = QuickEngine()
+    out = GenerationLoop(eng, ArgmaxSampler()).generate(prompts, GenerateOptions(sample_len=9, ignore_stop=True),
+                                                         on_token=lambda i, t: seen.append((i, t)))
+    for i, r in enumerate(out.results):
+        assert [t for j, t in seen if j == i] == r.tokens == expected(prompts[i], 9)[0]
