@@ -43,6 +43,10 @@ class IdAllocator:
     def held(self, i: int) -> bool:
         return 0 <= i < self.n and self._held[i]
 
+    def all_held(self, ids) -> bool:
+        """Whether every id of a (non-empty) list is held."""
+        return min(ids) >= 0 and max(ids) < self.n and all(map(self._held.__getitem__, ids))
+
     def acquire(self) -> int:
         if not self._free:
             raise CacheFull(f"no free {self.what} (all {self.n} are held)")

@@ -157,7 +157,10 @@ class Engine:
         if not self.use_graphs:
             return None
         cache = self.cache
-        slots, tokens = list(slots), list(tokens)
+        if type(slots) is not list:
+            slots = list(slots)
+        if type(tokens) is not list:
+            tokens = list(tokens)
         more = more and self.decode_ahead
         ahead, self._ahead = self._ahead, None
         cur = None
@@ -200,17 +203,15 @@ class Engine:
         cache = self.cache
         if len(set(slots)) != len(slots):
             raise ValueError(f"a slot appears twice in one step: {sorted(slots)}")
-        held, seq_len, vocab, longest = cache.slots.held, cache.seq_len, self.vocab_size, cache.max_seq_len
-        starts, grow = [], False
-        for s, t in zip(slots, tokens):
-            if not held(s):
-                raise CacheError(f"slot {s} is not held")
-            if not 0 <= t < vocab:
-                raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
-            n = seq_len[s]
-            starts.append(n)
-            if n % K.PAGE == 0 or n >= longest:
-                grow = True
+        # (the common case costs a few calls into the interpreter's built-ins, whatever the batch; the loops below only
+        # run to name the culprit)
+        if slots and not cache.slots.all_held(slots):
+            raise CacheError(f"slot {next(s for s in slots if not cache.slots.held(s))} is not held")
+        if tokens and not (min(tokens) >= 0 and max(tokens) < self.vocab_size):
+            bad = next(t for t in tokens if not 0 <= t < self.vocab_size)
+            raise ValueError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
+        starts = list(map(cache.seq_len.__getitem__, slots))
+        grow = bool(starts) and (0 in map(K.PAGE.__rmod__, starts) or max(starts) >= cache.max_seq_len)
         return starts, grow
 
     def _launch_ahead(self, cur):
