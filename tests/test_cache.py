@@ -154,3 +154,50 @@ def test_random_traffic_loses_nothing():
         assert c.slots.held_count == len(live)
     c.release_all()
     assert c.free_pages == c.n_pages and c.slots.free_count == c.max_seqs
+
+
+def test_random_traffic_of_whole_steps_keeps_the_block_tables_right():
+    """Steps that grow several sequences at once (one transfer of new block-table entries a group), in a cache of
+    two groups of which one looks back over a window and gives pages back: after every step each live sequence's row
+    of each group's table lists exactly the pages the group holds for it, at their places; no page is held twice or
+    lost in either group; a step that does not fit changes nothing."""
+    rng = random.Random(1)
+    full = CacheNeed("kv", n_kv_heads=1, head_dim=16)
+    win = CacheNeed("kv", n_kv_heads=1, head_dim=16, window=90)
+    c = Cache([full, win], [ScheduleEntry(0), ScheduleEntry(1)], 64 * 24, 6, 64 * 10, torch.float32, torch.device("cpu"))
+    live = {}
+    refused = 0
+    for _ in range(1500):
+        op = rng.random()
+        if op < 0.2 and c.slots.free_count:
+            live[c.acquire()] = 0
+        elif op < 0.85 and live:
+            some = rng.sample(sorted(live), rng.randint(1, len(live)))
+            growth = [(s, live[s] + rng.choice([1, 1, 1, rng.randint(2, 150)])) for s in some]
+            free_before = [g.pages.free_count for g in c._kv_groups]
+            try:
+                c.reserve(growth)
+                for s, n in growth:
+                    live[s] = n
+                    c.set_length(s, n)
+            except (CacheFull, ContextLengthExceeded):
+                refused += 1
+                # (the windowed group may have given pages back before the step was refused; nothing was acquired)
+                assert all(g.pages.free_count >= f for g, f in zip(c._kv_groups, free_before))
+        elif live:
+            s = rng.choice(sorted(live))
+            c.release(s)
+            del live[s]
+        for g in c._kv_groups:
+            held = [p for s in range(c.max_seqs) for p in g.live_pages(s)]
+            assert len(held) == len(set(held)) and len(held) + g.pages.free_count == c.n_pages
+            for s, n in live.items():
+                assert len(g.pages_of[s]) == -(-n // 64)
+                row = g.block_table[s].tolist()
+                for i, p in enumerate(g.pages_of[s]):
+                    assert (p is None and i < g.dropped[s]) or row[i] == p
+                if g.need.window and n > 0:
+                    assert g.dropped[s] <= max(0, n - g.need.window + 1) // 64      # nothing a coming token still sees
+    assert refused > 0
+    c.release_all()
+    assert all(g.pages.free_count == c.n_pages for g in c._kv_groups)
