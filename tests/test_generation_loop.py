@@ -297,3 +297,30 @@ def test_streaming_looks_at_every_token():
                                                          on_token=lambda i, t: seen.append((i, t)))
     for i, r in enumerate(out.results):
         assert [t for j, t in seen if j == i] == r.tokens == expected(prompts[i], 9)[0]
+
+
+def test_quiet_stretches_on_requests_drawn_at_random():
+    """Prompts, lengths, stop ids, context limits and batch sizes drawn at random (fixed seeds): the loop over an engine
+    with the short ways gives, request by request, what the loop that looks at every token gives."""
+    import random
+    for case in range(60):
+        rng = random.Random(case)
+        prompts = [[rng.randrange(VOCAB) for _ in range(rng.choice([1, 2, 5, 17, 40]))] for _ in range(rng.randint(1, 7))]
+        max_seq_len = rng.choice([24, 48, 64, 128])
+        stops = tuple(rng.sample(range(VOCAB), rng.choice([0, 1, 3, 8])))
+        opts = GenerateOptions(temperature=rng.choice([0.0, 0.5]), seed=1 + case, sample_len=rng.choice([1, 2, 3, 10, 50, 200]),
+                               stop_ids=stops, ignore_stop=rng.random() < 0.2, include_stop=rng.random() < 0.3,
+                               batch_size=rng.choice([None, 1, 2, 3]))
+        kw = dict(max_tokens=64 * 8, max_seqs=rng.choice([1, 2, 4]), max_seq_len=max_seq_len)
+        slow_eng = ScriptedEngine(**kw)
+        slow = GenerationLoop(slow_eng, ArgmaxSampler(), default_stop_ids=(13,)).generate(prompts, opts)
+        quick_eng = QuickEngine(**kw)
+        quick = GenerationLoop(quick_eng, ArgmaxSampler(), default_stop_ids=(13,)).generate(prompts, opts)
+        what = (case, opts, [len(p) for p in prompts], kw)
+        assert [r.tokens for r in quick.results] == [r.tokens for r in slow.results], what
+        assert [r.finish_reason for r in quick.results] == [r.finish_reason for r in slow.results], what
+        assert [type(r.error) for r in quick.results] == [type(r.error) for r in slow.results], what
+        assert (quick.stats.generated_tokens, quick.stats.decode_steps, quick.stats.batches) == \
+               (slow.stats.generated_tokens, slow.stats.decode_steps, slow.stats.batches), what
+        assert quick_eng.steps == slow_eng.steps, what
+        assert quick_eng.cache.slots.held_count == 0 and quick_eng.cache.free_pages == quick_eng.cache.n_pages
