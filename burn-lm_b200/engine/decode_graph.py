@@ -67,6 +67,11 @@ class DecodeGraph:
         self._host_meta_np = self.host_meta.numpy()             # the same pinned bytes, filled without a tensor in between
         self.host_sampled = torch.zeros(b, dtype=torch.int32, pin_memory=True)
         self._host_sampled_np = self.host_sampled.numpy()
+        # the buffer a sampling kernel writes the tokens to as well, where the device can address pinned host memory
+        try:
+            self.mirror = self.host_sampled if K.host_device_pointer(self.host_sampled) else None
+        except K.KernelError:
+            self.mirror = None
         self.tokens, self.pos, self.slots = self.meta[:b], self.meta[b:2 * b], self.meta[2 * b:]
         ar = torch.arange(b + 1, dtype=torch.int32, device=dev)
         self.ctx = StepContext(
@@ -140,7 +145,7 @@ class DecodeGraph:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with _capturing(g):
-                K.argmax(self._forward(), self.sampled, mirror=self.host_sampled, tickets=self.tickets)
+                K.argmax(self._forward(), self.sampled, mirror=self.mirror, tickets=self.tickets)
             self._greedy_graph = g
             return self.sampled
         self._greedy_graph.replay()
@@ -157,7 +162,7 @@ class DecodeGraph:
             if self._greedy_again is None or self._greedy_again[0] != stream:
                 # the captured argmax writes the pinned buffer itself (its `mirror`): nothing to copy out
                 self._greedy_again = (stream, K.graph_step(self._greedy_exec, self.meta, self.host_meta, self.host_sampled,
-                                                           self.sampled, written_by_graph=RESULTS_BY_POLLING))
+                                                           self.sampled, written_by_graph=RESULTS_BY_POLLING and self.mirror is not None))
             else:
                 self._greedy_again[1]()
             return self._host_sampled_np.tolist()
@@ -228,7 +233,7 @@ class DecodeGraph:
 
         def draw():
             K.sample(self._forward(), self._sample_f[0], self._sample_f[1], self._sample_ids[0], self._sample_ids[1],
-                     self._sample_counters, self.sampled, mirror=self.host_sampled)
+                     self._sample_counters, self.sampled, mirror=self.mirror)
 
         if self._sample_exec:
             self._host_meta_np[:] = [*tokens, *positions, *slots]
@@ -236,7 +241,7 @@ class DecodeGraph:
             if self._sample_again is None or self._sample_again[0] != stream:
                 self._sample_again = (stream, K.graph_step(self._sample_exec, self.meta, self.host_meta, self.host_sampled, self.sampled,
                                                            dev_in2=self._sample_counters, host_in2=self._host_counters,
-                                                           written_by_graph=RESULTS_BY_POLLING))
+                                                           written_by_graph=RESULTS_BY_POLLING and self.mirror is not None))
             else:
                 self._sample_again[1]()
             return self._host_sampled_np.tolist()
