@@ -1,7 +1,7 @@
 // The host side of a captured decode step in one call: the step's inputs (one or two buffers) from pinned host
-// memory to the device, the captured graph, the step's result back to pinned host memory, and the wait for it.  Four
-// driver calls issued back to back from native code instead of from the interpreter, which otherwise
-// costs the GPU tens of microseconds of idling per step.
+// memory to the device, the captured graph, and the step's result in pinned host memory: copied back and waited for, or
+// written there by the graph's own last kernel and polled for.  The driver calls are issued back to back from native
+// code instead of from the interpreter, which otherwise costs the GPU tens of microseconds of idling per step.
 #include "common.cuh"
 #include <time.h>
 
